@@ -1,0 +1,152 @@
+/* rtxb — C ABI of the sm_100a block-scaled quantize + GEMM kernels.
+ *
+ * The reference (achiya-deri-work/rtx) has no FFI: its seam is a set of Python
+ * `compile_*` factories that return launch callables `(tensors...) -> None`
+ * running asynchronously on the current CUDA stream.  Each entry point below
+ * replaces one of those callables; the citation names the factory and the
+ * call sites that bind it.
+ *
+ * Conventions (all entry points)
+ *   - plain device pointers and sizes; no allocation, no synchronisation, no
+ *     exceptions; work is enqueued on `stream` (a cudaStream_t passed as void*)
+ *     of the device that is current;
+ *   - returns 0 (RTXB_OK) or a negative RTXB_E_* code; rtxb_error_string()
+ *     explains it; a rejected call has launched nothing;
+ *   - payload matrices are K-major (row-major [rows, K] with K contiguous),
+ *     BF16 inputs may have a row pitch `ld` (elements) >= K;
+ *   - `status` is an optional device int the kernels set to a non-zero
+ *     RTXB_DEV_* code when a bounded wait runs out (they then leave through
+ *     their normal teardown); the caller zeroes and reads it;
+ *   - scale layouts use the reference's codes (rtx/formats/common.py:17):
+ *     0 = row_major [rows, blocks], 2 = mma128 (128-row tiles of 512 bytes,
+ *     byte (row%32)*16 + ((row/32)%4)*4 + block%4, tiles ordered
+ *     [row/128][block/4]); 1 = mma64 is an SM120-only layout and is rejected.
+ */
+#ifndef RTXB_H_
+#define RTXB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RTXB_OK 0
+#define RTXB_E_INVALID_ARGUMENT (-1)
+#define RTXB_E_UNSUPPORTED (-2)
+#define RTXB_E_ALIGNMENT (-3)
+#define RTXB_E_WORKSPACE (-4)
+#define RTXB_E_CUDA (-5)
+#define RTXB_E_DRIVER (-6)
+
+#define RTXB_SCALE_ROW_MAJOR 0
+#define RTXB_SCALE_MMA64 1
+#define RTXB_SCALE_MMA128 2
+
+#define RTXB_ROUND_FLOOR 0
+#define RTXB_ROUND_INFINITY 1
+
+#define RTXB_OUT_BF16 0
+#define RTXB_OUT_F32 1
+
+#define RTXB_TENSOR_SCALE_EXACT 0
+#define RTXB_TENSOR_SCALE_POWER2 1
+
+int rtxb_version(void);
+const char* rtxb_error_string(int code);
+/* last CUDA/driver error text recorded by this thread's most recent failing call */
+const char* rtxb_last_cuda_error(void);
+
+/* ---- sizes ------------------------------------------------------------- */
+
+/* padded K: 32-multiples (rtx/kernels/mxfp8.py:57-66, rtx/configs/nvfp4.py:15-28) */
+int64_t rtxb_mxfp8_storage_k(int64_t k);
+int64_t rtxb_nvfp4_storage_k(int64_t k);
+/* bytes of a scale buffer for `rows` x `k` in `layout` (mma128 includes row and K padding) */
+size_t rtxb_mxfp8_scale_bytes(int64_t rows, int64_t k, int layout);
+size_t rtxb_nvfp4_scale_bytes(int64_t rows, int64_t k, int layout);
+
+/* ---- MXFP8 quantizers ---------------------------------------------------
+ * compile_mxfp8_quant(rows, k, cfg) -> (src bf16, q e4m3[R,Kp], s e8m0)
+ *   rtx/kernels/mxfp8_quant.py:52-395; bound at rtx/fp8.py:783-786, :930-931.
+ * compile_mxfp8_transposed_quant -> same outputs for the logical transpose of a
+ *   stored [K, R] matrix: rtx/kernels/mxfp8_quant.py:526-1019; rtx/fp8_bwd.py:437-448. */
+int rtxb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                        int scale_layout, int rounding, void* stream);
+int rtxb_mxfp8_quantize_transposed(const void* src_bf16_k_by_rows, int64_t rows, int64_t k, int64_t ld, void* q,
+                                   void* scales, int scale_layout, int rounding, void* stream);
+
+/* ---- MXFP8 GEMM on packed operands ---------------------------------------
+ * compile_mxfp8_gemm(problem, cfg, ...) -> (qx, qw, sx, sw, out)
+ *   rtx/kernels/mxfp8_gemm.py:2048-2151; bound at rtx/fp8.py:932, :1260, :1338 and
+ *   rtx/fp8_bwd.py:458-505.  out[m, n] = bf16 or f32 of sum_k deq(qa) deq(qb)^T.
+ * Scales must be in the mma128 layout.  `k` is the logical K; rows of qa/qb are
+ * rtxb_mxfp8_storage_k(k) bytes apart. */
+int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
+                    int64_t k, int64_t ldo, int out_dtype, void* stream, int* status);
+/* SwiGLU gate/up projection with the activation fused into the epilogue:
+ * qb holds [2*inter, K] (gate rows first); out bf16 [m, inter] =
+ * silu(acc[:, :inter]) * acc[:, inter:], one BF16 rounding.  The reference
+ * computes this as linear + chunk + F.silu * up (rtx/models/decoder.py:382-384).
+ * inter must be a multiple of 128. */
+int rtxb_mxfp8_gemm_glu(const void* qa, const void* sa, const void* qb, const void* sb, void* out_bf16, int64_t m,
+                        int64_t inter, int64_t k, int64_t ldo, void* stream, int* status);
+
+/* ---- fused forward (quantize both operands + GEMM) ------------------------
+ * compile_mxfp8_fwd(problem, cfg) -> (x bf16, w bf16, out bf16[M,N])
+ *   rtx/kernels/mxfp8_fwd.py:2963-3029; bound at rtx/fp8.py:560, :581, :635.
+ * and the materialized pair compile_mxfp8_dual_quant + compile_mxfp8_gemm run by
+ *   _PrequantRunner (rtx/fp8.py:292-312).
+ * workspace: rtxb_mxfp8_linear_workspace_bytes(m, n, k); caller-owned, reusable
+ * across calls on the same stream. */
+size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int rtxb_mxfp8_linear_fwd(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n, int64_t k,
+                          int rounding, void* workspace, size_t workspace_bytes, void* stream, int* status);
+
+/* SwiGLU MLP forward: H = silu(X Wg^T) * (X Wu^T), Y = H Wd^T, every GEMM
+ * operand MXFP8-quantized along its K.  w_gate_up bf16 [2*inter, k], w_down
+ * bf16 [n_out, inter]; h_bf16 [m, inter] and y_bf16 [m, n_out] are outputs. */
+size_t rtxb_mxfp8_glu_mlp_workspace_bytes(int64_t m, int64_t k, int64_t inter, int64_t n_out);
+int rtxb_mxfp8_glu_mlp_fwd(const void* x_bf16, const void* w_gate_up_bf16, const void* w_down_bf16, void* h_bf16,
+                           void* y_bf16, int64_t m, int64_t k, int64_t inter, int64_t n_out, void* workspace,
+                           size_t workspace_bytes, void* stream, int* status);
+
+/* ---- MXFP8 backward --------------------------------------------------------
+ * _build_bwd_runner / _BwdRunner (rtx/fp8_bwd.py:521-568, :229-325):
+ *   dX[M,K] = dY[M,N] W[N,K]   (operands quantized along N)
+ *   dW[N,K] = dY^T[N,M] X[M,K] (operands quantized along M)
+ * dx is BF16; dw is BF16 (reference dtype) or FP32 (for a data-parallel
+ * all-reduce) per dw_dtype.  Either output may be NULL to skip that product. */
+size_t rtxb_mxfp8_backward_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int rtxb_mxfp8_linear_bwd(const void* dy_bf16, const void* x_bf16, const void* w_bf16, void* dx_bf16, void* dw,
+                          int dw_dtype, int64_t m, int64_t n, int64_t k, void* workspace, size_t workspace_bytes,
+                          void* stream, int* status);
+
+/* ---- NVFP4 -----------------------------------------------------------------
+ * Outer scale: the reference computes it with PyTorch reductions
+ * (_outer_tensor_scale, rtx/fp4.py:343-365).  rtxb_nvfp4_tensor_scale does the
+ * |max| reduction and the scale rule on the device: scale_out[0] = scale;
+ * when other_scale/out_scale are non-NULL also out_scale[0] = scale * other_scale[0].
+ * amax_scratch: 4 bytes of device memory. */
+int rtxb_nvfp4_tensor_scale(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, int mode, void* amax_scratch,
+                            float* scale_out, const float* other_scale, float* out_scale, void* stream);
+/* compile_nvfp4_quant(rows, k, cfg) -> (src bf16, q u8[R,Kp/2], s e4m3, tensor_scale f32[1])
+ *   rtx/kernels/nvfp4_quant.py:32-349; bound at rtx/fp4.py:696-697, :900, :1532.
+ * tensor_scale NULL = block policy (scale 1.0, compile_nvfp4_block_quant). */
+int rtxb_nvfp4_quantize(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                        int scale_layout, const float* tensor_scale, void* stream);
+/* compile_nvfp4_gemm(problem, cfg) -> (qx, qw, sx, sw, out bf16, output_scale f32[1])
+ *   rtx/kernels/nvfp4_gemm.py:22-64, epilogue rtx/kernels/mxfp8_gemm.py:779-781;
+ *   bound at rtx/fp4.py:707, :901, :1734, :2313.  output_scale NULL = 1 (block GEMM). */
+int rtxb_nvfp4_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
+                    int64_t k, int64_t ldo, int out_dtype, const float* output_scale, void* stream, int* status);
+/* _DynamicRunner (rtx/fp4.py:404-454): outer scales + dual quantize + GEMM. */
+size_t rtxb_nvfp4_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int rtxb_nvfp4_linear_fwd(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n, int64_t k,
+                          int scale_mode, void* workspace, size_t workspace_bytes, void* stream, int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RTXB_H_ */

@@ -1,0 +1,483 @@
+// extern "C" entry points of librtxb: argument checks, tensor-map encoding and
+// kernel launches.  No allocation, no synchronisation; everything is enqueued
+// on the caller's stream.
+#include "../../include/rtxb.h"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "gemm_blockscaled.cuh"
+#include "quant.cuh"
+
+using namespace rtxb;
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int fail_cuda(cudaError_t e, const char* where) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s", where, cudaGetErrorString(e));
+  return RTXB_E_CUDA;
+}
+int fail_msg(int code, const char* msg) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s", msg);
+  return code;
+}
+
+#define RTXB_CHECK_LAUNCH(where)                                \
+  do {                                                          \
+    cudaError_t e__ = cudaGetLastError();                       \
+    if (e__ != cudaSuccess) return fail_cuda(e__, where);       \
+  } while (0)
+
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// ---- driver entry point for tensor-map encoding (no link-time libcuda) ----
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// byte matrix [rows, row_bytes] (pitch row_bytes), boxes of 128 bytes x box_rows, 128-byte swizzle,
+// out-of-range elements read as zero
+int make_payload_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+  if (!aligned(base, 16) || row_bytes % 16 != 0) return fail_msg(RTXB_E_ALIGNMENT, "payload must be 16-byte aligned");
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_bytes)};
+  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return RTXB_E_DRIVER;
+  }
+  return RTXB_OK;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <int KIND, int EPI>
+int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
+                int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
+                const float* out_scale, cudaStream_t stream, int* status) {
+  using T = GemmTraits<KIND>;
+  CUtensorMap map_a, map_b;
+  int rc = make_payload_map(&map_a, qa, m, row_bytes, 128);
+  if (rc) return rc;
+  rc = make_payload_map(&map_b, qb, n_rows_b, row_bytes, 128);
+  if (rc) return rc;
+  GemmParams p;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n_rows_b);
+  p.k_tiles = static_cast<int>((row_bytes + kBlockKBytes - 1) / kBlockKBytes);
+  p.m_tiles = static_cast<int>((m + kBlockM - 1) / kBlockM);
+  p.n_tiles = glu_inter ? static_cast<int>((glu_inter + 127) / 128) : static_cast<int>((n_rows_b + kBlockN - 1) / kBlockN);
+  p.glu_inter = static_cast<int>(glu_inter);
+  p.sfa = static_cast<const uint8_t*>(sa);
+  p.sfb = static_cast<const uint8_t*>(sb);
+  p.sf_k_chunks = static_cast<int>(sf_k_chunks);
+  p.out = out;
+  p.ldo = ldo;
+  p.out_cols = static_cast<int>(out_cols);
+  p.out_vec_ok = (aligned(out, 16) && (ldo * (EPI == kEpiF32 ? 4 : 2)) % 16 == 0) ? 1 : 0;
+  p.out_scale = out_scale;
+  p.status = status;
+  auto kernel = gemm_blockscaled_kernel<KIND, EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(gemm)");
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  kernel<<<grid, kGemmThreads, T::kSmemBytes, stream>>>(map_a, map_b, p);
+  RTXB_CHECK_LAUNCH("gemm_blockscaled_kernel");
+  return RTXB_OK;
+}
+
+int check_gemm_args(const void* qa, const void* sa, const void* qb, const void* sb, const void* out, int64_t m,
+                    int64_t n, int64_t k, int64_t ldo, int64_t out_cols, int out_elem_bytes) {
+  if (!qa || !sa || !qb || !sb || !out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || n <= 0 || k <= 0) return fail_msg(RTXB_E_INVALID_ARGUMENT, "m, n, k must be positive");
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (ldo < out_cols) return fail_msg(RTXB_E_INVALID_ARGUMENT, "output pitch smaller than its width");
+  if (!aligned(sa, 16) || !aligned(sb, 16)) return fail_msg(RTXB_E_ALIGNMENT, "scale tiles must be 16-byte aligned");
+  if (!aligned(out, out_elem_bytes)) return fail_msg(RTXB_E_ALIGNMENT, "output pointer is not element aligned");
+  return RTXB_OK;
+}
+
+int quant_grid(int64_t tiles) {
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  return static_cast<int>(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
+}
+
+struct Carver {
+  uint8_t* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<uint8_t*>(p)) {}
+  uint8_t* take(size_t bytes) {
+    uint8_t* r = base ? base + off : nullptr;
+    off += static_cast<size_t>(round_up(static_cast<int64_t>(bytes), 256));
+    return r;
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+int rtxb_version(void) { return 100; }
+
+const char* rtxb_error_string(int code) {
+  switch (code) {
+    case RTXB_OK: return "ok";
+    case RTXB_E_INVALID_ARGUMENT: return "invalid argument";
+    case RTXB_E_UNSUPPORTED: return "unsupported configuration";
+    case RTXB_E_ALIGNMENT: return "pointer or pitch not aligned";
+    case RTXB_E_WORKSPACE: return "workspace too small";
+    case RTXB_E_CUDA: return "CUDA runtime error";
+    case RTXB_E_DRIVER: return "CUDA driver error";
+    default: return "unknown error";
+  }
+}
+
+const char* rtxb_last_cuda_error(void) { return g_last_error; }
+
+int64_t rtxb_mxfp8_storage_k(int64_t k) { return round_up(k, 32); }
+int64_t rtxb_nvfp4_storage_k(int64_t k) { return round_up(k, 32); }
+
+size_t rtxb_mxfp8_scale_bytes(int64_t rows, int64_t k, int layout) {
+  const int64_t nb = round_up(k, 32) / 32;
+  if (layout == RTXB_SCALE_ROW_MAJOR) return static_cast<size_t>(rows * nb);
+  if (layout == RTXB_SCALE_MMA128) return static_cast<size_t>(round_up(rows, 128) / 128 * ((nb + 3) / 4) * 512);
+  return 0;
+}
+
+size_t rtxb_nvfp4_scale_bytes(int64_t rows, int64_t k, int layout) {
+  const int64_t nb = round_up(k, 32) / 16;
+  if (layout == RTXB_SCALE_ROW_MAJOR) return static_cast<size_t>(rows * nb);
+  // tiles along K padded to whole 256-value GEMM K tiles (4 tiles of 64 values)
+  if (layout == RTXB_SCALE_MMA128) return static_cast<size_t>(round_up(rows, 128) / 128 * round_up((nb + 3) / 4, 4) * 512);
+  return 0;
+}
+
+int rtxb_mxfp8_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales, int scale_layout,
+                        int rounding, void* stream) {
+  if (!src || !q || !scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (rows > INT32_MAX || k > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  QuantMxParams p;
+  p.src = static_cast<const __nv_bfloat16*>(src);
+  p.q = static_cast<uint8_t*>(q);
+  p.scales = static_cast<uint8_t*>(scales);
+  p.rows = static_cast<int>(rows);
+  p.k = static_cast<int>(k);
+  p.kp = static_cast<int>(round_up(k, 32));
+  p.ld = ld;
+  p.nb = p.kp / 32;
+  p.sf_chunks = (p.nb + 3) / 4;
+  p.layout = scale_layout;
+  p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
+  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 255) / 256);
+  quant_mxfp8_rows_kernel<<<quant_grid(tiles), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RTXB_CHECK_LAUNCH("quant_mxfp8_rows_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_mxfp8_quantize_transposed(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                                   int scale_layout, int rounding, void* stream) {
+  if (!src || !q || !scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < rows) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (rows > INT32_MAX || k > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!aligned(q, 16)) return fail_msg(RTXB_E_ALIGNMENT, "q must be 16-byte aligned");
+  if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  QuantMxTParams p;
+  p.src = static_cast<const __nv_bfloat16*>(src);
+  p.q = static_cast<uint8_t*>(q);
+  p.scales = static_cast<uint8_t*>(scales);
+  p.rows = static_cast<int>(rows);
+  p.k = static_cast<int>(k);
+  p.kp = static_cast<int>(round_up(k, 32));
+  p.ld = ld;
+  p.nb = p.kp / 32;
+  p.sf_chunks = (p.nb + 3) / 4;
+  p.layout = scale_layout;
+  p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
+  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 127) / 128);
+  quant_mxfp8_transposed_kernel<<<quant_grid(tiles), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RTXB_CHECK_LAUNCH("quant_mxfp8_transposed_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
+                    int64_t k, int64_t ldo, int out_dtype, void* stream, int* status) {
+  if (out_dtype != RTXB_OUT_BF16 && out_dtype != RTXB_OUT_F32)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown output dtype");
+  int rc = check_gemm_args(qa, sa, qb, sb, out, m, n, k, ldo, n, out_dtype == RTXB_OUT_BF16 ? 2 : 4);
+  if (rc) return rc;
+  const int64_t kp = round_up(k, 32);
+  const int64_t chunks = (kp / 32 + 3) / 4;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == RTXB_OUT_BF16)
+    return launch_gemm<kKindMxfp8, kEpiBf16>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status);
+  return launch_gemm<kKindMxfp8, kEpiF32>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status);
+}
+
+int rtxb_mxfp8_gemm_glu(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m,
+                        int64_t inter, int64_t k, int64_t ldo, void* stream, int* status) {
+  int rc = check_gemm_args(qa, sa, qb, sb, out, m, 2 * inter, k, ldo, inter, 2);
+  if (rc) return rc;
+  if (inter % 128 != 0) return fail_msg(RTXB_E_UNSUPPORTED, "fused GLU epilogue needs inter % 128 == 0");
+  const int64_t kp = round_up(k, 32);
+  const int64_t chunks = (kp / 32 + 3) / 4;
+  return launch_gemm<kKindMxfp8, kEpiGluBf16>(qa, sa, qb, sb, out, m, 2 * inter, kp, chunks, ldo, inter, inter, nullptr,
+                                              static_cast<cudaStream_t>(stream), status);
+}
+
+size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  Carver c(nullptr);
+  const int64_t kp = round_up(k, 32);
+  c.take(m * kp);
+  c.take(rtxb_mxfp8_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  c.take(n * kp);
+  c.take(rtxb_mxfp8_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  return c.off;
+}
+
+int rtxb_mxfp8_linear_fwd(const void* x, const void* w, void* out, int64_t m, int64_t n, int64_t k, int rounding,
+                          void* workspace, size_t workspace_bytes, void* stream, int* status) {
+  if (!workspace || workspace_bytes < rtxb_mxfp8_linear_workspace_bytes(m, n, k))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_mxfp8_linear_fwd");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  Carver c(workspace);
+  const int64_t kp = round_up(k, 32);
+  uint8_t* qx = c.take(m * kp);
+  uint8_t* sx = c.take(rtxb_mxfp8_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  uint8_t* qw = c.take(n * kp);
+  uint8_t* sw = c.take(rtxb_mxfp8_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  int rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, rounding, stream);
+  if (rc) return rc;
+  rc = rtxb_mxfp8_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, rounding, stream);
+  if (rc) return rc;
+  return rtxb_mxfp8_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, stream, status);
+}
+
+size_t rtxb_mxfp8_glu_mlp_workspace_bytes(int64_t m, int64_t k, int64_t inter, int64_t n_out) {
+  Carver c(nullptr);
+  const int64_t kp = round_up(k, 32), ip = round_up(inter, 32);
+  c.take(m * kp);
+  c.take(rtxb_mxfp8_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  c.take(2 * inter * kp);
+  c.take(rtxb_mxfp8_scale_bytes(2 * inter, k, RTXB_SCALE_MMA128));
+  c.take(m * ip);
+  c.take(rtxb_mxfp8_scale_bytes(m, inter, RTXB_SCALE_MMA128));
+  c.take(n_out * ip);
+  c.take(rtxb_mxfp8_scale_bytes(n_out, inter, RTXB_SCALE_MMA128));
+  return c.off;
+}
+
+int rtxb_mxfp8_glu_mlp_fwd(const void* x, const void* w_gu, const void* w_down, void* h, void* y, int64_t m, int64_t k,
+                           int64_t inter, int64_t n_out, void* workspace, size_t workspace_bytes, void* stream,
+                           int* status) {
+  if (!workspace || workspace_bytes < rtxb_mxfp8_glu_mlp_workspace_bytes(m, k, inter, n_out))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_mxfp8_glu_mlp_fwd");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  if (inter % 128 != 0) return fail_msg(RTXB_E_UNSUPPORTED, "fused GLU epilogue needs inter % 128 == 0");
+  Carver c(workspace);
+  const int64_t kp = round_up(k, 32), ip = round_up(inter, 32);
+  uint8_t* qx = c.take(m * kp);
+  uint8_t* sx = c.take(rtxb_mxfp8_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  uint8_t* qg = c.take(2 * inter * kp);
+  uint8_t* sg = c.take(rtxb_mxfp8_scale_bytes(2 * inter, k, RTXB_SCALE_MMA128));
+  uint8_t* qh = c.take(m * ip);
+  uint8_t* sh = c.take(rtxb_mxfp8_scale_bytes(m, inter, RTXB_SCALE_MMA128));
+  uint8_t* qd = c.take(n_out * ip);
+  uint8_t* sd = c.take(rtxb_mxfp8_scale_bytes(n_out, inter, RTXB_SCALE_MMA128));
+  int rc;
+  if ((rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+  if ((rc = rtxb_mxfp8_quantize(w_gu, 2 * inter, k, k, qg, sg, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+  if ((rc = rtxb_mxfp8_quantize(w_down, n_out, inter, inter, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+    return rc;
+  if ((rc = rtxb_mxfp8_gemm_glu(qx, sx, qg, sg, h, m, inter, k, inter, stream, status))) return rc;
+  if ((rc = rtxb_mxfp8_quantize(h, m, inter, inter, qh, sh, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+  return rtxb_mxfp8_gemm(qh, sh, qd, sd, y, m, n_out, inter, n_out, RTXB_OUT_BF16, stream, status);
+}
+
+size_t rtxb_mxfp8_backward_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  Carver c(nullptr);
+  const int64_t np = round_up(n, 32), mp = round_up(m, 32);
+  c.take(m * np);  c.take(rtxb_mxfp8_scale_bytes(m, n, RTXB_SCALE_MMA128));   // dY rows
+  c.take(k * np);  c.take(rtxb_mxfp8_scale_bytes(k, n, RTXB_SCALE_MMA128));   // W^T
+  c.take(n * mp);  c.take(rtxb_mxfp8_scale_bytes(n, m, RTXB_SCALE_MMA128));   // dY^T
+  c.take(k * mp);  c.take(rtxb_mxfp8_scale_bytes(k, m, RTXB_SCALE_MMA128));   // X^T
+  return c.off;
+}
+
+int rtxb_mxfp8_linear_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw, int dw_dtype, int64_t m,
+                          int64_t n, int64_t k, void* workspace, size_t workspace_bytes, void* stream, int* status) {
+  if (!workspace || workspace_bytes < rtxb_mxfp8_backward_workspace_bytes(m, n, k))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_mxfp8_linear_bwd");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  if (!dy) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null dy");
+  Carver c(workspace);
+  const int64_t np = round_up(n, 32), mp = round_up(m, 32);
+  uint8_t* qa = c.take(m * np);  uint8_t* sa = c.take(rtxb_mxfp8_scale_bytes(m, n, RTXB_SCALE_MMA128));
+  uint8_t* qb = c.take(k * np);  uint8_t* sb = c.take(rtxb_mxfp8_scale_bytes(k, n, RTXB_SCALE_MMA128));
+  uint8_t* qc = c.take(n * mp);  uint8_t* sc = c.take(rtxb_mxfp8_scale_bytes(n, m, RTXB_SCALE_MMA128));
+  uint8_t* qd = c.take(k * mp);  uint8_t* sd = c.take(rtxb_mxfp8_scale_bytes(k, m, RTXB_SCALE_MMA128));
+  int rc;
+  if (dx) {
+    if (!w) return fail_msg(RTXB_E_INVALID_ARGUMENT, "dx needs w");
+    // A = dY [M, N] blocks along N; B = W^T as [K rows, N] blocks along N (W stored [N, K])
+    if ((rc = rtxb_mxfp8_quantize(dy, m, n, n, qa, sa, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+    if ((rc = rtxb_mxfp8_quantize_transposed(w, k, n, k, qb, sb, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+      return rc;
+    if ((rc = rtxb_mxfp8_gemm(qa, sa, qb, sb, dx, m, k, n, k, RTXB_OUT_BF16, stream, status))) return rc;
+  }
+  if (dw) {
+    if (!x) return fail_msg(RTXB_E_INVALID_ARGUMENT, "dw needs x");
+    // A = dY^T as [N rows, M] blocks along M (dY stored [M, N]); B = X^T as [K rows, M] (X stored [M, K])
+    if ((rc = rtxb_mxfp8_quantize_transposed(dy, n, m, n, qc, sc, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+      return rc;
+    if ((rc = rtxb_mxfp8_quantize_transposed(x, k, m, k, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+      return rc;
+    if ((rc = rtxb_mxfp8_gemm(qc, sc, qd, sd, dw, n, k, m, k, dw_dtype, stream, status))) return rc;
+  }
+  return RTXB_OK;
+}
+
+int rtxb_nvfp4_tensor_scale(const void* src, int64_t rows, int64_t k, int64_t ld, int mode, void* amax_scratch,
+                            float* scale_out, const float* other_scale, float* out_scale, void* stream) {
+  if (!src || !amax_scratch || !scale_out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (mode != RTXB_TENSOR_SCALE_EXACT && mode != RTXB_TENSOR_SCALE_POWER2)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown tensor scale mode");
+  if ((out_scale == nullptr) != (other_scale == nullptr))
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "other_scale and out_scale go together");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(amax_scratch, 0, 4, s);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(amax)");
+  const int64_t work = rows * k / 8 / 256 + 1;
+  const int grid = static_cast<int>(work < sm_count() * 8 ? work : sm_count() * 8);
+  amax_bf16_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), rows, k, ld,
+                                        static_cast<uint32_t*>(amax_scratch));
+  RTXB_CHECK_LAUNCH("amax_bf16_kernel");
+  nvfp4_tensor_scale_kernel<<<1, 1, 0, s>>>(static_cast<const uint32_t*>(amax_scratch), mode, scale_out, other_scale,
+                                            out_scale);
+  RTXB_CHECK_LAUNCH("nvfp4_tensor_scale_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_nvfp4_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales, int scale_layout,
+                        const float* tensor_scale, void* stream) {
+  if (!src || !q || !scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (rows > INT32_MAX || k > INT32_MAX - 512) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!aligned(q, 16)) return fail_msg(RTXB_E_ALIGNMENT, "q must be 16-byte aligned");
+  if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  QuantNvParams p;
+  p.src = static_cast<const __nv_bfloat16*>(src);
+  p.q = static_cast<uint8_t*>(q);
+  p.scales = static_cast<uint8_t*>(scales);
+  p.tensor_scale = tensor_scale;
+  p.rows = static_cast<int>(rows);
+  p.k = static_cast<int>(k);
+  p.kp = static_cast<int>(round_up(k, 32));
+  p.ld = ld;
+  p.nb = p.kp / 16;
+  p.sf_chunks = static_cast<int>(round_up((p.nb + 3) / 4, 4));
+  p.layout = scale_layout;
+  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 511) / 512);
+  quant_nvfp4_rows_kernel<<<quant_grid(tiles), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RTXB_CHECK_LAUNCH("quant_nvfp4_rows_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_nvfp4_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
+                    int64_t k, int64_t ldo, int out_dtype, const float* output_scale, void* stream, int* status) {
+  if (out_dtype != RTXB_OUT_BF16 && out_dtype != RTXB_OUT_F32)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown output dtype");
+  int rc = check_gemm_args(qa, sa, qb, sb, out, m, n, k, ldo, n, out_dtype == RTXB_OUT_BF16 ? 2 : 4);
+  if (rc) return rc;
+  const int64_t kp = round_up(k, 32);
+  const int64_t chunks = round_up((kp / 16 + 3) / 4, 4);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == RTXB_OUT_BF16)
+    return launch_gemm<kKindNvfp4, kEpiBf16>(qa, sa, qb, sb, out, m, n, kp / 2, chunks, ldo, n, 0, output_scale, s, status);
+  return launch_gemm<kKindNvfp4, kEpiF32>(qa, sa, qb, sb, out, m, n, kp / 2, chunks, ldo, n, 0, output_scale, s, status);
+}
+
+size_t rtxb_nvfp4_linear_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  Carver c(nullptr);
+  const int64_t kp = round_up(k, 32);
+  c.take(256);
+  c.take(m * kp / 2);
+  c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  c.take(n * kp / 2);
+  c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  return c.off;
+}
+
+int rtxb_nvfp4_linear_fwd(const void* x, const void* w, void* out, int64_t m, int64_t n, int64_t k, int scale_mode,
+                          void* workspace, size_t workspace_bytes, void* stream, int* status) {
+  if (!workspace || workspace_bytes < rtxb_nvfp4_linear_workspace_bytes(m, n, k))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_nvfp4_linear_fwd");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  Carver c(workspace);
+  const int64_t kp = round_up(k, 32);
+  uint8_t* scal = c.take(256);
+  uint8_t* qx = c.take(m * kp / 2);
+  uint8_t* sx = c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  uint8_t* qw = c.take(n * kp / 2);
+  uint8_t* sw = c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  // scalar block: [0] amax x, [4] amax w, [16] x scale, [20] w scale, [24] output scale
+  float* x_scale = reinterpret_cast<float*>(scal + 16);
+  float* w_scale = reinterpret_cast<float*>(scal + 20);
+  float* o_scale = reinterpret_cast<float*>(scal + 24);
+  int rc;
+  if ((rc = rtxb_nvfp4_tensor_scale(x, m, k, k, scale_mode, scal, x_scale, nullptr, nullptr, stream))) return rc;
+  if ((rc = rtxb_nvfp4_tensor_scale(w, n, k, k, scale_mode, scal + 4, w_scale, x_scale, o_scale, stream))) return rc;
+  if ((rc = rtxb_nvfp4_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, x_scale, stream))) return rc;
+  if ((rc = rtxb_nvfp4_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, w_scale, stream))) return rc;
+  return rtxb_nvfp4_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, o_scale, stream, status);
+}
+
+}  // extern "C"

@@ -1,0 +1,325 @@
+// HBM-bound quantizers for sm_100a: BF16 -> MXFP8 (rows and transposed) and
+// BF16 -> NVFP4, plus the per-tensor |max| reduction that feeds the NVFP4
+// outer scale.  They replace the reference's MXFP8QuantKernel /
+// MXFP8TransposedQuantKernel (rtx/kernels/mxfp8_quant.py:52-395, :526-1019)
+// and NVFP4QuantKernel (rtx/kernels/nvfp4_quant.py:32-349).
+//
+// Every kernel walks 128-row tiles with a grid-stride loop, reads 16 bytes per
+// thread per load, and stages the tile's scale factors in shared memory so
+// that the 128-row scale tiles (the layout tcgen05.cp consumes) leave the SM
+// as whole 16-byte segments.
+#pragma once
+
+#include "common.cuh"
+
+namespace rtxb {
+
+enum ScaleLayout : int { kScaleRowMajor = 0, kScaleMma64 = 1, kScaleMma128 = 2 };
+
+constexpr int kQuantThreads = 256;
+
+// ---------------------------------------------------------------------------
+// MXFP8 rows: src bf16 [rows, k] (pitch ld elements) -> q e4m3 [rows, kp],
+// scales e8m0.  Tile = 128 rows x 256 columns; a warp owns rows w, w+8, ...,
+// a lane owns 8 consecutive columns, four lanes share one block of 32.
+// ---------------------------------------------------------------------------
+struct QuantMxParams {
+  const __nv_bfloat16* src;
+  uint8_t* q;
+  uint8_t* scales;
+  int rows, k, kp;       // kp = k rounded up to 32
+  int64_t ld;            // source row pitch (elements)
+  int nb;                // kp / 32 scale blocks per row
+  int sf_chunks;         // 512-byte scale tiles per 128 rows (ceil(nb / 4))
+  int layout;            // ScaleLayout
+  int round_to_infinity; // 1 = default, 0 = OCP floor ablation
+};
+
+__device__ __forceinline__ void load8_bf16(const __nv_bfloat16* row_ptr, int col, int k, bool vec_ok, float (&v)[8]) {
+  if (vec_ok && col + 8 <= k) {
+    uint4 raw = __ldg(reinterpret_cast<const uint4*>(row_ptr + col));
+    v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
+    v[4] = bf16_lo(raw.z); v[5] = bf16_hi(raw.z); v[6] = bf16_lo(raw.w); v[7] = bf16_hi(raw.w);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (col + e < k) ? __bfloat162float(row_ptr[col + e]) : 0.0f;
+  }
+}
+
+__device__ __forceinline__ float amax8(const float (&v)[8]) {
+  float a = fabsf(v[0]);
+#pragma unroll
+  for (int e = 1; e < 8; ++e) a = fmax_nan(a, fabsf(v[e]));
+  return a;
+}
+
+// write one 128-row x (4*chunks) block tile of scale bytes held in shared
+// memory as tile[row][blocks_in_tile] to global in the requested layout
+template <int BLOCKS>
+__device__ __forceinline__ void store_scale_tile(const uint8_t (*tile)[BLOCKS], uint8_t* scales, int layout, int row0,
+                                                 int blk0, int rows, int nb, int sf_chunks) {
+  if (layout == kScaleMma128) {
+    // BLOCKS/4 tiles of 512 bytes; one 16-byte segment per (tile, row % 32)
+    for (int t = threadIdx.x; t < (BLOCKS / 4) * 32; t += blockDim.x) {
+      const int chunk = t >> 5, r32 = t & 31;
+      if ((blk0 >> 2) + chunk >= sf_chunks) continue;
+      uint32_t w[4];
+#pragma unroll
+      for (int rg = 0; rg < 4; ++rg) {
+        const uint8_t* s = tile[rg * 32 + r32] + chunk * 4;
+        w[rg] = s[0] | (s[1] << 8) | (s[2] << 16) | (static_cast<uint32_t>(s[3]) << 24);
+      }
+      uint8_t* dst = scales + (static_cast<size_t>(row0 >> 7) * sf_chunks + (blk0 >> 2) + chunk) * 512 + r32 * 16;
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+    for (int t = threadIdx.x; t < 128 * BLOCKS; t += blockDim.x) {
+      const int r = t / BLOCKS, b = t % BLOCKS;
+      if (row0 + r < rows && blk0 + b < nb) scales[static_cast<size_t>(row0 + r) * nb + blk0 + b] = tile[r][b];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kQuantThreads) quant_mxfp8_rows_kernel(const QuantMxParams p) {
+  __shared__ __align__(16) uint8_t tile_scales[128][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col_tiles = (p.kp + 255) / 256;
+  const int row_tiles = (p.rows + 127) / 128;
+  const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
+  const bool q_vec_ok = (reinterpret_cast<uintptr_t>(p.q) & 7) == 0;  // kp % 32 == 0 keeps rows 8-byte aligned
+  for (int tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
+    const int row0 = (tile / col_tiles) * 128;
+    const int col0 = (tile % col_tiles) * 256;
+    const int col = col0 + lane * 8;
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int r = warp + 8 * i;
+      const int row = row0 + r;
+      float v[8];
+      if (row < p.rows && col < p.kp) {
+        load8_bf16(p.src + static_cast<int64_t>(row) * p.ld, col, p.k, vec_ok, v);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+      }
+      float a = amax8(v);
+      a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 1));
+      a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 2));
+      const uint32_t code = e8m0_from_amax(a, p.round_to_infinity != 0);
+      const float recip = e8m0_reciprocal(code);
+      if ((lane & 3) == 0) tile_scales[r][lane >> 2] = (row < p.rows && col < p.kp) ? static_cast<uint8_t>(code) : 0;
+      if (row < p.rows && col < p.kp) {
+        const uint32_t lo = cvt_e4m3x2(v[0] * recip, v[1] * recip) | (cvt_e4m3x2(v[2] * recip, v[3] * recip) << 16);
+        const uint32_t hi = cvt_e4m3x2(v[4] * recip, v[5] * recip) | (cvt_e4m3x2(v[6] * recip, v[7] * recip) << 16);
+        uint8_t* dst = p.q + static_cast<int64_t>(row) * p.kp + col;
+        if (q_vec_ok) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+        } else {
+          for (int e = 0; e < 4; ++e) { dst[e] = lo >> (8 * e); dst[4 + e] = hi >> (8 * e); }
+        }
+      }
+    }
+    __syncthreads();
+    store_scale_tile<8>(tile_scales, p.scales, p.layout, row0, col0 / 32, p.rows, p.nb, p.sf_chunks);
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// MXFP8 transposed: src bf16 stored [k, rows] (pitch ld) -> q e4m3 [rows, kp]
+// K-major with blocks of 32 along the stored row index k; equal to quantising
+// src^T.contiguous() by rows.  Tile = 128 output rows x 128 k: the CTA reads
+// 128 source rows of 128 values (coalesced), keeps them in shared memory and
+// each thread then walks one output row's 32-value blocks down a column.
+// ---------------------------------------------------------------------------
+struct QuantMxTParams {
+  const __nv_bfloat16* src;  // [k, rows]
+  uint8_t* q;                // [rows, kp]
+  uint8_t* scales;
+  int rows, k, kp;
+  int64_t ld;
+  int nb, sf_chunks, layout, round_to_infinity;
+};
+
+__global__ void __launch_bounds__(kQuantThreads) quant_mxfp8_transposed_kernel(const QuantMxTParams p) {
+  // [k_local][row_local] BF16 bits; pitch 130 halfwords = 65 words (odd) so a warp reading
+  // one k with 32 consecutive rows, or one row with consecutive k, stays conflict free
+  __shared__ uint16_t tile[128][130];
+  __shared__ __align__(16) uint8_t tile_scales[128][4];
+  const int row_tiles = (p.rows + 127) / 128;
+  const int k_tiles = (p.kp + 127) / 128;
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(p.src);
+  for (int t = blockIdx.x; t < row_tiles * k_tiles; t += gridDim.x) {
+    const int row0 = (t % row_tiles) * 128;  // output rows = source columns
+    const int k0 = (t / row_tiles) * 128;
+    // load: 128 source rows (k) x 128 source columns; 2 values per thread per pass
+    for (int i = threadIdx.x; i < 128 * 64; i += kQuantThreads) {
+      const int kk = i >> 6, c2 = (i & 63) * 2;
+      const int gk = k0 + kk, gc = row0 + c2;
+      uint16_t a = 0, b = 0;
+      if (gk < p.k) {
+        const uint16_t* rp = src + static_cast<int64_t>(gk) * p.ld;
+        if (gc < p.rows) a = rp[gc];
+        if (gc + 1 < p.rows) b = rp[gc + 1];
+      }
+      tile[kk][c2] = a;
+      tile[kk][c2 + 1] = b;
+    }
+    __syncthreads();
+    // quantise: thread -> (output row r, block j of 32 along k); 128 rows x 4 blocks = 512 items
+    for (int item = threadIdx.x; item < 512; item += kQuantThreads) {
+      const int r = item & 127, j = item >> 7;
+      float v[32];
+      float a = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        v[e] = __uint_as_float(static_cast<uint32_t>(tile[j * 32 + e][r]) << 16);
+        a = fmax_nan(a, fabsf(v[e]));
+      }
+      const uint32_t code = e8m0_from_amax(a, p.round_to_infinity != 0);
+      const float recip = e8m0_reciprocal(code);
+      const int row = row0 + r, kcol = k0 + j * 32;
+      const bool live = row < p.rows && kcol < p.kp;
+      tile_scales[r][j] = live ? static_cast<uint8_t>(code) : 0;
+      if (live) {
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          w[e] = cvt_e4m3x2(v[4 * e] * recip, v[4 * e + 1] * recip) |
+                 (cvt_e4m3x2(v[4 * e + 2] * recip, v[4 * e + 3] * recip) << 16);
+        uint4* dst = reinterpret_cast<uint4*>(p.q + static_cast<int64_t>(row) * p.kp + kcol);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    }
+    __syncthreads();
+    store_scale_tile<4>(tile_scales, p.scales, p.layout, row0, k0 / 32, p.rows, p.nb, p.sf_chunks);
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// per-tensor |max| (NaN-propagating) of a BF16 matrix, accumulated with an
+// integer atomic max on the FP32 bit pattern (non-negative floats order like
+// integers and every NaN pattern is larger than infinity)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) amax_bf16_kernel(const __nv_bfloat16* src, int64_t rows, int64_t k, int64_t ld,
+                                                        uint32_t* amax_bits) {
+  uint32_t m = 0;
+  const bool vec_ok = (ld % 8 == 0) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  if (vec_ok) {
+    const int64_t vec_per_row = k / 8;
+    const int64_t total = rows * vec_per_row;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int64_t r = i / vec_per_row, c = (i % vec_per_row) * 8;
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + r * ld + c));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+        m = max(m, w[e] & 0x7FFF0000u);
+      }
+    }
+  } else {
+    const int64_t total = rows * k;
+    const uint16_t* s = reinterpret_cast<const uint16_t*>(src);
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      m = max(m, (static_cast<uint32_t>(s[(i / k) * ld + (i % k)]) << 16) & 0x7FFFFFFFu);
+    }
+  }
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(amax_bits, m);
+}
+
+// mode 0: exact amax/(448*6); mode 1: power of two 2^ceil(log2(max(amax/2688, 2^-126)));
+// 1.0 when amax == 0.  Optionally also publishes out_scale = scale * other_scale[0].
+__global__ void nvfp4_tensor_scale_kernel(const uint32_t* amax_bits, int mode, float* scale, const float* other_scale,
+                                          float* out_scale) {
+  const float amax = __uint_as_float(*amax_bits);
+  float s;
+  if (mode == 0) {
+    s = __fdiv_rn(amax, 2688.0f);
+  } else {
+    const float target = fmax_nan(__fdiv_rn(amax, 2688.0f), 1.17549435e-38f);
+    const uint32_t bits = __float_as_uint(target);
+    uint32_t ebits = bits & 0x7F800000u;
+    if (bits & 0x007FFFFFu) ebits += 1u << 23;
+    s = __uint_as_float(ebits);
+  }
+  if (amax == 0.0f) s = 1.0f;
+  *scale = s;
+  if (out_scale) *out_scale = s * *other_scale;
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4: src bf16 [rows, k] -> packed e2m1 [rows, kp/2] (kp = k rounded up to
+// 32), E4M3 block scale per 16 values.  Tile = 128 rows x 512 columns; a lane
+// owns one whole block of 16 values (two 16-byte loads, one 8-byte store).
+// ---------------------------------------------------------------------------
+struct QuantNvParams {
+  const __nv_bfloat16* src;
+  uint8_t* q;
+  uint8_t* scales;
+  const float* tensor_scale;  // device scalar, nullptr = 1.0 (block policy)
+  int rows, k, kp;
+  int64_t ld;
+  int nb;         // kp / 16
+  int sf_chunks;  // 512-byte tiles per 128 rows
+  int layout;
+};
+
+__global__ void __launch_bounds__(kQuantThreads) quant_nvfp4_rows_kernel(const QuantNvParams p) {
+  __shared__ __align__(16) uint8_t tile_scales[128][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col_tiles = (p.kp + 511) / 512;
+  const int row_tiles = (p.rows + 127) / 128;
+  const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
+  const float st = p.tensor_scale ? __ldg(p.tensor_scale) : 1.0f;
+  const float six_st = 6.0f * st;
+  const float inv_st = __fdiv_rn(1.0f, st);
+  const int row_bytes = p.kp / 2;
+  for (int tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
+    const int row0 = (tile / col_tiles) * 128;
+    const int col0 = (tile % col_tiles) * 512;
+    const int col = col0 + lane * 16;
+#pragma unroll 2
+    for (int i = 0; i < 16; ++i) {
+      const int r = warp + 8 * i;
+      const int row = row0 + r;
+      const bool live = row < p.rows && col < p.kp;
+      float v[16];
+      if (live) {
+        const __nv_bfloat16* rp = p.src + static_cast<int64_t>(row) * p.ld;
+        load8_bf16(rp, col, p.k, vec_ok, *reinterpret_cast<float(*)[8]>(&v[0]));
+        load8_bf16(rp, col + 8, p.k, vec_ok, *reinterpret_cast<float(*)[8]>(&v[8]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = 0.0f;
+      }
+      float a = fabsf(v[0]);
+#pragma unroll
+      for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
+      float raw = __fdiv_rn(a, six_st);
+      raw = fmin_nan(fmax_nan(raw, 0.015625f), 448.0f);
+      const uint32_t sb = cvt_e4m3x2(raw, raw) & 0xFF;
+      const float recip = __fdiv_rn(inv_st, e4m3_to_float(sb));
+      tile_scales[r][lane] = live ? static_cast<uint8_t>(sb) : 0;
+      if (live) {
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          w0 |= cvt_e2m1x2(v[2 * e] * recip, v[2 * e + 1] * recip) << (8 * e);
+          w1 |= cvt_e2m1x2(v[8 + 2 * e] * recip, v[8 + 2 * e + 1] * recip) << (8 * e);
+        }
+        *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(row) * row_bytes + col / 2) = make_uint2(w0, w1);
+      }
+    }
+    __syncthreads();
+    store_scale_tile<32>(tile_scales, p.scales, p.layout, row0, col0 / 16, p.rows, p.nb, p.sf_chunks);
+    __syncthreads();
+  }
+}
+
+}  // namespace rtxb

@@ -1,0 +1,264 @@
+"""Tensor-level launchers over the C ABI.
+
+Each function mirrors one launch callable the reference obtains from its
+`compile_*` factories (rtx/kernels/*.py) — same operand order, contiguous CUDA
+tensors, asynchronous on the current stream — but runs the sm_100a kernels of
+librtxb.  PyTorch is used only for device memory and the stream handle.
+"""
+
+from __future__ import annotations
+
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+_status_lock = threading.Lock()
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels set when a bounded wait runs out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with _status_lock:
+        word = _status_words.get(idx)
+        if word is None:
+            word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+            _status_words[idx] = word
+    return word
+
+
+def check_device_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel on `device` reported a wait that ran out."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"rtx_b200 kernel reported: {N.DEVICE_STATUS_NAMES.get(code, code)}")
+
+
+def _require(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if t.device.type != "cuda":
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if t.dim() != 2 or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous 2-D tensor")
+
+
+def mx_storage_k(k: int) -> int:
+    return (k + 31) // 32 * 32
+
+
+def mxfp8_scale_numel(rows: int, k: int, layout: int) -> int:
+    return N.query("rtxb_mxfp8_scale_bytes", rows, k, layout)
+
+
+def nvfp4_scale_numel(rows: int, k: int, layout: int) -> int:
+    return N.query("rtxb_nvfp4_scale_bytes", rows, k, layout)
+
+
+# ---------------------------------------------------------------------------
+# MXFP8
+# ---------------------------------------------------------------------------
+
+def mxfp8_quantize(src: torch.Tensor, *, layout: int = N.SCALE_MMA128, rounding: int = N.ROUND_INFINITY,
+                   q: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None
+                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(src bf16 [R,K]) -> (q u8 [R,Kp] E4M3 codes, scales u8 E8M0 codes in `layout`)."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    kp = mx_storage_k(k)
+    if q is None:
+        q = torch.empty(rows, kp, dtype=torch.uint8, device=src.device)
+    if scales is None:
+        scales = torch.empty(mxfp8_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        N.call("rtxb_mxfp8_quantize", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout, rounding,
+               _stream_ptr())
+    return q, scales
+
+
+def mxfp8_quantize_transposed(src: torch.Tensor, *, layout: int = N.SCALE_MMA128,
+                              rounding: int = N.ROUND_INFINITY) -> Tuple[torch.Tensor, torch.Tensor]:
+    """src bf16 stored [K,R] -> quantisation of src.T: q u8 [R,Kp] with 32-blocks along K."""
+    _require(src, torch.bfloat16, "src")
+    k, rows = src.shape
+    kp = mx_storage_k(k)
+    q = torch.empty(rows, kp, dtype=torch.uint8, device=src.device)
+    scales = torch.empty(mxfp8_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        N.call("rtxb_mxfp8_quantize_transposed", src.data_ptr(), rows, k, rows, q.data_ptr(), scales.data_ptr(),
+               layout, rounding, _stream_ptr())
+    return q, scales
+
+
+def mxfp8_gemm(qa, sa, qb, sb, m: int, n: int, k: int, *, out_dtype: torch.dtype = torch.bfloat16,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(qx, qw, sx, sw) -> out[m,n]; scales in the mma128 layout."""
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=qa.device)
+    code = N.OUT_BF16 if out.dtype == torch.bfloat16 else N.OUT_F32
+    with torch.cuda.device(qa.device):
+        N.call("rtxb_mxfp8_gemm", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k,
+               out.stride(0), code, _stream_ptr(), status_word(qa.device).data_ptr())
+    return out
+
+
+def mxfp8_gemm_glu(qa, sa, qb, sb, m: int, inter: int, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(m, inter, dtype=torch.bfloat16, device=qa.device)
+    with torch.cuda.device(qa.device):
+        N.call("rtxb_mxfp8_gemm_glu", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(), m,
+               inter, k, out.stride(0), _stream_ptr(), status_word(qa.device).data_ptr())
+    return out
+
+
+class Workspace:
+    """Caller-owned scratch for the composite entry points; grows on demand and is
+    reused by every call made on the stream it was created for."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.buf: Optional[torch.Tensor] = None
+
+    def get(self, nbytes: int) -> torch.Tensor:
+        if self.buf is None or self.buf.numel() < nbytes:
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        return self.buf
+
+
+def mxfp8_linear_fwd(x: torch.Tensor, w: torch.Tensor, ws: Workspace, out: Optional[torch.Tensor] = None,
+                     rounding: int = N.ROUND_INFINITY) -> torch.Tensor:
+    """(x bf16 [M,K], w bf16 [N,K]) -> out bf16 [M,N]: quantize both, block-scaled GEMM."""
+    _require(x, torch.bfloat16, "x")
+    _require(w, torch.bfloat16, "weight")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError("x and weight disagree on K")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    nbytes = N.query("rtxb_mxfp8_linear_workspace_bytes", m, n, k)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_mxfp8_linear_fwd", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, rounding, buf.data_ptr(),
+               buf.numel(), _stream_ptr(), status_word(x.device).data_ptr())
+    return out
+
+
+def mxfp8_glu_mlp_fwd(x, w_gate_up, w_down, ws: Workspace, h: Optional[torch.Tensor] = None,
+                      y: Optional[torch.Tensor] = None):
+    _require(x, torch.bfloat16, "x")
+    _require(w_gate_up, torch.bfloat16, "w_gate_up")
+    _require(w_down, torch.bfloat16, "w_down")
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    n_out = w_down.shape[0]
+    if w_gate_up.shape[1] != k or w_down.shape[1] != inter:
+        raise ValueError("weight shapes do not chain")
+    if h is None:
+        h = torch.empty(m, inter, dtype=torch.bfloat16, device=x.device)
+    if y is None:
+        y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x.device)
+    nbytes = N.query("rtxb_mxfp8_glu_mlp_workspace_bytes", m, k, inter, n_out)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_mxfp8_glu_mlp_fwd", x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), h.data_ptr(),
+               y.data_ptr(), m, k, inter, n_out, buf.data_ptr(), buf.numel(), _stream_ptr(),
+               status_word(x.device).data_ptr())
+    return h, y
+
+
+def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: bool = True,
+                     dw_dtype: torch.dtype = torch.bfloat16):
+    """(dY [M,N], X [M,K], W [N,K]) -> (dX bf16 [M,K] | None, dW [N,K] | None)."""
+    _require(dy, torch.bfloat16, "grad_output")
+    m, n = dy.shape
+    k = w.shape[1] if w is not None else x.shape[1]
+    dx = torch.empty(m, k, dtype=torch.bfloat16, device=dy.device) if need_dx else None
+    dw = torch.empty(n, k, dtype=dw_dtype, device=dy.device) if need_dw else None
+    if need_dx:
+        _require(w, torch.bfloat16, "weight")
+    if need_dw:
+        _require(x, torch.bfloat16, "x")
+    nbytes = N.query("rtxb_mxfp8_backward_workspace_bytes", m, n, k)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(dy.device):
+        N.call("rtxb_mxfp8_linear_bwd", dy.data_ptr(), x.data_ptr() if x is not None else None,
+               w.data_ptr() if w is not None else None, dx.data_ptr() if need_dx else None,
+               dw.data_ptr() if need_dw else None, N.OUT_BF16 if dw_dtype == torch.bfloat16 else N.OUT_F32, m, n, k,
+               buf.data_ptr(), buf.numel(), _stream_ptr(), status_word(dy.device).data_ptr())
+    return dx, dw
+
+
+# ---------------------------------------------------------------------------
+# NVFP4
+# ---------------------------------------------------------------------------
+
+def nvfp4_tensor_scale(src: torch.Tensor, mode: int = N.TENSOR_SCALE_POWER2,
+                       other_scale: Optional[torch.Tensor] = None):
+    """Device-side |max| reduction + outer-scale rule.  Returns scale f32[1], and
+    also scale*other_scale f32[1] when `other_scale` is given."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    scratch = torch.empty(1, dtype=torch.int32, device=src.device)
+    scale = torch.empty(1, dtype=torch.float32, device=src.device)
+    prod = torch.empty(1, dtype=torch.float32, device=src.device) if other_scale is not None else None
+    with torch.cuda.device(src.device):
+        N.call("rtxb_nvfp4_tensor_scale", src.data_ptr(), rows, k, k, mode, scratch.data_ptr(), scale.data_ptr(),
+               other_scale.data_ptr() if other_scale is not None else None,
+               prod.data_ptr() if prod is not None else None, _stream_ptr())
+    return (scale, prod) if other_scale is not None else scale
+
+
+def nvfp4_quantize(src: torch.Tensor, tensor_scale: Optional[torch.Tensor], *, layout: int = N.SCALE_MMA128):
+    """(src bf16 [R,K], tensor_scale f32[1] | None) -> (q u8 [R,Kp/2], scales u8 E4M3 codes)."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    kp = mx_storage_k(k)
+    q = torch.empty(rows, kp // 2, dtype=torch.uint8, device=src.device)
+    scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        N.call("rtxb_nvfp4_quantize", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout,
+               tensor_scale.data_ptr() if tensor_scale is not None else None, _stream_ptr())
+    return q, scales
+
+
+def nvfp4_gemm(qa, sa, qb, sb, m: int, n: int, k: int, output_scale: Optional[torch.Tensor], *,
+               out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=qa.device)
+    code = N.OUT_BF16 if out.dtype == torch.bfloat16 else N.OUT_F32
+    with torch.cuda.device(qa.device):
+        N.call("rtxb_nvfp4_gemm", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k,
+               out.stride(0), code, output_scale.data_ptr() if output_scale is not None else None, _stream_ptr(),
+               status_word(qa.device).data_ptr())
+    return out
+
+
+def nvfp4_linear_fwd(x, w, ws: Workspace, out: Optional[torch.Tensor] = None,
+                     scale_mode: int = N.TENSOR_SCALE_POWER2) -> torch.Tensor:
+    _require(x, torch.bfloat16, "x")
+    _require(w, torch.bfloat16, "weight")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError("x and weight disagree on K")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    nbytes = N.query("rtxb_nvfp4_linear_workspace_bytes", m, n, k)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_nvfp4_linear_fwd", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, scale_mode,
+               buf.data_ptr(), buf.numel(), _stream_ptr(), status_word(x.device).data_ptr())
+    return out

@@ -1,0 +1,158 @@
+"""Pins the CPU oracle to the reference: every array in tests/golden/ was
+produced by executing the reference's own functions (see make_golden.py)."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mx_oracle as O
+
+
+def _bf16_from_bits(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def _sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(_bits(t).tobytes()).hexdigest()
+
+
+def test_known_answer_480(golden):
+    """tests/test_mxfp8_quant.py:186-220: 480 -> |q| 448 / code 127 (floor), 240 / code 128 (infinity)."""
+    arrays, _ = golden
+    src = torch.zeros(1, 32)
+    src[0, 0] = 480
+    for rounding, want_max, want_code in (("floor", 448.0, 127), ("infinity", 240.0, 128)):
+        q, s = O.mxfp8_quantize(src.bfloat16(), rounding)
+        assert O.e4m3_decode(q).abs().max().item() == want_max
+        assert int(s[0, 0]) == want_code
+        assert np.array_equal(q.numpy(), arrays[f"ka480_{rounding}_q"])
+        assert np.array_equal(s.numpy(), arrays[f"ka480_{rounding}_s"])
+
+
+@pytest.mark.parametrize("name", ["q1701", "q1703", "qrag", "qtiny", "q33", "special"])
+@pytest.mark.parametrize("rounding", ["infinity", "floor"])
+def test_quantizer_matches_reference_bytes(golden, name, rounding):
+    arrays, _ = golden
+    x = _bf16_from_bits(arrays[f"{name}_x"])
+    q, s = O.mxfp8_quantize(x, rounding)
+    assert np.array_equal(q.numpy(), arrays[f"{name}_{rounding}_q"])
+    assert np.array_equal(s.numpy(), arrays[f"{name}_{rounding}_s"])
+
+
+def test_golden_inputs_regenerate_from_seeds(golden):
+    arrays, manifest = golden
+    for name in ("q1701", "q1703", "qrag"):
+        torch.manual_seed(manifest[name]["seed"])
+        x = torch.randn(*manifest[name]["shape"]).bfloat16()
+        assert np.array_equal(_bits(x), arrays[f"{name}_x"])
+
+
+@pytest.mark.parametrize("mnk", [(128, 128, 128), (37, 70, 128), (5, 129, 256), (3, 5, 1), (7, 11, 17), (9, 131, 127)])
+def test_forward_matches_reference_bits(golden, mnk):
+    """tests/test_mxfp8_fwd.py:359-380 shapes, rtol=0 atol=0 against the reference's `_reference_linear`."""
+    arrays, _ = golden
+    m, n, k = mnk
+    torch.manual_seed(123)
+    x = (torch.randn(m, k) * 0.5).bfloat16()
+    w = (torch.randn(n, k) * 0.5).bfloat16()
+    assert np.array_equal(_bits(O.mxfp8_linear(x, w)), arrays[f"fwd_{m}_{n}_{k}_y"])
+
+
+def test_forward_digests(golden):
+    arrays, manifest = golden
+    torch.manual_seed(321)
+    x = (torch.randn(257, 256) * 0.5).bfloat16()
+    w = (torch.randn(385, 256) * 0.5).bfloat16()
+    assert _sha(O.mxfp8_linear(x, w)) == manifest["fwd_257_385_256"]["sha256_y"]
+    inp = O.make_inputs(1)
+    y = O.mxfp8_linear(inp["x"], inp["w"])
+    assert np.array_equal(_bits(y[:16, :16].contiguous()), arrays["config1_y_corner"])
+    assert _sha(y) == manifest["config1"]["sha256_y"]
+
+
+def test_e4m3_codec_against_torch_cast():
+    codes = torch.arange(256, dtype=torch.uint8)
+    want = codes.view(torch.float8_e4m3fn).float()
+    got = O.e4m3_decode(codes)
+    assert torch.equal(torch.nan_to_num(got, nan=-1.0), torch.nan_to_num(want, nan=-1.0))
+    finite = want[~want.isnan()].sort().values
+    mids = (finite[1:] + finite[:-1]) / 2
+    g = torch.Generator().manual_seed(3)
+    v = torch.cat([mids, finite, torch.randn(100000, generator=g) * 30, torch.randn(100000, generator=g) * 0.01])
+    v = v.clamp(-448, 448)
+    assert torch.equal(O.e4m3_encode(v), v.to(torch.float8_e4m3fn).view(torch.uint8))
+    assert int(O.e4m3_encode(torch.tensor([1e9]))[0]) == 0x7E
+    assert int(O.e4m3_encode(torch.tensor([float("nan")]))[0]) == 0x7F
+
+
+def test_e2m1_codec_round_trip_and_ties():
+    codes = torch.arange(16, dtype=torch.uint8)
+    assert torch.equal(O.e2m1_encode(O.e2m1_decode(codes)) & 0x7, codes & 0x7)
+    ties = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -0.25, -5.0])
+    assert O.e2m1_encode(ties).tolist() == [0, 2, 2, 4, 4, 6, 6, 7, 8, 14]
+
+
+def test_scale_layout_formula():
+    """tests/test_mxfp8_quant.py:108-120: physical = (row%32)*16 + ((row//32)%4)*4 + block%4."""
+    s = (torch.arange(256 * 8) % 251).to(torch.uint8).reshape(256, 8)
+    tiles = O.scales_to_mma128(s)
+    assert tiles.shape == (2, 2, 512)
+    for row, blk in [(0, 0), (33, 5), (127, 3), (128, 4), (255, 7)]:
+        phys = (row % 32) * 16 + ((row // 32) % 4) * 4 + blk % 4
+        assert tiles[row // 128, blk // 4, phys] == s[row, blk]
+    assert torch.equal(O.scales_from_mma128(tiles, 256, 8), s)
+
+
+def test_transposed_quant_is_quant_of_transpose():
+    """tests/test_mxfp8_bwd.py:695-730."""
+    torch.manual_seed(5)
+    x = torch.randn(96, 40).bfloat16()
+    q, s = O.mxfp8_quantize_transposed(x)
+    q2, s2 = O.mxfp8_quantize(x.t().contiguous())
+    assert torch.equal(q, q2) and torch.equal(s, s2)
+    assert q.shape == (40, 96)
+
+
+def test_nvfp4_internal_consistency():
+    """NVFP4 parity is unpinned (no TorchAO here); check the restatement's invariants:
+    storage K (rtx tests/test_nvfp4.py:222-229), scale rules, dequantisation error."""
+    assert [O.nvfp4_storage_k(k) for k in (17, 129, 144, 145)] == [32, 160, 160, 160]
+    torch.manual_seed(1907)
+    x = torch.randn(128, 128).bfloat16()
+    st = O.nvfp4_tensor_scale(x, "exact")
+    assert torch.equal(st, (x.float().abs().amax() / 2688.0).reshape(1))
+    p2 = O.nvfp4_tensor_scale(x, "power2")
+    assert float(torch.log2(p2)) == round(float(torch.log2(p2))) and p2 >= st and p2 < 2 * st
+    assert float(O.nvfp4_tensor_scale(torch.zeros(4, 32), "power2")) == 1.0
+    assert float(O.nvfp4_tensor_scale(x, "block")) == 1.0
+    q, sb = O.nvfp4_quantize(x, st)
+    assert q.shape == (128, 64) and sb.shape == (128, 8) and q.dtype == torch.uint8
+    deq = O.nvfp4_dequantize(q, sb, st)
+    rel = ((deq - x.float()).norm() / x.float().norm()).item()
+    assert rel < 0.12
+    # the block holding the tensor amax uses the top of both ranges: scale 448, payload +-6
+    r, c = divmod(int(x.float().abs().argmax()), 128)
+    assert int(sb[r, c // 16]) == 0x7E
+    nib = (int(q[r, c // 2]) >> (4 * (c % 2))) & 0x7
+    assert nib == 7
+
+
+def test_glu_and_backward_shapes():
+    torch.manual_seed(0)
+    x = torch.randn(64, 96).bfloat16()
+    wgu = (torch.randn(256, 96) / 10).bfloat16()
+    wd = (torch.randn(80, 128) / 11).bfloat16()
+    h, y = O.mxfp8_glu_mlp(x, wgu, wd)
+    h2, _ = O.mxfp8_glu_mlp(x, wgu, wd, fused_rounding=False)
+    assert h.shape == (64, 128) and y.shape == (64, 80)
+    assert (O.bf16_ulp_distance(h, h2) <= 2).float().mean() > 0.95
+    dy = (torch.randn(64, 256) * 0.1).bfloat16()
+    dx, dw = O.mxfp8_backward(x, wgu, dy)
+    assert dx.shape == (64, 96) and dw.shape == (256, 96)
+    ref_dx = dy.float() @ wgu.float()
+    assert ((dx.float() - ref_dx).norm() / ref_dx.norm()) < 0.07
