@@ -1,0 +1,280 @@
+"""Schedule descriptions of the sm_100a kernels.
+
+The public class names are the reference's (rtx/configs/mxfp8.py:18-343,
+rtx/kernels/mxfp8.py:45-545, rtx/kernels/mxfp8_bwd.py:23-464,
+rtx/configs/nvfp4.py); the reference's fields described SM120 schedules (99 KB
+of shared memory, ldmatrix widths, warp-level MMA atoms) and are replaced by the
+knobs the tcgen05 kernels have: CTA tile, pipeline stages, CTA-group size,
+scale layout and rounding.  Every config is frozen, hashable, has an explicit
+`rejection()` legality check returning a reason string or None, and travels
+through custom ops as an interned JSON key (`to_key` / `config_from_key`).
+"""
+
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field, fields
+from typing import ClassVar, Optional
+
+SMEM_CAPACITY_BYTES = 227 * 1024
+TMEM_COLUMNS = 512
+SM_COUNT = 148
+
+_REGISTRY: dict[str, type] = {}
+
+
+def _register(cls):
+    _REGISTRY[cls.__name__] = cls
+    return cls
+
+
+class _Config:
+    def to_dict(self) -> dict:
+        out = {"type": type(self).__name__}
+        for f in fields(self):
+            v = getattr(self, f.name)
+            out[f.name] = v.to_dict() if isinstance(v, _Config) else v
+        return out
+
+    def to_key(self) -> str:
+        return json.dumps(self.to_dict(), sort_keys=True, separators=(",", ":"))
+
+    @classmethod
+    def from_dict(cls, d: dict):
+        kwargs = {}
+        for f in fields(cls):
+            if f.name in d:
+                v = d[f.name]
+                kwargs[f.name] = _REGISTRY[v["type"]].from_dict(v) if isinstance(v, dict) and "type" in v else v
+        return cls(**kwargs)
+
+
+def config_from_key(key: str):
+    d = json.loads(key)
+    return _REGISTRY[d["type"]].from_dict(d)
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8Problem(_Config):
+    """Y[m,n] = X[m,k] W[n,k]^T (rtx/kernels/mxfp8.py:45-66)."""
+    m: int
+    n: int
+    k: int
+
+    @property
+    def storage_k(self) -> int:
+        return (self.k + 31) // 32 * 32
+
+    def rejection(self) -> Optional[str]:
+        if min(self.m, self.n, self.k) <= 0:
+            return "m, n and k must be positive"
+        if max(self.m, self.n, self.k) >= 2 ** 31:
+            return "dimensions must fit in 32 bits"
+        return None
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8QuantConfig(_Config):
+    """BF16 -> MXFP8 quantizer (rtx/configs/mxfp8.py:18-107)."""
+    scale_layout: str = "mma128"       # row_major | mma128 (the tcgen05.cp tiling)
+    scale_rounding: str = "infinity"   # infinity (default) | floor (OCP ablation)
+    rows_per_tile: int = 128
+    threads: int = 256
+
+    def rejection(self, rows: int = 1, k: int = 1) -> Optional[str]:
+        if self.scale_layout == "mma64":
+            return "mma64 is an SM120 scale schedule; sm_100a uses row_major or mma128"
+        if self.scale_layout not in ("row_major", "mma128"):
+            return f"unknown scale layout {self.scale_layout!r}"
+        if self.scale_rounding not in ("infinity", "floor"):
+            return f"unknown scale rounding {self.scale_rounding!r}"
+        if rows <= 0 or k <= 0:
+            return "rows and k must be positive"
+        if (self.rows_per_tile, self.threads) != (128, 256):
+            return "the sm_100a quantizer is built for 128-row tiles and 256 threads"
+        return None
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8GemmConfig(_Config):
+    """tcgen05 block-scaled GEMM on packed operands (rtx/configs/mxfp8.py:110-343)."""
+    tile_m: int = 128
+    tile_n: int = 256
+    tile_k_bytes: int = 128
+    stages: int = 4
+    cta_group: int = 1
+    accumulator_windows: int = 2       # overlapping TMEM windows [0,256) and [192,448)
+    epilogue: str = "direct"           # direct vectorised stores
+    raster: str = "m_fastest"
+
+    BUILT: ClassVar[tuple] = ((128, 256, 128, 4, 1),)
+
+    def smem_bytes(self, sf_bytes_per_stage: int = 1536) -> int:
+        return self.stages * ((self.tile_m + self.tile_n) * self.tile_k_bytes + sf_bytes_per_stage) + 1280
+
+    def rejection(self, problem: Optional[MXFP8Problem] = None) -> Optional[str]:
+        if (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group) not in self.BUILT:
+            return ("no kernel is built for this tile/stage/cta_group combination; built: "
+                    + ", ".join(map(str, self.BUILT)))
+        if self.smem_bytes() > SMEM_CAPACITY_BYTES:
+            return "pipeline does not fit 227 KB of shared memory"
+        if problem is not None:
+            return problem.rejection()
+        return None
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8FwdConfig(_Config):
+    """Forward schedule (rtx/kernels/mxfp8.py:68-545): `pipeline` picks quantize-once +
+    packed GEMM ("materialized") — the only forward pipeline built so far."""
+    pipeline: str = "materialized"
+    quant: MXFP8QuantConfig = field(default_factory=MXFP8QuantConfig)
+    gemm: MXFP8GemmConfig = field(default_factory=MXFP8GemmConfig)
+    glu_epilogue: bool = False
+
+    def rejection(self, problem: Optional[MXFP8Problem] = None) -> Optional[str]:
+        if self.pipeline != "materialized":
+            return f"forward pipeline {self.pipeline!r} is not built"
+        if self.quant.scale_layout != "mma128":
+            return "the GEMM consumes mma128 scales"
+        return self.quant.rejection() or self.gemm.rejection(problem)
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8PrequantConfig(_Config):
+    """Quantize-then-GEMM pair (rtx/fp8.py `MXFP8PrequantConfig`)."""
+    quant: MXFP8QuantConfig = field(default_factory=MXFP8QuantConfig)
+    gemm: MXFP8GemmConfig = field(default_factory=MXFP8GemmConfig)
+
+    def rejection(self, problem: Optional[MXFP8Problem] = None) -> Optional[str]:
+        if self.quant.scale_layout != "mma128":
+            return "the GEMM consumes mma128 scales"
+        return self.quant.rejection() or self.gemm.rejection(problem)
+
+
+MXFP8WeightPrequantConfig = MXFP8PrequantConfig
+MXFP8FullyPrequantConfig = MXFP8GemmConfig
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8BwdMatmulConfig(_Config):
+    """One backward product (rtx/kernels/mxfp8_bwd.py:23-356)."""
+    gemm: MXFP8GemmConfig = field(default_factory=MXFP8GemmConfig)
+    output_dtype: str = "bf16"   # bf16 (reference dtype) | f32 (data-parallel all-reduce)
+
+    def rejection(self) -> Optional[str]:
+        if self.output_dtype not in ("bf16", "f32"):
+            return f"unknown output dtype {self.output_dtype!r}"
+        return self.gemm.rejection()
+
+
+@_register
+@dataclass(frozen=True)
+class MXFP8BwdConfig(_Config):
+    """dX = dY W, dW = dY^T X, operands requantized along their contraction dimension
+    (rtx/kernels/mxfp8_bwd.py:358-464)."""
+    dx: MXFP8BwdMatmulConfig = field(default_factory=MXFP8BwdMatmulConfig)
+    dw: MXFP8BwdMatmulConfig = field(default_factory=MXFP8BwdMatmulConfig)
+    schedule: str = "decomposed"    # quantizers + packed GEMMs
+    streams: str = "single"         # single | dual_stream (dX and dW on two streams)
+
+    def rejection(self) -> Optional[str]:
+        if self.schedule != "decomposed":
+            return f"backward schedule {self.schedule!r} is not built"
+        if self.streams not in ("single", "dual_stream"):
+            return f"unknown stream policy {self.streams!r}"
+        return self.dx.rejection() or self.dw.rejection()
+
+
+@_register
+@dataclass(frozen=True)
+class NVFP4Problem(_Config):
+    m: int
+    n: int
+    k: int
+
+    @property
+    def storage_k(self) -> int:
+        return (self.k + 31) // 32 * 32
+
+    def rejection(self) -> Optional[str]:
+        if min(self.m, self.n, self.k) <= 0:
+            return "m, n and k must be positive"
+        return None
+
+
+@_register
+@dataclass(frozen=True)
+class NVFP4QuantConfig(_Config):
+    """BF16 -> NVFP4 quantizer (rtx/configs/nvfp4.py `NVFP4QuantConfig`)."""
+    scale_layout: str = "mma128"
+    scale_reciprocal: str = "direct"   # (1 / tensor_scale) / block_scale, two IEEE divisions
+    rows_per_tile: int = 128
+    threads: int = 256
+
+    def rejection(self, rows: int = 1, k: int = 1) -> Optional[str]:
+        if self.scale_layout not in ("row_major", "mma128"):
+            return f"unknown scale layout {self.scale_layout!r}"
+        if self.scale_reciprocal != "direct":
+            return "only the reference-default 'direct' reciprocal is built (bit-exact payloads)"
+        if rows <= 0 or k <= 0:
+            return "rows and k must be positive"
+        return None
+
+
+@_register
+@dataclass(frozen=True)
+class NVFP4ScaleConfig(_Config):
+    """Outer-scale policy (rtx/configs/nvfp4.py `NVFP4ScaleConfig`)."""
+    policy: str = "current"            # current | block   (jit_row_region, delayed: not built)
+    tensor_scale_mode: str = "power2"  # power2 (dynamic default) | exact (offline weights)
+
+    def rejection(self) -> Optional[str]:
+        if self.policy not in ("current", "block"):
+            return f"NVFP4 scaling policy {self.policy!r} is not built for sm_100a yet"
+        if self.tensor_scale_mode not in ("power2", "exact"):
+            return f"unknown tensor scale mode {self.tensor_scale_mode!r}"
+        return None
+
+
+@_register
+@dataclass(frozen=True)
+class NVFP4GemmConfig(_Config):
+    tile_m: int = 128
+    tile_n: int = 256
+    tile_k_bytes: int = 128            # 256 E2M1 values
+    stages: int = 4
+    cta_group: int = 1
+
+    def rejection(self, problem: Optional[NVFP4Problem] = None) -> Optional[str]:
+        if (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group) != (128, 256, 128, 4, 1):
+            return "no kernel is built for this tile/stage/cta_group combination"
+        return problem.rejection() if problem is not None else None
+
+
+@_register
+@dataclass(frozen=True)
+class NVFP4DynamicConfig(_Config):
+    quant: NVFP4QuantConfig = field(default_factory=NVFP4QuantConfig)
+    gemm: NVFP4GemmConfig = field(default_factory=NVFP4GemmConfig)
+    scale: NVFP4ScaleConfig = field(default_factory=NVFP4ScaleConfig)
+
+    def rejection(self, problem: Optional[NVFP4Problem] = None) -> Optional[str]:
+        return self.quant.rejection() or self.scale.rejection() or self.gemm.rejection(problem)
+
+
+NVFP4WeightPrequantConfig = NVFP4DynamicConfig
+NVFP4FullyPrequantConfig = NVFP4GemmConfig
+
+DEFAULT_MXFP8_PREQUANT_CONFIG = MXFP8PrequantConfig()
+DEFAULT_MXFP8_INFERENCE_CONFIG = MXFP8PrequantConfig()
+DEFAULT_MXFP8_BWD_CONFIG = MXFP8BwdConfig()
+DEFAULT_FUSED_MXFP8_BWD_CONFIG = MXFP8BwdConfig()
+DEFAULT_NVFP4_QUANT_CONFIG = NVFP4QuantConfig()
+DEFAULT_NVFP4_DYNAMIC_CONFIG = NVFP4DynamicConfig()

@@ -188,12 +188,12 @@ size_t rtxb_nvfp4_scale_bytes(int64_t rows, int64_t k, int layout) {
 
 int rtxb_mxfp8_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales, int scale_layout,
                         int rounding, void* stream) {
-  if (!src || !q || !scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
-  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
-  if (rows > INT32_MAX || k > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
   if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
   if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
     return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!src || !q || !scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (rows > INT32_MAX || k > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
   if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
     return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
   QuantMxParams p;

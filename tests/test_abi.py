@@ -37,7 +37,8 @@ def test_queries_and_argument_checks(native_lib):
     assert N.query("rtxb_nvfp4_scale_bytes", 128, 256, N.SCALE_MMA128) == 4 * 512
     assert N.query("rtxb_mxfp8_linear_workspace_bytes", 256, 1024, 1024) >= (256 + 1024) * 1024
     # rejected before any CUDA call: null operands, bad layouts, short workspace
-    assert native_lib.rtxb_mxfp8_quantize(None, 1, 32, 32, None, None, 0, 1, None) == N.SCALE_ROW_MAJOR - 1
+    assert native_lib.rtxb_mxfp8_quantize(None, 1, 32, 32, None, None, 0, 1, None) == -1
+    assert native_lib.rtxb_mxfp8_quantize(None, 1, 32, 32, None, None, N.SCALE_MMA64, 1, None) == -2
     assert native_lib.rtxb_mxfp8_gemm(None, None, None, None, None, 1, 1, 1, 1, 0, None, None) == -1
     assert native_lib.rtxb_mxfp8_linear_fwd(None, None, None, 8, 8, 32, 1, None, 0, None, None) == -4
     with pytest.raises(N.NativeError, match="workspace"):

@@ -1,0 +1,352 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the
+committed golden fixtures.  Bars: quantized payloads and scales bit exact;
+GEMM outputs rel-Frobenius <= 1e-3 and <= 1 BF16 ulp on >= 99.9 % of elements
+versus the FP32-accumulated dequantized oracle (bit exact on the reference's
+own small shapes)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_FRO_MAX = 1e-3
+FRAC_1ULP_MIN = 0.999
+
+
+@pytest.fixture(scope="module")
+def gpu(native_lib):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    from rtx_b200 import _native as N
+    from rtx_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    return ops, N, dev, ops.Workspace(dev)
+
+
+def _unpack_scales(t, rows, nb, chunks):
+    return O.scales_from_mma128(t.cpu().reshape(-1, chunks, 512), rows, nb)
+
+
+def _canon_nan(q):
+    q = q.clone()
+    q[(q & 0x7F) == 0x7F] = 0x7F
+    return q
+
+
+def _assert_output(got, want, bit_exact=False):
+    rep = O.parity_report(got.cpu(), want)
+    if bit_exact:
+        assert rep["bit_equal"], rep
+    assert rep["rel_fro"] <= REL_FRO_MAX and rep["frac_le_1ulp"] >= FRAC_1ULP_MIN, rep
+
+
+def _ok(ops, dev):
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)
+
+
+# ----------------------------------------------------------------------------- quantizers
+
+@pytest.mark.parametrize("shape", [(128, 256), (64, 256), (1, 32), (1, 1), (5, 33), (9, 127), (257, 385), (300, 1000)])
+@pytest.mark.parametrize("rounding", ["infinity", "floor"])
+def test_mxfp8_quantizer_bit_exact(gpu, shape, rounding):
+    ops, N, dev, _ = gpu
+    torch.manual_seed(1701)
+    x = torch.randn(*shape).bfloat16()
+    qo, so = O.mxfp8_quantize(x, rounding)
+    nb = so.shape[1]
+    for layout in (N.SCALE_ROW_MAJOR, N.SCALE_MMA128):
+        q, s = ops.mxfp8_quantize(x.to(dev), layout=layout, rounding=N.ROUND_INFINITY if rounding == "infinity" else N.ROUND_FLOOR)
+        _ok(ops, dev)
+        s = s.cpu().reshape(shape[0], nb) if layout == N.SCALE_ROW_MAJOR else _unpack_scales(s, shape[0], nb, (nb + 3) // 4)
+        assert torch.equal(q.cpu(), qo)
+        assert torch.equal(s, so)
+
+
+def test_mxfp8_quantizer_golden_fixtures(gpu, golden):
+    """Bytes produced by executing the reference (tests/golden/make_golden.py)."""
+    ops, N, dev, _ = gpu
+    arrays, _ = golden
+    for name in ("q1701", "q1703", "qrag", "qtiny", "q33", "special"):
+        x = torch.from_numpy(arrays[f"{name}_x"].view(np.int16).copy()).view(torch.bfloat16)
+        for rounding, code in (("infinity", N.ROUND_INFINITY), ("floor", N.ROUND_FLOOR)):
+            q, s = ops.mxfp8_quantize(x.to(dev), layout=N.SCALE_ROW_MAJOR, rounding=code)
+            _ok(ops, dev)
+            want_q = torch.from_numpy(arrays[f"{name}_{rounding}_q"].copy())
+            want_s = torch.from_numpy(arrays[f"{name}_{rounding}_s"].copy())
+            assert torch.equal(_canon_nan(q.cpu()), _canon_nan(want_q)), (name, rounding)
+            assert torch.equal(s.cpu().reshape(want_s.shape), want_s), (name, rounding)
+
+
+def test_mxfp8_known_answer_480(gpu):
+    ops, N, dev, _ = gpu
+    src = torch.zeros(1, 32)
+    src[0, 0] = 480
+    for code, want_max, want_scale in ((N.ROUND_FLOOR, 448.0, 127), (N.ROUND_INFINITY, 240.0, 128)):
+        q, s = ops.mxfp8_quantize(src.bfloat16().to(dev), layout=N.SCALE_ROW_MAJOR, rounding=code)
+        _ok(ops, dev)
+        assert O.e4m3_decode(q.cpu()).abs().max().item() == want_max
+        assert int(s.cpu()[0]) == want_scale
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 64), (33, 5), (127, 9), (385, 257), (1, 1), (2048, 96)])
+def test_mxfp8_transposed_quantizer_equals_quant_of_transpose(gpu, shape):
+    """rtx tests/test_mxfp8_bwd.py:695-730."""
+    ops, N, dev, _ = gpu
+    torch.manual_seed(1705)
+    x = torch.randn(*shape).bfloat16()   # stored [K, R]
+    qo, so = O.mxfp8_quantize(x.t().contiguous())
+    k, r = shape
+    nb = so.shape[1]
+    for layout in (N.SCALE_ROW_MAJOR, N.SCALE_MMA128):
+        q, s = ops.mxfp8_quantize_transposed(x.to(dev), layout=layout)
+        _ok(ops, dev)
+        s = s.cpu().reshape(r, nb) if layout == N.SCALE_ROW_MAJOR else _unpack_scales(s, r, nb, (nb + 3) // 4)
+        assert torch.equal(q.cpu(), qo) and torch.equal(s, so)
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (5, 17), (9, 129), (257, 400), (1, 1)])
+@pytest.mark.parametrize("mode", ["exact", "power2", "block"])
+def test_nvfp4_quantizer_bit_exact(gpu, shape, mode):
+    ops, N, dev, _ = gpu
+    torch.manual_seed(1907)
+    x = torch.randn(*shape).bfloat16()
+    st_o = O.nvfp4_tensor_scale(x, mode)
+    if mode == "block":
+        st = None
+    else:
+        st = ops.nvfp4_tensor_scale(x.to(dev), N.TENSOR_SCALE_EXACT if mode == "exact" else N.TENSOR_SCALE_POWER2)
+        _ok(ops, dev)
+        assert torch.equal(st.cpu(), st_o)
+    qo, so = O.nvfp4_quantize(x, st_o)
+    nb = so.shape[1]
+    for layout in (N.SCALE_ROW_MAJOR, N.SCALE_MMA128):
+        q, s = ops.nvfp4_quantize(x.to(dev), st, layout=layout)
+        _ok(ops, dev)
+        chunks = ((nb + 3) // 4 + 3) // 4 * 4
+        s = s.cpu().reshape(shape[0], nb) if layout == N.SCALE_ROW_MAJOR else _unpack_scales(s, shape[0], nb, chunks)
+        assert torch.equal(q.cpu(), qo) and torch.equal(s, so)
+
+
+def test_nvfp4_tensor_scale_zero_tensor(gpu):
+    ops, N, dev, _ = gpu
+    st = ops.nvfp4_tensor_scale(torch.zeros(16, 64, dtype=torch.bfloat16, device=dev))
+    assert float(st.cpu()) == 1.0
+
+
+def test_quantizers_reject_bad_arguments(gpu):
+    ops, N, dev, _ = gpu
+    x = torch.zeros(4, 32, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(N.NativeError, match="mma64"):
+        ops.mxfp8_quantize(x, layout=N.SCALE_MMA64)
+    with pytest.raises(TypeError):
+        ops.mxfp8_quantize(x.float())
+    with pytest.raises(ValueError):
+        ops.mxfp8_quantize(x.cpu())
+
+
+# ----------------------------------------------------------------------------- forward
+
+@pytest.mark.parametrize("mnk", [(128, 128, 128), (37, 70, 128), (5, 129, 256), (3, 5, 1), (7, 11, 17), (9, 131, 127)])
+def test_mxfp8_forward_reference_shapes_bit_exact(gpu, golden, mnk):
+    """rtx tests/test_mxfp8_fwd.py:359-380: fused output rtol=0, atol=0; compared with the
+    reference's own output bits and with the oracle."""
+    ops, N, dev, ws = gpu
+    arrays, _ = golden
+    m, n, k = mnk
+    torch.manual_seed(123)
+    x = (torch.randn(m, k) * 0.5).bfloat16()
+    w = (torch.randn(n, k) * 0.5).bfloat16()
+    y = ops.mxfp8_linear_fwd(x.to(dev), w.to(dev), ws)
+    _ok(ops, dev)
+    want = torch.from_numpy(arrays[f"fwd_{m}_{n}_{k}_y"].view(np.int16).copy()).view(torch.bfloat16)
+    assert torch.equal(y.cpu().view(torch.int16), want.view(torch.int16))
+    _assert_output(y, O.mxfp8_linear(x, w), bit_exact=True)
+
+
+@pytest.mark.parametrize("mnk", [(257, 385, 256), (256, 1024, 1024), (1000, 3000, 2048), (129, 257, 4096)])
+def test_mxfp8_forward_larger_shapes(gpu, mnk):
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    if mnk == (256, 1024, 1024):
+        inp = O.make_inputs(1)          # benchmark configuration 1, seed 0
+        x, w = inp["x"], inp["w"]
+    else:
+        torch.manual_seed(321)
+        x = (torch.randn(m, k) * 0.5).bfloat16()
+        w = (torch.randn(n, k) * 0.5).bfloat16()
+    y = ops.mxfp8_linear_fwd(x.to(dev), w.to(dev), ws)
+    _ok(ops, dev)
+    _assert_output(y, O.mxfp8_linear(x, w))
+
+
+def test_mxfp8_forward_floor_rounding_ablation(gpu):
+    ops, N, dev, ws = gpu
+    torch.manual_seed(9)
+    x = torch.randn(130, 200).bfloat16()
+    w = torch.randn(90, 200).bfloat16()
+    y = ops.mxfp8_linear_fwd(x.to(dev), w.to(dev), ws, rounding=N.ROUND_FLOOR)
+    _ok(ops, dev)
+    _assert_output(y, O.mxfp8_linear(x, w, "floor"))
+
+
+def test_mxfp8_prequantized_gemm_f32_and_repeatability(gpu):
+    """Packed-operand GEMM (rtx tests/test_mxfp8_quant.py:222-254), FP32 output, and eight
+    repeats into NaN-poisoned outputs to catch stale-barrier races (rtx tests/test_mxfp8_fwd.py:664-672)."""
+    ops, N, dev, _ = gpu
+    torch.manual_seed(1702)
+    m, n, k = 384, 640, 512
+    x, w = torch.randn(m, k).bfloat16(), torch.randn(n, k).bfloat16()
+    qa, sa = ops.mxfp8_quantize(x.to(dev))
+    qb, sb = ops.mxfp8_quantize(w.to(dev))
+    want = O.mxfp8_linear_f32(x, w)
+    first = None
+    for _ in range(8):
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device=dev)
+        ops.mxfp8_gemm(qa, sa, qb, sb, m, n, k, out=out)
+        _ok(ops, dev)
+        got = out.cpu()
+        assert not torch.isnan(got).any()
+        assert ((got - want).norm() / want.norm()) < 1e-5
+        first = got if first is None else first
+        assert torch.equal(got, first)
+
+
+@pytest.mark.parametrize("dims", [(128, 128, 128, 128), (256, 512, 384, 512), (300, 256, 256, 200), (64, 96, 128, 80)])
+def test_mxfp8_glu_mlp(gpu, dims):
+    ops, N, dev, ws = gpu
+    m, k, inter, n_out = dims
+    inp = O.make_inputs(2, m=m, k=k, inter=inter)
+    x, wgu = inp["x"], inp["w_gate_up"]
+    torch.manual_seed(4)
+    wd = (torch.randn(n_out, inter) / inter ** 0.5).bfloat16()
+    h, y = ops.mxfp8_glu_mlp_fwd(x.to(dev), wgu.to(dev), wd.to(dev), ws)
+    _ok(ops, dev)
+    ho, yo = O.mxfp8_glu_mlp(x, wgu, wd)
+    _assert_output(h, ho)
+    # Y is compared on the device's own H so that one-ulp differences in H do not compound
+    _assert_output(y, O.mxfp8_linear(h.cpu(), wd))
+    rep = O.parity_report(y.cpu(), yo)
+    assert rep["rel_fro"] <= 5e-3, rep
+
+
+def test_mxfp8_glu_rejects_ragged_inter(gpu):
+    ops, N, dev, ws = gpu
+    x = torch.zeros(8, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(N.NativeError, match="inter"):
+        ops.mxfp8_glu_mlp_fwd(x, torch.zeros(2 * 96, 64, dtype=torch.bfloat16, device=dev),
+                              torch.zeros(32, 96, dtype=torch.bfloat16, device=dev), ws)
+
+
+# ----------------------------------------------------------------------------- backward
+
+@pytest.mark.parametrize("mnk", [(128, 128, 128), (256, 384, 512), (100, 70, 50), (512, 256, 1024), (33, 1, 7)])
+@pytest.mark.parametrize("dw_dtype", [torch.bfloat16, torch.float32])
+def test_mxfp8_backward(gpu, mnk, dw_dtype):
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    inp = O.make_inputs(4, m=m, n=n, k=k)
+    x, w, dy = inp["x"], inp["w"], inp["dy"]
+    dx, dw = ops.mxfp8_linear_bwd(dy.to(dev), x.to(dev), w.to(dev), ws, dw_dtype=dw_dtype)
+    _ok(ops, dev)
+    dxo, dwo = O.mxfp8_backward(x, w, dy, dw_dtype=torch.float32)
+    _assert_output(dx, dxo)
+    if dw_dtype == torch.bfloat16:
+        _assert_output(dw, dwo.bfloat16())
+    else:
+        assert ((dw.cpu() - dwo).norm() / dwo.norm().clamp(min=1e-30)) < 1e-5
+    # sanity against the unquantized FP32 product (rtx tests/test_mxfp8_bwd.py:634-653: < 7 %)
+    if min(m, n, k) >= 32:
+        ref = dy.float() @ w.float()
+        assert ((dx.float().cpu() - ref).norm() / ref.norm()) < 0.07
+
+
+def test_mxfp8_backward_single_outputs(gpu):
+    ops, N, dev, ws = gpu
+    inp = O.make_inputs(4, m=128, n=128, k=128)
+    x, w, dy = (inp[k].to(dev) for k in ("x", "w", "dy"))
+    dx, dw = ops.mxfp8_linear_bwd(dy, x, w, ws)
+    dx2, none = ops.mxfp8_linear_bwd(dy, None, w, ws, need_dw=False)
+    none2, dw2 = ops.mxfp8_linear_bwd(dy, x, None, ws, need_dx=False)
+    _ok(ops, dev)
+    assert none is None and none2 is None
+    assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
+
+
+# ----------------------------------------------------------------------------- NVFP4
+
+@pytest.mark.parametrize("mnk", [(128, 256, 256), (128, 128, 128), (37, 70, 128), (5, 129, 272), (257, 385, 512), (9, 131, 127), (512, 1024, 2048)])
+@pytest.mark.parametrize("mode", ["power2", "exact"])
+def test_nvfp4_forward(gpu, mnk, mode):
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    inp = O.make_inputs(3, m=m, n=n, k=k)
+    x, w = inp["x"], inp["w"]
+    y = ops.nvfp4_linear_fwd(x.to(dev), w.to(dev), ws,
+                             scale_mode=N.TENSOR_SCALE_POWER2 if mode == "power2" else N.TENSOR_SCALE_EXACT)
+    _ok(ops, dev)
+    _assert_output(y, O.nvfp4_linear(x, w, mode=mode))
+    ref = x.float() @ w.float().t()
+    if k >= 128:   # rtx benchmarks/validate_production.py:75-76: NVFP4 forward rel-L2 < 18 %
+        assert ((y.float().cpu() - ref).norm() / ref.norm()) < 0.18
+
+
+# ----------------------------------------------------------------------------- full-size properties
+
+def _deq_mx_gpu(q, s_tiles, rows, k):
+    """Dequantise on the device with plain torch ops (checker only)."""
+    nb = (k + 31) // 32
+    chunks = (nb + 3) // 4
+    r = torch.arange(rows, device=q.device).unsqueeze(1)
+    b = torch.arange(nb, device=q.device).unsqueeze(0)
+    idx = ((r // 128) * chunks + b // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + b % 4
+    codes = s_tiles[idx.reshape(-1)].reshape(rows, nb).to(torch.int32)
+    scale = (codes.clamp(min=1) << 23).view(torch.float32)
+    return q.view(torch.float8_e4m3fn).float() * scale.repeat_interleave(32, dim=1)
+
+
+def test_full_size_config2_properties(gpu):
+    """Benchmark configuration 2 at full size: sampled rows of every payload against the oracle,
+    GEMM tiles from the first/middle/last tile rows and columns against an FP32 matmul of the
+    device-dequantised operands, and a column checksum (linearity) over the whole output."""
+    ops, N, dev, ws = gpu
+    inp = O.make_inputs(2)
+    x, wgu, wd = inp["x"], inp["w_gate_up"], inp["w_down"]
+    m, k = x.shape
+    inter = wgu.shape[0] // 2
+    xd, wgud, wdd = x.to(dev), wgu.to(dev), wd.to(dev)
+    qx, sx = ops.mxfp8_quantize(xd)
+    qg, sg = ops.mxfp8_quantize(wgud)
+    _ok(ops, dev)
+    for rows in (slice(0, 64), slice(4000, 4064), slice(m - 64, m)):
+        qo, _ = O.mxfp8_quantize(x[rows])
+        assert torch.equal(qx[rows].cpu(), qo)
+    qo, so = O.mxfp8_quantize(wgu[-128:])
+    assert torch.equal(qg[-128:].cpu(), qo)
+    h, y = ops.mxfp8_glu_mlp_fwd(xd, wgud, wdd, ws)
+    _ok(ops, dev)
+    dx = _deq_mx_gpu(qx, sx, m, k)
+    dg = _deq_mx_gpu(qg, sg, 2 * inter, k)
+    for r0 in (0, 4096 - 64, m - 128):
+        for c0 in (0, 7168 - 64, inter - 128):
+            acc_g = dx[r0:r0 + 128] @ dg[c0:c0 + 128].t()
+            acc_u = dx[r0:r0 + 128] @ dg[inter + c0:inter + c0 + 128].t()
+            want = (torch.nn.functional.silu(acc_g) * acc_u).bfloat16()
+            _assert_output(h[r0:r0 + 128, c0:c0 + 128].contiguous(), want.cpu())
+    # linearity: column sums of the plain GEMM equal (sum of rows of deq X) @ deq W^T
+    yg = ops.mxfp8_gemm(qx, sx, qg, sg, m, 2 * inter, k, out_dtype=torch.float32)
+    _ok(ops, dev)
+    want = dx.double().sum(dim=0) @ dg.double().t()
+    got = yg.double().sum(dim=0)
+    assert ((got - want).norm() / want.norm()) < 1e-5
+    # down projection on the device's own H
+    qh, sh = ops.mxfp8_quantize(h)
+    qd, sd = ops.mxfp8_quantize(wdd)
+    dh, dd = _deq_mx_gpu(qh, sh, m, inter), _deq_mx_gpu(qd, sd, wd.shape[0], inter)
+    for r0 in (0, m - 128):
+        want = (dh[r0:r0 + 128] @ dd.t()).bfloat16()
+        _assert_output(y[r0:r0 + 128].contiguous(), want.cpu())
