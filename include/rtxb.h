@@ -39,6 +39,7 @@ extern "C" {
 #define RTXB_E_WORKSPACE (-4)
 #define RTXB_E_CUDA (-5)
 #define RTXB_E_DRIVER (-6)
+#define RTXB_E_SCRATCH_CAPACITY (-7)
 
 #define RTXB_SCALE_ROW_MAJOR 0
 #define RTXB_SCALE_MMA64 1
@@ -103,6 +104,28 @@ int rtxb_mxfp8_gemm_glu(const void* qa, const void* sa, const void* qb, const vo
 size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int rtxb_mxfp8_linear_fwd(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n, int64_t k,
                           int rounding, void* workspace, size_t workspace_bytes, void* stream, int* status);
+
+/* The same forward with no scratch argument, for callers that cannot allocate.
+ * (No counterpart in the reference, whose runners allocate their workspaces with
+ * PyTorch.)  Meant for hosts that only hold the input and output buffers they were
+ * given — generated wrappers calling `launcher(x, w, out=buf)`, plugins inside another
+ * runtime's memory pool, sections where cudaMalloc's device-wide synchronisation is
+ * not acceptable.  The quantized operands go to a fixed RTXB_NOALLOC_SCRATCH_BYTES
+ * array that is part of the library image on every GPU that loads it; the call
+ * allocates and frees nothing.
+ *   - Shapes whose operands need more than that array (the value
+ *     rtxb_mxfp8_linear_workspace_bytes(m, n, k) reports) are refused with
+ *     RTXB_E_SCRATCH_CAPACITY and nothing is launched.
+ *   - The first call on each device looks up that device's address of the array
+ *     (the device must be current, as for every entry point); make that first call
+ *     before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the last call's
+ *     contents.  Nothing in it needs clearing between calls (each call rewrites all
+ *     it reads), but two calls whose kernels overlap on the GPU — different streams
+ *     without an ordering between them — race on it.  Order them. */
+#define RTXB_NOALLOC_SCRATCH_BYTES (32 * 1024 * 1024)
+int rtxb_mxfp8_linear_fwd_noalloc(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n,
+                                  int64_t k, int rounding, void* stream, int* status);
 
 /* SwiGLU MLP forward: H = silu(X Wg^T) * (X Wu^T), Y = H Wd^T, every GEMM
  * operand MXFP8-quantized along its K.  w_gate_up bf16 [2*inter, k], w_down

@@ -19,6 +19,8 @@ SCALE_ROW_MAJOR, SCALE_MMA64, SCALE_MMA128 = 0, 1, 2
 ROUND_FLOOR, ROUND_INFINITY = 0, 1
 OUT_BF16, OUT_F32 = 0, 1
 TENSOR_SCALE_EXACT, TENSOR_SCALE_POWER2 = 0, 1
+E_SCRATCH_CAPACITY = -7
+NOALLOC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 DEVICE_STATUS_NAMES = {
     0: "ok",
@@ -45,6 +47,7 @@ SIGNATURES = {
     "rtxb_mxfp8_gemm_glu": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "rtxb_mxfp8_linear_workspace_bytes": (_Z, [_L, _L, _L]),
     "rtxb_mxfp8_linear_fwd": (_I, [_P, _P, _P, _L, _L, _L, _I, _P, _Z, _P, _P]),
+    "rtxb_mxfp8_linear_fwd_noalloc": (_I, [_P, _P, _P, _L, _L, _L, _I, _P, _P]),
     "rtxb_mxfp8_glu_mlp_workspace_bytes": (_Z, [_L, _L, _L, _L]),
     "rtxb_mxfp8_glu_mlp_fwd": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _Z, _P, _P]),
     "rtxb_mxfp8_backward_workspace_bytes": (_Z, [_L, _L, _L]),

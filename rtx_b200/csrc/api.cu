@@ -162,6 +162,7 @@ const char* rtxb_error_string(int code) {
     case RTXB_E_WORKSPACE: return "workspace too small";
     case RTXB_E_CUDA: return "CUDA runtime error";
     case RTXB_E_DRIVER: return "CUDA driver error";
+    case RTXB_E_SCRATCH_CAPACITY: return "shape exceeds the built-in scratch array of the no-allocation entry point";
     default: return "unknown error";
   }
 }
