@@ -131,8 +131,9 @@ int check_gemm_args(const void* qa, const void* sa, const void* qb, const void* 
   return RTXB_OK;
 }
 
-int quant_grid(int64_t tiles) {
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+// grid-stride kernels: one wave of resident CTAs (per_sm = CTAs that fit one SM)
+int quant_grid(int64_t tiles, int per_sm) {
+  const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm;
   return static_cast<int>(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
 }
 
@@ -209,8 +210,8 @@ int rtxb_mxfp8_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, vo
   p.sf_chunks = (p.nb + 3) / 4;
   p.layout = scale_layout;
   p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
-  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 255) / 256);
-  quant_mxfp8_rows_kernel<<<quant_grid(tiles), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 127) / 128);
+  quant_mxfp8_rows_kernel<<<quant_grid(tiles, 6), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   RTXB_CHECK_LAUNCH("quant_mxfp8_rows_kernel");
   return RTXB_OK;
 }
@@ -239,7 +240,7 @@ int rtxb_mxfp8_quantize_transposed(const void* src, int64_t rows, int64_t k, int
   p.layout = scale_layout;
   p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
   const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 127) / 128);
-  quant_mxfp8_transposed_kernel<<<quant_grid(tiles), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  quant_mxfp8_transposed_kernel<<<quant_grid(tiles, 4), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   RTXB_CHECK_LAUNCH("quant_mxfp8_transposed_kernel");
   return RTXB_OK;
 }
@@ -392,7 +393,7 @@ int rtxb_nvfp4_tensor_scale(const void* src, int64_t rows, int64_t k, int64_t ld
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(amax_scratch, 0, 4, s);
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(amax)");
-  const int64_t work = rows * k / 8 / 256 + 1;
+  const int64_t work = rows * k / 8 / 256 / 4 + 1;
   const int grid = static_cast<int>(work < sm_count() * 8 ? work : sm_count() * 8);
   amax_bf16_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), rows, k, ld,
                                         static_cast<uint32_t*>(amax_scratch));
@@ -426,8 +427,8 @@ int rtxb_nvfp4_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, vo
   p.nb = p.kp / 16;
   p.sf_chunks = static_cast<int>(round_up((p.nb + 3) / 4, 4));
   p.layout = scale_layout;
-  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 511) / 512);
-  quant_nvfp4_rows_kernel<<<quant_grid(tiles), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 255) / 256);
+  quant_nvfp4_rows_kernel<<<quant_grid(tiles, 4), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   RTXB_CHECK_LAUNCH("quant_nvfp4_rows_kernel");
   return RTXB_OK;
 }

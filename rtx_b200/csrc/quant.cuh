@@ -20,8 +20,7 @@ constexpr int kQuantThreads = 256;
 
 // ---------------------------------------------------------------------------
 // MXFP8 rows: src bf16 [rows, k] (pitch ld elements) -> q e4m3 [rows, kp],
-// scales e8m0.  Tile = 128 rows x 256 columns; a warp owns rows w, w+8, ...,
-// a lane owns 8 consecutive columns, four lanes share one block of 32.
+// scales e8m0.
 // ---------------------------------------------------------------------------
 struct QuantMxParams {
   const __nv_bfloat16* src;
@@ -80,47 +79,76 @@ __device__ __forceinline__ void store_scale_tile(const uint8_t (*tile)[BLOCKS], 
   }
 }
 
-__global__ void __launch_bounds__(kQuantThreads) quant_mxfp8_rows_kernel(const QuantMxParams p) {
-  __shared__ __align__(16) uint8_t tile_scales[128][8];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col_tiles = (p.kp + 255) / 256;
+// raw 16-byte load of 8 BF16 values (zero beyond k); scalar path for ragged or unaligned rows
+__device__ __forceinline__ uint4 load8_raw(const __nv_bfloat16* row_ptr, int col, int k, bool vec_ok) {
+  if (vec_ok && col + 8 <= k) return __ldg(reinterpret_cast<const uint4*>(row_ptr + col));
+  const uint16_t* s = reinterpret_cast<const uint16_t*>(row_ptr);
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const uint32_t lo = (col + 2 * e < k) ? s[col + 2 * e] : 0u;
+    const uint32_t hi = (col + 2 * e + 1 < k) ? s[col + 2 * e + 1] : 0u;
+    w[e] = lo | (hi << 16);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ void unpack8(const uint4 raw, float (&v)[8]) {
+  v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
+  v[4] = bf16_lo(raw.z); v[5] = bf16_hi(raw.z); v[6] = bf16_lo(raw.w); v[7] = bf16_hi(raw.w);
+}
+
+// Tile = 128 rows x 128 columns (exactly one 512-byte scale tile).  Thread t owns 8 columns
+// (t & 15) of row (t >> 4) + 16 i; four neighbouring lanes share a block of 32.  Four row loads
+// are issued before any is consumed so that each thread keeps 64 bytes in flight.
+__global__ void __launch_bounds__(kQuantThreads, 6) quant_mxfp8_rows_kernel(const QuantMxParams p) {
+  __shared__ __align__(16) uint8_t tile_scales[128][4];
+  const int sub = threadIdx.x & 15, rsel = threadIdx.x >> 4;
+  const int col_tiles = (p.kp + 127) / 128;
   const int row_tiles = (p.rows + 127) / 128;
   const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
   const bool q_vec_ok = (reinterpret_cast<uintptr_t>(p.q) & 7) == 0;  // kp % 32 == 0 keeps rows 8-byte aligned
+  const bool rinf = p.round_to_infinity != 0;
   for (int tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
     const int row0 = (tile / col_tiles) * 128;
-    const int col0 = (tile % col_tiles) * 256;
-    const int col = col0 + lane * 8;
-#pragma unroll 4
-    for (int i = 0; i < 16; ++i) {
-      const int r = warp + 8 * i;
-      const int row = row0 + r;
-      float v[8];
-      if (row < p.rows && col < p.kp) {
-        load8_bf16(p.src + static_cast<int64_t>(row) * p.ld, col, p.k, vec_ok, v);
-      } else {
+    const int col = (tile % col_tiles) * 128 + sub * 8;
+    const bool col_ok = col < p.kp;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+    for (int half = 0; half < 2; ++half) {
+      uint4 raw[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = row0 + rsel + 16 * (half * 4 + j);
+        raw[j] = (row < p.rows && col_ok) ? load8_raw(p.src + static_cast<int64_t>(row) * p.ld, col, p.k, vec_ok)
+                                          : make_uint4(0, 0, 0, 0);
       }
-      float a = amax8(v);
-      a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 1));
-      a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 2));
-      const uint32_t code = e8m0_from_amax(a, p.round_to_infinity != 0);
-      const float recip = e8m0_reciprocal(code);
-      if ((lane & 3) == 0) tile_scales[r][lane >> 2] = (row < p.rows && col < p.kp) ? static_cast<uint8_t>(code) : 0;
-      if (row < p.rows && col < p.kp) {
-        const uint32_t lo = cvt_e4m3x2(v[0] * recip, v[1] * recip) | (cvt_e4m3x2(v[2] * recip, v[3] * recip) << 16);
-        const uint32_t hi = cvt_e4m3x2(v[4] * recip, v[5] * recip) | (cvt_e4m3x2(v[6] * recip, v[7] * recip) << 16);
-        uint8_t* dst = p.q + static_cast<int64_t>(row) * p.kp + col;
-        if (q_vec_ok) {
-          *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
-        } else {
-          for (int e = 0; e < 4; ++e) { dst[e] = lo >> (8 * e); dst[4 + e] = hi >> (8 * e); }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = rsel + 16 * (half * 4 + j);
+        const int row = row0 + r;
+        const bool live = row < p.rows && col_ok;
+        float v[8];
+        unpack8(raw[j], v);
+        float a = amax8(v);
+        a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 1));
+        a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 2));
+        const uint32_t code = e8m0_from_amax(a, rinf);
+        const float recip = e8m0_reciprocal(code);
+        if ((sub & 3) == 0) tile_scales[r][sub >> 2] = live ? static_cast<uint8_t>(code) : 0;
+        if (live) {
+          const uint32_t lo = cvt_e4m3x2(v[0] * recip, v[1] * recip) | (cvt_e4m3x2(v[2] * recip, v[3] * recip) << 16);
+          const uint32_t hi = cvt_e4m3x2(v[4] * recip, v[5] * recip) | (cvt_e4m3x2(v[6] * recip, v[7] * recip) << 16);
+          uint8_t* dst = p.q + static_cast<int64_t>(row) * p.kp + col;
+          if (q_vec_ok) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+          } else {
+            for (int e = 0; e < 4; ++e) { dst[e] = lo >> (8 * e); dst[4 + e] = hi >> (8 * e); }
+          }
         }
       }
     }
     __syncthreads();
-    store_scale_tile<8>(tile_scales, p.scales, p.layout, row0, col0 / 32, p.rows, p.nb, p.sf_chunks);
+    store_scale_tile<4>(tile_scales, p.scales, p.layout, row0, (tile % col_tiles) * 4, p.rows, p.nb, p.sf_chunks);
     __syncthreads();
   }
 }
@@ -149,21 +177,39 @@ __global__ void __launch_bounds__(kQuantThreads) quant_mxfp8_transposed_kernel(c
   const int row_tiles = (p.rows + 127) / 128;
   const int k_tiles = (p.kp + 127) / 128;
   const uint16_t* src = reinterpret_cast<const uint16_t*>(p.src);
+  const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
   for (int t = blockIdx.x; t < row_tiles * k_tiles; t += gridDim.x) {
     const int row0 = (t % row_tiles) * 128;  // output rows = source columns
     const int k0 = (t / row_tiles) * 128;
-    // load: 128 source rows (k) x 128 source columns; 2 values per thread per pass
-    for (int i = threadIdx.x; i < 128 * 64; i += kQuantThreads) {
-      const int kk = i >> 6, c2 = (i & 63) * 2;
-      const int gk = k0 + kk, gc = row0 + c2;
-      uint16_t a = 0, b = 0;
-      if (gk < p.k) {
-        const uint16_t* rp = src + static_cast<int64_t>(gk) * p.ld;
-        if (gc < p.rows) a = rp[gc];
-        if (gc + 1 < p.rows) b = rp[gc + 1];
+    // load: 128 source rows (k) x 128 source columns.  Aligned case: eight 16-byte loads per
+    // thread, all issued before the first shared-memory store.
+    if (vec_ok && row0 + 128 <= p.rows) {
+      uint4 raw[8];
+      const int c8 = (threadIdx.x & 15) * 8, kr = threadIdx.x >> 4;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int gk = k0 + kr + 16 * j;
+        raw[j] = gk < p.k ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<int64_t>(gk) * p.ld + row0 + c8))
+                          : make_uint4(0, 0, 0, 0);
       }
-      tile[kk][c2] = a;
-      tile[kk][c2 + 1] = b;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[kr + 16 * j][c8]);
+        dst[0] = raw[j].x; dst[1] = raw[j].y; dst[2] = raw[j].z; dst[3] = raw[j].w;
+      }
+    } else {
+      for (int i = threadIdx.x; i < 128 * 64; i += kQuantThreads) {
+        const int kk = i >> 6, c2 = (i & 63) * 2;
+        const int gk = k0 + kk, gc = row0 + c2;
+        uint16_t a = 0, b = 0;
+        if (gk < p.k) {
+          const uint16_t* rp = src + static_cast<int64_t>(gk) * p.ld;
+          if (gc < p.rows) a = rp[gc];
+          if (gc + 1 < p.rows) b = rp[gc + 1];
+        }
+        tile[kk][c2] = a;
+        tile[kk][c2 + 1] = b;
+      }
     }
     __syncthreads();
     // quantise: thread -> (output row r, block j of 32 along k); 128 rows x 4 blocks = 512 items
@@ -208,17 +254,26 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const __nv_bfloat16* src
   uint32_t m = 0;
   const bool vec_ok = (ld % 8 == 0) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
   if (vec_ok) {
+    // four 16-byte loads in flight per thread
     const int64_t vec_per_row = k / 8;
     const int64_t total = rows * vec_per_row;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-      const int64_t r = i / vec_per_row, c = (i % vec_per_row) * 8;
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + r * ld + c));
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < total; i0 += 4 * stride) {
+      uint4 raw[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
-        m = max(m, w[e] & 0x7FFF0000u);
+      for (int j = 0; j < 4; ++j) {
+        const int64_t i = i0 + j * stride;
+        raw[j] = i < total ? __ldg(reinterpret_cast<const uint4*>(src + (i / vec_per_row) * ld + (i % vec_per_row) * 8))
+                           : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+          m = max(m, w[e] & 0x7FFF0000u);
+        }
       }
     }
   } else {
@@ -255,8 +310,8 @@ __global__ void nvfp4_tensor_scale_kernel(const uint32_t* amax_bits, int mode, f
 
 // ---------------------------------------------------------------------------
 // NVFP4: src bf16 [rows, k] -> packed e2m1 [rows, kp/2] (kp = k rounded up to
-// 32), E4M3 block scale per 16 values.  Tile = 128 rows x 512 columns; a lane
-// owns one whole block of 16 values (two 16-byte loads, one 8-byte store).
+// 32), E4M3 block scale per 16 values; a thread owns one whole block of 16
+// values (two 16-byte loads, one 8-byte store).
 // ---------------------------------------------------------------------------
 struct QuantNvParams {
   const __nv_bfloat16* src;
@@ -270,10 +325,13 @@ struct QuantNvParams {
   int layout;
 };
 
-__global__ void __launch_bounds__(kQuantThreads) quant_nvfp4_rows_kernel(const QuantNvParams p) {
-  __shared__ __align__(16) uint8_t tile_scales[128][32];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col_tiles = (p.kp + 511) / 512;
+// Tile = 128 rows x 256 columns (16 blocks = four 512-byte scale tiles).  Thread t owns the
+// block (t & 15) of row (t >> 4) + 16 i; the loads of two rows (four 16-byte loads) are issued
+// before the first is consumed.
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_rows_kernel(const QuantNvParams p) {
+  __shared__ __align__(16) uint8_t tile_scales[128][16];
+  const int sub = threadIdx.x & 15, rsel = threadIdx.x >> 4;
+  const int col_tiles = (p.kp + 255) / 256;
   const int row_tiles = (p.rows + 127) / 128;
   const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
   const float st = p.tensor_scale ? __ldg(p.tensor_scale) : 1.0f;
@@ -282,42 +340,51 @@ __global__ void __launch_bounds__(kQuantThreads) quant_nvfp4_rows_kernel(const Q
   const int row_bytes = p.kp / 2;
   for (int tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
     const int row0 = (tile / col_tiles) * 128;
-    const int col0 = (tile % col_tiles) * 512;
-    const int col = col0 + lane * 16;
-#pragma unroll 2
-    for (int i = 0; i < 16; ++i) {
-      const int r = warp + 8 * i;
-      const int row = row0 + r;
-      const bool live = row < p.rows && col < p.kp;
-      float v[16];
-      if (live) {
-        const __nv_bfloat16* rp = p.src + static_cast<int64_t>(row) * p.ld;
-        load8_bf16(rp, col, p.k, vec_ok, *reinterpret_cast<float(*)[8]>(&v[0]));
-        load8_bf16(rp, col + 8, p.k, vec_ok, *reinterpret_cast<float(*)[8]>(&v[8]));
-      } else {
+    const int col = (tile % col_tiles) * 256 + sub * 16;
+    const bool col_ok = col < p.kp;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = 0.0f;
-      }
-      float a = fabsf(v[0]);
+    for (int pair = 0; pair < 4; ++pair) {
+      uint4 raw[2][2];
 #pragma unroll
-      for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
-      float raw = __fdiv_rn(a, six_st);
-      raw = fmin_nan(fmax_nan(raw, 0.015625f), 448.0f);
-      const uint32_t sb = cvt_e4m3x2(raw, raw) & 0xFF;
-      const float recip = __fdiv_rn(inv_st, e4m3_to_float(sb));
-      tile_scales[r][lane] = live ? static_cast<uint8_t>(sb) : 0;
-      if (live) {
-        uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          w0 |= cvt_e2m1x2(v[2 * e] * recip, v[2 * e + 1] * recip) << (8 * e);
-          w1 |= cvt_e2m1x2(v[8 + 2 * e] * recip, v[8 + 2 * e + 1] * recip) << (8 * e);
+      for (int j = 0; j < 2; ++j) {
+        const int row = row0 + rsel + 16 * (pair * 2 + j);
+        if (row < p.rows && col_ok) {
+          const __nv_bfloat16* rp = p.src + static_cast<int64_t>(row) * p.ld;
+          raw[j][0] = load8_raw(rp, col, p.k, vec_ok);
+          raw[j][1] = load8_raw(rp, col + 8, p.k, vec_ok);
+        } else {
+          raw[j][0] = raw[j][1] = make_uint4(0, 0, 0, 0);
         }
-        *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(row) * row_bytes + col / 2) = make_uint2(w0, w1);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int r = rsel + 16 * (pair * 2 + j);
+        const int row = row0 + r;
+        const bool live = row < p.rows && col_ok;
+        float v[16];
+        unpack8(raw[j][0], *reinterpret_cast<float(*)[8]>(&v[0]));
+        unpack8(raw[j][1], *reinterpret_cast<float(*)[8]>(&v[8]));
+        float a = fabsf(v[0]);
+#pragma unroll
+        for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
+        float rawscale = __fdiv_rn(a, six_st);
+        rawscale = fmin_nan(fmax_nan(rawscale, 0.015625f), 448.0f);
+        const uint32_t sb = cvt_e4m3x2(rawscale, rawscale) & 0xFF;
+        const float recip = __fdiv_rn(inv_st, e4m3_to_float(sb));
+        tile_scales[r][sub] = live ? static_cast<uint8_t>(sb) : 0;
+        if (live) {
+          uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            w0 |= cvt_e2m1x2(v[2 * e] * recip, v[2 * e + 1] * recip) << (8 * e);
+            w1 |= cvt_e2m1x2(v[8 + 2 * e] * recip, v[8 + 2 * e + 1] * recip) << (8 * e);
+          }
+          *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(row) * row_bytes + col / 2) = make_uint2(w0, w1);
+        }
       }
     }
     __syncthreads();
-    store_scale_tile<32>(tile_scales, p.scales, p.layout, row0, col0 / 16, p.rows, p.nb, p.sf_chunks);
+    store_scale_tile<16>(tile_scales, p.scales, p.layout, row0, (tile % col_tiles) * 16, p.rows, p.nb, p.sf_chunks);
     __syncthreads();
   }
 }
