@@ -4,6 +4,7 @@
 #include "../../include/rtxb.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -72,6 +73,25 @@ int make_payload_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
   return RTXB_OK;
 }
 
+// scale tiles as a matrix of 512-byte rows (128 x uint32), boxes of `box_rows` consecutive tiles
+int make_scale_map(CUtensorMap* map, const void* base, int64_t total_tiles, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[2] = {128u, static_cast<cuuint64_t>(total_tiles)};
+  cuuint64_t gstride[1] = {512u};
+  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(scales) failed with CUresult %d",
+             static_cast<int>(r));
+    return RTXB_E_DRIVER;
+  }
+  return RTXB_OK;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -82,6 +102,16 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+// RTXB_GEMM_PAIR=1 selects the CTA-pair (cta_group::2) GEMM, 0 the single-CTA one
+bool use_pair_kernel() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* v = getenv("RTXB_GEMM_PAIR");
+    cached = (v && v[0] == '1') ? 1 : 0;
+  }
+  return cached == 1;
 }
 
 template <int KIND, int EPI>
@@ -110,6 +140,27 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.out_vec_ok = (aligned(out, 16) && (ldo * (EPI == kEpiF32 ? 4 : 2)) % 16 == 0) ? 1 : 0;
   p.out_scale = out_scale;
   p.status = status;
+  {
+    const char* dbg = getenv("RTXB_GEMM_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
+  }
+  if (use_pair_kernel()) {
+    using P = PairTraits<KIND>;
+    CUtensorMap map_sfa, map_sfb;
+    rc = make_scale_map(&map_sfa, sa, static_cast<int64_t>(p.m_tiles) * sf_k_chunks, P::kSfChunks);
+    if (rc) return rc;
+    rc = make_scale_map(&map_sfb, sb, (n_rows_b + 127) / 128 * sf_k_chunks, P::kSfChunks);
+    if (rc) return rc;
+    auto pk = gemm_blockscaled_pair_kernel<KIND, EPI>;
+    cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmemBytes);
+    if (pe != cudaSuccess) return fail_cuda(pe, "cudaFuncSetAttribute(pair gemm)");
+    const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles;
+    const int max_pairs = sm_count() / 2;
+    const int pairs = static_cast<int>(pair_tiles < max_pairs ? pair_tiles : max_pairs);
+    pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, p);
+    RTXB_CHECK_LAUNCH("gemm_blockscaled_pair_kernel");
+    return RTXB_OK;
+  }
   auto kernel = gemm_blockscaled_kernel<KIND, EPI>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
   if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(gemm)");

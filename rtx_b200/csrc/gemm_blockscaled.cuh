@@ -6,18 +6,23 @@
 // mma.sync kernels MXFP8GemmKernel (rtx/kernels/mxfp8_gemm.py:45-2033) and
 // NVFP4GemmKernel (rtx/kernels/nvfp4_gemm.py:22-64).
 //
-// One persistent CTA per SM, 192 threads:
+// Two kernels share the roles, the TMEM plan and the epilogue:
+//   gemm_blockscaled_kernel       one CTA per 128 x 256 tile (tcgen05 cta_group::1)
+//   gemm_blockscaled_pair_kernel  a cluster of two CTAs per 256 x 256 tile (cta_group::2)
+// Persistent CTAs, 192 threads:
 //   warp 0      TMA producer: payload tiles (128-byte swizzled boxes) and
-//               scale-factor tiles (1-D bulk copies) into a 4-stage ring
+//               scale-factor tiles into a multi-stage ring
 //   warp 1      owns TMEM; one lane copies scale factors shared->TMEM
 //               (tcgen05.cp) and issues tcgen05.mma ... block_scale
 //   warps 2..5  epilogue: tcgen05.ld the FP32 accumulators, apply the output
 //               scale / SwiGLU, round once to BF16 (or keep FP32), store
-// The 128x256 FP32 accumulator lives in TMEM.  Two accumulator windows
-// [0,256) and [192,448) overlap by 64 columns; the epilogue drains the shared
-// 64 columns of a tile first and then lets the next tile's MMAs start, so the
-// rest of the drain overlaps the next main loop.  Scale factors use columns
-// [448,512).
+//
+// TMEM plan (512 columns): scale factors sit at the top in two sets that
+// alternate per K step (so the copy for step i+1 never overwrites what the MMAs
+// of step i read); the 128 x 256 FP32 accumulator uses one of two windows,
+// [0,256) and [W1, W1+256), that alternate per tile and overlap by 256-W1
+// columns.  The epilogue drains the shared columns of a tile first and then lets
+// the next tile's MMAs start, so the rest of the drain overlaps the next main loop.
 #pragma once
 
 #include "common.cuh"
@@ -37,21 +42,27 @@ constexpr int kBlockKBytes = 128;  // one swizzle row: 128 E4M3 values or 256 E2
 constexpr int kStages = 4;
 constexpr int kGemmThreads = 192;
 constexpr int kAccCols = 256;
-constexpr int kAccWindow1 = 192;   // second accumulator window starts here
-constexpr int kOverlapCols = 64;   // columns shared by both windows: [192,256)
-constexpr int kSfColBase = 448;
 constexpr int kTmemCols = 512;
 
 template <int KIND>
-struct GemmTraits {
-  // bytes of scale factors per 128 rows per K tile: MXFP8 4 blocks of 32,
-  // NVFP4 16 blocks of 16 -> 1 or 4 tiles of 512 bytes
+struct TmemPlan {
+  // 512-byte scale tiles per 128 rows per K step: MXFP8 4 blocks of 32 -> 1, NVFP4 16 blocks of 16 -> 4
   static constexpr int kSfChunks = KIND == kKindMxfp8 ? 1 : 4;
+  static constexpr int kSfSetCols = KIND == kKindMxfp8 ? 16 : 48;  // SFA 4c + SFB 8c columns (c = chunks), padded
+  static constexpr int kSfBase = kTmemCols - 2 * kSfSetCols;       // 480 / 416
+  static constexpr int kAccWindow1 = kSfBase - kAccCols;           // 224 / 160
+  static constexpr int kOverlapChunks = (kAccCols - kAccWindow1) / 32;  // 1 / 3 groups of 32 shared columns
+  __device__ static constexpr int sfa_col(int set) { return kSfBase + set * kSfSetCols; }
+  __device__ static constexpr int sfb_col(int set) { return kSfBase + set * kSfSetCols + 4 * kSfChunks; }
+};
+
+template <int KIND>
+struct GemmTraits {
+  static constexpr int kSfChunks = TmemPlan<KIND>::kSfChunks;
   static constexpr int kSfaBytes = 512 * kSfChunks;
   static constexpr int kSfbBytes = 2 * kSfaBytes;
   static constexpr int kABytes = kBlockM * kBlockKBytes;
   static constexpr int kBBytes = kBlockN * kBlockKBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   // ring layout: [A x stages][B x stages][SFA x stages][SFB x stages][barriers];
   // payload tiles stay 1024-byte aligned (swizzle atoms), scale tiles 16-byte aligned
   static constexpr int kOffB = kStages * kABytes;
@@ -59,15 +70,13 @@ struct GemmTraits {
   static constexpr int kOffSfb = kOffSfa + kStages * kSfaBytes;
   static constexpr int kOffBars = kOffSfb + kStages * kSfbBytes;
   static constexpr int kSmemBytes = kOffBars + 1024 /*align slack*/ + 256 /*barriers*/;
-  static constexpr int kSfaCol = kSfColBase;                 // 4 (MX) or 16 (NV) columns
-  static constexpr int kSfbCol = kSfColBase + 4 * kSfChunks; // 8 (MX) or 32 (NV) columns
   static constexpr uint32_t kIdesc =
       idesc_block_scaled(kBlockM, kBlockN, KIND == kKindMxfp8 ? 0u : 1u, KIND == kKindMxfp8 ? 1u : 0u);
 };
 
 struct GemmParams {
   int m, n, k_tiles;      // n = rows of B (for GLU: 2 * inter); k_tiles = ceil(Kbytes / 128)
-  int m_tiles, n_tiles;   // n_tiles counts 256-wide accumulator tiles
+  int m_tiles, n_tiles;   // 128-row blocks of A; 256-wide accumulator tiles
   int glu_inter;          // GLU: rows of the gate half of B (= output columns); else 0
   const uint8_t* sfa;     // [ceil(M/128)][sf_k_chunks][512]
   const uint8_t* sfb;     // [ceil(N/128)][sf_k_chunks][512]
@@ -78,15 +87,241 @@ struct GemmParams {
   int out_vec_ok;         // 1 when out and its row pitch are 16-byte aligned (vector stores allowed)
   const float* out_scale; // device scalar or nullptr (= 1)
   int* status;            // device status word or nullptr
+  int debug;              // experiments only (results invalid when set): bit0 = copy scale factors on the
+                          // first K step only, bit1 = stop loading once the ring is filled,
+                          // bit2 = issue the scale copy of step i+1 before the MMAs of step i
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+__device__ __forceinline__ void store_bf16x8(__nv_bfloat16* out, int col, int out_cols, bool vec_ok,
+                                             const uint32_t (&w)[4]) {
+  if (vec_ok && col + 8 <= out_cols) {
+    *reinterpret_cast<uint4*>(out + col) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    for (int e = 0; e < 8; ++e)
+      if (col + e < out_cols) out[col + e] = reinterpret_cast<const __nv_bfloat16*>(w)[e];
+  }
+}
+
+// Drains one 128 x 256 accumulator window of this warp's 32 TMEM lanes.  `tacc` already holds the
+// lane quadrant and the window's first column.  The columns the two windows share are at the top of
+// the even window and at the bottom of the odd one; they are read first and `overlap_bar_addr` is
+// signalled as soon as they are in registers.
+template <int KIND, int EPI>
+__device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tacc, int row, bool row_ok, int n_idx,
+                                               bool odd, uint32_t overlap_bar_addr, float out_scale, int lane) {
+  using TP = TmemPlan<KIND>;
+  if (EPI == kEpiGluBf16) {
+    // accumulator columns [0,128) = gate, [128,256) = up of the same 128 output columns; pairs of
+    // 32-column groups (gate c, up 128+c).  Shared columns: up group 96 (even window) or gate
+    // group 0 (odd window) -- the first pair visited holds them.
+    static_assert(EPI != kEpiGluBf16 || TP::kOverlapChunks == 1, "GLU epilogue assumes a 32-column overlap");
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+    const int col0 = n_idx * 128;
+    const int c_first = odd ? 0 : 96;
+#pragma unroll 1
+    for (int i = 0; i < 4; ++i) {
+      const int c = (c_first + 32 * i) & 127;
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(tacc + c, g);
+      tmem_ld_32x32(tacc + 128 + c, u);
+      tmem_ld_wait();
+      if (i == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(overlap_bar_addr);
+      }
+      if (!row_ok) continue;
+#pragma unroll
+      for (int v = 0; v < 32; v += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(
+              silu_mul(__uint_as_float(g[v + 2 * e]), __uint_as_float(u[v + 2 * e])),
+              silu_mul(__uint_as_float(g[v + 2 * e + 1]), __uint_as_float(u[v + 2 * e + 1])));
+          w[e] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        store_bf16x8(out, col0 + c + v, p.out_cols, p.out_vec_ok != 0, w);
+      }
+    }
+  } else {
+    const int shared0 = odd ? 0 : TP::kAccWindow1;  // local column where the shared columns start
+    const int col_base = n_idx * kBlockN;
+#pragma unroll 1
+    for (int i = 0; i < kAccCols / 32; ++i) {
+      // visit the shared 32-column groups first, then the rest in order
+      const int c = (shared0 + 32 * i) % kAccCols;
+      uint32_t r[32];
+      tmem_ld_32x32(tacc + c, r);
+      tmem_ld_wait();
+      if (i == TP::kOverlapChunks - 1) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(overlap_bar_addr);
+      }
+      if (!row_ok) continue;
+      const int col = col_base + c;
+      if (EPI == kEpiBf16) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+#pragma unroll
+        for (int v = 0; v < 32; v += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[v + 2 * e]) * out_scale,
+                                                     __uint_as_float(r[v + 2 * e + 1]) * out_scale);
+            w[e] = *reinterpret_cast<uint32_t*>(&b);
+          }
+          store_bf16x8(out, col + v, p.out_cols, p.out_vec_ok != 0, w);
+        }
+      } else {
+        float* out = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+#pragma unroll
+        for (int v = 0; v < 32; v += 4) {
+          if (p.out_vec_ok && col + v + 4 <= p.out_cols) {
+            *reinterpret_cast<float4*>(out + col + v) =
+                make_float4(__uint_as_float(r[v]) * out_scale, __uint_as_float(r[v + 1]) * out_scale,
+                            __uint_as_float(r[v + 2]) * out_scale, __uint_as_float(r[v + 3]) * out_scale);
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (col + v + e < p.out_cols) out[col + v + e] = __uint_as_float(r[v + e]) * out_scale;
+          }
+        }
+      }
+    }
+  }
+}
+
+// shared -> TMEM copy of one K step's scale factors into scale set `set`.
+// SFA tile c -> columns sfa + 4c; SFB (row block nb, tile c) -> sfb + 8c + 4nb.
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void issue_scale_copy(uint32_t tmem_base, uint32_t ssfa, uint32_t ssfb, int set) {
+  using TP = TmemPlan<KIND>;
+  constexpr int kSfaBytes = 512 * TP::kSfChunks;
+  const uint32_t ta = tmem_base + TP::sfa_col(set), tb = tmem_base + TP::sfb_col(set);
+#pragma unroll
+  for (int c = 0; c < TP::kSfChunks; ++c) {
+    if (PAIR) {
+      tc_cp_32x128b_warpx4_pair(ta + 4 * c, umma_desc_sf(ssfa + 512 * c));
+      tc_cp_32x128b_warpx4_pair(tb + 8 * c, umma_desc_sf(ssfb + 512 * c));
+      tc_cp_32x128b_warpx4_pair(tb + 8 * c + 4, umma_desc_sf(ssfb + kSfaBytes + 512 * c));
+    } else {
+      tc_cp_32x128b_warpx4(ta + 4 * c, umma_desc_sf(ssfa + 512 * c));
+      tc_cp_32x128b_warpx4(tb + 8 * c, umma_desc_sf(ssfb + 512 * c));
+      tc_cp_32x128b_warpx4(tb + 8 * c + 4, umma_desc_sf(ssfb + kSfaBytes + 512 * c));
+    }
+  }
+}
+
+// the four MMAs (32 bytes of K each) of one K step
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void issue_k_step(uint32_t tmem_base, uint32_t acc_col, uint32_t sa, uint32_t sb, int set,
+                                             uint32_t idesc, bool first_step) {
+  using TP = TmemPlan<KIND>;
+  const uint64_t da = umma_desc_sw128(sa);
+  const uint64_t db = umma_desc_sw128(sb);
+  const uint32_t ta = tmem_base + TP::sfa_col(set), tb = tmem_base + TP::sfb_col(set);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t acc = (!first_step || j > 0) ? 1u : 0u;
+    if (KIND == kKindMxfp8) {
+      // one scale byte per row per MMA: byte j of the 32-bit column
+      if (PAIR)
+        tc_mma_mxf8f6f4_pair(tmem_base + acc_col, da + 2 * j, db + 2 * j, idesc_with_sf_ids(idesc, j, j), ta, tb, acc);
+      else
+        tc_mma_mxf8f6f4(tmem_base + acc_col, da + 2 * j, db + 2 * j, idesc_with_sf_ids(idesc, j, j), ta, tb, acc);
+    } else {
+      // four scale bytes per row per MMA: a whole column group per MMA
+      if (PAIR)
+        tc_mma_mxf4nvf4_pair(tmem_base + acc_col, da + 2 * j, db + 2 * j, idesc, ta + 4 * j, tb + 8 * j, acc);
+      else
+        tc_mma_mxf4nvf4(tmem_base + acc_col, da + 2 * j, db + 2 * j, idesc, ta + 4 * j, tb + 8 * j, acc);
+    }
+  }
+}
+
+// The MMA issuer's loop over this CTA's (or pair's) tiles; the integer parameters describe the ring.
+// All 32 lanes of the warp run it with identical control flow -- addresses, descriptors and loop
+// state then stay in uniform registers, which is what keeps the issue cost of a tcgen05
+// instruction low -- and one elected lane (always the same one) issues the tcgen05 instructions.
+template <int KIND, bool PAIR, int STAGES, int A_BYTES, int B_BYTES, int OFF_B, int OFF_SFA, int OFF_SFB, int SFA_BYTES,
+          int SFB_BYTES>
+__device__ __forceinline__ void mma_issuer_loop(const GemmParams& p, uint8_t* smem, uint64_t* full_bar,
+                                                uint64_t* empty_bar, uint64_t* acc_full_bar, uint64_t* acc_overlap_bar,
+                                                volatile int* abort_flag, uint32_t tmem_base, uint32_t idesc,
+                                                int first_tile, int tile_stride, int total_tiles) {
+  using TP = TmemPlan<KIND>;
+  int stage = 0;
+  uint32_t phase = 0;
+  uint32_t local_tile = 0;
+  uint32_t step = 0;  // global K-step counter: picks the scale set
+  const bool prefetch_sf = (p.debug & 4) != 0;
+  const bool leader = elect_one_sync();
+  for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local_tile) {
+    const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;
+    if (local_tile > 0) {
+      // previous tile's epilogue has drained the columns both windows share
+      if (!mbar_wait(acc_overlap_bar, (local_tile - 1) & 1, abort_flag)) {
+        if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
+        *abort_flag = 1;
+        return;
+      }
+      tc_fence_after_sync();
+    }
+    for (int kt = 0; kt < p.k_tiles; ++kt, ++step) {
+      const int set = step & 1;
+      const bool have_sf = prefetch_sf && kt > 0;  // copied while issuing the previous step
+      if (!have_sf) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
+          *abort_flag = 1;
+          return;
+        }
+        tc_fence_after_sync();
+        if (leader && (!(p.debug & 1) || kt == 0))
+          issue_scale_copy<KIND, PAIR>(tmem_base, smem_u32(smem + OFF_SFA + stage * SFA_BYTES),
+                                       smem_u32(smem + OFF_SFB + stage * SFB_BYTES), set);
+      }
+      if (prefetch_sf && kt + 1 < p.k_tiles) {
+        int nstage = stage + 1;
+        uint32_t nphase = phase;
+        if (nstage == STAGES) { nstage = 0; nphase ^= 1; }
+        if (!mbar_wait(&full_bar[nstage], nphase, abort_flag)) {
+          if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
+          *abort_flag = 1;
+          return;
+        }
+        tc_fence_after_sync();
+        if (leader)
+          issue_scale_copy<KIND, PAIR>(tmem_base, smem_u32(smem + OFF_SFA + nstage * SFA_BYTES),
+                                       smem_u32(smem + OFF_SFB + nstage * SFB_BYTES), set ^ 1);
+      }
+      if (leader) {
+        issue_k_step<KIND, PAIR>(tmem_base, acc_col, smem_u32(smem + stage * A_BYTES),
+                                 smem_u32(smem + OFF_B + stage * B_BYTES), set, idesc, kt == 0);
+        // stage reusable once these MMAs (and the copies before them) have read it
+        if (PAIR) tc_commit_pair(&empty_bar[stage], 3);
+        else tc_commit(&empty_bar[stage]);
+      }
+      __syncwarp();
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+    }
+    if (leader) {
+      if (PAIR) tc_commit_pair(acc_full_bar, 3);
+      else tc_commit(acc_full_bar);
+    }
+    __syncwarp();
+  }
+}
 
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const GemmParams p) {
   using T = GemmTraits<KIND>;
+  using TP = TmemPlan<KIND>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::kOffBars);
@@ -122,9 +357,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      prefetch_tensormap(&map_a);
-      prefetch_tensormap(&map_b);
+    // all lanes run the loop (uniform control flow); one elected lane issues the copies
+    {
+      const bool leader = elect_one_sync();
+      if (leader) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+      }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -146,24 +385,31 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const bool b1_valid = b_row1 < p.n;  // second half may lie past the last row of B
         for (int kt = 0; kt < p.k_tiles; ++kt) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
-            if (p.status) atomicCAS(p.status, 0, kStatusWaitProducer);
+            if (p.status && leader) atomicCAS(p.status, 0, kStatusWaitProducer);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          uint8_t* sa = smem + stage * T::kABytes;
-          uint8_t* sb = smem + T::kOffB + stage * T::kBBytes;
-          uint8_t* ssfa = smem + T::kOffSfa + stage * T::kSfaBytes;
-          uint8_t* ssfb = smem + T::kOffSfb + stage * T::kSfbBytes;
-          mbar_expect_tx(&full_bar[stage], T::kABytes + T::kBBytes + T::kSfaBytes +
-                                               (b1_valid ? T::kSfbBytes : T::kSfaBytes));
-          tma_load_2d(sa, &map_a, &full_bar[stage], kt * kBlockKBytes, m0);
-          tma_load_2d(sb, &map_b, &full_bar[stage], kt * kBlockKBytes, b_row0);
-          tma_load_2d(sb + 128 * kBlockKBytes, &map_b, &full_bar[stage], kt * kBlockKBytes, b_row1);
-          const size_t sf_off = static_cast<size_t>(kt) * T::kSfaBytes;
-          bulk_load_1d(ssfa, sfa_src + sf_off, T::kSfaBytes, &full_bar[stage]);
-          bulk_load_1d(ssfb, sfb_src0 + sf_off, T::kSfaBytes, &full_bar[stage]);
-          if (b1_valid) bulk_load_1d(ssfb + T::kSfaBytes, sfb_src1 + sf_off, T::kSfaBytes, &full_bar[stage]);
+          if (leader) {
+            uint8_t* sa = smem + stage * T::kABytes;
+            uint8_t* sb = smem + T::kOffB + stage * T::kBBytes;
+            uint8_t* ssfa = smem + T::kOffSfa + stage * T::kSfaBytes;
+            uint8_t* ssfb = smem + T::kOffSfb + stage * T::kSfbBytes;
+            if ((p.debug & 2) && (kt >= kStages || tile != static_cast<int>(blockIdx.x))) {
+              mbar_arrive(&full_bar[stage]);  // experiment: reuse whatever the stage holds, no loads
+            } else {
+              mbar_expect_tx(&full_bar[stage], T::kABytes + T::kBBytes + T::kSfaBytes +
+                                                   (b1_valid ? T::kSfbBytes : T::kSfaBytes));
+              tma_load_2d(sa, &map_a, &full_bar[stage], kt * kBlockKBytes, m0);
+              tma_load_2d(sb, &map_b, &full_bar[stage], kt * kBlockKBytes, b_row0);
+              tma_load_2d(sb + 128 * kBlockKBytes, &map_b, &full_bar[stage], kt * kBlockKBytes, b_row1);
+              const size_t sf_off = static_cast<size_t>(kt) * T::kSfaBytes;
+              bulk_load_1d(ssfa, sfa_src + sf_off, T::kSfaBytes, &full_bar[stage]);
+              bulk_load_1d(ssfb, sfb_src0 + sf_off, T::kSfaBytes, &full_bar[stage]);
+              if (b1_valid) bulk_load_1d(ssfb + T::kSfaBytes, sfb_src1 + sf_off, T::kSfaBytes, &full_bar[stage]);
+            }
+          }
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -171,62 +417,10 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t local_tile = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
-        const uint32_t acc_col = (local_tile & 1) ? kAccWindow1 : 0;
-        if (local_tile > 0) {
-          // previous tile's epilogue has drained the columns both windows share
-          if (!mbar_wait(acc_overlap_bar, (local_tile - 1) & 1, abort_flag)) {
-            if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
-            *abort_flag = 1;
-            break;
-          }
-          tc_fence_after_sync();
-        }
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
-            if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * T::kABytes);
-          const uint32_t sb = smem_u32(smem + T::kOffB + stage * T::kBBytes);
-          const uint32_t ssfa = smem_u32(smem + T::kOffSfa + stage * T::kSfaBytes);
-          const uint32_t ssfb = smem_u32(smem + T::kOffSfb + stage * T::kSfbBytes);
-          // scale factors: each 512-byte tile -> 4 TMEM columns.
-          // SFA tile c -> columns kSfaCol + 4c; SFB (row block nb, tile c) -> kSfbCol + 8c + 4nb.
-#pragma unroll
-          for (int c = 0; c < T::kSfChunks; ++c) {
-            tc_cp_32x128b_warpx4(tmem_base + T::kSfaCol + 4 * c, umma_desc_sf(ssfa + 512 * c));
-            tc_cp_32x128b_warpx4(tmem_base + T::kSfbCol + 8 * c, umma_desc_sf(ssfb + 512 * c));
-            tc_cp_32x128b_warpx4(tmem_base + T::kSfbCol + 8 * c + 4, umma_desc_sf(ssfb + T::kSfaBytes + 512 * c));
-          }
-          const uint64_t da = umma_desc_sw128(sa);
-          const uint64_t db = umma_desc_sw128(sb);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {  // four MMAs of 32 bytes of K each
-            const uint32_t acc = (kt > 0 || j > 0) ? 1u : 0u;
-            if (KIND == kKindMxfp8) {
-              // one scale byte per row per MMA: byte j of the 32-bit column
-              tc_mma_mxf8f6f4(tmem_base + acc_col, da + 2 * j, db + 2 * j, idesc_with_sf_ids(T::kIdesc, j, j),
-                              tmem_base + T::kSfaCol, tmem_base + T::kSfbCol, acc);
-            } else {
-              // four scale bytes per row per MMA: a whole column group per MMA
-              tc_mma_mxf4nvf4(tmem_base + acc_col, da + 2 * j, db + 2 * j, T::kIdesc,
-                              tmem_base + T::kSfaCol + 4 * j, tmem_base + T::kSfbCol + 8 * j, acc);
-            }
-          }
-          tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
-        if (ok) tc_commit(acc_full_bar);
-      }
+    {
+      mma_issuer_loop<KIND, false, kStages, T::kABytes, T::kBBytes, T::kOffB, T::kOffSfa, T::kOffSfb, T::kSfaBytes,
+                      T::kSfbBytes>(p, smem, full_bar, empty_bar, acc_full_bar, acc_overlap_bar, abort_flag, tmem_base,
+                                    T::kIdesc, blockIdx.x, gridDim.x, total_tiles);
     }
     __syncwarp();
   } else {
@@ -239,143 +433,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const int m_idx = tile % p.m_tiles, n_idx = tile / p.m_tiles;
       const int row = m_idx * kBlockM + quad * 32 + lane;
       const bool row_ok = row < p.m;
-      const uint32_t acc_col = (local_tile & 1) ? kAccWindow1 : 0;
-      // local column where the shared 64 columns start for this window
-      const int shared0 = (local_tile & 1) ? 0 : kAccWindow1;
+      const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;
       if (!mbar_wait(acc_full_bar, local_tile & 1, abort_flag)) {
         if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusWaitEpilogue);
         *abort_flag = 1;
         break;
       }
       tc_fence_after_sync();
-      const uint32_t tacc = tmem_base + lane_base + acc_col;
-
-      if (EPI == kEpiGluBf16) {
-        // accumulator columns [0,128) = gate, [128,256) = up, same output columns
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
-        const int col0 = n_idx * 128;
-        uint32_t held[2][32];
-        // 1) read the shared columns first and release them
-        //    window 0: up columns 64..127 (local 192..255); window 1: gate columns 0..63
-        tmem_ld_32x32(tacc + shared0, held[0]);
-        tmem_ld_32x32(tacc + shared0 + 32, held[1]);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_overlap_bar);
-        const int c_first = (local_tile & 1) ? 0 : 64;  // gate/up column pair index of the held data
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t other[32];
-          const int c = c_first + 32 * h;
-          tmem_ld_32x32(tacc + ((local_tile & 1) ? 128 + c : c), other);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 32; v += 8) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float g0 = __uint_as_float((local_tile & 1) ? held[h][v + 2 * e] : other[v + 2 * e]);
-                float u0 = __uint_as_float((local_tile & 1) ? other[v + 2 * e] : held[h][v + 2 * e]);
-                float g1 = __uint_as_float((local_tile & 1) ? held[h][v + 2 * e + 1] : other[v + 2 * e + 1]);
-                float u1 = __uint_as_float((local_tile & 1) ? other[v + 2 * e + 1] : held[h][v + 2 * e + 1]);
-                __nv_bfloat162 b = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
-                w[e] = *reinterpret_cast<uint32_t*>(&b);
-              }
-              const int col = col0 + c + v;
-              if (p.out_vec_ok && col + 8 <= p.out_cols) {
-                *reinterpret_cast<uint4*>(out + col) = make_uint4(w[0], w[1], w[2], w[3]);
-              } else {
-                for (int e = 0; e < 8; ++e)
-                  if (col + e < p.out_cols)
-                    out[col + e] = reinterpret_cast<__nv_bfloat16*>(w)[e];
-              }
-            }
-          }
-        }
-        // 2) the remaining 64 column pairs
-        const int c_rest = (local_tile & 1) ? 64 : 0;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t g[32], u[32];
-          const int c = c_rest + 32 * h;
-          tmem_ld_32x32(tacc + c, g);
-          tmem_ld_32x32(tacc + 128 + c, u);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 32; v += 8) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 b = __floats2bfloat162_rn(
-                    silu_mul(__uint_as_float(g[v + 2 * e]), __uint_as_float(u[v + 2 * e])),
-                    silu_mul(__uint_as_float(g[v + 2 * e + 1]), __uint_as_float(u[v + 2 * e + 1])));
-                w[e] = *reinterpret_cast<uint32_t*>(&b);
-              }
-              const int col = col0 + c + v;
-              if (p.out_vec_ok && col + 8 <= p.out_cols) {
-                *reinterpret_cast<uint4*>(out + col) = make_uint4(w[0], w[1], w[2], w[3]);
-              } else {
-                for (int e = 0; e < 8; ++e)
-                  if (col + e < p.out_cols)
-                    out[col + e] = reinterpret_cast<__nv_bfloat16*>(w)[e];
-              }
-            }
-          }
-        }
-      } else {
-        const int col_base = n_idx * kBlockN;
-#pragma unroll 1
-        for (int i = 0; i < kAccCols / 32; ++i) {
-          // visit the two shared 32-column groups first, then the rest in order
-          const int c = (shared0 + 32 * i) % kAccCols;
-          uint32_t r[32];
-          tmem_ld_32x32(tacc + c, r);
-          tmem_ld_wait();
-          if (i == 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_overlap_bar);
-          }
-          if (!row_ok) continue;
-          const int col = col_base + c;
-          if (EPI == kEpiBf16) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
-#pragma unroll
-            for (int v = 0; v < 32; v += 8) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[v + 2 * e]) * out_scale,
-                                                         __uint_as_float(r[v + 2 * e + 1]) * out_scale);
-                w[e] = *reinterpret_cast<uint32_t*>(&b);
-              }
-              if (p.out_vec_ok && col + v + 8 <= p.out_cols) {
-                *reinterpret_cast<uint4*>(out + col + v) = make_uint4(w[0], w[1], w[2], w[3]);
-              } else {
-                for (int e = 0; e < 8; ++e)
-                  if (col + v + e < p.out_cols)
-                    out[col + v + e] = reinterpret_cast<__nv_bfloat16*>(w)[e];
-              }
-            }
-          } else {
-            float* out = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo;
-#pragma unroll
-            for (int v = 0; v < 32; v += 4) {
-              if (p.out_vec_ok && col + v + 4 <= p.out_cols) {
-                *reinterpret_cast<float4*>(out + col + v) =
-                    make_float4(__uint_as_float(r[v]) * out_scale, __uint_as_float(r[v + 1]) * out_scale,
-                                __uint_as_float(r[v + 2]) * out_scale, __uint_as_float(r[v + 3]) * out_scale);
-              } else {
-                for (int e = 0; e < 4; ++e)
-                  if (col + v + e < p.out_cols) out[col + v + e] = __uint_as_float(r[v + e]) * out_scale;
-              }
-            }
-          }
-        }
-      }
+      epilogue_drain<KIND, EPI>(p, tmem_base + lane_base + acc_col, row, row_ok, n_idx, (local_tile & 1) != 0,
+                                smem_u32(acc_overlap_bar), out_scale, lane);
     }
   }
 
@@ -385,6 +451,174 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ===========================================================================
+// CTA-pair variant (cluster of two CTAs, tcgen05 cta_group::2): pair tile 256 x 256.
+//
+// Each CTA of the pair owns 128 rows of A and 128 of the 256 rows of B (for the GLU epilogue:
+// rank 0 the gate rows, rank 1 the up rows) and fetches only those, so an SM pulls 32 KB per
+// 128-byte K step from L2 instead of 48 KB; the MMA issued by the rank-0 CTA reads A and B from
+// both CTAs' shared memory and writes a 128 x 256 accumulator into each CTA's TMEM.  No TMA
+// multicast is used.  Scale factors: each CTA loads its own SFA tile and the SFB tiles of all 256
+// B rows.  All TMA loads of both CTAs signal the rank-0 CTA's `full` barrier; the MMA's commits
+// arrive on the `empty` / `acc_full` barriers of both CTAs.  Epilogue as in the single-CTA kernel.
+// ===========================================================================
+template <int KIND>
+struct PairTraits {
+  static constexpr int kStagesP = KIND == kKindMxfp8 ? 6 : 5;
+  static constexpr int kSfChunks = TmemPlan<KIND>::kSfChunks;
+  static constexpr int kSfaBytes = 512 * kSfChunks;
+  static constexpr int kSfbBytes = 2 * kSfaBytes;
+  static constexpr int kABytes = 128 * kBlockKBytes;
+  static constexpr int kBBytes = 128 * kBlockKBytes;   // this CTA's half of the 256 B rows
+  static constexpr int kOffB = kStagesP * kABytes;
+  static constexpr int kOffSfa = kOffB + kStagesP * kBBytes;
+  static constexpr int kOffSfb = kOffSfa + kStagesP * kSfaBytes;
+  static constexpr int kOffBars = kOffSfb + kStagesP * kSfbBytes;
+  static constexpr int kSmemBytes = kOffBars + 1024 + 256;
+  static constexpr int kTxBytesPerCta = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr uint32_t kIdesc =
+      idesc_block_scaled(256, 256, KIND == kKindMxfp8 ? 0u : 1u, KIND == kKindMxfp8 ? 1u : 0u);
+};
+
+template <int KIND, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                             const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                             const GemmParams p) {
+  using T = PairTraits<KIND>;
+  using TP = TmemPlan<KIND>;
+  constexpr int S = T::kStagesP;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::kOffBars);
+  uint64_t* full_bar = bars;              // [S] used in the rank-0 CTA: both CTAs' loads land
+  uint64_t* empty_bar = bars + S;         // [S] in each CTA: stage free again
+  uint64_t* acc_full_bar = bars + 2 * S;  // in each CTA: tile accumulated
+  uint64_t* acc_overlap_bar = acc_full_bar + 1;  // rank 0: shared columns drained by all 8 epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_overlap_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int m_pairs = (p.m_tiles + 1) >> 1;
+  const int total_tiles = m_pairs * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full_bar, 1);
+    mbar_init(acc_overlap_bar, 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    {
+      const bool leader = elect_one_sync();
+      if (leader) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        prefetch_tensormap(&map_sfa);
+        prefetch_tensormap(&map_sfb);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
+        const int mp_idx = tile % m_pairs, n_idx = tile / m_pairs;
+        const int m_blk = mp_idx * 2 + static_cast<int>(rank);   // 128-row block of A this CTA owns
+        int b_blk0, b_blk1;                                      // 128-row blocks of B behind columns [0,128), [128,256)
+        if (EPI == kEpiGluBf16) {
+          b_blk0 = n_idx;
+          b_blk1 = (p.glu_inter >> 7) + n_idx;
+        } else {
+          b_blk0 = n_idx * 2;
+          b_blk1 = b_blk0 + 1;
+        }
+        const int b_mine = rank == 0 ? b_blk0 : b_blk1;
+        for (int kt = 0; kt < p.k_tiles; ++kt) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            if (p.status && leader) atomicCAS(p.status, 0, kStatusWaitProducer);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          if (leader) {
+            const uint32_t full_addr = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * T::kTxBytesPerCta);
+            tma_load_2d_pair(smem + stage * T::kABytes, &map_a, full_addr, kt * kBlockKBytes, m_blk * 128);
+            tma_load_2d_pair(smem + T::kOffB + stage * T::kBBytes, &map_b, full_addr, kt * kBlockKBytes, b_mine * 128);
+            // scale tiles: rows of the maps are 512-byte tiles, [row block][K tile]
+            const int sf_col = kt * T::kSfChunks;
+            tma_load_2d_pair(smem + T::kOffSfa + stage * T::kSfaBytes, &map_sfa, full_addr, 0,
+                             m_blk * p.sf_k_chunks + sf_col);
+            tma_load_2d_pair(smem + T::kOffSfb + stage * T::kSfbBytes, &map_sfb, full_addr, 0,
+                             b_blk0 * p.sf_k_chunks + sf_col);
+            tma_load_2d_pair(smem + T::kOffSfb + stage * T::kSfbBytes + T::kSfaBytes, &map_sfb, full_addr, 0,
+                             b_blk1 * p.sf_k_chunks + sf_col);
+          }
+          __syncwarp();
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (rank 0 only) ------------------------------
+    if (rank == 0) {
+      mma_issuer_loop<KIND, true, S, T::kABytes, T::kBBytes, T::kOffB, T::kOffSfa, T::kOffSfb, T::kSfaBytes,
+                      T::kSfbBytes>(p, smem, full_bar, empty_bar, acc_full_bar, acc_overlap_bar, abort_flag, tmem_base,
+                                    T::kIdesc, pair_id, num_pairs, total_tiles);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const float out_scale = p.out_scale ? __ldg(p.out_scale) : 1.0f;
+    const uint32_t overlap_addr = mapa_shared(smem_u32(acc_overlap_bar), 0);
+    uint32_t local_tile = 0;
+    for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++local_tile) {
+      const int mp_idx = tile % m_pairs, n_idx = tile / m_pairs;
+      const int row = (mp_idx * 2 + static_cast<int>(rank)) * 128 + quad * 32 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;
+      if (!mbar_wait(acc_full_bar, local_tile & 1, abort_flag)) {
+        if (p.status && lane == 0) atomicCAS(p.status, 0, kStatusWaitEpilogue);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      epilogue_drain<KIND, EPI>(p, tmem_base + lane_base + acc_col, row, row_ok, n_idx, (local_tile & 1) != 0,
+                                overlap_addr, out_scale, lane);
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA frees TMEM or leaves while the pair may still touch it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
