@@ -12,7 +12,7 @@ import os
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "_lib", "librtxb.so")
+LIB_PATH = os.environ.get("RTXB_LIBRARY") or os.path.join(_HERE, "_lib", "librtxb.so")
 
 OK = 0
 SCALE_ROW_MAJOR, SCALE_MMA64, SCALE_MMA128 = 0, 1, 2

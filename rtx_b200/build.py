@@ -41,20 +41,22 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, out: str = OUT) -> str:
+    if not force and out == OUT and not _stale():
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
     cmd = [_nvcc(), *NVCC_FLAGS]
+    # schedule tunables (see gemm_blockscaled.cuh), e.g. RTXB_DEFINES="RTXB_PAIR_KS_MX=3"
+    cmd += [f"-D{d}" for d in os.environ.get("RTXB_DEFINES", "").split()]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", OUT, *[os.path.join(CSRC, s) for s in SOURCES]]
+    cmd += ["-o", out, *[os.path.join(CSRC, s) for s in SOURCES]]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed building librtxb.so")
-    return OUT
+    return out
 
 
 if __name__ == "__main__":

@@ -110,10 +110,11 @@ class MXFP8GemmConfig(_Config):
     epilogue: str = "direct"           # direct vectorised stores
     raster: str = "m_fastest"
 
-    BUILT: ClassVar[tuple] = ((128, 256, 128, 4, 1),)
+    BUILT: ClassVar[tuple] = ((128, 256, 128, 4, 1), (256, 256, 128, 6, 2))
 
     def smem_bytes(self, sf_bytes_per_stage: int = 1536) -> int:
-        return self.stages * ((self.tile_m + self.tile_n) * self.tile_k_bytes + sf_bytes_per_stage) + 1280
+        rows = self.tile_m // self.cta_group + self.tile_n // self.cta_group   # per CTA
+        return self.stages * (rows * self.tile_k_bytes + sf_bytes_per_stage) + 1280
 
     def rejection(self, problem: Optional[MXFP8Problem] = None) -> Optional[str]:
         if (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group) not in self.BUILT:

@@ -104,14 +104,16 @@ int sm_count() {
   return cached[dev];
 }
 
-// RTXB_GEMM_PAIR=1 selects the CTA-pair (cta_group::2) GEMM, 0 the single-CTA one
-bool use_pair_kernel() {
-  static int cached = -1;
-  if (cached < 0) {
+// Schedule choice: the CTA-pair kernel (256 x 256 pair tiles) unless the problem has a single
+// 128-row block of A, where half of every pair would idle.  RTXB_GEMM_PAIR=0/1 forces one.
+bool use_pair_kernel(int m_tiles) {
+  static int forced = -2;
+  if (forced == -2) {
     const char* v = getenv("RTXB_GEMM_PAIR");
-    cached = (v && v[0] == '1') ? 1 : 0;
+    forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
   }
-  return cached == 1;
+  if (forced >= 0) return forced == 1;
+  return m_tiles >= 2;
 }
 
 template <int KIND, int EPI>
@@ -144,7 +146,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     const char* dbg = getenv("RTXB_GEMM_DEBUG");
     p.debug = dbg ? atoi(dbg) : 0;
   }
-  if (use_pair_kernel()) {
+  if (use_pair_kernel(p.m_tiles)) {
     using P = PairTraits<KIND>;
     CUtensorMap map_sfa, map_sfb;
     rc = make_scale_map(&map_sfa, sa, static_cast<int64_t>(p.m_tiles) * sf_k_chunks, P::kSfChunks);

@@ -39,7 +39,26 @@ enum GemmEpilogue : int {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockKBytes = 128;  // one swizzle row: 128 E4M3 values or 256 E2M1 values
-constexpr int kStages = 4;
+constexpr int kStages = 4;        // ring slots (one K step each) of the single-CTA kernel
+// K steps handed over per full/empty barrier (compile-time tunables)
+#ifndef RTXB_SINGLE_KS_MX
+#define RTXB_SINGLE_KS_MX 2
+#endif
+#ifndef RTXB_SINGLE_KS_NV
+#define RTXB_SINGLE_KS_NV 1
+#endif
+#ifndef RTXB_PAIR_KS_MX
+#define RTXB_PAIR_KS_MX 2
+#endif
+#ifndef RTXB_PAIR_KS_NV
+#define RTXB_PAIR_KS_NV 1
+#endif
+#ifndef RTXB_PAIR_SLOTS_MX
+#define RTXB_PAIR_SLOTS_MX 6
+#endif
+#ifndef RTXB_PAIR_SLOTS_NV
+#define RTXB_PAIR_SLOTS_NV 5
+#endif
 constexpr int kGemmThreads = 192;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
@@ -70,6 +89,7 @@ struct GemmTraits {
   static constexpr int kOffSfb = kOffSfa + kStages * kSfaBytes;
   static constexpr int kOffBars = kOffSfb + kStages * kSfbBytes;
   static constexpr int kSmemBytes = kOffBars + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kStepsPerBarrier = KIND == kKindMxfp8 ? RTXB_SINGLE_KS_MX : RTXB_SINGLE_KS_NV;
   static constexpr uint32_t kIdesc =
       idesc_block_scaled(kBlockM, kBlockN, KIND == kKindMxfp8 ? 0u : 1u, KIND == kKindMxfp8 ? 1u : 0u);
 };
@@ -242,22 +262,27 @@ __device__ __forceinline__ void issue_k_step(uint32_t tmem_base, uint32_t acc_co
   }
 }
 
-// The MMA issuer's loop over this CTA's (or pair's) tiles; the integer parameters describe the ring.
+// The MMA issuer's loop over this CTA's (or pair's) tiles; the integer parameters describe the ring:
+// SLOTS slots of one K step each (A, B, SFA, SFB), handed over in groups of KS slots per barrier,
+// so one wait and one commit cover KS K steps (4 KS MMAs).
 // All 32 lanes of the warp run it with identical control flow -- addresses, descriptors and loop
 // state then stay in uniform registers, which is what keeps the issue cost of a tcgen05
 // instruction low -- and one elected lane (always the same one) issues the tcgen05 instructions.
-template <int KIND, bool PAIR, int STAGES, int A_BYTES, int B_BYTES, int OFF_B, int OFF_SFA, int OFF_SFB, int SFA_BYTES,
-          int SFB_BYTES>
+template <int KIND, bool PAIR, int SLOTS, int KS, int A_BYTES, int B_BYTES, int OFF_B, int OFF_SFA, int OFF_SFB,
+          int SFA_BYTES, int SFB_BYTES>
 __device__ __forceinline__ void mma_issuer_loop(const GemmParams& p, uint8_t* smem, uint64_t* full_bar,
                                                 uint64_t* empty_bar, uint64_t* acc_full_bar, uint64_t* acc_overlap_bar,
                                                 volatile int* abort_flag, uint32_t tmem_base, uint32_t idesc,
                                                 int first_tile, int tile_stride, int total_tiles) {
   using TP = TmemPlan<KIND>;
-  int stage = 0;
+  constexpr int GROUPS = SLOTS / KS;
+  static_assert(SLOTS % KS == 0, "ring slots must split evenly into barrier groups");
+  const uint32_t smem_base = smem_u32(smem);
+  const int k_groups = (p.k_tiles + KS - 1) / KS;
+  int group = 0;
   uint32_t phase = 0;
   uint32_t local_tile = 0;
   uint32_t step = 0;  // global K-step counter: picks the scale set
-  const bool prefetch_sf = (p.debug & 4) != 0;
   const bool leader = elect_one_sync();
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local_tile) {
     const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;
@@ -270,43 +295,29 @@ __device__ __forceinline__ void mma_issuer_loop(const GemmParams& p, uint8_t* sm
       }
       tc_fence_after_sync();
     }
-    for (int kt = 0; kt < p.k_tiles; ++kt, ++step) {
-      const int set = step & 1;
-      const bool have_sf = prefetch_sf && kt > 0;  // copied while issuing the previous step
-      if (!have_sf) {
-        if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
-          if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
-          *abort_flag = 1;
-          return;
-        }
-        tc_fence_after_sync();
-        if (leader && (!(p.debug & 1) || kt == 0))
-          issue_scale_copy<KIND, PAIR>(tmem_base, smem_u32(smem + OFF_SFA + stage * SFA_BYTES),
-                                       smem_u32(smem + OFF_SFB + stage * SFB_BYTES), set);
-      }
-      if (prefetch_sf && kt + 1 < p.k_tiles) {
-        int nstage = stage + 1;
-        uint32_t nphase = phase;
-        if (nstage == STAGES) { nstage = 0; nphase ^= 1; }
-        if (!mbar_wait(&full_bar[nstage], nphase, abort_flag)) {
-          if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
-          *abort_flag = 1;
-          return;
-        }
-        tc_fence_after_sync();
-        if (leader)
-          issue_scale_copy<KIND, PAIR>(tmem_base, smem_u32(smem + OFF_SFA + nstage * SFA_BYTES),
-                                       smem_u32(smem + OFF_SFB + nstage * SFB_BYTES), set ^ 1);
+    for (int kg = 0; kg < k_groups; ++kg) {
+      if (!mbar_wait(&full_bar[group], phase, abort_flag)) {
+        if (p.status) atomicCAS(p.status, 0, kStatusWaitMma);
+        *abort_flag = 1;
+        return;
       }
       if (leader) {
-        issue_k_step<KIND, PAIR>(tmem_base, acc_col, smem_u32(smem + stage * A_BYTES),
-                                 smem_u32(smem + OFF_B + stage * B_BYTES), set, idesc, kt == 0);
-        // stage reusable once these MMAs (and the copies before them) have read it
-        if (PAIR) tc_commit_pair(&empty_bar[stage], 3);
-        else tc_commit(&empty_bar[stage]);
+#pragma unroll
+        for (int sub = 0; sub < KS; ++sub, ++step) {
+          const int slot = group * KS + sub;
+          const int set = step & 1;
+          if (!(p.debug & 1) || (kg == 0 && sub == 0))
+            issue_scale_copy<KIND, PAIR>(tmem_base, smem_base + OFF_SFA + slot * SFA_BYTES,
+                                         smem_base + OFF_SFB + slot * SFB_BYTES, set);
+          issue_k_step<KIND, PAIR>(tmem_base, acc_col, smem_base + slot * A_BYTES, smem_base + OFF_B + slot * B_BYTES,
+                                   set, idesc, kg == 0 && sub == 0);
+        }
+        // slots reusable once these MMAs (and the copies before them) have read them
+        if (PAIR) tc_commit_pair(&empty_bar[group], 3);
+        else tc_commit(&empty_bar[group]);
       }
       __syncwarp();
-      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      if (++group == GROUPS) { group = 0; phase ^= 1; }
     }
     if (leader) {
       if (PAIR) tc_commit_pair(acc_full_bar, 3);
@@ -346,6 +357,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     *abort_flag = 0;
     fence_barrier_init();
   }
+  // scale slots start as zeros: a K step past the end of K reuses whatever its slot holds, and
+  // that must never decode to NaN (its payload is zero, so any finite scale contributes nothing)
+  for (int i = threadIdx.x; i < (T::kOffBars - T::kOffSfa) / 4; i += kGemmThreads)
+    reinterpret_cast<uint32_t*>(smem + T::kOffSfa)[i] = 0u;
+  fence_proxy_async_smem();
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -364,7 +380,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
       }
-      int stage = 0;
+      constexpr int KS = T::kStepsPerBarrier;
+      const int k_groups = (p.k_tiles + KS - 1) / KS;
+      int group = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -383,34 +401,43 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const uint8_t* sfb_src0 = p.sfb + static_cast<size_t>(b_row0 >> 7) * p.sf_k_chunks * 512;
         const uint8_t* sfb_src1 = p.sfb + static_cast<size_t>(b_row1 >> 7) * p.sf_k_chunks * 512;
         const bool b1_valid = b_row1 < p.n;  // second half may lie past the last row of B
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+        for (int kg = 0; kg < k_groups; ++kg) {
+          if (!mbar_wait(&empty_bar[group], phase ^ 1, abort_flag)) {
             if (p.status && leader) atomicCAS(p.status, 0, kStatusWaitProducer);
             *abort_flag = 1;
             ok = false;
             break;
           }
           if (leader) {
-            uint8_t* sa = smem + stage * T::kABytes;
-            uint8_t* sb = smem + T::kOffB + stage * T::kBBytes;
-            uint8_t* ssfa = smem + T::kOffSfa + stage * T::kSfaBytes;
-            uint8_t* ssfb = smem + T::kOffSfb + stage * T::kSfbBytes;
-            if ((p.debug & 2) && (kt >= kStages || tile != static_cast<int>(blockIdx.x))) {
-              mbar_arrive(&full_bar[stage]);  // experiment: reuse whatever the stage holds, no loads
+            if ((p.debug & 2) && (kg * KS >= kStages || tile != static_cast<int>(blockIdx.x))) {
+              mbar_arrive(&full_bar[group]);  // experiment: reuse whatever the slots hold, no loads
             } else {
-              mbar_expect_tx(&full_bar[stage], T::kABytes + T::kBBytes + T::kSfaBytes +
-                                                   (b1_valid ? T::kSfbBytes : T::kSfaBytes));
-              tma_load_2d(sa, &map_a, &full_bar[stage], kt * kBlockKBytes, m0);
-              tma_load_2d(sb, &map_b, &full_bar[stage], kt * kBlockKBytes, b_row0);
-              tma_load_2d(sb + 128 * kBlockKBytes, &map_b, &full_bar[stage], kt * kBlockKBytes, b_row1);
-              const size_t sf_off = static_cast<size_t>(kt) * T::kSfaBytes;
-              bulk_load_1d(ssfa, sfa_src + sf_off, T::kSfaBytes, &full_bar[stage]);
-              bulk_load_1d(ssfb, sfb_src0 + sf_off, T::kSfaBytes, &full_bar[stage]);
-              if (b1_valid) bulk_load_1d(ssfb + T::kSfaBytes, sfb_src1 + sf_off, T::kSfaBytes, &full_bar[stage]);
+              // K steps past the end of K fetch zero payload (TMA fill) and no scale tiles
+              const int live = min(KS, p.k_tiles - kg * KS);
+              mbar_expect_tx(&full_bar[group], KS * (T::kABytes + T::kBBytes) +
+                                                   live * (T::kSfaBytes + (b1_valid ? T::kSfbBytes : T::kSfaBytes)));
+#pragma unroll
+              for (int sub = 0; sub < KS; ++sub) {
+                const int slot = group * KS + sub;
+                const int kt = kg * KS + sub;
+                uint8_t* sa = smem + slot * T::kABytes;
+                uint8_t* sb = smem + T::kOffB + slot * T::kBBytes;
+                uint8_t* ssfa = smem + T::kOffSfa + slot * T::kSfaBytes;
+                uint8_t* ssfb = smem + T::kOffSfb + slot * T::kSfbBytes;
+                tma_load_2d(sa, &map_a, &full_bar[group], kt * kBlockKBytes, m0);
+                tma_load_2d(sb, &map_b, &full_bar[group], kt * kBlockKBytes, b_row0);
+                tma_load_2d(sb + 128 * kBlockKBytes, &map_b, &full_bar[group], kt * kBlockKBytes, b_row1);
+                if (sub < live) {
+                  const size_t sf_off = static_cast<size_t>(kt) * T::kSfaBytes;
+                  bulk_load_1d(ssfa, sfa_src + sf_off, T::kSfaBytes, &full_bar[group]);
+                  bulk_load_1d(ssfb, sfb_src0 + sf_off, T::kSfaBytes, &full_bar[group]);
+                  if (b1_valid) bulk_load_1d(ssfb + T::kSfaBytes, sfb_src1 + sf_off, T::kSfaBytes, &full_bar[group]);
+                }
+              }
             }
           }
           __syncwarp();
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++group == kStages / KS) { group = 0; phase ^= 1; }
         }
       }
     }
@@ -418,7 +445,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     {
-      mma_issuer_loop<KIND, false, kStages, T::kABytes, T::kBBytes, T::kOffB, T::kOffSfa, T::kOffSfb, T::kSfaBytes,
+      mma_issuer_loop<KIND, false, kStages, T::kStepsPerBarrier, T::kABytes, T::kBBytes, T::kOffB, T::kOffSfa, T::kOffSfb, T::kSfaBytes,
                       T::kSfbBytes>(p, smem, full_bar, empty_bar, acc_full_bar, acc_overlap_bar, abort_flag, tmem_base,
                                     T::kIdesc, blockIdx.x, gridDim.x, total_tiles);
     }
@@ -467,7 +494,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 // ===========================================================================
 template <int KIND>
 struct PairTraits {
-  static constexpr int kStagesP = KIND == kKindMxfp8 ? 6 : 5;
+  static constexpr int kStagesP = KIND == kKindMxfp8 ? RTXB_PAIR_SLOTS_MX : RTXB_PAIR_SLOTS_NV;   // ring slots
+  static constexpr int kStepsPerBarrierP = KIND == kKindMxfp8 ? RTXB_PAIR_KS_MX : RTXB_PAIR_KS_NV;
   static constexpr int kSfChunks = TmemPlan<KIND>::kSfChunks;
   static constexpr int kSfaBytes = 512 * kSfChunks;
   static constexpr int kSfbBytes = 2 * kSfaBytes;
@@ -539,7 +567,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
         prefetch_tensormap(&map_sfa);
         prefetch_tensormap(&map_sfb);
       }
-      int stage = 0;
+      constexpr int KS = T::kStepsPerBarrierP;
+      const int k_groups = (p.k_tiles + KS - 1) / KS;
+      int group = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
@@ -554,29 +584,34 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
           b_blk1 = b_blk0 + 1;
         }
         const int b_mine = rank == 0 ? b_blk0 : b_blk1;
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+        for (int kg = 0; kg < k_groups; ++kg) {
+          if (!mbar_wait(&empty_bar[group], phase ^ 1, abort_flag)) {
             if (p.status && leader) atomicCAS(p.status, 0, kStatusWaitProducer);
             *abort_flag = 1;
             ok = false;
             break;
           }
           if (leader) {
-            const uint32_t full_addr = mapa_shared(smem_u32(&full_bar[stage]), 0);
-            if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * T::kTxBytesPerCta);
-            tma_load_2d_pair(smem + stage * T::kABytes, &map_a, full_addr, kt * kBlockKBytes, m_blk * 128);
-            tma_load_2d_pair(smem + T::kOffB + stage * T::kBBytes, &map_b, full_addr, kt * kBlockKBytes, b_mine * 128);
-            // scale tiles: rows of the maps are 512-byte tiles, [row block][K tile]
-            const int sf_col = kt * T::kSfChunks;
-            tma_load_2d_pair(smem + T::kOffSfa + stage * T::kSfaBytes, &map_sfa, full_addr, 0,
-                             m_blk * p.sf_k_chunks + sf_col);
-            tma_load_2d_pair(smem + T::kOffSfb + stage * T::kSfbBytes, &map_sfb, full_addr, 0,
-                             b_blk0 * p.sf_k_chunks + sf_col);
-            tma_load_2d_pair(smem + T::kOffSfb + stage * T::kSfbBytes + T::kSfaBytes, &map_sfb, full_addr, 0,
-                             b_blk1 * p.sf_k_chunks + sf_col);
+            const uint32_t full_addr = mapa_shared(smem_u32(&full_bar[group]), 0);
+            if (rank == 0) mbar_expect_tx(&full_bar[group], 2 * KS * T::kTxBytesPerCta);
+#pragma unroll
+            for (int sub = 0; sub < KS; ++sub) {
+              const int slot = group * KS + sub;
+              const int kt = kg * KS + sub;   // past the end of K: zero payload (TMA fill), any finite scales
+              tma_load_2d_pair(smem + slot * T::kABytes, &map_a, full_addr, kt * kBlockKBytes, m_blk * 128);
+              tma_load_2d_pair(smem + T::kOffB + slot * T::kBBytes, &map_b, full_addr, kt * kBlockKBytes, b_mine * 128);
+              // scale tiles: rows of the maps are 512-byte tiles, [row block][K tile]
+              const int sf_col = kt * T::kSfChunks;
+              tma_load_2d_pair(smem + T::kOffSfa + slot * T::kSfaBytes, &map_sfa, full_addr, 0,
+                               m_blk * p.sf_k_chunks + sf_col);
+              tma_load_2d_pair(smem + T::kOffSfb + slot * T::kSfbBytes, &map_sfb, full_addr, 0,
+                               b_blk0 * p.sf_k_chunks + sf_col);
+              tma_load_2d_pair(smem + T::kOffSfb + slot * T::kSfbBytes + T::kSfaBytes, &map_sfb, full_addr, 0,
+                               b_blk1 * p.sf_k_chunks + sf_col);
+            }
           }
           __syncwarp();
-          if (++stage == S) { stage = 0; phase ^= 1; }
+          if (++group == S / KS) { group = 0; phase ^= 1; }
         }
       }
     }
@@ -584,7 +619,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (rank 0 only) ------------------------------
     if (rank == 0) {
-      mma_issuer_loop<KIND, true, S, T::kABytes, T::kBBytes, T::kOffB, T::kOffSfa, T::kOffSfb, T::kSfaBytes,
+      mma_issuer_loop<KIND, true, S, T::kStepsPerBarrierP, T::kABytes, T::kBBytes, T::kOffB, T::kOffSfa, T::kOffSfb, T::kSfaBytes,
                       T::kSfbBytes>(p, smem, full_bar, empty_bar, acc_full_bar, acc_overlap_bar, abort_flag, tmem_base,
                                     T::kIdesc, pair_id, num_pairs, total_tiles);
     }

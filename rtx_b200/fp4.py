@@ -1,0 +1,420 @@
+"""NVFP4 frontend: `NVFP4Linear`, `nvfp4_linear`, `quantize_nvfp4` and the `rtx::nvfp4_*`
+custom ops, with the reference's signatures (rtx/fp4.py:1501-1540, :1543-1973,
+:2676-2942, :2945-3642) on top of the sm_100a kernels.
+
+Numerics (PRECISION_POLICY of the reference): NVFP4 forward — E2M1 payload, E4M3
+scale per 16 values, FP32 per-tensor outer scale — and MXFP8 backward on the saved
+BF16 operands (rtx/fp4.py:1772-1794).  Scaling policies built for sm_100a:
+`current` (outer scale from the tensor's present |max|; power-of-two for dynamic
+operands, exact `amax/2688` for offline weights) and `block` (outer scale 1).
+`jit_row_region` and `delayed` are not built yet and raise NotImplementedError.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import _native as N
+from . import fp8 as _fp8
+from . import ops
+from .configs import (DEFAULT_NVFP4_QUANT_CONFIG, MXFP8BwdConfig, NVFP4DynamicConfig, NVFP4Problem, NVFP4QuantConfig,
+                      NVFP4ScaleConfig, config_from_key)
+from .formats import (PACKED_OPERAND_SCHEMA_VERSION, SCALE_LAYOUT_CODES, SCALE_LAYOUT_NAMES, NVFP4Tensor,
+                      make_nvfp4_tensor, nvfp4_matrix_shape, nvfp4_qdata_2d, nvfp4_scale_layout,
+                      nvfp4_scales_for_kernel, nvfp4_storage_k, reject_packed_dtype_conversion)
+from .types import AutotuneMode
+
+DEFAULT_NVFP4_X_SCALE_REGION_ROWS = 5
+DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS = 4
+_LAYOUT_CODE = {"row_major": N.SCALE_ROW_MAJOR, "mma128": N.SCALE_MMA128}
+_SCALE_MODE = {"exact": N.TENSOR_SCALE_EXACT, "power2": N.TENSOR_SCALE_POWER2}
+
+
+def _current_tensor_scale(tensor: torch.Tensor) -> torch.Tensor:
+    """Exact two-level decode scale amax / (448 * 6); 1.0 for an all-zero tensor (rtx/fp4.py:343-350).
+    One device pass (|max| reduction + scale rule), no host synchronisation."""
+    return ops.nvfp4_tensor_scale(tensor.reshape(-1, tensor.shape[-1]), N.TENSOR_SCALE_EXACT)
+
+
+def _outer_tensor_scale(tensor: torch.Tensor, mode: str) -> torch.Tensor:
+    """Outer decode scale consumed by the quantizer (rtx/fp4.py:354-365): `exact` or `power2`
+    = 2^ceil(log2(max(amax/2688, FLT_MIN))), evaluated with the integer exponent rule of
+    rtx/kernels/nvfp4_quant.py:117-143."""
+    if mode not in _SCALE_MODE:
+        raise ValueError(f"unknown NVFP4 tensor scale mode {mode!r}")
+    return ops.nvfp4_tensor_scale(tensor.reshape(-1, tensor.shape[-1]), _SCALE_MODE[mode])
+
+
+def _check_bf16_cuda(t: torch.Tensor, name: str) -> None:
+    if t.device.type != "cuda":
+        raise ValueError(f"NVFP4 {name} must be a CUDA tensor")
+    if t.dtype is not torch.bfloat16:
+        raise TypeError(f"NVFP4 {name} must be BF16, got {t.dtype}")
+
+
+def quantize_nvfp4(tensor: torch.Tensor, *, tensor_scale: Optional[torch.Tensor] = None,
+                   config: Optional[NVFP4QuantConfig] = None) -> NVFP4Tensor:
+    """Prequantize BF16 into the packed NVFP4 tensor (rtx/fp4.py:1501-1540); the default outer scale
+    is the exact `amax / 2688`."""
+    if tensor.ndim < 1 or tensor.dtype is not torch.bfloat16:
+        raise TypeError("NVFP4 quantization requires a BF16 tensor")
+    if tensor.device.type != "cuda":
+        raise ValueError("NVFP4 quantization requires a CUDA tensor")
+    source = tensor.reshape(-1, tensor.shape[-1])
+    source = source if source.is_contiguous() else source.contiguous()
+    rows, k = int(source.shape[0]), int(source.shape[1])
+    selected = config or DEFAULT_NVFP4_QUANT_CONFIG
+    rejection = selected.rejection(rows, k)
+    if rejection is not None:
+        raise RuntimeError(f"NVFP4 operand cannot be quantized: {rejection}")
+    scale = _current_tensor_scale(source) if tensor_scale is None else tensor_scale
+    if scale.dtype is not torch.float32 or scale.numel() != 1:
+        raise TypeError("NVFP4 tensor_scale must be one FP32 value")
+    if scale.device != source.device:
+        raise ValueError("NVFP4 tensor_scale and source must share one device")
+    q, s = ops.nvfp4_quantize(source, scale.reshape(1), layout=_LAYOUT_CODE[selected.scale_layout])
+    q._base_inputs = (source, scale)
+    s._base_inputs = (source, scale)
+    return make_nvfp4_tensor(q, s, scale.reshape(()), tuple(int(v) for v in tensor.shape), selected.scale_layout)
+
+
+def _resolve_dynamic(key: str) -> NVFP4DynamicConfig:
+    cfg = config_from_key(key)
+    if not isinstance(cfg, NVFP4DynamicConfig):
+        raise RuntimeError(f"config key does not name an NVFP4 forward schedule: {type(cfg).__name__}")
+    rejection = cfg.rejection()
+    if rejection is not None:
+        raise RuntimeError(f"illegal NVFP4 forward schedule: {rejection}")
+    return cfg
+
+
+def _materialized_forward(x, weight, x_scale, weight_scale, output_scale):
+    x = x if x.is_contiguous() else x.contiguous()
+    weight = weight if weight.is_contiguous() else weight.contiguous()
+    m, k = x.shape
+    n = weight.shape[0]
+    qx, sx = ops.nvfp4_quantize(x, x_scale)
+    qw, sw = ops.nvfp4_quantize(weight, weight_scale)
+    return ops.nvfp4_gemm(qx, sx, qw, sw, int(m), int(n), int(k), output_scale)
+
+
+# --------------------------------------------------------------------------- custom ops
+
+@torch.library.custom_op("rtx::nvfp4_linear_materialized_fwd", mutates_args=(), device_types="cuda")
+def nvfp4_linear_materialized_fwd(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor,
+                                  weight_scale: torch.Tensor, output_scale: torch.Tensor, key: str) -> torch.Tensor:
+    """`current` policy: outer scales computed by the caller, dual quantize, GEMM x output_scale
+    (rtx/fp4.py:1260-1313, _DynamicRunner :404-454)."""
+    _resolve_dynamic(key)
+    return _materialized_forward(x, weight, x_scale, weight_scale, output_scale)
+
+
+@nvfp4_linear_materialized_fwd.register_fake
+def _(x, weight, x_scale, weight_scale, output_scale, key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_materialized_train", mutates_args=(), device_types="cuda")
+def nvfp4_linear_materialized_train(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor,
+                                    weight_scale: torch.Tensor, output_scale: torch.Tensor, key: str,
+                                    bwd_key: str) -> torch.Tensor:
+    _resolve_dynamic(key)
+    return _materialized_forward(x, weight, x_scale, weight_scale, output_scale)
+
+
+@nvfp4_linear_materialized_train.register_fake
+def _(x, weight, x_scale, weight_scale, output_scale, key, bwd_key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+def _nv_train_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[0], inputs[1])
+    ctx.bwd_key = inputs[-1]
+    ctx.n_inputs = len(inputs)
+
+
+def _nv_train_backward(ctx, grad_output):
+    """Backward of every NVFP4 op is the MXFP8 backward on the saved BF16 operands (rtx/fp4.py:1772-1794)."""
+    from . import fp8_bwd  # noqa: F401  (registers the backward ops)
+
+    x, weight = ctx.saved_tensors
+    need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+    grad_output = grad_output.contiguous()
+    dx = dw = None
+    if need_dx and need_dw:
+        dx, dw = torch.ops.rtx.mxfp8_linear_bwd(grad_output, x, weight, ctx.bwd_key)
+    elif need_dx:
+        dx = torch.ops.rtx.mxfp8_linear_dx(grad_output, weight, ctx.bwd_key)
+    elif need_dw:
+        dw = torch.ops.rtx.mxfp8_linear_dw(grad_output, x, ctx.bwd_key)
+    return (dx, dw) + (None,) * (ctx.n_inputs - 2)
+
+
+nvfp4_linear_materialized_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_block_fwd", mutates_args=(), device_types="cuda")
+def nvfp4_linear_block_fwd(x: torch.Tensor, weight: torch.Tensor, key: str) -> torch.Tensor:
+    """`block` policy: outer scale 1 folded out of both kernels (rtx/fp4.py:859-875)."""
+    _resolve_dynamic(key)
+    return _materialized_forward(x, weight, None, None, None)
+
+
+@nvfp4_linear_block_fwd.register_fake
+def _(x, weight, key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_block_train", mutates_args=(), device_types="cuda")
+def nvfp4_linear_block_train(x: torch.Tensor, weight: torch.Tensor, key: str, bwd_key: str) -> torch.Tensor:
+    _resolve_dynamic(key)
+    return _materialized_forward(x, weight, None, None, None)
+
+
+@nvfp4_linear_block_train.register_fake
+def _(x, weight, key, bwd_key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+nvfp4_linear_block_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
+def nvfp4_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor, weight_block_scales: torch.Tensor,
+                                      x_scale: torch.Tensor, output_scale: torch.Tensor, n: int, k: int, layout: str,
+                                      key: str) -> torch.Tensor:
+    """Packed weight, BF16 activations quantized on the fly (rtx/fp4.py:1628-1686)."""
+    if x.dtype is not torch.bfloat16 or x.ndim != 2 or x.shape[1] != k:
+        raise TypeError("x must be BF16 [M, K]")
+    x = x if x.is_contiguous() else x.contiguous()
+    qx, sx = ops.nvfp4_quantize(x, x_scale)
+    sw = _kernel_block_scales(weight_block_scales, n, k, layout)
+    return ops.nvfp4_gemm(qx, sx, weight_data.view(torch.uint8), sw, int(x.shape[0]), n, k, output_scale)
+
+
+@nvfp4_linear_dynamic_x_prequant_w.register_fake
+def _(x, weight_data, weight_block_scales, x_scale, output_scale, n, k, layout, key):
+    return x.new_empty((x.shape[0], n), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_prequantized", mutates_args=(), device_types="cuda")
+def nvfp4_linear_prequantized(x_data: torch.Tensor, weight_data: torch.Tensor, x_block_scales: torch.Tensor,
+                              weight_block_scales: torch.Tensor, output_scale: torch.Tensor, m: int, n: int, k: int,
+                              x_layout: str, weight_layout: str, key: str) -> torch.Tensor:
+    """Both operands packed (rtx/fp4.py:1689-1760)."""
+    sx = _kernel_block_scales(x_block_scales, m, k, x_layout)
+    sw = _kernel_block_scales(weight_block_scales, n, k, weight_layout)
+    return ops.nvfp4_gemm(x_data.view(torch.uint8), sx, weight_data.view(torch.uint8), sw, m, n, k, output_scale)
+
+
+@nvfp4_linear_prequantized.register_fake
+def _(x_data, weight_data, x_block_scales, weight_block_scales, output_scale, m, n, k, x_layout, weight_layout, key):
+    return x_data.new_empty((m, n), dtype=torch.bfloat16)
+
+
+def _kernel_block_scales(scales: torch.Tensor, rows: int, k: int, layout: str) -> torch.Tensor:
+    from .formats.common import scales_row_major_to_mma128
+    from .formats.nvfp4 import nvfp4_scale_chunks
+
+    storage_k = nvfp4_storage_k(k)
+    if layout == "mma128":
+        return scales.reshape(-1).view(torch.uint8)
+    if layout == "row_major":
+        return scales_row_major_to_mma128(scales, rows, storage_k // 16, nvfp4_scale_chunks(storage_k))
+    raise RuntimeError(f"NVFP4 scale layout {layout!r} cannot feed the sm_100a GEMM")
+
+
+# --------------------------------------------------------------------------- functional
+
+def _dynamic_key(dynamic_config, scale_config, scaling):
+    cfg = dynamic_config or NVFP4DynamicConfig(
+        scale=scale_config or NVFP4ScaleConfig(policy=scaling,
+                                               tensor_scale_mode="power2" if scaling == "current" else "exact"))
+    rejection = cfg.rejection()
+    if rejection is not None:
+        raise RuntimeError(f"illegal NVFP4 forward schedule: {rejection}")
+    return cfg, cfg.to_key()
+
+
+def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
+                 backward_config: Optional[MXFP8BwdConfig] = None, scaling: Optional[str] = None,
+                 scale_region_rows: Optional[int] = None, x_scale_region_rows: Optional[int] = None,
+                 weight_scale_region_rows: Optional[int] = None, backend: str = "auto",
+                 autotune: "AutotuneMode | bool | None" = None, tuning_policy: object = None,
+                 autotune_cache_dir: "Path | str | None" = None, dynamic_config: Optional[NVFP4DynamicConfig] = None,
+                 weight_prequant_config=None, fully_prequant_config=None) -> torch.Tensor:
+    """Apply NVFP4 forward and MXFP8 backward to BF16 or packed operands (rtx/fp4.py:2676-2942)."""
+    w_packed, x_packed = isinstance(weight, NVFP4Tensor), isinstance(x, NVFP4Tensor)
+    if scaling is None:
+        # the reference defaults dynamic operands to jit_row_region, which is not built for sm_100a
+        scaling = "current"
+    if scaling not in ("current", "jit_row_region", "block"):
+        raise ValueError("functional NVFP4 scaling must be current, jit_row_region, or block")
+    if scaling == "jit_row_region":
+        raise NotImplementedError("NVFP4 jit_row_region scaling is not built for sm_100a yet; use scaling='current'")
+    _fp8._normalize_backend(backend)
+    _fp8._autotune_mode(autotune)
+    if x_packed and not w_packed:
+        raise ValueError("a packed activation requires a packed weight")
+    bwd_key = (backward_config or MXFP8BwdConfig()).to_key()
+    cfg, key = _dynamic_key(dynamic_config, scale_config, scaling)
+    if w_packed:
+        n, k = nvfp4_matrix_shape(weight)
+        wq, wscales = nvfp4_qdata_2d(weight), nvfp4_scales_for_kernel(weight)
+        w_scale = weight.per_tensor_scale.reshape(1).float()
+        if x_packed:
+            m, kx = nvfp4_matrix_shape(x)
+            if kx != k:
+                raise ValueError(f"K mismatch: x has {kx}, weight has {k}")
+            out_scale = x.per_tensor_scale.reshape(1).float() * w_scale
+            out = torch.ops.rtx.nvfp4_linear_prequantized(nvfp4_qdata_2d(x), wq, nvfp4_scales_for_kernel(x), wscales,
+                                                          out_scale, m, n, k, "mma128", "mma128", key)
+            return out.reshape(*x._rtx_logical_shape[:-1], n)
+        _check_bf16_cuda(x, "activation")
+        if x.shape[-1] != k:
+            raise ValueError(f"K mismatch: x has {x.shape[-1]}, weight has {k}")
+        if x.requires_grad:
+            raise RuntimeError("a prequantized NVFP4 weight is inference-only; keep the BF16 master weight to train")
+        x2d = x.reshape(-1, k)
+        x_scale = _current_tensor_scale(x2d)            # rtx/fp4.py:3421-3446: exact scale for packed weights
+        out = torch.ops.rtx.nvfp4_linear_dynamic_x_prequant_w(x2d, wq, wscales, x_scale, x_scale * w_scale, n, k,
+                                                              "mma128", key)
+        return out.reshape(*x.shape[:-1], n)
+    _check_bf16_cuda(x, "activation")
+    _check_bf16_cuda(weight, "weight")
+    if x.shape[-1] != weight.shape[-1]:
+        raise ValueError(f"K mismatch: x has {x.shape[-1]}, weight has {weight.shape[-1]}")
+    x2d = x.reshape(-1, x.shape[-1])
+    train = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    if train:
+        from . import fp8_bwd  # noqa: F401
+    if cfg.scale.policy == "block":
+        out = (torch.ops.rtx.nvfp4_linear_block_train(x2d, weight, key, bwd_key) if train
+               else torch.ops.rtx.nvfp4_linear_block_fwd(x2d, weight, key))
+    else:
+        mode = cfg.scale.tensor_scale_mode
+        x_scale = _outer_tensor_scale(x2d.detach(), mode)
+        w_scale = _outer_tensor_scale(weight.detach(), mode)
+        output_scale = x_scale * w_scale                # rtx/fp4.py:2919-2921
+        out = (torch.ops.rtx.nvfp4_linear_materialized_train(x2d, weight, x_scale, w_scale, output_scale, key, bwd_key)
+               if train else
+               torch.ops.rtx.nvfp4_linear_materialized_fwd(x2d, weight, x_scale, w_scale, output_scale, key))
+    return out.reshape(*x.shape[:-1], weight.shape[0])
+
+
+# --------------------------------------------------------------------------- module
+
+class NVFP4Linear(nn.Module):
+    """No-bias BF16-master linear with NVFP4 forward and MXFP8 backward (rtx/fp4.py:2945-3642).
+    Packed modules store `weight_data`, `weight_block_scales`, `weight_tensor_scale`,
+    `weight_packing_meta = [schema, layout code, in_features, storage_k]` (rtx/fp4.py:3176-3196)."""
+
+    __constants__ = ["in_features", "out_features", "scaling", "weight_mode"]
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, *, device=None,
+                 dtype: torch.dtype = torch.bfloat16, scale_config: Optional[NVFP4ScaleConfig] = None,
+                 backward_config: Optional[MXFP8BwdConfig] = None, scaling: Optional[str] = None,
+                 scale_region_rows: Optional[int] = None, x_scale_region_rows: Optional[int] = None,
+                 weight_scale_region_rows: Optional[int] = None, backend: str = "auto",
+                 packed_weight: Optional[NVFP4Tensor] = None, autotune: "AutotuneMode | bool | None" = None,
+                 tuning_policy: object = None, autotune_cache_dir: "Path | str | None" = None,
+                 dynamic_config: Optional[NVFP4DynamicConfig] = None, weight_prequant_config=None,
+                 fully_prequant_config=None) -> None:
+        super().__init__()
+        if bias:
+            raise NotImplementedError("NVFP4Linear is a no-bias linear layer; pass bias=False")
+        if dtype is not torch.bfloat16:
+            raise TypeError(f"NVFP4Linear parameters must be BF16, got {dtype}")
+        if scaling is None:
+            scaling = "current"
+        if scaling in ("jit_row_region", "delayed"):
+            raise NotImplementedError(f"NVFP4 {scaling} scaling is not built for sm_100a yet; use 'current' or 'block'")
+        if scaling not in ("current", "block"):
+            raise ValueError(f"unknown NVFP4 scaling {scaling!r}")
+        self.in_features, self.out_features = int(in_features), int(out_features)
+        self.scaling = scaling
+        self.scale_config = scale_config
+        self.backward_config = backward_config
+        self.backend = _fp8._normalize_backend(backend)
+        self.autotune = autotune
+        self.tuning_policy = tuning_policy
+        self.autotune_cache_dir = autotune_cache_dir
+        self.dynamic_config = dynamic_config
+        self.x_scale_region_rows = x_scale_region_rows or scale_region_rows or DEFAULT_NVFP4_X_SCALE_REGION_ROWS
+        self.weight_scale_region_rows = (weight_scale_region_rows or scale_region_rows
+                                         or DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS)
+        self.weight_mode = "prequantized" if packed_weight is not None else "dynamic"
+        if packed_weight is None:
+            self.weight = nn.Parameter(torch.empty(self.out_features, self.in_features, device=device,
+                                                   dtype=torch.bfloat16))
+            nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+        else:
+            n, k = nvfp4_matrix_shape(packed_weight)
+            if (n, k) != (self.out_features, self.in_features):
+                raise ValueError(f"packed weight is {n}x{k}, module is {self.out_features}x{self.in_features}")
+            layout = nvfp4_scale_layout(packed_weight)
+            self.register_parameter("weight", None)
+            self.register_buffer("weight_data", nvfp4_qdata_2d(packed_weight))
+            self.register_buffer("weight_block_scales", packed_weight.scale.reshape(-1).view(torch.uint8))
+            self.register_buffer("weight_tensor_scale", packed_weight.per_tensor_scale.reshape(1).float())
+            self.register_buffer("weight_packing_meta", torch.tensor(
+                [PACKED_OPERAND_SCHEMA_VERSION, SCALE_LAYOUT_CODES[layout], self.in_features,
+                 nvfp4_storage_k(self.in_features)], dtype=torch.int64))
+
+    @classmethod
+    def from_float(cls, module: nn.Linear, **kwargs) -> "NVFP4Linear":
+        if module.bias is not None:
+            raise NotImplementedError("NVFP4Linear is a no-bias linear layer")
+        out = cls(module.in_features, module.out_features, device=module.weight.device, **kwargs)
+        with torch.no_grad():
+            out.weight.copy_(module.weight.to(torch.bfloat16))
+        return out
+
+    def to_quantized_weight(self, *, config: Optional[NVFP4QuantConfig] = None) -> "NVFP4Linear":
+        if self.weight_mode == "prequantized":
+            return self
+        packed = quantize_nvfp4(self.weight.detach(), config=config)
+        return NVFP4Linear(self.in_features, self.out_features, device=self.weight.device, scaling="current",
+                           packed_weight=packed)
+
+    def packed_weight(self) -> NVFP4Tensor:
+        if self.weight_mode != "prequantized":
+            raise RuntimeError("module holds a BF16 weight; call to_quantized_weight() first")
+        layout = SCALE_LAYOUT_NAMES[int(self.weight_packing_meta[1])]
+        return make_nvfp4_tensor(self.weight_data, self.weight_block_scales, self.weight_tensor_scale.reshape(()),
+                                 (self.out_features, self.in_features), layout)
+
+    def reset_delayed_scales(self) -> None:
+        """Delayed scaling keeps an amax history in the reference; nothing to reset for `current`/`block`."""
+
+    def explain(self) -> dict:
+        return {"format": "nvfp4", "weight_mode": self.weight_mode, "scaling": self.scaling,
+                "pipeline": "outer scale + quantize once + tcgen05 mxf4nvf4 GEMM (sm_100a)", "backward": "mxfp8"}
+
+    def to(self, *args, **kwargs):
+        if self.weight_mode == "prequantized":
+            reject_packed_dtype_conversion(args, kwargs, format_name="NVFP4")
+        return super().to(*args, **kwargs)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bias=False, "
+                f"weight_mode={self.weight_mode}, scaling={self.scaling}")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.weight_mode == "prequantized":
+            return nvfp4_linear(x, self.packed_weight(), scaling="current")
+        return nvfp4_linear(x, self.weight, scale_config=self.scale_config, backward_config=self.backward_config,
+                            scaling=self.scaling, backend=self.backend, autotune=self.autotune,
+                            dynamic_config=self.dynamic_config)
+
+
+def _clear_runtime_caches() -> dict:
+    return {}
+
+
+__all__ = ["NVFP4Linear", "nvfp4_linear", "quantize_nvfp4", "DEFAULT_NVFP4_X_SCALE_REGION_ROWS",
+           "DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS"]
