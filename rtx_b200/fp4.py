@@ -34,10 +34,24 @@ _LAYOUT_CODE = {"row_major": N.SCALE_ROW_MAJOR, "mma128": N.SCALE_MMA128}
 _SCALE_MODE = {"exact": N.TENSOR_SCALE_EXACT, "power2": N.TENSOR_SCALE_POWER2}
 
 
+@torch.library.custom_op("rtx::nvfp4_outer_scale", mutates_args=(), device_types="cuda")
+def nvfp4_outer_scale(x: torch.Tensor, mode: str) -> torch.Tensor:
+    """FP32[1] outer decode scale of a BF16 matrix: one device pass (|max| reduction + scale rule),
+    no host synchronisation.  The reference computes it with PyTorch reductions (rtx/fp4.py:343-365)."""
+    if mode not in _SCALE_MODE:
+        raise ValueError(f"unknown NVFP4 tensor scale mode {mode!r}")
+    x = x if x.is_contiguous() else x.contiguous()
+    return ops.nvfp4_tensor_scale(x, _SCALE_MODE[mode])
+
+
+@nvfp4_outer_scale.register_fake
+def _(x, mode):
+    return x.new_empty((1,), dtype=torch.float32)
+
+
 def _current_tensor_scale(tensor: torch.Tensor) -> torch.Tensor:
-    """Exact two-level decode scale amax / (448 * 6); 1.0 for an all-zero tensor (rtx/fp4.py:343-350).
-    One device pass (|max| reduction + scale rule), no host synchronisation."""
-    return ops.nvfp4_tensor_scale(tensor.reshape(-1, tensor.shape[-1]), N.TENSOR_SCALE_EXACT)
+    """Exact two-level decode scale amax / (448 * 6); 1.0 for an all-zero tensor (rtx/fp4.py:343-350)."""
+    return torch.ops.rtx.nvfp4_outer_scale(tensor.detach().reshape(-1, tensor.shape[-1]), "exact")
 
 
 def _outer_tensor_scale(tensor: torch.Tensor, mode: str) -> torch.Tensor:
@@ -46,7 +60,7 @@ def _outer_tensor_scale(tensor: torch.Tensor, mode: str) -> torch.Tensor:
     rtx/kernels/nvfp4_quant.py:117-143."""
     if mode not in _SCALE_MODE:
         raise ValueError(f"unknown NVFP4 tensor scale mode {mode!r}")
-    return ops.nvfp4_tensor_scale(tensor.reshape(-1, tensor.shape[-1]), _SCALE_MODE[mode])
+    return torch.ops.rtx.nvfp4_outer_scale(tensor.detach().reshape(-1, tensor.shape[-1]), mode)
 
 
 def _check_bf16_cuda(t: torch.Tensor, name: str) -> None:
@@ -230,6 +244,12 @@ def _kernel_block_scales(scales: torch.Tensor, rows: int, k: int, layout: str) -
 
 # --------------------------------------------------------------------------- functional
 
+@torch._dynamo.assume_constant_result
+def _bwd_key(backward_config):
+    return (backward_config or MXFP8BwdConfig()).to_key()
+
+
+@torch._dynamo.assume_constant_result
 def _dynamic_key(dynamic_config, scale_config, scaling):
     cfg = dynamic_config or NVFP4DynamicConfig(
         scale=scale_config or NVFP4ScaleConfig(policy=scaling,
@@ -260,7 +280,7 @@ def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
     _fp8._autotune_mode(autotune)
     if x_packed and not w_packed:
         raise ValueError("a packed activation requires a packed weight")
-    bwd_key = (backward_config or MXFP8BwdConfig()).to_key()
+    bwd_key = _bwd_key(backward_config)
     cfg, key = _dynamic_key(dynamic_config, scale_config, scaling)
     if w_packed:
         n, k = nvfp4_matrix_shape(weight)
@@ -348,6 +368,8 @@ class NVFP4Linear(nn.Module):
         self.weight_scale_region_rows = (weight_scale_region_rows or scale_region_rows
                                          or DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS)
         self.weight_mode = "prequantized" if packed_weight is not None else "dynamic"
+        self._dynamic_config, self._forward_key = _dynamic_key(dynamic_config, scale_config, scaling)
+        self._backward_key = _bwd_key(backward_config)
         if packed_weight is None:
             self.weight = nn.Parameter(torch.empty(self.out_features, self.in_features, device=device,
                                                    dtype=torch.bfloat16))
@@ -357,6 +379,7 @@ class NVFP4Linear(nn.Module):
             if (n, k) != (self.out_features, self.in_features):
                 raise ValueError(f"packed weight is {n}x{k}, module is {self.out_features}x{self.in_features}")
             layout = nvfp4_scale_layout(packed_weight)
+            self._weight_scale_layout = layout
             self.register_parameter("weight", None)
             self.register_buffer("weight_data", nvfp4_qdata_2d(packed_weight))
             self.register_buffer("weight_block_scales", packed_weight.scale.reshape(-1).view(torch.uint8))
@@ -405,11 +428,34 @@ class NVFP4Linear(nn.Module):
                 f"weight_mode={self.weight_mode}, scaling={self.scaling}")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        k, n = self.in_features, self.out_features
+        if x.shape[-1] != k:
+            raise ValueError(f"K mismatch: x has {x.shape[-1]}, weight has {k}")
+        x2d = x.reshape(-1, k)
+        key, bwd_key = self._forward_key, self._backward_key
         if self.weight_mode == "prequantized":
-            return nvfp4_linear(x, self.packed_weight(), scaling="current")
-        return nvfp4_linear(x, self.weight, scale_config=self.scale_config, backward_config=self.backward_config,
-                            scaling=self.scaling, backend=self.backend, autotune=self.autotune,
-                            dynamic_config=self.dynamic_config)
+            if x.requires_grad and torch.is_grad_enabled():
+                raise RuntimeError("a prequantized NVFP4 weight is inference-only; keep the BF16 master weight to train")
+            x_scale = torch.ops.rtx.nvfp4_outer_scale(x2d.detach(), "exact")   # rtx/fp4.py:3421-3446
+            out = torch.ops.rtx.nvfp4_linear_dynamic_x_prequant_w(
+                x2d, self.weight_data, self.weight_block_scales, x_scale, x_scale * self.weight_tensor_scale, n, k,
+                self._weight_scale_layout, key)
+            return out.reshape(*x.shape[:-1], n)
+        train = torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad)
+        if train:
+            from . import fp8_bwd  # noqa: F401  (registers the backward ops)
+        if self._dynamic_config.scale.policy == "block":
+            out = (torch.ops.rtx.nvfp4_linear_block_train(x2d, self.weight, key, bwd_key) if train
+                   else torch.ops.rtx.nvfp4_linear_block_fwd(x2d, self.weight, key))
+        else:
+            mode = self._dynamic_config.scale.tensor_scale_mode
+            x_scale = torch.ops.rtx.nvfp4_outer_scale(x2d.detach(), mode)
+            w_scale = torch.ops.rtx.nvfp4_outer_scale(self.weight.detach(), mode)
+            output_scale = x_scale * w_scale                                   # rtx/fp4.py:2919-2921
+            out = (torch.ops.rtx.nvfp4_linear_materialized_train(x2d, self.weight, x_scale, w_scale, output_scale, key,
+                                                                 bwd_key) if train else
+                   torch.ops.rtx.nvfp4_linear_materialized_fwd(x2d, self.weight, x_scale, w_scale, output_scale, key))
+        return out.reshape(*x.shape[:-1], n)
 
 
 def _clear_runtime_caches() -> dict:

@@ -199,7 +199,9 @@ def _(x_data, weight_data, x_scales, weight_scales, m, n, k, x_scale_layout, wei
 
 # --------------------------------------------------------------------------- functional
 
+@torch._dynamo.assume_constant_result
 def _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, packed: bool):
+    """Interned (forward, backward) schedule keys; a constant under torch.compile."""
     if config is not None and forward_config is not None:
         raise ValueError("pass only forward_config, not both config aliases")
     if prequant_config is not None and dynamic_config is not None:
@@ -302,6 +304,9 @@ class MXFP8Linear(nn.Module):
         self.backend = _normalize_backend(backend)
         _autotune_mode(autotune)
         self.weight_mode = "prequantized" if packed_weight is not None else "dynamic"
+        # schedules travel as interned strings so that a compiled graph sees constants (rtx/fp8.py:376-415)
+        self._forward_config_key, self._backward_config_key = _select_keys(
+            self.forward_config, None, self.dynamic_config, None, backward_config, packed_weight is not None)
         if packed_weight is None:
             weight = torch.empty(self.out_features, self.in_features, device=device, dtype=torch.bfloat16)
             self.weight = nn.Parameter(weight)
@@ -311,6 +316,7 @@ class MXFP8Linear(nn.Module):
             if (n, k) != (self.out_features, self.in_features):
                 raise ValueError(f"packed weight is {n}x{k}, module is {self.out_features}x{self.in_features}")
             layout = mxfp8_scale_layout(packed_weight)
+            self._weight_scale_layout = layout
             self.register_parameter("weight", None)
             self.register_buffer("weight_data", mxfp8_qdata_2d(packed_weight).view(torch.uint8))
             self.register_buffer("weight_scales", packed_weight.scale.reshape(-1).view(torch.uint8))
@@ -362,11 +368,23 @@ class MXFP8Linear(nn.Module):
                 f"weight_mode={self.weight_mode}, backend={self.backend}")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        k, n = self.in_features, self.out_features
+        if x.shape[-1] != k:
+            raise ValueError(f"K mismatch: x has {x.shape[-1]}, weight has {k}")
+        x2d = x.reshape(-1, k)
         if self.weight_mode == "prequantized":
-            return mxfp8_linear(x, self.packed_weight(), dynamic_config=self.dynamic_config)
-        return mxfp8_linear(x, self.weight, forward_config=self.forward_config, dynamic_config=self.dynamic_config,
-                            backward_config=self.backward_config, backend=self.backend, autotune=self.autotune,
-                            tuning_policy=self.tuning_policy, autotune_cache_dir=self.autotune_cache_dir)
+            if x.requires_grad and torch.is_grad_enabled():
+                raise RuntimeError("a prequantized MXFP8 weight is inference-only; keep the BF16 master weight to train")
+            out = torch.ops.rtx.mxfp8_linear_dynamic_x_prequant_w(x2d, self.weight_data, self.weight_scales, n, k,
+                                                                  self._weight_scale_layout, self._forward_config_key)
+        elif torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
+            from . import fp8_bwd  # noqa: F401  (registers rtx::mxfp8_linear_train)
+
+            out = torch.ops.rtx.mxfp8_linear_train(x2d, self.weight, self._forward_config_key,
+                                                   self._backward_config_key)
+        else:
+            out = torch.ops.rtx.mxfp8_linear_prequant(x2d, self.weight, self._forward_config_key)
+        return out.reshape(*x.shape[:-1], n)
 
 
 __all__ = ["MXFP8Linear", "mxfp8_linear", "quantize_mxfp8", "MXFP8PrequantConfig", "DEFAULT_MXFP8_PREQUANT_CONFIG",

@@ -1,0 +1,251 @@
+"""CPU contract tests of the Python boundary (mirrors rtx tests/test_linear_frontends.py,
+test_runtime_contract.py and the config halves of test_mxfp8_fwd.py / test_nvfp4.py):
+no GPU, no kernel launch."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_lazy_import_touches_neither_cuda_nor_the_library():
+    code = ("import sys; sys.path.insert(0, %r); import rtx_b200; "
+            "assert 'rtx_b200.fp8' not in sys.modules and 'rtx_b200._native' not in sys.modules; "
+            "assert 'MXFP8Linear' in dir(rtx_b200); print(rtx_b200.__version__)") % ROOT
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    with pytest.raises(AttributeError):
+        import rtx_b200
+
+        rtx_b200.not_a_symbol
+
+
+def test_public_names_match_the_reference_surface():
+    import rtx_b200
+
+    for name in ("MXFP8Linear", "NVFP4Linear", "mxfp8_linear", "nvfp4_linear", "quantize_mxfp8", "quantize_nvfp4",
+                 "mxfp8_linear_backward", "MXTensor", "MXFP8Tensor", "NVFP4Tensor", "MXFP8QuantConfig",
+                 "MXFP8GemmConfig", "MXFP8FwdConfig", "MXFP8Problem", "MXFP8BwdConfig", "NVFP4QuantConfig",
+                 "NVFP4GemmConfig", "NVFP4Problem", "clear_runtime_caches", "validate_runtime_environment",
+                 "DEFAULT_MXFP8_BWD_CONFIG", "DEFAULT_NVFP4_X_SCALE_REGION_ROWS"):
+        assert getattr(rtx_b200, name) is not None
+
+
+def test_configs_round_trip_and_reject_explicitly():
+    from rtx_b200 import configs as C
+
+    for cfg in (C.MXFP8FwdConfig(), C.MXFP8PrequantConfig(), C.MXFP8BwdConfig(streams="dual_stream"),
+                C.NVFP4DynamicConfig(), C.MXFP8QuantConfig(scale_rounding="floor", scale_layout="row_major")):
+        key = cfg.to_key()
+        assert json.loads(key)["type"] == type(cfg).__name__
+        assert C.config_from_key(key) == cfg
+        assert hash(cfg) == hash(C.config_from_key(key))
+    assert C.MXFP8QuantConfig(scale_layout="mma64").rejection(128, 128).startswith("mma64")
+    assert "rounding" in C.MXFP8QuantConfig(scale_rounding="nearest").rejection(1, 1)
+    assert "no kernel is built" in C.MXFP8GemmConfig(tile_n=128).rejection()
+    assert C.MXFP8GemmConfig(tile_m=256, cta_group=2, stages=6).rejection() is None
+    assert C.MXFP8GemmConfig().rejection(C.MXFP8Problem(0, 1, 1)) == "m, n and k must be positive"
+    assert C.MXFP8FwdConfig(pipeline="fused").rejection() == "forward pipeline 'fused' is not built"
+    assert "not built" in C.NVFP4ScaleConfig(policy="jit_row_region").rejection()
+    assert C.NVFP4QuantConfig(scale_reciprocal="rcp_approx").rejection() is not None
+    assert C.MXFP8Problem(3, 5, 1).storage_k == 32 and C.NVFP4Problem(1, 1, 129).storage_k == 160
+    assert C.MXFP8GemmConfig().smem_bytes() <= C.SMEM_CAPACITY_BYTES
+
+
+def test_bounded_cache_lru_and_env_limits(monkeypatch):
+    from rtx_b200.runtime import BoundedCache, runner_cache_limit
+
+    cache = BoundedCache(2)
+    cache["a"], cache["b"] = 1, 2
+    assert cache["a"] == 1
+    cache["c"] = 3                       # evicts b (least recently used)
+    assert "b" not in cache and set(cache) == {"a", "c"}
+    assert cache.get("zz") is None
+    stats = cache.stats()
+    assert stats["evictions"] == 1 and stats["hits"] == 1 and stats["misses"] >= 1 and stats["max_entries"] == 2
+    zero = BoundedCache(0)
+    zero["k"] = 1
+    assert len(zero) == 0
+    with pytest.raises(ValueError):
+        BoundedCache(-1)
+    monkeypatch.setenv("RTX_MXFP8_PREQUANT_CACHE_ENTRIES", "3")
+    assert runner_cache_limit("prequant") == 3
+    monkeypatch.setenv("RTX_MXFP8_PREQUANT_CACHE_ENTRIES", "x")
+    with pytest.raises(ValueError, match="must be an integer"):
+        runner_cache_limit("prequant")
+    monkeypatch.delenv("RTX_MXFP8_PREQUANT_CACHE_ENTRIES")
+    monkeypatch.setenv("RTX_NVFP4_RUNNER_CACHE_ENTRIES", "5")
+    assert runner_cache_limit("dynamic", namespace="NVFP4") == 5
+
+
+def test_runtime_environment_contract(native_lib):
+    from rtx_b200.runtime import validate_runtime_environment
+
+    facts = validate_runtime_environment()
+    assert facts["abi_version"] >= 100 and facts["torch_cuda"]
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no CUDA device"):
+            validate_runtime_environment(require_device=True)
+
+
+def test_module_constructors_and_state_dict_schema():
+    from rtx_b200 import MXFP8Linear, NVFP4Linear
+
+    with pytest.raises(NotImplementedError):
+        MXFP8Linear(8, 8, bias=True)
+    with pytest.raises(TypeError):
+        MXFP8Linear(8, 8, dtype=torch.float16)
+    with pytest.raises(ValueError, match="unknown MXFP8 backend"):
+        MXFP8Linear(8, 8, backend="cutlass")
+    from rtx_b200.configs import MXFP8FwdConfig, MXFP8PrequantConfig
+
+    with pytest.raises(ValueError, match="both config aliases"):
+        MXFP8Linear(8, 8, config=MXFP8FwdConfig(), forward_config=MXFP8FwdConfig())
+    with pytest.raises(ValueError, match="materialized config aliases"):
+        MXFP8Linear(8, 8, prequant_config=MXFP8PrequantConfig(), dynamic_config=MXFP8PrequantConfig())
+    layer = MXFP8Linear(64, 32)
+    assert list(layer.state_dict()) == ["weight"] and layer.weight.dtype is torch.bfloat16
+    assert layer.weight.shape == (32, 64) and layer.weight_mode == "dynamic"
+    assert "weight_mode=dynamic" in repr(layer) and layer.explain()["format"] == "mxfp8"
+    ref = torch.nn.Linear(64, 32, bias=False)
+    assert torch.equal(MXFP8Linear.from_float(ref).weight, ref.weight.bfloat16())
+    with pytest.raises(NotImplementedError):
+        MXFP8Linear.from_float(torch.nn.Linear(4, 4, bias=True))
+    nv = NVFP4Linear(64, 32)
+    assert list(nv.state_dict()) == ["weight"] and nv.scaling == "current"
+    with pytest.raises(NotImplementedError, match="jit_row_region"):
+        NVFP4Linear(8, 8, scaling="jit_row_region")
+    with pytest.raises(NotImplementedError, match="delayed"):
+        NVFP4Linear(8, 8, scaling="delayed")
+    with pytest.raises(ValueError):
+        NVFP4Linear(8, 8, scaling="per_channel")
+    # BF16 / MXFP8 / NVFP4 dynamic modules share checkpoints
+    nv.load_state_dict(layer.state_dict())
+    assert torch.equal(nv.weight, layer.weight)
+
+
+def test_functional_argument_errors_before_any_launch():
+    from rtx_b200 import mxfp8_linear, mxfp8_linear_backward, nvfp4_linear, quantize_mxfp8, quantize_nvfp4
+
+    x, w = torch.zeros(4, 32, dtype=torch.bfloat16), torch.zeros(8, 32, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        mxfp8_linear(x, w)
+    with pytest.raises(ValueError, match="K mismatch"):
+        mxfp8_linear(x, torch.zeros(8, 64, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="unknown MXFP8 backend"):
+        mxfp8_linear(x, w, backend="x")
+    with pytest.raises(ValueError, match="CUDA"):
+        quantize_mxfp8(x)
+    with pytest.raises(TypeError):
+        quantize_nvfp4(x.float())
+    with pytest.raises(NotImplementedError, match="jit_row_region"):
+        nvfp4_linear(x, w, scaling="jit_row_region")
+    with pytest.raises(ValueError, match="scaling must be"):
+        nvfp4_linear(x, w, scaling="nope")
+    assert callable(mxfp8_linear_backward)
+
+
+def test_custom_ops_dispatch_on_fake_cuda_tensors():
+    """rtx tests/test_linear_frontends.py:362-441: every op has a schema and a fake kernel."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import rtx_b200.fp4  # noqa: F401
+    import rtx_b200.fp8  # noqa: F401
+    import rtx_b200.fp8_bwd  # noqa: F401
+    from rtx_b200.configs import MXFP8BwdConfig, MXFP8PrequantConfig, NVFP4DynamicConfig
+
+    fk, bk, nk = MXFP8PrequantConfig().to_key(), MXFP8BwdConfig().to_key(), NVFP4DynamicConfig().to_key()
+    with FakeTensorMode():
+        x = torch.empty(48, 96, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(80, 96, dtype=torch.bfloat16, device="cuda")
+        g = torch.empty(48, 80, dtype=torch.bfloat16, device="cuda")
+        s = torch.empty(1, dtype=torch.float32, device="cuda")
+        ops = torch.ops.rtx
+        assert ops.mxfp8_linear_fwd(x, w, fk).shape == (48, 80)
+        assert ops.mxfp8_linear_prequant(x, w, fk).dtype is torch.bfloat16
+        assert ops.mxfp8_linear_train(x, w, fk, bk).shape == (48, 80)
+        dx, dw = ops.mxfp8_linear_bwd(g, x, w, bk)
+        assert dx.shape == x.shape and dw.shape == w.shape and dw.dtype is torch.bfloat16
+        assert ops.mxfp8_linear_bwd_packed(g, x, w, bk).numel() == 48 * 96 + 80 * 96
+        assert ops.mxfp8_linear_dx(g, w, bk).shape == (48, 96)
+        assert ops.mxfp8_linear_dw(g, x, bk).shape == (80, 96)
+        assert ops.mxfp8_linear_dw_f32(g, x, bk).dtype is torch.float32
+        q = torch.empty(80, 96, dtype=torch.uint8, device="cuda")
+        sc = torch.empty(512 * 1, dtype=torch.uint8, device="cuda")
+        assert ops.mxfp8_linear_dynamic_x_prequant_w(x, q, sc, 80, 96, "mma128", fk).shape == (48, 80)
+        assert ops.mxfp8_linear_prequantized(q, q, sc, sc, 80, 80, 96, "mma128", "mma128", fk).shape == (80, 80)
+        assert ops.nvfp4_linear_materialized_fwd(x, w, s, s, s, nk).shape == (48, 80)
+        assert ops.nvfp4_linear_materialized_train(x, w, s, s, s, nk, bk).shape == (48, 80)
+        assert ops.nvfp4_linear_block_fwd(x, w, nk).shape == (48, 80)
+        assert ops.nvfp4_linear_block_train(x, w, nk, bk).shape == (48, 80)
+        assert ops.nvfp4_linear_dynamic_x_prequant_w(x, q, sc, s, s, 80, 96, "mma128", nk).shape == (48, 80)
+        assert ops.nvfp4_linear_prequantized(q, q, sc, sc, s, 80, 80, 96, "mma128", "mma128", nk).shape == (80, 80)
+    schema = str(torch.ops.rtx.mxfp8_linear_fwd.default._schema)
+    assert "Tensor x, Tensor weight, str config_key" in schema
+
+
+def test_scale_layout_conversion_matches_the_oracle():
+    from oracle import mx_oracle as O
+    from rtx_b200.formats import scales_mma128_to_row_major, scales_row_major_to_mma128
+
+    s = (torch.arange(300 * 9) % 251).to(torch.uint8).reshape(300, 9)
+    tiles = scales_row_major_to_mma128(s, 300, 9, 3)
+    assert torch.equal(tiles.reshape(3, 3, 512), O.scales_to_mma128(s))
+    assert torch.equal(scales_mma128_to_row_major(tiles, 300, 9, 3), s)
+    # NVFP4: tiles along K padded to whole 256-value K steps (4 tiles)
+    s4 = (torch.arange(130 * 10) % 200).to(torch.uint8).reshape(130, 10)
+    tiles4 = scales_row_major_to_mma128(s4, 130, 10, 4)
+    assert tiles4.numel() == 2 * 4 * 512
+    assert torch.equal(scales_mma128_to_row_major(tiles4, 130, 10, 4), s4)
+
+
+def test_packed_tensor_containers_validate_storage():
+    from rtx_b200.formats import make_mxfp8_tensor, make_nvfp4_tensor, mxfp8_scale_layout
+
+    q = torch.zeros(8, 64, dtype=torch.uint8)
+    t = make_mxfp8_tensor(q, torch.zeros(8 * 2, dtype=torch.uint8), (2, 4, 40), "row_major")
+    assert tuple(t.shape) == (2, 4, 40) and t.qdata.shape == (2, 4, 64) and t.block_size == 32
+    assert t.scale.dtype is torch.float8_e8m0fnu and mxfp8_scale_layout(t) == "row_major"
+    with pytest.raises(ValueError, match="expected"):
+        make_mxfp8_tensor(q, torch.zeros(7, dtype=torch.uint8), (8, 40), "row_major")
+    with pytest.raises(ValueError, match="mma64"):
+        make_mxfp8_tensor(q, torch.zeros(512, dtype=torch.uint8), (8, 40), "mma64")
+    nv = make_nvfp4_tensor(torch.zeros(8, 16, dtype=torch.uint8), torch.zeros(8 * 2, dtype=torch.uint8),
+                           torch.ones(1), (8, 17), "row_major")
+    assert nv.block_size == 16 and tuple(nv.shape) == (8, 17)
+    with pytest.raises(ValueError, match="storage K"):
+        make_nvfp4_tensor(torch.zeros(8, 8, dtype=torch.uint8), torch.zeros(8, dtype=torch.uint8), torch.ones(1),
+                          (8, 17), "row_major")
+
+
+def test_autotune_adapter_and_winner_cache(tmp_path):
+    from rtx_b200 import autotune as A
+
+    adapter = A.make_mxfp8_prequant_fwd_adapter()
+    assert isinstance(adapter, A.KernelAdapter)
+    ctx = A.KernelContext("mxfp8_prequant_fwd", 8192, 28672, 4096)
+    cands = adapter.candidates(ctx)
+    assert len(cands) == 2 and all(adapter.rejection(c, ctx) is None for c in cands)
+    assert adapter.decode(adapter.encode(cands[1])) == cands[1]
+    assert A.pick(ctx, adapter, None, mode="off") == adapter.default(ctx)
+    assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == adapter.default(ctx)
+    times = {adapter.encode(cands[0]): 2.0, adapter.encode(cands[1]): 1.0}
+    calls = []
+
+    def evaluate(cfg):
+        calls.append(cfg)
+        return A.TrialOutcome("ok", median_ms=times[adapter.encode(cfg)])
+
+    best = A.pick(ctx, adapter, evaluate, mode="balanced", cache_dir=tmp_path)
+    assert best == cands[1] and len(calls) == 2
+    path = A.runtime_winner_path(ctx, tmp_path)
+    assert path.name == "m8192_n28672_k4096_hot_default_rev1.json" and path.parent.name == "b200"
+    assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == cands[1]
+    assert set(A.ADAPTERS) == set(A.FAMILIES)
+    failing = A.pick(A.KernelContext("mxfp8_prequant_fwd", 1, 1, 1), adapter,
+                     lambda c: A.TrialOutcome("failed", detail="x"), mode="balanced", cache_dir=tmp_path)
+    assert failing == adapter.default(ctx)

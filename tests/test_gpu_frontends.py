@@ -1,0 +1,219 @@
+"""The reference-facing Python API on a B200: modules, functionals, custom ops, autograd,
+packed weights — compared with the CPU oracle (same bars as test_gpu_parity.py)."""
+import pytest
+import torch
+
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev(native_lib):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    d = torch.device("cuda", 0)
+    torch.cuda.set_device(d)
+    return d
+
+
+def _close(got, want, bit_exact=False):
+    rep = O.parity_report(got.detach().cpu(), want)
+    if bit_exact:
+        assert rep["bit_equal"], rep
+    assert rep["rel_fro"] <= 1e-3 and rep["frac_le_1ulp"] >= 0.999, rep
+
+
+def _done(dev):
+    from rtx_b200 import ops
+
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)
+
+
+def test_mxfp8_linear_module_forward_backward(dev):
+    import rtx_b200 as rtx
+
+    torch.manual_seed(0)
+    layer = rtx.MXFP8Linear(160, 96, device=dev)
+    x = torch.randn(2, 3, 64, 160).bfloat16().to(dev).requires_grad_(True)   # leading dims are flattened
+    y = layer(x)
+    assert y.shape == (2, 3, 64, 96) and y.dtype is torch.bfloat16
+    w_cpu, x_cpu = layer.weight.detach().cpu(), x.detach().cpu()
+    _close(y, O.mxfp8_linear(x_cpu, w_cpu))
+    g = (torch.randn(2, 3, 64, 96) * 0.1).bfloat16().to(dev)
+    y.backward(g)
+    _done(dev)
+    dx, dw = O.mxfp8_backward(x_cpu.reshape(-1, 160), w_cpu, g.cpu().reshape(-1, 96), dw_dtype=torch.float32)
+    _close(x.grad.reshape(-1, 160), dx)
+    _close(layer.weight.grad, dw.bfloat16())
+    assert x.grad.dtype is torch.bfloat16 and layer.weight.grad.dtype is torch.bfloat16
+    # no_grad path takes the inference op and gives the same bits
+    with torch.no_grad():
+        assert torch.equal(layer(x), y)
+
+
+def test_only_one_gradient_requested(dev):
+    import rtx_b200 as rtx
+
+    torch.manual_seed(1)
+    w = (torch.randn(64, 128) / 11).bfloat16().to(dev)
+    x = torch.randn(96, 128).bfloat16().to(dev).requires_grad_(True)
+    rtx.mxfp8_linear(x, w).sum().backward()
+    _done(dev)
+    g = torch.ones(96, 64).bfloat16()
+    dx, _ = O.mxfp8_backward(x.detach().cpu(), w.cpu(), g)
+    _close(x.grad, dx)
+
+
+def test_mxfp8_packed_weight_states_are_bit_identical(dev):
+    """rtx tests/test_mxfp8_quant.py:467-546: dynamic, weight-prequantized and fully-prequantized
+    operands give the same bits, including a ragged shape with storage K = 64."""
+    import rtx_b200 as rtx
+
+    for (m, n, k) in ((128, 128, 256), (17, 29, 33)):
+        torch.manual_seed(1702)
+        x = torch.randn(m, k).bfloat16().to(dev)
+        layer = rtx.MXFP8Linear(k, n, device=dev)
+        y_dyn = layer(x)
+        packed_layer = layer.to_quantized_weight()
+        assert sorted(packed_layer.state_dict()) == ["weight_data", "weight_packing_meta", "weight_scales"]
+        meta = packed_layer.weight_packing_meta.tolist()
+        assert meta == [3, 2, k, (k + 31) // 32 * 32]
+        y_wq = packed_layer(x)
+        y_full = rtx.mxfp8_linear(rtx.quantize_mxfp8(x), packed_layer.packed_weight())
+        _done(dev)
+        assert torch.equal(y_dyn, y_wq) and torch.equal(y_dyn, y_full)
+        # row-major scales from an interchange checkpoint are re-tiled on the fly
+        from rtx_b200.configs import MXFP8QuantConfig
+
+        rm = rtx.quantize_mxfp8(layer.weight.detach(), config=MXFP8QuantConfig(scale_layout="row_major"))
+        assert torch.equal(rtx.mxfp8_linear(x, rm), y_dyn)
+        with pytest.raises(TypeError, match="cannot be cast"):
+            packed_layer.to(torch.float16)
+        with pytest.raises(RuntimeError, match="inference-only"):
+            packed_layer(x.clone().requires_grad_(True))
+
+
+def test_quantize_mxfp8_tensor_matches_oracle(dev):
+    import rtx_b200 as rtx
+    from rtx_b200.configs import MXFP8QuantConfig
+
+    torch.manual_seed(3)
+    x = torch.randn(4, 40, 100).bfloat16()
+    t = rtx.quantize_mxfp8(x.to(dev), config=MXFP8QuantConfig(scale_layout="row_major"))
+    _done(dev)
+    qo, so = O.mxfp8_quantize(x.reshape(-1, 100))
+    assert tuple(t.shape) == (4, 40, 100)
+    assert torch.equal(t.qdata.reshape(-1, 128).view(torch.uint8).cpu(), qo)
+    assert torch.equal(t.scale.reshape(-1, 4).view(torch.uint8).cpu(), so)
+    want = O.mxfp8_dequantize(qo, so)[:, :100].reshape(4, 40, 100)
+    assert torch.equal(t.dequantize(torch.float32).cpu(), want)
+
+
+def test_mxfp8_linear_backward_functional_and_packed_op(dev):
+    import rtx_b200 as rtx
+    from rtx_b200.fp8_bwd import unpack_bwd
+
+    inp = O.make_inputs(4, m=256, n=128, k=192)
+    x, w, dy = (inp[k].to(dev) for k in ("x", "w", "dy"))
+    dx, dw = rtx.mxfp8_linear_backward(dy.reshape(2, 128, 128), x.reshape(2, 128, 192), w)
+    flat = torch.ops.rtx.mxfp8_linear_bwd_packed(dy, x, w, rtx.MXFP8BwdConfig().to_key())
+    _done(dev)
+    dxo, dwo = O.mxfp8_backward(inp["x"], inp["w"], inp["dy"], dw_dtype=torch.float32)
+    assert dx.shape == (2, 128, 192)
+    _close(dx.reshape(-1, 192), dxo)
+    _close(dw, dwo.bfloat16())
+    dx2, dw2 = unpack_bwd(flat, (256, 192), (128, 192))
+    assert torch.equal(dx2, dx.reshape(-1, 192)) and torch.equal(dw2, dw)
+
+
+def test_nvfp4_linear_module_and_packed_weight(dev):
+    import rtx_b200 as rtx
+
+    torch.manual_seed(1905)
+    layer = rtx.NVFP4Linear(256, 192, device=dev)
+    x = torch.randn(3, 50, 256).bfloat16().to(dev).requires_grad_(True)
+    y = layer(x)
+    w_cpu, x_cpu = layer.weight.detach().cpu(), x.detach().cpu()
+    _close(y, O.nvfp4_linear(x_cpu, w_cpu, mode="power2"))
+    g = (torch.randn(3, 50, 192) * 0.1).bfloat16().to(dev)
+    y.backward(g)
+    _done(dev)
+    dx, dw = O.mxfp8_backward(x_cpu.reshape(-1, 256), w_cpu, g.cpu().reshape(-1, 192), dw_dtype=torch.float32)
+    _close(x.grad.reshape(-1, 256), dx)          # NVFP4 forward, MXFP8 backward
+    _close(layer.weight.grad, dw.bfloat16())
+    # block policy: outer scales are 1
+    blk = rtx.NVFP4Linear(256, 192, device=dev, scaling="block")
+    with torch.no_grad():
+        blk.weight.copy_(layer.weight)
+        yb = blk(x.detach())
+    one = torch.ones(1)
+    _close(yb, O.nvfp4_linear(x_cpu, w_cpu, x_scale=one, w_scale=one))
+    # packed weight: exact outer scales for both operands (rtx/fp4.py:3421-3446)
+    packed = layer.to_quantized_weight()
+    assert sorted(packed.state_dict()) == ["weight_block_scales", "weight_data", "weight_packing_meta",
+                                           "weight_tensor_scale"]
+    with torch.no_grad():
+        yp = packed(x.detach())
+    _done(dev)
+    x2 = x_cpu.reshape(-1, 256)
+    want = O.nvfp4_linear(x2, w_cpu, x_scale=O.nvfp4_tensor_scale(x2, "exact"), w_scale=O.nvfp4_tensor_scale(w_cpu, "exact"))
+    _close(yp.reshape(-1, 192), want)
+    t = rtx.quantize_nvfp4(layer.weight.detach())
+    qo, so = O.nvfp4_quantize(w_cpu, O.nvfp4_tensor_scale(w_cpu, "exact"))
+    assert torch.equal(t.qdata.view(torch.uint8).cpu().reshape(192, 128), qo)
+
+
+def test_glu_mlp_functional(dev):
+    import rtx_b200 as rtx
+
+    inp = O.make_inputs(2, m=192, k=256, inter=384)
+    x, wgu, wd = inp["x"], inp["w_gate_up"], inp["w_down"]
+    y, h = rtx.mxfp8_glu_mlp(x.to(dev).reshape(3, 64, 256), wgu.to(dev), wd.to(dev), return_hidden=True)
+    _done(dev)
+    ho, _ = O.mxfp8_glu_mlp(x, wgu, wd)
+    _close(h.reshape(-1, 384), ho)
+    _close(y.reshape(-1, 256), O.mxfp8_linear(h.reshape(-1, 384).cpu(), wd))
+    # a width the fused epilogue cannot pair takes the unfused composition
+    inp = O.make_inputs(2, m=64, k=128, inter=96)
+    y2 = rtx.mxfp8_glu_mlp(inp["x"].to(dev), inp["w_gate_up"].to(dev), inp["w_down"].to(dev))
+    _done(dev)
+    _, yo = O.mxfp8_glu_mlp(inp["x"], inp["w_gate_up"], inp["w_down"], fused_rounding=False)
+    rep = O.parity_report(y2.cpu(), yo)
+    assert rep["rel_fro"] < 2e-2, rep
+
+
+def test_data_parallel_backward_single_rank(dev):
+    import rtx_b200 as rtx
+
+    inp = O.make_inputs(4, m=256, n=128, k=128)
+    x, w, dy = (inp[k].to(dev) for k in ("x", "w", "dy"))
+    dx, dw = rtx.data_parallel_linear_backward(dy, x, w)
+    dx1, dw1 = rtx.mxfp8_linear_backward(dy, x, w)
+    _done(dev)
+    assert torch.equal(dx, dx1) and torch.equal(dw, dw1)   # FP32 -> BF16 once either way
+
+
+def test_torch_compile_fullgraph_matches_eager(dev):
+    """rtx tests/test_mxfp8_bwd.py:520-589: a compiled stack equals eager bit for bit."""
+    import rtx_b200 as rtx
+
+    torch.manual_seed(7)
+    model = torch.nn.Sequential(rtx.MXFP8Linear(128, 256, device=dev), torch.nn.GELU(),
+                                rtx.NVFP4Linear(256, 128, device=dev))
+    x = torch.randn(64, 128).bfloat16().to(dev)
+    with torch.no_grad():
+        eager = model(x)
+        compiled = torch.compile(model, fullgraph=True, dynamic=False)(x)
+    _done(dev)
+    assert torch.equal(eager, compiled)
+
+
+def test_runtime_caches_clear(dev):
+    import rtx_b200 as rtx
+
+    rtx.mxfp8_linear(torch.zeros(32, 32, dtype=torch.bfloat16, device=dev), torch.zeros(32, 32, dtype=torch.bfloat16, device=dev))
+    released = rtx.clear_runtime_caches()
+    assert released["fp8"]["workspaces"]["entries"] >= 1
+    assert rtx.validate_runtime_environment(require_device=True)["capability"][0] == 10
