@@ -46,60 +46,74 @@ def measured_peaks() -> dict:
 
 
 class ClockSampler:
-    """Polls SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Samples SM clock, power and throttle reasons with `nvidia-smi -lms` (read-only) in a child process
+    while the timed loops run; samples are kept only if their timestamp falls inside a marked region."""
 
-    def __init__(self, index: int, period_s: float = 0.01):
-        self.index, self.period = index, period_s
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int, period_ms: int = 10):
+        self.index, self.period_ms = index, period_ms
+        self.proc, self.path, self.regions = None, None, []
 
     def start(self):
+        import subprocess
+        import tempfile
+
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
         try:
-            import pynvml
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", str(self.period_ms), "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+            time.sleep(0.3)   # let it print its first lines before the timed loops start
+        except OSError:
+            self.proc = None
 
-            pynvml.nvmlInit()
-            self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
-        except Exception:
-            self._nv = None
-            return
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        self._thread.start()
-
-    def _run(self):
-        nv = self._nv
-        names = {
-            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
-            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
-            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
-            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
-                try:
-                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
-                except Exception:
-                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
-                for bit, name in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(self.period)
+    def mark(self, t0: float, t1: float):
+        self.regions.append((t0, t1))
 
     def stop(self) -> dict:
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join(timeout=1.0)
-        return {
-            "sm_mhz": statistics.median(self.samples) if self.samples else None,
-            "sm_max_mhz": self.max_mhz,
-            "reasons": sorted(self.reasons),
-            "samples": len(self.samples),
-        }
+        import datetime
+
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        clocks, powers, reasons, max_mhz, total = [], [], set(), None, 0
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        try:
+            lines = open(self.path).read().splitlines()
+            os.unlink(self.path)
+        except OSError:
+            lines = []
+        for line in lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                mhz, mx, watts = float(parts[1]), float(parts[2]), float(parts[3])
+            except ValueError:
+                continue
+            total += 1
+            max_mhz = mx
+            if not any(t0 - 0.005 <= ts <= t1 + 0.005 for t0, t1 in self.regions):
+                continue
+            clocks.append(mhz)
+            powers.append(watts)
+            for name, flag in zip(names, parts[4:8]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_mhz,
+                "power_w": statistics.median(powers) if powers else None, "reasons": sorted(reasons),
+                "samples": len(clocks), "samples_total": total,
+                "regions": "timed steps, end-to-end steps and the dominant-kernel loop"}
 
 
 def physical_gpu_index(local_rank: int) -> int:
@@ -204,14 +218,13 @@ def run_own_arm(args) -> None:
     wd = inp["w_down"].to(dev)
     del inp
     m_local = per
-    h = torch.empty(m_local, INTER, dtype=torch.bfloat16, device=dev)
     y = torch.empty(m_local, N_OUT, dtype=torch.bfloat16, device=dev)
     y_host = torch.empty(m_local, N_OUT, dtype=torch.bfloat16).pin_memory()
     ws = ops.Workspace(dev)
-    launches_per_step = 6  # quantize X, W_gate_up, W_down, H + two GEMMs
+    launches_per_step = 5  # quantize X, W_gate_up, W_down + gate/up GEMM (SiLU*up and H quantization fused) + down GEMM
 
     def step():
-        ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, h, y)
+        ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, None, y, want_hidden=False)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -223,45 +236,54 @@ def run_own_arm(args) -> None:
     barrier()
     torch.cuda.synchronize()
     sampler.start()
+    torch.cuda.synchronize()
+    w0 = time.time()
     ev0.record()
     for _ in range(args.steps):
         step()
     ev1.record()
     torch.cuda.synchronize()
+    sampler.mark(w0, time.time())
     barrier()
-    clocks = sampler.stop()
     ms_total = ev0.elapsed_time(ev1)
     ops.check_device_status(dev)
 
-    # end to end through host buffers: H2D of the step's X from pinned memory, the MLP, D2H of Y
-    def e2e_step():
-        x.copy_(x_host, non_blocking=True)
-        ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, h, y)
-        y_host.copy_(y, non_blocking=True)
+    # end to end through host buffers (rtx_b200.host.GluMlpHostSession): every step copies that step's X
+    # from pinned host memory to the device and its Y back to pinned host memory; copy-in of step i+1 and
+    # copy-out of step i-1 overlap the compute of step i (three streams, two buffer sets)
+    from rtx_b200.host import GluMlpHostSession
 
-    for _ in range(2):
-        e2e_step()
+    session = GluMlpHostSession(wgu, wd, m_local)
+    x_hosts = [x_host, x_host.clone().pin_memory()]
+    y_hosts = [y_host, torch.empty_like(y_host).pin_memory()]
+    for i in range(3):
+        session.submit(x_hosts[i % 2], y_hosts[i % 2])
+    session.drain()
     barrier()
     torch.cuda.synchronize()
-    ev0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    ev1.record()
-    torch.cuda.synchronize()
+    w0 = time.time()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        session.submit(x_hosts[i % 2], y_hosts[i % 2])
+    session.drain()
+    e2e_ms_total = (time.perf_counter() - t0) * 1e3   # spans three streams: host clock around submit..drain
+    sampler.mark(w0, time.time())
     barrier()
-    e2e_ms_total = ev0.elapsed_time(ev1)
 
     # dominant kernel alone: the gate/up GEMM with the fused SwiGLU epilogue
     qx, sx = ops.mxfp8_quantize(x)
     qg, sg = ops.mxfp8_quantize(wgu)
     for _ in range(3):
-        ops.mxfp8_gemm_glu(qx, sx, qg, sg, m_local, INTER, K, out=h)
+        ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, m_local, INTER, K)
     torch.cuda.synchronize()
+    w0 = time.time()
     ev0.record()
     for _ in range(args.steps):
-        ops.mxfp8_gemm_glu(qx, sx, qg, sg, m_local, INTER, K, out=h)
+        ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, m_local, INTER, K)
     ev1.record()
     torch.cuda.synchronize()
+    sampler.mark(w0, time.time())
+    clocks = sampler.stop()
     gemm_ms = ev0.elapsed_time(ev1) / args.steps
     ops.check_device_status(dev)
 
@@ -289,15 +311,17 @@ def run_own_arm(args) -> None:
             "data": "synthetic",
             "config": {"workload": f"mxfp8_glu_mlp_fwd_m{M}_k{K}_i{INTER}", "m_per_gpu": m_local, "k": K,
                        "inter": INTER, "n_out": N_OUT, "parallelism": f"dp{world} (token rows sharded, weights replicated)",
-                       "l2": "inputs exceed L2 (X 67 MB + weights 352 MB bf16 re-read every step)"},
+                       "l2": "inputs exceed L2 (X 67 MB + weights 352 MB bf16 re-read every step)",
+                       "hidden": "H leaves the gate/up epilogue already MXFP8-encoded; no BF16 H is materialized"},
             "tflops_per_gpu": value / world,
             "pct_of_nominal_fp8_peak": 100.0 * value / world / NOMINAL_FP8_TFLOPS,
             "pct_of_measured_fp8_proxy": 100.0 * value / world / fp8_peak,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2 * world,
-                    "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": e2e_ms_total / args.steps},
+                    "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": e2e_ms_total / args.steps,
+                    "api": "rtx_b200.host.GluMlpHostSession.submit/drain (copies overlapped with compute)"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
-            "roofline": {"kernel": "gemm_blockscaled_kernel<mxfp8, glu> (gate/up GEMM + SiLU*up)", "bound": "tensor",
+            "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, glu_mx> (gate/up GEMM + SiLU*up + MXFP8 encode of H)", "bound": "tensor",
                          "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
                          "traffic": traffic, "ms_per_launch": gemm_ms,
                          "peak_note": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s) as the "
@@ -305,12 +329,12 @@ def run_own_arm(args) -> None:
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            m_s = 1024
-            times, flops = cpu_sample_run(m_s, INTER, threads, 1, 0)
+            m_s = M
+            times, flops = cpu_sample_run(m_s, INTER, threads, 3, 1)
             line["cpu_baseline"] = {
-                "value": flops / times[0] / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                "sample": f"one run of the CPU path on X[:{m_s}] of {M} rows with the full weights "
-                          f"({flops:.3e} flop, {times[0]:.1f} s)"}
+                "value": flops * len(times) / sum(times) / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"{len(times)} runs (after 1 warm-up) of the reference CPU path on the whole workload: "
+                          f"X {m_s} rows, full weights, {flops:.3e} flop per run, {sum(times):.1f} s in total"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -94,6 +94,13 @@ int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* 
 int rtxb_mxfp8_gemm_glu(const void* qa, const void* sa, const void* qb, const void* sb, void* out_bf16, int64_t m,
                         int64_t inter, int64_t k, int64_t ldo, void* stream, int* status);
 
+/* The same GEMM whose epilogue also quantizes H for the next projection: q_h e4m3 [m, inter] and
+ * s_h (E8M0, mma128 tiles) are bit-identical to rtxb_mxfp8_quantize applied to the BF16 H (each
+ * 32-column group a thread holds is one MX block).  h_bf16 may be NULL when only the packed H is
+ * needed; that removes a BF16 write and read of H and one quantizer launch from the MLP. */
+int rtxb_mxfp8_gemm_glu_mx(const void* qa, const void* sa, const void* qb, const void* sb, void* h_bf16, void* q_h,
+                           void* s_h, int64_t m, int64_t inter, int64_t k, int64_t ldo, void* stream, int* status);
+
 /* ---- fused forward (quantize both operands + GEMM) ------------------------
  * compile_mxfp8_fwd(problem, cfg) -> (x bf16, w bf16, out bf16[M,N])
  *   rtx/kernels/mxfp8_fwd.py:2963-3029; bound at rtx/fp8.py:560, :581, :635.
@@ -129,7 +136,8 @@ int rtxb_mxfp8_linear_fwd_noalloc(const void* x_bf16, const void* w_bf16, void* 
 
 /* SwiGLU MLP forward: H = silu(X Wg^T) * (X Wu^T), Y = H Wd^T, every GEMM
  * operand MXFP8-quantized along its K.  w_gate_up bf16 [2*inter, k], w_down
- * bf16 [n_out, inter]; h_bf16 [m, inter] and y_bf16 [m, n_out] are outputs. */
+ * bf16 [n_out, inter]; y_bf16 [m, n_out] is the output; h_bf16 [m, inter] is an optional output
+ * (NULL: H only ever exists in its MXFP8 form, written by the gate/up epilogue). */
 size_t rtxb_mxfp8_glu_mlp_workspace_bytes(int64_t m, int64_t k, int64_t inter, int64_t n_out);
 int rtxb_mxfp8_glu_mlp_fwd(const void* x_bf16, const void* w_gate_up_bf16, const void* w_down_bf16, void* h_bf16,
                            void* y_bf16, int64_t m, int64_t k, int64_t inter, int64_t n_out, void* workspace,

@@ -119,7 +119,8 @@ bool use_pair_kernel(int m_tiles) {
 template <int KIND, int EPI>
 int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
                 int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
-                const float* out_scale, cudaStream_t stream, int* status) {
+                const float* out_scale, cudaStream_t stream, int* status, void* q_out = nullptr,
+                void* sf_out = nullptr) {
   using T = GemmTraits<KIND>;
   CUtensorMap map_a, map_b;
   int rc = make_payload_map(&map_a, qa, m, row_bytes, 128);
@@ -141,6 +142,9 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.out_cols = static_cast<int>(out_cols);
   p.out_vec_ok = (aligned(out, 16) && (ldo * (EPI == kEpiF32 ? 4 : 2)) % 16 == 0) ? 1 : 0;
   p.out_scale = out_scale;
+  p.q_out = static_cast<uint8_t*>(q_out);
+  p.sf_out = static_cast<uint8_t*>(sf_out);
+  p.sf_out_chunks = static_cast<int>((out_cols / 32 + 3) / 4);
   p.status = status;
   {
     const char* dbg = getenv("RTXB_GEMM_DEBUG");
@@ -323,6 +327,20 @@ int rtxb_mxfp8_gemm_glu(const void* qa, const void* sa, const void* qb, const vo
                                               static_cast<cudaStream_t>(stream), status);
 }
 
+int rtxb_mxfp8_gemm_glu_mx(const void* qa, const void* sa, const void* qb, const void* sb, void* h_bf16, void* q_h,
+                           void* s_h, int64_t m, int64_t inter, int64_t k, int64_t ldo, void* stream, int* status) {
+  if (!q_h || !s_h) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null packed output");
+  int rc = check_gemm_args(qa, sa, qb, sb, q_h, m, 2 * inter, k, h_bf16 ? ldo : inter, inter, 1);
+  if (rc) return rc;
+  if (inter % 128 != 0) return fail_msg(RTXB_E_UNSUPPORTED, "fused GLU epilogue needs inter % 128 == 0");
+  if (!aligned(q_h, 16) || !aligned(s_h, 16)) return fail_msg(RTXB_E_ALIGNMENT, "packed outputs must be 16-byte aligned");
+  if (h_bf16 && !aligned(h_bf16, 2)) return fail_msg(RTXB_E_ALIGNMENT, "output pointer is not element aligned");
+  const int64_t kp = round_up(k, 32);
+  const int64_t chunks = (kp / 32 + 3) / 4;
+  return launch_gemm<kKindMxfp8, kEpiGluMx>(qa, sa, qb, sb, h_bf16, m, 2 * inter, kp, chunks, h_bf16 ? ldo : inter, inter,
+                                            inter, nullptr, static_cast<cudaStream_t>(stream), status, q_h, s_h);
+}
+
 size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k) {
   Carver c(nullptr);
   const int64_t kp = round_up(k, 32);
@@ -387,8 +405,9 @@ int rtxb_mxfp8_glu_mlp_fwd(const void* x, const void* w_gu, const void* w_down, 
   if ((rc = rtxb_mxfp8_quantize(w_gu, 2 * inter, k, k, qg, sg, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
   if ((rc = rtxb_mxfp8_quantize(w_down, n_out, inter, inter, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
     return rc;
-  if ((rc = rtxb_mxfp8_gemm_glu(qx, sx, qg, sg, h, m, inter, k, inter, stream, status))) return rc;
-  if ((rc = rtxb_mxfp8_quantize(h, m, inter, inter, qh, sh, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+  // gate/up GEMM whose epilogue applies SiLU*up and writes H already quantized for the down projection
+  // (and in BF16 too when the caller wants it)
+  if ((rc = rtxb_mxfp8_gemm_glu_mx(qx, sx, qg, sg, h, qh, sh, m, inter, k, inter, stream, status))) return rc;
   return rtxb_mxfp8_gemm(qh, sh, qd, sd, y, m, n_out, inter, n_out, RTXB_OUT_BF16, stream, status);
 }
 

@@ -33,8 +33,10 @@ enum GemmKind : int { kKindMxfp8 = 0, kKindNvfp4 = 1 };
 enum GemmEpilogue : int {
   kEpiBf16 = 0,   // D bf16 = acc * out_scale
   kEpiF32 = 1,    // D f32  = acc * out_scale
-  kEpiGluBf16 = 2 // D bf16[M, N/2] = silu(acc[:, gate]) * acc[:, up]
+  kEpiGluBf16 = 2, // D bf16[M, N/2] = silu(acc[:, gate]) * acc[:, up]
+  kEpiGluMx = 3    // the same H, also (or only) emitted as MXFP8: E4M3 payload + E8M0 scale tiles
 };
+__host__ __device__ constexpr bool epi_is_glu(int epi) { return epi == kEpiGluBf16 || epi == kEpiGluMx; }
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
@@ -106,6 +108,9 @@ struct GemmParams {
   int out_cols;           // n, or inter for GLU
   int out_vec_ok;         // 1 when out and its row pitch are 16-byte aligned (vector stores allowed)
   const float* out_scale; // device scalar or nullptr (= 1)
+  uint8_t* q_out;         // kEpiGluMx: E4M3 payload of H, [M, out_cols] (out may then be nullptr)
+  uint8_t* sf_out;        // kEpiGluMx: E8M0 scales of H in 128-row tiles, sf_out_chunks tiles per row block
+  int sf_out_chunks;
   int* status;            // device status word or nullptr
   int debug;              // experiments only (results invalid when set): bit0 = copy scale factors on the
                           // first K step only, bit1 = stop loading once the ring is filled,
@@ -132,14 +137,15 @@ template <int KIND, int EPI>
 __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tacc, int row, bool row_ok, int n_idx,
                                                bool odd, uint32_t overlap_bar_addr, float out_scale, int lane) {
   using TP = TmemPlan<KIND>;
-  if (EPI == kEpiGluBf16) {
+  if (epi_is_glu(EPI)) {
     // accumulator columns [0,128) = gate, [128,256) = up of the same 128 output columns; pairs of
     // 32-column groups (gate c, up 128+c).  Shared columns: up group 96 (even window) or gate
     // group 0 (odd window) -- the first pair visited holds them.
-    static_assert(EPI != kEpiGluBf16 || TP::kOverlapChunks == 1, "GLU epilogue assumes a 32-column overlap");
+    static_assert(!epi_is_glu(EPI) || TP::kOverlapChunks == 1, "GLU epilogue assumes a 32-column overlap");
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
     const int col0 = n_idx * 128;
     const int c_first = odd ? 0 : 96;
+    uint32_t scale_word = 0;  // kEpiGluMx: the four E8M0 codes of this row's blocks col0/32 .. col0/32+3
 #pragma unroll 1
     for (int i = 0; i < 4; ++i) {
       const int c = (c_first + 32 * i) & 127;
@@ -153,18 +159,46 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
         if (lane == 0) mbar_arrive_cluster(overlap_bar_addr);
       }
       if (!row_ok) continue;
+      // H in BF16 (one rounding of the FP32 result), packed two per word
+      uint32_t hw[16];
 #pragma unroll
-      for (int v = 0; v < 32; v += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 b = __floats2bfloat162_rn(
-              silu_mul(__uint_as_float(g[v + 2 * e]), __uint_as_float(u[v + 2 * e])),
-              silu_mul(__uint_as_float(g[v + 2 * e + 1]), __uint_as_float(u[v + 2 * e + 1])));
-          w[e] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        store_bf16x8(out, col0 + c + v, p.out_cols, p.out_vec_ok != 0, w);
+      for (int e = 0; e < 16; ++e) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(silu_mul(__uint_as_float(g[2 * e]), __uint_as_float(u[2 * e])),
+                                                 silu_mul(__uint_as_float(g[2 * e + 1]), __uint_as_float(u[2 * e + 1])));
+        hw[e] = *reinterpret_cast<uint32_t*>(&b);
       }
+      if (EPI == kEpiGluBf16 || p.out != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint32_t w[4] = {hw[4 * v], hw[4 * v + 1], hw[4 * v + 2], hw[4 * v + 3]};
+          store_bf16x8(out, col0 + c + 8 * v, p.out_cols, p.out_vec_ok != 0, w);
+        }
+      }
+      if (EPI == kEpiGluMx) {
+        // these 32 columns are exactly one MX block of H's row: quantize the BF16 values as the
+        // row quantizer would (same scale rule, same converter)
+        float a = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) a = fmax_nan(a, fmax_nan(fabsf(bf16_lo(hw[e])), fabsf(bf16_hi(hw[e]))));
+        const uint32_t code = e8m0_from_amax(a, true);
+        const float recip = e8m0_reciprocal(code);
+        scale_word |= code << (8 * (c >> 5));
+        uint32_t q[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          q[e] = cvt_e4m3x2(bf16_lo(hw[2 * e]) * recip, bf16_hi(hw[2 * e]) * recip) |
+                 (cvt_e4m3x2(bf16_lo(hw[2 * e + 1]) * recip, bf16_hi(hw[2 * e + 1]) * recip) << 16);
+        uint4* dst = reinterpret_cast<uint4*>(p.q_out + static_cast<int64_t>(row) * p.out_cols + col0 + c);
+        dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+        dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+      }
+    }
+    if (EPI == kEpiGluMx) {
+      // rows past M inside the last 128-row tile get zero scales (their payload is never read as non-zero)
+      const int tile_row = row & 127;
+      uint8_t* tile = p.sf_out + (static_cast<size_t>(row >> 7) * p.sf_out_chunks + n_idx) * 512;
+      if ((row >> 7) < p.m_tiles)
+        *reinterpret_cast<uint32_t*>(tile + (tile_row & 31) * 16 + (tile_row >> 5) * 4) = row_ok ? scale_word : 0u;
     }
   } else {
     const int shared0 = odd ? 0 : TP::kAccWindow1;  // local column where the shared columns start
@@ -390,7 +424,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int m0 = m_idx * kBlockM;
         // rows of B feeding accumulator columns [0,128) and [128,256)
         int b_row0, b_row1;
-        if (EPI == kEpiGluBf16) {
+        if (epi_is_glu(EPI)) {
           b_row0 = n_idx * 128;
           b_row1 = p.glu_inter + n_idx * 128;
         } else {
@@ -576,7 +610,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
         const int mp_idx = tile % m_pairs, n_idx = tile / m_pairs;
         const int m_blk = mp_idx * 2 + static_cast<int>(rank);   // 128-row block of A this CTA owns
         int b_blk0, b_blk1;                                      // 128-row blocks of B behind columns [0,128), [128,256)
-        if (EPI == kEpiGluBf16) {
+        if (epi_is_glu(EPI)) {
           b_blk0 = n_idx;
           b_blk1 = (p.glu_inter >> 7) + n_idx;
         } else {

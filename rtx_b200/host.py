@@ -1,0 +1,71 @@
+"""Host-buffer entry point for the SwiGLU MLP: the call a user with activations in
+host memory makes.  Each `submit` copies X from pinned host memory to the device,
+runs the MXFP8 MLP (quantize, gate/up GEMM with fused SiLU*up, quantize, down GEMM)
+and copies Y back to pinned host memory.  Three streams and two device buffer sets
+let the copy-in of step i+1 and the copy-out of step i-1 overlap the compute of
+step i; `drain()` waits for everything submitted.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import ops
+
+
+class GluMlpHostSession:
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, max_rows: int, depth: int = 2):
+        if w_gate_up.device.type != "cuda":
+            raise ValueError("weights must already be resident on the GPU")
+        self.device = w_gate_up.device
+        self.w_gate_up, self.w_down = w_gate_up.contiguous(), w_down.contiguous()
+        self.k = w_gate_up.shape[1]
+        self.inter = w_gate_up.shape[0] // 2
+        self.n_out = w_down.shape[0]
+        self.max_rows = max_rows
+        self.depth = depth
+        with torch.cuda.device(self.device):
+            self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream() for _ in range(3))
+        self.x = [torch.empty(max_rows, self.k, dtype=torch.bfloat16, device=self.device) for _ in range(depth)]
+        self.y = [torch.empty(max_rows, self.n_out, dtype=torch.bfloat16, device=self.device) for _ in range(depth)]
+        self.ws = ops.Workspace(self.device)
+        self._in_done: List[Optional[torch.cuda.Event]] = [None] * depth
+        self._compute_done: List[Optional[torch.cuda.Event]] = [None] * depth
+        self._out_done: List[Optional[torch.cuda.Event]] = [None] * depth
+        self._step = 0
+
+    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """Enqueue one MLP forward; `x_host` / `y_host` must be pinned and stay alive until `drain()`."""
+        if not (x_host.is_pinned() and y_host.is_pinned()):
+            raise ValueError("host buffers must be pinned for asynchronous copies")
+        m = x_host.shape[0]
+        if m > self.max_rows or x_host.shape[1] != self.k:
+            raise ValueError("activation shape does not fit this session")
+        b = self._step % self.depth
+        with torch.cuda.device(self.device):
+            # the buffer set is free once its previous occupant has been copied out
+            if self._out_done[b] is not None:
+                self.copy_in.wait_event(self._out_done[b])
+            with torch.cuda.stream(self.copy_in):
+                self.x[b][:m].copy_(x_host, non_blocking=True)
+                self._in_done[b] = torch.cuda.Event()
+                self._in_done[b].record(self.copy_in)
+            self.compute.wait_event(self._in_done[b])
+            with torch.cuda.stream(self.compute):
+                ops.mxfp8_glu_mlp_fwd(self.x[b][:m], self.w_gate_up, self.w_down, self.ws, None, self.y[b][:m],
+                                      want_hidden=False)
+                self._compute_done[b] = torch.cuda.Event()
+                self._compute_done[b].record(self.compute)
+            self.copy_out.wait_event(self._compute_done[b])
+            with torch.cuda.stream(self.copy_out):
+                y_host.copy_(self.y[b][:m], non_blocking=True)
+                self._out_done[b] = torch.cuda.Event()
+                self._out_done[b].record(self.copy_out)
+        self._step += 1
+
+    def drain(self) -> None:
+        for s in (self.copy_in, self.compute, self.copy_out):
+            s.synchronize()
+        ops.check_device_status(self.device)

@@ -156,8 +156,21 @@ def mxfp8_linear_fwd(x: torch.Tensor, w: torch.Tensor, ws: Workspace, out: Optio
     return out
 
 
+def mxfp8_gemm_glu_mx(qa, sa, qb, sb, m: int, inter: int, k: int, *, want_bf16: bool = False):
+    """GLU GEMM whose epilogue emits H as MXFP8: returns (q_h u8 [m, inter], s_h u8 tiles, h bf16 | None)."""
+    q = torch.empty(m, inter, dtype=torch.uint8, device=qa.device)
+    s = torch.empty(mxfp8_scale_numel(m, inter, N.SCALE_MMA128), dtype=torch.uint8, device=qa.device)
+    h = torch.empty(m, inter, dtype=torch.bfloat16, device=qa.device) if want_bf16 else None
+    with torch.cuda.device(qa.device):
+        N.call("rtxb_mxfp8_gemm_glu_mx", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(),
+               h.data_ptr() if want_bf16 else None, q.data_ptr(), s.data_ptr(), m, inter, k, inter, _stream_ptr(),
+               status_word(qa.device).data_ptr())
+    return q, s, h
+
+
 def mxfp8_glu_mlp_fwd(x, w_gate_up, w_down, ws: Workspace, h: Optional[torch.Tensor] = None,
-                      y: Optional[torch.Tensor] = None):
+                      y: Optional[torch.Tensor] = None, want_hidden: bool = True):
+    """want_hidden=False: H is never materialized in BF16 (returned as None)."""
     _require(x, torch.bfloat16, "x")
     _require(w_gate_up, torch.bfloat16, "w_gate_up")
     _require(w_down, torch.bfloat16, "w_down")
@@ -166,15 +179,15 @@ def mxfp8_glu_mlp_fwd(x, w_gate_up, w_down, ws: Workspace, h: Optional[torch.Ten
     n_out = w_down.shape[0]
     if w_gate_up.shape[1] != k or w_down.shape[1] != inter:
         raise ValueError("weight shapes do not chain")
-    if h is None:
+    if h is None and want_hidden:
         h = torch.empty(m, inter, dtype=torch.bfloat16, device=x.device)
     if y is None:
         y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x.device)
     nbytes = N.query("rtxb_mxfp8_glu_mlp_workspace_bytes", m, k, inter, n_out)
     buf = ws.get(nbytes)
     with torch.cuda.device(x.device):
-        N.call("rtxb_mxfp8_glu_mlp_fwd", x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), h.data_ptr(),
-               y.data_ptr(), m, k, inter, n_out, buf.data_ptr(), buf.numel(), _stream_ptr(),
+        N.call("rtxb_mxfp8_glu_mlp_fwd", x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(),
+               h.data_ptr() if h is not None else None, y.data_ptr(), m, k, inter, n_out, buf.data_ptr(), buf.numel(), _stream_ptr(),
                status_word(x.device).data_ptr())
     return h, y
 

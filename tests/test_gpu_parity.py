@@ -234,6 +234,34 @@ def test_mxfp8_glu_mlp(gpu, dims):
     assert rep["rel_fro"] <= 5e-3, rep
 
 
+@pytest.mark.parametrize("dims", [(128, 128, 128), (300, 256, 384), (2048, 512, 1024)])
+def test_glu_epilogue_emits_h_as_mxfp8(gpu, dims):
+    """The quantizing GLU epilogue equals quantizing its own BF16 H with the row quantizer, bit for bit,
+    whether or not the BF16 copy is also written; the MLP result does not depend on materializing H."""
+    ops, N, dev, ws = gpu
+    m, k, inter = dims
+    inp = O.make_inputs(2, m=m, k=k, inter=inter)
+    x, wgu, wd = inp["x"].to(dev), inp["w_gate_up"].to(dev), inp["w_down"].to(dev)
+    qx, sx = ops.mxfp8_quantize(x)
+    qg, sg = ops.mxfp8_quantize(wgu)
+    q1, s1, h = ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, m, inter, k, want_bf16=True)
+    q2, s2, none = ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, m, inter, k, want_bf16=False)
+    h_ref = ops.mxfp8_gemm_glu(qx, sx, qg, sg, m, inter, k)
+    qh, sh = ops.mxfp8_quantize(h)
+    _ok(ops, dev)
+    assert none is None
+    assert torch.equal(h, h_ref)
+    assert torch.equal(q1, qh) and torch.equal(q1, q2)
+    nb = inter // 32
+    want_s = _unpack_scales(sh, m, nb, (nb + 3) // 4)
+    assert torch.equal(_unpack_scales(s1, m, nb, (nb + 3) // 4), want_s)
+    assert torch.equal(_unpack_scales(s2, m, nb, (nb + 3) // 4), want_s)
+    h1, y1 = ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, want_hidden=True)
+    h0, y0 = ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, want_hidden=False)
+    _ok(ops, dev)
+    assert h0 is None and torch.equal(y0, y1) and torch.equal(h1, h)
+
+
 def test_mxfp8_glu_rejects_ragged_inter(gpu):
     ops, N, dev, ws = gpu
     x = torch.zeros(8, 64, dtype=torch.bfloat16, device=dev)
