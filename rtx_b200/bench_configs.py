@@ -1,0 +1,196 @@
+"""Device-timed measurements of benchmark configurations 3, 4 and 5 (configuration 2 is `bench.py`).
+
+    python -m rtx_b200.bench_configs --config 3            # NVFP4 forward 16384 x 28672 x 8192
+    python -m rtx_b200.bench_configs --config 4            # MXFP8 backward dX + dW, 16384 x 4096 x 4096
+    python -m rtx_b200.bench_configs --config 5            # NVFP4 decode, packed weights, M in {1, 8, 16, 64}
+    python -m torch.distributed.run --nproc-per-node N ... -m rtx_b200.bench_configs --config 4
+
+One JSON line per measured case (rank 0).  Token rows are sharded over ranks (weak scaling: the
+configuration's M per GPU); configuration 4 all-reduces the FP32 dW with NCCL inside the timed
+region.  Timing: CUDA events around K steps after W warm-ups, max over ranks; inputs exceed L2 for
+configurations 3 and 4; configuration 5 rotates over enough weight copies to exceed L2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _native as N
+from . import ops, parallel
+from .workloads import make_inputs
+
+NOMINAL = {"fp8": 4500.0, "fp4": 9000.0, "hbm": 8000.0}
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def _time(fn, steps, warmup, world, dev):
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier(device_ids=[dev.index])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ops.check_device_status(dev)
+    return float(t.item())
+
+
+def config3(args, rank, world, dev):
+    m, n, k = 16384, 28672, 8192
+    inp = make_inputs(3, m=m)            # every rank: the same tensors; weak scaling keeps M per GPU
+    x, w = inp["x"].to(dev), inp["w"].to(dev)
+    ws = ops.Workspace(dev)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    ms = _time(lambda: ops.nvfp4_linear_fwd(x, w, ws, out), args.steps, args.warmup, world, dev)
+    sx = ops.nvfp4_tensor_scale(x)
+    sw, so = ops.nvfp4_tensor_scale(w, other_scale=sx)
+    qa, sa = ops.nvfp4_quantize(x, sx)
+    qb, sb = ops.nvfp4_quantize(w, sw)
+    gemm_ms = _time(lambda: ops.nvfp4_gemm(qa, sa, qb, sb, m, n, k, so, out=out), args.steps, args.warmup, world, dev)
+    flops = 2.0 * m * n * k
+    peak = 4.0 * _peaks()["bf16_tflops"]
+    return [{
+        "metric": "fused quant+GEMM TFLOPS (NVFP4 linear forward, outer scales + quantization included)",
+        "value": flops * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "ms_per_step": ms,
+        "scaling": "weak", "dtype": "nvfp4 (e2m1 x e4m3 x f32), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "nvfp4_linear_fwd_m16384_n28672_k8192", "m_per_gpu": m, "scaling_policy": "current/power2"},
+        "pct_of_nominal_fp4_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / NOMINAL["fp4"], "gpu_launches_per_step": 7,
+        "roofline": {"kernel": "gemm_blockscaled_pair_kernel<nvfp4, bf16>", "bound": "tensor",
+                     "achieved": flops / (gemm_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                     "frac": flops / (gemm_ms * 1e-3) / 1e12 / peak, "ms_per_launch": gemm_ms, "traffic": None,
+                     "peak_note": "4 x measured cuBLAS bf16 burst as the dense FP4 proxy; nominal dense FP4 is 9000"},
+    }]
+
+
+def config4(args, rank, world, dev):
+    m, n, k = 16384, 4096, 4096
+    inp = make_inputs(4, m=m)
+    x, w, dy = inp["x"].to(dev), inp["w"].to(dev), inp["dy"].to(dev)
+    ws = ops.Workspace(dev)
+
+    def step():
+        # dW first so that its all-reduce overlaps the dX quantize + GEMM
+        _, dw = ops.mxfp8_linear_bwd(dy, x, None, ws, need_dx=False, dw_dtype=torch.float32)
+        handle = parallel.all_reduce_dw(dw, async_op=True) if world > 1 else None
+        dx, _ = ops.mxfp8_linear_bwd(dy, None, w, ws, need_dw=False)
+        if handle is not None:
+            handle.wait()
+        return dx, dw.to(torch.bfloat16)
+
+    ms = _time(step, args.steps, args.warmup, world, dev)
+    qc, sc = ops.mxfp8_quantize_transposed(dy)
+    qd, sd = ops.mxfp8_quantize_transposed(x)
+    dwbuf = torch.empty(n, k, dtype=torch.float32, device=dev)
+    gemm_ms = _time(lambda: ops.mxfp8_gemm(qc, sc, qd, sd, n, k, m, out=dwbuf), args.steps, args.warmup, world, dev)
+    flops = 4.0 * m * n * k
+    peak = 2.0 * _peaks()["bf16_tflops"]
+    return [{
+        "metric": "fused quant+GEMM TFLOPS (MXFP8 backward dX + dW, four operand quantizations included)",
+        "value": flops * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "ms_per_step": ms,
+        "scaling": "weak", "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "mxfp8_linear_bwd_m16384_n4096_k4096", "m_per_gpu": m,
+                   "collective": "NCCL all-reduce(sum) of FP32 dW (67 MB) overlapped with dX" if world > 1 else "none"},
+        "pct_of_nominal_fp8_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / NOMINAL["fp8"], "gpu_launches_per_step": 7,
+        "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, f32> (dW, K = 16384)", "bound": "tensor",
+                     "achieved": flops / 2 / (gemm_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                     "frac": flops / 2 / (gemm_ms * 1e-3) / 1e12 / peak, "ms_per_launch": gemm_ms, "traffic": None},
+    }]
+
+
+def config5(args, rank, world, dev):
+    lines = []
+    k = 8192
+    hbm = _peaks()["hbm_gbs"]
+    for n in (8192, 28672):
+        inp = make_inputs(5, m=64, n=n)
+        w = inp["w"].to(dev)
+        w_scale = ops.nvfp4_tensor_scale(w, N.TENSOR_SCALE_EXACT)
+        qw, sw = ops.nvfp4_quantize(w, w_scale)
+        # rotate over copies of the packed weight so that every launch streams it from HBM
+        copies = max(2, int(2 * 126e6 // (qw.numel() + sw.numel())) + 1)
+        qws = [qw.clone() for _ in range(copies)]
+        sws = [sw.clone() for _ in range(copies)]
+        del w
+        for m in (1, 8, 16, 64):
+            x = inp["x"][:m].contiguous().to(dev)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            state = {"i": 0}
+
+            def step():
+                i = state["i"] = (state["i"] + 1) % copies
+                x_scale, o_scale = ops.nvfp4_tensor_scale(x, N.TENSOR_SCALE_EXACT, other_scale=w_scale)
+                qx, sx = ops.nvfp4_quantize(x, x_scale)
+                ops.nvfp4_gemm(qx, sx, qws[i], sws[i], m, n, k, o_scale, out=out)
+
+            ms = _time(step, args.steps, args.warmup, world, dev)
+            x_scale, o_scale = ops.nvfp4_tensor_scale(x, N.TENSOR_SCALE_EXACT, other_scale=w_scale)
+            qx, sx = ops.nvfp4_quantize(x, x_scale)
+
+            def gemm_only():
+                i = state["i"] = (state["i"] + 1) % copies
+                ops.nvfp4_gemm(qx, sx, qws[i], sws[i], m, n, k, o_scale, out=out)
+
+            gemm_ms = _time(gemm_only, args.steps, args.warmup, world, dev)
+            algo_bytes = n * k / 2 + n * k / 16 + m * k * 2 + m * n * 2
+            lines.append({
+                "metric": "NVFP4 decode GB/s (packed weights streamed once, activations quantized on the fly)",
+                "value": algo_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "ms_per_step": ms,
+                "dtype": "nvfp4", "data": "synthetic",
+                "config": {"workload": f"nvfp4_decode_m{m}_n{n}_k{k}", "weight_copies_rotated": copies},
+                "pct_of_nominal_hbm": 100.0 * algo_bytes / (ms * 1e-3) / 1e9 / NOMINAL["hbm"], "gpu_launches_per_step": 4,
+                "roofline": {"kernel": "gemm_blockscaled_kernel<nvfp4, bf16>", "bound": "hbm",
+                             "achieved": algo_bytes / (gemm_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                             "frac": algo_bytes / (gemm_ms * 1e-3) / 1e9 / hbm, "ms_per_launch": gemm_ms, "traffic": None,
+                             "algorithmic_bytes": algo_bytes},
+            })
+    return lines
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5))
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("a CUDA device is required; there is no CPU fallback for the measured path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lines = {3: config3, 4: config4, 5: config5}[args.config](args, rank, world, dev)
+    if rank == 0:
+        for line in lines:
+            line.update({"steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True})
+            print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
