@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "gemm_blockscaled.cuh"
+#include "gemm_skinny.cuh"
 #include "quant.cuh"
 
 using namespace rtxb;
@@ -116,6 +117,20 @@ bool use_pair_kernel(int m_tiles) {
   return m_tiles >= 2;
 }
 
+// M <= 128 and too few 256-wide tiles to occupy the SMs: the 128 x 64 skinny kernel.  With many
+// 256-wide tiles (N >= ~19k) the large-tile kernel already keeps more bytes in flight per SM and
+// streams faster.  RTXB_GEMM_SKINNY=0/1 forces the choice.
+bool use_skinny_kernel(int m_tiles, int64_t n_rows_b) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* v = getenv("RTXB_GEMM_SKINNY");
+    forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
+  }
+  if (m_tiles != 1) return false;
+  if (forced >= 0) return forced == 1;
+  return (n_rows_b + kBlockN - 1) / kBlockN < 74;
+}
+
 template <int KIND, int EPI>
 int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
                 int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
@@ -149,6 +164,20 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   {
     const char* dbg = getenv("RTXB_GEMM_DEBUG");
     p.debug = dbg ? atoi(dbg) : 0;
+  }
+  if (use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI)) {
+    // one 128-row block of A: the bandwidth-shaped 128 x 64 kernel streams B once over all SMs
+    using S = SkinnyTraits<KIND>;
+    rc = make_payload_map(&map_b, qb, n_rows_b, row_bytes, kSkinnyN);
+    if (rc) return rc;
+    p.n_tiles = static_cast<int>((n_rows_b + kSkinnyN - 1) / kSkinnyN);
+    auto sk = gemm_skinny_kernel<KIND, EPI == kEpiF32 ? kEpiF32 : kEpiBf16>;
+    cudaError_t se = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+    if (se != cudaSuccess) return fail_cuda(se, "cudaFuncSetAttribute(skinny gemm)");
+    const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
+    sk<<<grid, kGemmThreads, S::kSmemBytes, stream>>>(map_a, map_b, p);
+    RTXB_CHECK_LAUNCH("gemm_skinny_kernel");
+    return RTXB_OK;
   }
   if (use_pair_kernel(p.m_tiles)) {
     using P = PairTraits<KIND>;

@@ -323,6 +323,40 @@ def test_nvfp4_forward(gpu, mnk, mode):
         assert ((y.float().cpu() - ref).norm() / ref.norm()) < 0.18
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 64, 128])
+def test_nvfp4_decode_with_prequantized_weight(gpu, m):
+    """Benchmark configuration 5 in small: packed weights (exact outer scale), activations quantized on the
+    fly; M <= 128 takes the 128 x 64 streaming kernel."""
+    ops, N, dev, _ = gpu
+    n, k = 1536, 2048
+    inp = O.make_inputs(5, m=m, n=n, k=k)
+    x, w = inp["x"], inp["w"]
+    ws_o, xs_o = O.nvfp4_tensor_scale(w, "exact"), O.nvfp4_tensor_scale(x, "exact")
+    w_scale = ops.nvfp4_tensor_scale(w.to(dev), N.TENSOR_SCALE_EXACT)
+    qw, sw = ops.nvfp4_quantize(w.to(dev), w_scale)
+    xd = x.to(dev)
+    x_scale, o_scale = ops.nvfp4_tensor_scale(xd, N.TENSOR_SCALE_EXACT, other_scale=w_scale)
+    qx, sx = ops.nvfp4_quantize(xd, x_scale)
+    y = ops.nvfp4_gemm(qx, sx, qw, sw, m, n, k, o_scale)
+    y32 = ops.nvfp4_gemm(qx, sx, qw, sw, m, n, k, o_scale, out_dtype=torch.float32)
+    _ok(ops, dev)
+    want = O.nvfp4_linear(x, w, x_scale=xs_o, w_scale=ws_o)
+    _assert_output(y, want)
+    _assert_output(y32.bfloat16(), want)
+
+
+@pytest.mark.parametrize("mnk", [(1, 64, 32), (128, 8192, 512), (100, 4100, 1000), (17, 63, 4096)])
+def test_mxfp8_skinny_shapes(gpu, mnk):
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    torch.manual_seed(77)
+    x = torch.randn(m, k).bfloat16()
+    w = (torch.randn(n, k) / k ** 0.5).bfloat16()
+    y = ops.mxfp8_linear_fwd(x.to(dev), w.to(dev), ws)
+    _ok(ops, dev)
+    _assert_output(y, O.mxfp8_linear(x, w))
+
+
 # ----------------------------------------------------------------------------- full-size properties
 
 def _deq_mx_gpu(q, s_tiles, rows, k):
