@@ -149,6 +149,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.m_tiles = static_cast<int>((m + kBlockM - 1) / kBlockM);
   p.n_tiles = glu_inter ? static_cast<int>((glu_inter + 127) / 128) : static_cast<int>((n_rows_b + kBlockN - 1) / kBlockN);
   p.glu_inter = static_cast<int>(glu_inter);
+  p.group_m = p.m_tiles;  // refined per kernel below
   p.sfa = static_cast<const uint8_t*>(sa);
   p.sfb = static_cast<const uint8_t*>(sb);
   p.sf_k_chunks = static_cast<int>(sf_k_chunks);
@@ -189,6 +190,13 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     auto pk = gemm_blockscaled_pair_kernel<KIND, EPI>;
     cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmemBytes);
     if (pe != cudaSuccess) return fail_cuda(pe, "cudaFuncSetAttribute(pair gemm)");
+    {
+      // A panel of a raster group: about 32 MB (group_m pairs x 256 rows x row_bytes) so that it stays in L2
+      const int m_pairs = (p.m_tiles + 1) / 2;
+      int64_t g = (32ll << 20) / (256 * row_bytes);
+      if (const char* v = getenv("RTXB_GEMM_GROUP_M")) g = atoi(v);
+      p.group_m = static_cast<int>(g < 4 ? 4 : (g > m_pairs ? m_pairs : g));
+    }
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles;
     const int max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(pair_tiles < max_pairs ? pair_tiles : max_pairs);

@@ -99,6 +99,8 @@ struct GemmTraits {
 struct GemmParams {
   int m, n, k_tiles;      // n = rows of B (for GLU: 2 * inter); k_tiles = ceil(Kbytes / 128)
   int m_tiles, n_tiles;   // 128-row blocks of A; 256-wide accumulator tiles
+  int group_m;            // raster: M blocks (pairs) per group; a group's A panel stays L2 resident while
+                          // the group walks every N tile
   int glu_inter;          // GLU: rows of the gate half of B (= output columns); else 0
   const uint8_t* sfa;     // [ceil(M/128)][sf_k_chunks][512]
   const uint8_t* sfb;     // [ceil(N/128)][sf_k_chunks][512]
@@ -116,6 +118,17 @@ struct GemmParams {
                           // first K step only, bit1 = stop loading once the ring is filled,
                           // bit2 = issue the scale copy of step i+1 before the MMAs of step i
 };
+
+// Tile order: groups of `group_m` M blocks; inside a group M runs fastest, then N.  CTAs that run at
+// the same time then share one or two B tiles and a group-sized A panel that fits L2.
+__device__ __forceinline__ void tile_coords(int tile, int m_count, int n_tiles, int group_m, int& m_idx, int& n_idx) {
+  const int per_group = group_m * n_tiles;
+  const int g = tile / per_group;
+  const int r = tile - g * per_group;
+  const int m_in_group = min(group_m, m_count - g * group_m);
+  n_idx = r / m_in_group;
+  m_idx = g * group_m + (r - n_idx * m_in_group);
+}
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
@@ -420,7 +433,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m_idx = tile % p.m_tiles, n_idx = tile / p.m_tiles;
+        int m_idx, n_idx;
+        tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_idx, n_idx);
         const int m0 = m_idx * kBlockM;
         // rows of B feeding accumulator columns [0,128) and [128,256)
         int b_row0, b_row1;
@@ -491,7 +505,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const float out_scale = p.out_scale ? __ldg(p.out_scale) : 1.0f;
     uint32_t local_tile = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
-      const int m_idx = tile % p.m_tiles, n_idx = tile / p.m_tiles;
+      int m_idx, n_idx;
+      tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_idx, n_idx);
       const int row = m_idx * kBlockM + quad * 32 + lane;
       const bool row_ok = row < p.m;
       const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;
@@ -607,7 +622,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
-        const int mp_idx = tile % m_pairs, n_idx = tile / m_pairs;
+        int mp_idx, n_idx;
+        tile_coords(tile, m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
         const int m_blk = mp_idx * 2 + static_cast<int>(rank);   // 128-row block of A this CTA owns
         int b_blk0, b_blk1;                                      // 128-row blocks of B behind columns [0,128), [128,256)
         if (epi_is_glu(EPI)) {
@@ -666,7 +682,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
     const uint32_t overlap_addr = mapa_shared(smem_u32(acc_overlap_bar), 0);
     uint32_t local_tile = 0;
     for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++local_tile) {
-      const int mp_idx = tile % m_pairs, n_idx = tile / m_pairs;
+      int mp_idx, n_idx;
+      tile_coords(tile, m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
       const int row = (mp_idx * 2 + static_cast<int>(rank)) * 128 + quad * 32 + lane;
       const bool row_ok = row < p.m;
       const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;

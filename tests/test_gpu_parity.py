@@ -345,7 +345,7 @@ def test_nvfp4_decode_with_prequantized_weight(gpu, m):
     _assert_output(y32.bfloat16(), want)
 
 
-@pytest.mark.parametrize("mnk", [(1, 64, 32), (128, 8192, 512), (100, 4100, 1000), (17, 63, 4096)])
+@pytest.mark.parametrize("mnk", [(1, 64, 32), (128, 8192, 512), (100, 4100, 1000), (17, 63, 4096), (16, 19456, 256)])
 def test_mxfp8_skinny_shapes(gpu, mnk):
     ops, N, dev, ws = gpu
     m, n, k = mnk
