@@ -167,6 +167,16 @@ int rtxb_nvfp4_tensor_scale(const void* src_bf16, int64_t rows, int64_t k, int64
  * tensor_scale NULL = block policy (scale 1.0, compile_nvfp4_block_quant). */
 int rtxb_nvfp4_quantize(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
                         int scale_layout, const float* tensor_scale, void* stream);
+/* Outer scale + quantization of one tensor with the scale taken from its own current |max|
+ * (NVFP4Linear.forward with scaling="current": _outer_tensor_scale, rtx/fp4.py:343-365, then
+ * compile_nvfp4_quant).  Same results as rtxb_nvfp4_tensor_scale followed by rtxb_nvfp4_quantize;
+ * tensors of at most 64 tiles of 128 x 256 values (decode activations) take two launches chained
+ * by programmatic dependent launch (per-CTA |max| partials, then scale rule + quantization in
+ * every CTA; no memset, no finalize launch), larger ones the three launches.
+ * amax_scratch: 256 bytes of device memory, 4-byte aligned. */
+int rtxb_nvfp4_quantize_dynamic(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, int mode, void* q,
+                                void* scales, int scale_layout, float* scale_out, const float* other_scale,
+                                float* out_scale, void* amax_scratch, void* stream);
 /* compile_nvfp4_gemm(problem, cfg) -> (qx, qw, sx, sw, out bf16, output_scale f32[1])
  *   rtx/kernels/nvfp4_gemm.py:22-64, epilogue rtx/kernels/mxfp8_gemm.py:779-781;
  *   bound at rtx/fp4.py:707, :901, :1734, :2313.  output_scale NULL = 1 (block GEMM). */
@@ -176,6 +186,18 @@ int rtxb_nvfp4_gemm(const void* qa, const void* sa, const void* qb, const void* 
 size_t rtxb_nvfp4_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int rtxb_nvfp4_linear_fwd(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n, int64_t k,
                           int scale_mode, void* workspace, size_t workspace_bytes, void* stream, int* status);
+
+/* _DynamicXRunner (rtx/fp4.py:639-668) behind the op nvfp4_linear_dynamic_x_prequant_w
+ * (rtx/fp4.py:1628-1686), with the activation's outer scale taken from its current |max| in the
+ * same call: x BF16 [M,K]; qw / sw the packed weight [N, Kp/2] and its mma128 block scales;
+ * w_scale its FP32 outer scale (device scalar).  Three launches for decode-sized M (|max|
+ * partials, quantizer, GEMM), each a programmatic dependent of the one before: the GEMM streams
+ * the weights into shared memory while the activations are still being quantized.  The packed weight must therefore
+ * be complete before this call is enqueued (any earlier work on the stream is fine). */
+size_t rtxb_nvfp4_linear_prequant_w_workspace_bytes(int64_t m, int64_t k);
+int rtxb_nvfp4_linear_fwd_prequant_w(const void* x_bf16, const void* qw, const void* sw, const float* w_scale,
+                                     void* out_bf16, int64_t m, int64_t n, int64_t k, int scale_mode, void* workspace,
+                                     size_t workspace_bytes, void* stream, int* status);
 
 #ifdef __cplusplus
 }

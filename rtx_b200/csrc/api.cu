@@ -74,6 +74,28 @@ int make_payload_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
   return RTXB_OK;
 }
 
+// the same byte matrix viewed as [row_bytes / 128][rows][128]: boxes of `box_k` consecutive 128-byte
+// K chunks x box_rows rows, each chunk landing as its own swizzled tile.  Needs row_bytes % 128 == 0
+// (otherwise the last chunk of a row would run into the next row instead of reading zeros).
+int make_payload_map_ksteps(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows,
+                            int box_k) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+  if (!aligned(base, 16) || row_bytes % 128 != 0) return fail_msg(RTXB_E_ALIGNMENT, "payload rows must be 128-byte multiples");
+  cuuint64_t gdim[3] = {128u, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(row_bytes / 128)};
+  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(row_bytes), 128u};
+  cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_k)};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(3d) failed with CUresult %d", static_cast<int>(r));
+    return RTXB_E_DRIVER;
+  }
+  return RTXB_OK;
+}
+
 // scale tiles as a matrix of 512-byte rows (128 x uint32), boxes of `box_rows` consecutive tiles
 int make_scale_map(CUtensorMap* map, const void* base, int64_t total_tiles, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
@@ -103,6 +125,24 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+// launch `kernel` so that it may start while the kernel before it on the stream is still running
+// (both sides use griddepcontrol to order their memory accesses)
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+                             bool dependent, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 // Schedule choice: the CTA-pair kernel (256 x 256 pair tiles) unless the problem has a single
@@ -135,7 +175,9 @@ template <int KIND, int EPI>
 int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
                 int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
                 const float* out_scale, cudaStream_t stream, int* status, void* q_out = nullptr,
-                void* sf_out = nullptr) {
+                void* sf_out = nullptr, bool overlap_previous = false) {
+  // overlap_previous: B and its scales do not depend on the kernel launched just before this one on
+  // the stream, so the streaming kernel may start fetching them while that kernel is still running
   using T = GemmTraits<KIND>;
   CUtensorMap map_a, map_b;
   int rc = make_payload_map(&map_a, qa, m, row_bytes, 128);
@@ -162,6 +204,11 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.sf_out = static_cast<uint8_t*>(sf_out);
   p.sf_out_chunks = static_cast<int>((out_cols / 32 + 3) / 4);
   p.status = status;
+  p.a_box_rows = 128;
+  p.slots = 0;
+  p.ks = 1;
+  p.map3d = 0;
+  p.overlap_previous = overlap_previous ? 1 : 0;
   {
     const char* dbg = getenv("RTXB_GEMM_DEBUG");
     p.debug = dbg ? atoi(dbg) : 0;
@@ -169,15 +216,37 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   if (use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI)) {
     // one 128-row block of A: the bandwidth-shaped 128 x 64 kernel streams B once over all SMs
     using S = SkinnyTraits<KIND>;
-    rc = make_payload_map(&map_b, qb, n_rows_b, row_bytes, kSkinnyN);
-    if (rc) return rc;
+    p.a_box_rows = static_cast<int>(round_up(m, 8));
+    // K steps per ring slot: as many as still leave four slots (one TMA instruction per operand and slot)
+    p.map3d = row_bytes % 128 == 0 ? 1 : 0;
+    p.ks = 1;
+    if (p.map3d) {
+      for (int ks = 4; ks >= 2; ks >>= 1)
+        if (S::slots_for(p.a_box_rows, ks) >= 4 && p.k_tiles >= ks) { p.ks = ks; break; }
+    }
+    if (const char* v = getenv("RTXB_SKINNY_KS")) {
+      const int ks = atoi(v);
+      if (ks >= 1 && ks <= 8 && (ks == 1 || p.map3d) && S::slots_for(p.a_box_rows, ks) >= 2) p.ks = ks;
+    }
+    p.slots = S::slots_for(p.a_box_rows, p.ks);
+    if (p.map3d) {
+      rc = make_payload_map_ksteps(&map_a, qa, m, row_bytes, p.a_box_rows, p.ks);
+      if (rc) return rc;
+      rc = make_payload_map_ksteps(&map_b, qb, n_rows_b, row_bytes, kSkinnyN, p.ks);
+      if (rc) return rc;
+    } else {
+      rc = make_payload_map(&map_a, qa, m, row_bytes, p.a_box_rows);
+      if (rc) return rc;
+      rc = make_payload_map(&map_b, qb, n_rows_b, row_bytes, kSkinnyN);
+      if (rc) return rc;
+    }
     p.n_tiles = static_cast<int>((n_rows_b + kSkinnyN - 1) / kSkinnyN);
     auto sk = gemm_skinny_kernel<KIND, EPI == kEpiF32 ? kEpiF32 : kEpiBf16>;
-    cudaError_t se = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+    cudaError_t se = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnySmemBudget);
     if (se != cudaSuccess) return fail_cuda(se, "cudaFuncSetAttribute(skinny gemm)");
-    const int grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-    sk<<<grid, kGemmThreads, S::kSmemBytes, stream>>>(map_a, map_b, p);
-    RTXB_CHECK_LAUNCH("gemm_skinny_kernel");
+    se = launch_dependent(sk, p.n_tiles < sm_count() ? p.n_tiles : sm_count(), kGemmThreads,
+                          S::smem_bytes(p.a_box_rows, p.ks, p.slots), stream, overlap_previous, map_a, map_b, p);
+    if (se != cudaSuccess) return fail_cuda(se, "gemm_skinny_kernel launch");
     return RTXB_OK;
   }
   if (use_pair_kernel(p.m_tiles)) {
@@ -209,8 +278,8 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(gemm)");
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  kernel<<<grid, kGemmThreads, T::kSmemBytes, stream>>>(map_a, map_b, p);
-  RTXB_CHECK_LAUNCH("gemm_blockscaled_kernel");
+  e = launch_dependent(kernel, grid, kGemmThreads, T::kSmemBytes, stream, overlap_previous, map_a, map_b, p);
+  if (e != cudaSuccess) return fail_cuda(e, "gemm_blockscaled_kernel launch");
   return RTXB_OK;
 }
 
@@ -542,6 +611,58 @@ int rtxb_nvfp4_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, vo
   return RTXB_OK;
 }
 
+int rtxb_nvfp4_quantize_dynamic(const void* src, int64_t rows, int64_t k, int64_t ld, int mode, void* q, void* scales,
+                                int scale_layout, float* scale_out, const float* other_scale, float* out_scale,
+                                void* amax_scratch, void* stream) {
+  if (!src || !q || !scales || !scale_out || !amax_scratch) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (mode != RTXB_TENSOR_SCALE_EXACT && mode != RTXB_TENSOR_SCALE_POWER2)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown tensor scale mode");
+  if ((out_scale == nullptr) != (other_scale == nullptr))
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "other_scale and out_scale go together");
+  if (!aligned(amax_scratch, 4)) return fail_msg(RTXB_E_ALIGNMENT, "amax_scratch must be 4-byte aligned");
+  const int64_t kp = round_up(k, 32);
+  const int64_t tiles = ((rows + 127) / 128) * ((kp + 255) / 256);
+  if (tiles > kDynamicMaxPartials) {
+    // large tensors: the grid-wide |max| pass, the finalize launch and the quantizer
+    int rc = rtxb_nvfp4_tensor_scale(src, rows, k, ld, mode, amax_scratch, scale_out, other_scale, out_scale, stream);
+    if (rc) return rc;
+    return rtxb_nvfp4_quantize(src, rows, k, ld, q, scales, scale_layout, scale_out, stream);
+  }
+  if (rows > INT32_MAX || k > INT32_MAX - 512) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!aligned(q, 16)) return fail_msg(RTXB_E_ALIGNMENT, "q must be 16-byte aligned");
+  if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  QuantNvDynamicParams dp;
+  dp.q.src = static_cast<const __nv_bfloat16*>(src);
+  dp.q.q = static_cast<uint8_t*>(q);
+  dp.q.scales = static_cast<uint8_t*>(scales);
+  dp.q.tensor_scale = nullptr;
+  dp.q.rows = static_cast<int>(rows);
+  dp.q.k = static_cast<int>(k);
+  dp.q.kp = static_cast<int>(kp);
+  dp.q.ld = ld;
+  dp.q.nb = dp.q.kp / 16;
+  dp.q.sf_chunks = static_cast<int>(round_up((dp.q.nb + 3) / 4, 4));
+  dp.q.layout = scale_layout;
+  dp.mode = mode;
+  dp.partials = static_cast<const uint32_t*>(amax_scratch);
+  dp.n_partials = static_cast<int>(tiles);
+  dp.scale_out = scale_out;
+  dp.other_scale = other_scale;
+  dp.out_scale = out_scale;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_dependent(amax_partials_kernel, static_cast<int>(tiles), kQuantThreads, 0, s, true, dp.q,
+                                   static_cast<uint32_t*>(amax_scratch));
+  if (e != cudaSuccess) return fail_cuda(e, "amax_partials_kernel launch");
+  e = launch_dependent(quant_nvfp4_dynamic_kernel, static_cast<int>(tiles), kQuantThreads, 0, s, true, dp);
+  if (e != cudaSuccess) return fail_cuda(e, "quant_nvfp4_dynamic_kernel launch");
+  return RTXB_OK;
+}
+
 int rtxb_nvfp4_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
                     int64_t k, int64_t ldo, int out_dtype, const float* output_scale, void* stream, int* status) {
   if (out_dtype != RTXB_OUT_BF16 && out_dtype != RTXB_OUT_F32)
@@ -590,5 +711,49 @@ int rtxb_nvfp4_linear_fwd(const void* x, const void* w, void* out, int64_t m, in
   if ((rc = rtxb_nvfp4_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, w_scale, stream))) return rc;
   return rtxb_nvfp4_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, o_scale, stream, status);
 }
+
+size_t rtxb_nvfp4_linear_prequant_w_workspace_bytes(int64_t m, int64_t k) {
+  Carver c(nullptr);
+  const int64_t kp = round_up(k, 32);
+  c.take(512);
+  c.take(m * kp / 2);
+  c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  return c.off;
+}
+
+int rtxb_nvfp4_linear_fwd_prequant_w(const void* x, const void* qw, const void* sw, const float* w_scale, void* out,
+                                     int64_t m, int64_t n, int64_t k, int scale_mode, void* workspace,
+                                     size_t workspace_bytes, void* stream, int* status) {
+  if (!w_scale) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null weight scale");
+  if (!workspace || workspace_bytes < rtxb_nvfp4_linear_prequant_w_workspace_bytes(m, k))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_nvfp4_linear_fwd_prequant_w");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  int rc = check_gemm_args(x, sw, qw, sw, out, m, n, k, n, n, 2);
+  if (rc) return rc;
+  Carver c(workspace);
+  const int64_t kp = round_up(k, 32);
+  uint8_t* scal = c.take(512);
+  uint8_t* qx = c.take(m * kp / 2);
+  uint8_t* sx = c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  // scalar block: [0, 256) |max| partials, [256] x scale, [264] output scale
+  float* x_scale = reinterpret_cast<float*>(scal + 256);
+  float* o_scale = reinterpret_cast<float*>(scal + 264);
+  rc = rtxb_nvfp4_quantize_dynamic(x, m, k, k, scale_mode, qx, sx, RTXB_SCALE_MMA128, x_scale, w_scale, o_scale, scal,
+                                   stream);
+  if (rc) return rc;
+  // The packed weight was written before the activation quantizer was launched, so the GEMM may
+  // start fetching it while that quantizer runs.
+  const int64_t chunks = round_up((kp / 16 + 3) / 4, 4);
+  return launch_gemm<kKindNvfp4, kEpiBf16>(qx, sx, qw, sw, out, m, n, kp / 2, chunks, n, n, 0, o_scale,
+                                           static_cast<cudaStream_t>(stream), status, nullptr, nullptr, true);
+}
+
+#ifdef RTXB_TRACE
+// development builds only: copy the streaming kernel's timeline probe to the host
+int rtxb_debug_skinny_trace(unsigned long long* host_out) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_skinny_trace, sizeof(unsigned long long) * 160 * 16);
+  return e == cudaSuccess ? 0 : -1;
+}
+#endif
 
 }  // extern "C"

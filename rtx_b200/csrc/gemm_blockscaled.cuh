@@ -114,6 +114,12 @@ struct GemmParams {
   uint8_t* sf_out;        // kEpiGluMx: E8M0 scales of H in 128-row tiles, sf_out_chunks tiles per row block
   int sf_out_chunks;
   int* status;            // device status word or nullptr
+  int a_box_rows;         // streaming kernel (M <= 128): rows of A fetched per K step (M rounded up to 8)
+  int slots;              // streaming kernel: ring slots that fit shared memory with that A box
+  int ks;                 // streaming kernel: K steps per ring slot
+  int map3d;              // streaming kernel: payload maps are [K/128][rows][128] views (one load per slot)
+  int overlap_previous;   // streaming kernel: launched as a programmatic dependent; A / SFA / out_scale may
+                          // come from the grid before it, B / SFB do not
   int debug;              // experiments only (results invalid when set): bit0 = copy scale factors on the
                           // first K step only, bit1 = stop loading once the ring is filled,
                           // bit2 = issue the scale copy of step i+1 before the MMAs of step i
@@ -427,6 +433,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
       }
+      griddep_wait();   // operands may come from the kernel launched just before this one
       constexpr int KS = T::kStepsPerBarrier;
       const int k_groups = (p.k_tiles + KS - 1) / KS;
       int group = 0;
@@ -500,6 +507,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncwarp();
   } else {
     // ------------------------------ epilogue ------------------------------
+    griddep_wait();   // the output scale may come from the kernel launched just before this one
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float out_scale = p.out_scale ? __ldg(p.out_scale) : 1.0f;

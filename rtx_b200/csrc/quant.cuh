@@ -290,9 +290,8 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const __nv_bfloat16* src
 
 // mode 0: exact amax/(448*6); mode 1: power of two 2^ceil(log2(max(amax/2688, 2^-126)));
 // 1.0 when amax == 0.  Optionally also publishes out_scale = scale * other_scale[0].
-__global__ void nvfp4_tensor_scale_kernel(const uint32_t* amax_bits, int mode, float* scale, const float* other_scale,
-                                          float* out_scale) {
-  const float amax = __uint_as_float(*amax_bits);
+__device__ __forceinline__ float nvfp4_scale_from_amax_bits(uint32_t amax_bits, int mode) {
+  const float amax = __uint_as_float(amax_bits);
   float s;
   if (mode == 0) {
     s = __fdiv_rn(amax, 2688.0f);
@@ -304,6 +303,12 @@ __global__ void nvfp4_tensor_scale_kernel(const uint32_t* amax_bits, int mode, f
     s = __uint_as_float(ebits);
   }
   if (amax == 0.0f) s = 1.0f;
+  return s;
+}
+
+__global__ void nvfp4_tensor_scale_kernel(const uint32_t* amax_bits, int mode, float* scale, const float* other_scale,
+                                          float* out_scale) {
+  const float s = nvfp4_scale_from_amax_bits(*amax_bits, mode);
   *scale = s;
   if (out_scale) *out_scale = s * *other_scale;
 }
@@ -328,65 +333,162 @@ struct QuantNvParams {
 // Tile = 128 rows x 256 columns (16 blocks = four 512-byte scale tiles).  Thread t owns the
 // block (t & 15) of row (t >> 4) + 16 i; the loads of two rows (four 16-byte loads) are issued
 // before the first is consumed.
-__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_rows_kernel(const QuantNvParams p) {
-  __shared__ __align__(16) uint8_t tile_scales[128][16];
-  const int sub = threadIdx.x & 15, rsel = threadIdx.x >> 4;
-  const int col_tiles = (p.kp + 255) / 256;
-  const int row_tiles = (p.rows + 127) / 128;
-  const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
-  const float st = p.tensor_scale ? __ldg(p.tensor_scale) : 1.0f;
-  const float six_st = 6.0f * st;
-  const float inv_st = __fdiv_rn(1.0f, st);
-  const int row_bytes = p.kp / 2;
-  for (int tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
-    const int row0 = (tile / col_tiles) * 128;
-    const int col = (tile % col_tiles) * 256 + sub * 16;
-    const bool col_ok = col < p.kp;
+struct QuantNvTileCtx {
+  int sub, rsel, col_tiles, row_bytes;
+  bool vec_ok;
+  float six_st, inv_st;
+};
+
+__device__ __forceinline__ QuantNvTileCtx quant_nvfp4_ctx(const QuantNvParams& p, float st) {
+  QuantNvTileCtx c;
+  c.sub = threadIdx.x & 15;
+  c.rsel = threadIdx.x >> 4;
+  c.col_tiles = (p.kp + 255) / 256;
+  c.row_bytes = p.kp / 2;
+  c.vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
+  c.six_st = 6.0f * st;
+  c.inv_st = __fdiv_rn(1.0f, st);
+  return c;
+}
+
+// one 128 x 256 tile: payload bytes and the tile's scale bytes (block-wide: ends with a barrier)
+__device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const QuantNvTileCtx& c, int tile,
+                                                 uint8_t (*tile_scales)[16]) {
+  const int row0 = (tile / c.col_tiles) * 128;
+  const int col = (tile % c.col_tiles) * 256 + c.sub * 16;
+  const bool col_ok = col < p.kp;
 #pragma unroll
-    for (int pair = 0; pair < 4; ++pair) {
-      uint4 raw[2][2];
+  for (int pair = 0; pair < 4; ++pair) {
+    uint4 raw[2][2];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int row = row0 + rsel + 16 * (pair * 2 + j);
-        if (row < p.rows && col_ok) {
-          const __nv_bfloat16* rp = p.src + static_cast<int64_t>(row) * p.ld;
-          raw[j][0] = load8_raw(rp, col, p.k, vec_ok);
-          raw[j][1] = load8_raw(rp, col + 8, p.k, vec_ok);
-        } else {
-          raw[j][0] = raw[j][1] = make_uint4(0, 0, 0, 0);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int r = rsel + 16 * (pair * 2 + j);
-        const int row = row0 + r;
-        const bool live = row < p.rows && col_ok;
-        float v[16];
-        unpack8(raw[j][0], *reinterpret_cast<float(*)[8]>(&v[0]));
-        unpack8(raw[j][1], *reinterpret_cast<float(*)[8]>(&v[8]));
-        float a = fabsf(v[0]);
-#pragma unroll
-        for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
-        float rawscale = __fdiv_rn(a, six_st);
-        rawscale = fmin_nan(fmax_nan(rawscale, 0.015625f), 448.0f);
-        const uint32_t sb = cvt_e4m3x2(rawscale, rawscale) & 0xFF;
-        const float recip = __fdiv_rn(inv_st, e4m3_to_float(sb));
-        tile_scales[r][sub] = live ? static_cast<uint8_t>(sb) : 0;
-        if (live) {
-          uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            w0 |= cvt_e2m1x2(v[2 * e] * recip, v[2 * e + 1] * recip) << (8 * e);
-            w1 |= cvt_e2m1x2(v[8 + 2 * e] * recip, v[8 + 2 * e + 1] * recip) << (8 * e);
-          }
-          *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(row) * row_bytes + col / 2) = make_uint2(w0, w1);
-        }
+    for (int j = 0; j < 2; ++j) {
+      const int row = row0 + c.rsel + 16 * (pair * 2 + j);
+      if (row < p.rows && col_ok) {
+        const __nv_bfloat16* rp = p.src + static_cast<int64_t>(row) * p.ld;
+        raw[j][0] = load8_raw(rp, col, p.k, c.vec_ok);
+        raw[j][1] = load8_raw(rp, col + 8, p.k, c.vec_ok);
+      } else {
+        raw[j][0] = raw[j][1] = make_uint4(0, 0, 0, 0);
       }
     }
-    __syncthreads();
-    store_scale_tile<16>(tile_scales, p.scales, p.layout, row0, (tile % col_tiles) * 16, p.rows, p.nb, p.sf_chunks);
-    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = c.rsel + 16 * (pair * 2 + j);
+      const int row = row0 + r;
+      const bool live = row < p.rows && col_ok;
+      float v[16];
+      unpack8(raw[j][0], *reinterpret_cast<float(*)[8]>(&v[0]));
+      unpack8(raw[j][1], *reinterpret_cast<float(*)[8]>(&v[8]));
+      float a = fabsf(v[0]);
+#pragma unroll
+      for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
+      float rawscale = __fdiv_rn(a, c.six_st);
+      rawscale = fmin_nan(fmax_nan(rawscale, 0.015625f), 448.0f);
+      const uint32_t sb = cvt_e4m3x2(rawscale, rawscale) & 0xFF;
+      const float recip = __fdiv_rn(c.inv_st, e4m3_to_float(sb));
+      tile_scales[r][c.sub] = live ? static_cast<uint8_t>(sb) : 0;
+      if (live) {
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          w0 |= cvt_e2m1x2(v[2 * e] * recip, v[2 * e + 1] * recip) << (8 * e);
+          w1 |= cvt_e2m1x2(v[8 + 2 * e] * recip, v[8 + 2 * e + 1] * recip) << (8 * e);
+        }
+        *reinterpret_cast<uint2*>(p.q + static_cast<int64_t>(row) * c.row_bytes + col / 2) = make_uint2(w0, w1);
+      }
+    }
   }
+  __syncthreads();
+  store_scale_tile<16>(tile_scales, p.scales, p.layout, row0, (tile % c.col_tiles) * 16, p.rows, p.nb, p.sf_chunks);
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_rows_kernel(const QuantNvParams p) {
+  __shared__ __align__(16) uint8_t tile_scales[128][16];
+  const float st = p.tensor_scale ? __ldg(p.tensor_scale) : 1.0f;
+  const QuantNvTileCtx c = quant_nvfp4_ctx(p, st);
+  const int row_tiles = (p.rows + 127) / 128;
+  for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x) quant_nvfp4_tile(p, c, tile, tile_scales);
+}
+
+// ---------------------------------------------------------------------------
+// Small tensors (decode activations): the outer scale from the tensor's own |max| and the
+// quantization as two launches chained by programmatic dependent launch, with no memset and no
+// one-thread finalize launch in between:
+//   amax_partials_kernel     CTA p writes the |max| bits of tiles p, p + P, ... to partials[p]
+//   quant_nvfp4_dynamic_kernel  every CTA reduces the P partials itself, applies the scale rule
+//                            (all CTAs get the same bits), CTA 0 publishes the scale(s), then the
+//                            tiles are quantized with the code of the two-pass path.
+// Both let their dependents start early (griddepcontrol.launch_dependents first thing) and wait
+// for their own predecessor before touching global memory that it may still use.
+// Replaces, for small M, the reference's torch reductions of `_outer_tensor_scale`
+// (rtx/fp4.py:343-365) followed by compile_nvfp4_quant (rtx/kernels/nvfp4_quant.py:32-349).
+// ---------------------------------------------------------------------------
+constexpr int kDynamicMaxPartials = 64;
+
+__global__ void __launch_bounds__(kQuantThreads) amax_partials_kernel(const QuantNvParams p, uint32_t* partials) {
+  __shared__ uint32_t cta_amax;
+  griddep_launch_dependents();
+  if (threadIdx.x == 0) cta_amax = 0;
+  griddep_wait();   // src may be the output of the kernel before this one; partials may still be read by it
+  __syncthreads();
+  const QuantNvTileCtx c = quant_nvfp4_ctx(p, 1.0f);
+  const int tiles = c.col_tiles * ((p.rows + 127) / 128);
+  uint32_t m = 0;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int row0 = (tile / c.col_tiles) * 128;
+    const int col = (tile % c.col_tiles) * 256 + c.sub * 16;
+    if (col >= p.kp) continue;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = row0 + c.rsel + 16 * i;
+      if (row >= p.rows) continue;
+      const __nv_bfloat16* rp = p.src + static_cast<int64_t>(row) * p.ld;
+      const uint4 a = load8_raw(rp, col, p.k, c.vec_ok), b = load8_raw(rp, col + 8, p.k, c.vec_ok);
+      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+        m = max(m, w[e] & 0x7FFF0000u);
+      }
+    }
+  }
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(&cta_amax, m);
+  __syncthreads();
+  if (threadIdx.x == 0) partials[blockIdx.x] = cta_amax;
+}
+
+struct QuantNvDynamicParams {
+  QuantNvParams q;           // q.tensor_scale is not read
+  int mode;                  // 0 exact, 1 power of two
+  const uint32_t* partials;  // [n_partials] |max| bits
+  int n_partials;            // <= kDynamicMaxPartials
+  float* scale_out;          // [1]
+  const float* other_scale;  // nullptr or [1]
+  float* out_scale;          // nullptr or [1] = scale * other_scale
+};
+
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_dynamic_kernel(const QuantNvDynamicParams dp) {
+  __shared__ __align__(16) uint8_t tile_scales[128][16];
+  __shared__ uint32_t warp_amax[2];
+  griddep_launch_dependents();
+  griddep_wait();
+  const QuantNvParams& p = dp.q;
+  if (threadIdx.x < 64) {
+    uint32_t v = threadIdx.x < dp.n_partials ? dp.partials[threadIdx.x] : 0u;
+    v = __reduce_max_sync(0xffffffffu, v);
+    if ((threadIdx.x & 31) == 0) warp_amax[threadIdx.x >> 5] = v;
+  }
+  __syncthreads();
+  const float st = nvfp4_scale_from_amax_bits(max(warp_amax[0], warp_amax[1]), dp.mode);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *dp.scale_out = st;
+    if (dp.out_scale) *dp.out_scale = st * *dp.other_scale;
+  }
+  const QuantNvTileCtx c = quant_nvfp4_ctx(p, st);
+  const int tiles = c.col_tiles * ((p.rows + 127) / 128);
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) quant_nvfp4_tile(p, c, tile, tile_scales);
 }
 
 }  // namespace rtxb

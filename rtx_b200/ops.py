@@ -247,6 +247,42 @@ def nvfp4_quantize(src: torch.Tensor, tensor_scale: Optional[torch.Tensor], *, l
     return q, scales
 
 
+def nvfp4_quantize_dynamic(src: torch.Tensor, mode: int = N.TENSOR_SCALE_POWER2,
+                           other_scale: Optional[torch.Tensor] = None, *, layout: int = N.SCALE_MMA128):
+    """Outer scale from the tensor's own |max| and quantization in one call (two chained launches
+    for decode-sized tensors).  Returns (q, scales, tensor_scale f32[1], scale*other_scale f32[1] | None)."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    kp = mx_storage_k(k)
+    q = torch.empty(rows, kp // 2, dtype=torch.uint8, device=src.device)
+    scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
+    scratch = torch.empty(64, dtype=torch.int32, device=src.device)
+    scale = torch.empty(1, dtype=torch.float32, device=src.device)
+    prod = torch.empty(1, dtype=torch.float32, device=src.device) if other_scale is not None else None
+    with torch.cuda.device(src.device):
+        N.call("rtxb_nvfp4_quantize_dynamic", src.data_ptr(), rows, k, k, mode, q.data_ptr(), scales.data_ptr(), layout,
+               scale.data_ptr(), other_scale.data_ptr() if other_scale is not None else None,
+               prod.data_ptr() if prod is not None else None, scratch.data_ptr(), _stream_ptr())
+    return q, scales, scale, prod
+
+
+def nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n: int, ws: Workspace, out: Optional[torch.Tensor] = None,
+                                scale_mode: int = N.TENSOR_SCALE_POWER2) -> torch.Tensor:
+    """Packed weight (payload, mma128 block scales, outer scale), BF16 activations quantized on the
+    fly with their current outer scale; the GEMM overlaps the activation quantizer."""
+    _require(x, torch.bfloat16, "x")
+    m, k = x.shape
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    nbytes = N.query("rtxb_nvfp4_linear_prequant_w_workspace_bytes", m, k)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_nvfp4_linear_fwd_prequant_w", x.data_ptr(), qw.data_ptr(), sw.data_ptr(), w_scale.data_ptr(),
+               out.data_ptr(), m, n, k, scale_mode, buf.data_ptr(), buf.numel(), _stream_ptr(),
+               status_word(x.device).data_ptr())
+    return out
+
+
 def nvfp4_gemm(qa, sa, qb, sb, m: int, n: int, k: int, output_scale: Optional[torch.Tensor], *,
                out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if out is None:

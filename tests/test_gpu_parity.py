@@ -345,6 +345,61 @@ def test_nvfp4_decode_with_prequantized_weight(gpu, m):
     _assert_output(y32.bfloat16(), want)
 
 
+@pytest.mark.parametrize("shape", [(1, 8192), (8, 8192), (8, 8256), (64, 2048), (64, 8192), (100, 1000), (128, 4128),
+                                   (300, 8192)])
+@pytest.mark.parametrize("mode", ["exact", "power2"])
+def test_nvfp4_quantize_dynamic_equals_two_pass(gpu, shape, mode):
+    """The small-tensor route of the dynamic quantizer (two chained launches: per-CTA |max| partials,
+    then scale rule + quantize) gives the bytes of the separate |max| / finalize / quantize launches
+    (whole buffers, padding included) and of the oracle; (300, 8192) is above its size limit and takes
+    the three-launch route behind the same entry point."""
+    ops, N, dev, _ = gpu
+    rows, k = shape
+    torch.manual_seed(rows * 131 + k)
+    x = (torch.randn(rows, k) * 3).bfloat16()
+    x[0, 0] = 97.0
+    code = N.TENSOR_SCALE_EXACT if mode == "exact" else N.TENSOR_SCALE_POWER2
+    xd = x.to(dev)
+    other = torch.tensor([0.375], dtype=torch.float32, device=dev)
+    q, s, scale, prod = ops.nvfp4_quantize_dynamic(xd, code, other_scale=other)
+    scale2, prod2 = ops.nvfp4_tensor_scale(xd, code, other_scale=other)
+    q2, s2 = ops.nvfp4_quantize(xd, scale2)
+    _ok(ops, dev)
+    assert torch.equal(scale, scale2) and torch.equal(prod, prod2)
+    assert torch.equal(q, q2) and torch.equal(s, s2)
+    st = O.nvfp4_tensor_scale(x, mode)
+    assert float(scale.cpu()) == float(st)
+    qo, so = O.nvfp4_quantize(x, st)
+    assert torch.equal(q.cpu(), qo)
+    q_rm, s_rm, _, _ = ops.nvfp4_quantize_dynamic(xd, code, layout=N.SCALE_ROW_MAJOR)
+    assert torch.equal(q_rm, q2)
+    assert torch.equal(s_rm.cpu().view(rows, -1)[:, :so.shape[1]], so)
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 64, 128])
+@pytest.mark.parametrize("n", [1536, 19456])
+def test_nvfp4_linear_fwd_prequant_w(gpu, m, n):
+    """Decode entry point: packed weight + activations quantized on the fly, the GEMM launched as a
+    programmatic dependent of the quantizer.  Equal to the step-by-step route bit for bit and to the
+    oracle within the output tolerance; N = 19456 takes the 128 x 256 kernel, 1536 the streaming one."""
+    ops, N, dev, ws = gpu
+    k = 2048
+    inp = O.make_inputs(5, m=m, n=n, k=k)
+    x, w = inp["x"], inp["w"]
+    wd, xd = w.to(dev), x.to(dev)
+    w_scale = ops.nvfp4_tensor_scale(wd, N.TENSOR_SCALE_EXACT)
+    qw, sw = ops.nvfp4_quantize(wd, w_scale)
+    for _ in range(2):
+        y = ops.nvfp4_linear_fwd_prequant_w(xd, qw, sw, w_scale, n, ws, scale_mode=N.TENSOR_SCALE_EXACT)
+    x_scale, o_scale = ops.nvfp4_tensor_scale(xd, N.TENSOR_SCALE_EXACT, other_scale=w_scale)
+    qx, sx = ops.nvfp4_quantize(xd, x_scale)
+    y2 = ops.nvfp4_gemm(qx, sx, qw, sw, m, n, k, o_scale)
+    _ok(ops, dev)
+    assert torch.equal(y, y2)
+    want = O.nvfp4_linear(x, w, x_scale=O.nvfp4_tensor_scale(x, "exact"), w_scale=O.nvfp4_tensor_scale(w, "exact"))
+    _assert_output(y, want)
+
+
 @pytest.mark.parametrize("mnk", [(1, 64, 32), (128, 8192, 512), (100, 4100, 1000), (17, 63, 4096), (16, 19456, 256)])
 def test_mxfp8_skinny_shapes(gpu, mnk):
     ops, N, dev, ws = gpu
