@@ -115,6 +115,27 @@ int make_scale_map(CUtensorMap* map, const void* base, int64_t total_tiles, int 
   return RTXB_OK;
 }
 
+// scale tiles of B for the pair kernel: [2 halves][rows = 512-byte tiles][128 words], the second half
+// `delta_tiles` tiles after the first, so one box brings the tiles of both 128-row blocks behind a
+// 256-wide accumulator tile.  Rows are limited to those whose second half lies inside the buffer.
+int make_scale_map_halves(CUtensorMap* map, const void* base, int64_t total_tiles, int box_rows, int64_t delta_tiles) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[3] = {128u, static_cast<cuuint64_t>(total_tiles - delta_tiles), 2u};
+  cuuint64_t gstride[2] = {512u, static_cast<cuuint64_t>(delta_tiles) * 512u};
+  cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), 2u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(scale halves) failed with CUresult %d",
+             static_cast<int>(r));
+    return RTXB_E_DRIVER;
+  }
+  return RTXB_OK;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -208,6 +229,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.slots = 0;
   p.ks = 1;
   p.map3d = 0;
+  p.sfb3d = 0;
   p.overlap_previous = overlap_previous ? 1 : 0;
   {
     const char* dbg = getenv("RTXB_GEMM_DEBUG");
@@ -251,10 +273,26 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   }
   if (use_pair_kernel(p.m_tiles)) {
     using P = PairTraits<KIND>;
+    constexpr int KS = P::kStepsPerBarrierP;
     CUtensorMap map_sfa, map_sfb;
-    rc = make_scale_map(&map_sfa, sa, static_cast<int64_t>(p.m_tiles) * sf_k_chunks, P::kSfChunks);
+    // one load per operand brings the KS K steps of a barrier group
+    p.map3d = row_bytes % 128 == 0 ? 1 : 0;
+    if (p.map3d) {
+      rc = make_payload_map_ksteps(&map_a, qa, m, row_bytes, 128, KS);
+      if (rc) return rc;
+      rc = make_payload_map_ksteps(&map_b, qb, n_rows_b, row_bytes, 128, KS);
+      if (rc) return rc;
+    }
+    rc = make_scale_map(&map_sfa, sa, static_cast<int64_t>(p.m_tiles) * sf_k_chunks, KS * P::kSfChunks);
     if (rc) return rc;
-    rc = make_scale_map(&map_sfb, sb, (n_rows_b + 127) / 128 * sf_k_chunks, P::kSfChunks);
+    // both halves of a 256-wide tile in one box when the second half always exists
+    const int64_t b_blocks = (n_rows_b + 127) / 128;
+    const int64_t half_delta = glu_inter ? glu_inter / 128 : 1;
+    p.sfb3d = (glu_inter ? (glu_inter % 128 == 0 && n_rows_b == 2 * glu_inter) : (b_blocks % 2 == 0)) ? 1 : 0;
+    if (p.sfb3d)
+      rc = make_scale_map_halves(&map_sfb, sb, b_blocks * sf_k_chunks, KS * P::kSfChunks, half_delta * sf_k_chunks);
+    else
+      rc = make_scale_map(&map_sfb, sb, b_blocks * sf_k_chunks, KS * P::kSfChunks);
     if (rc) return rc;
     auto pk = gemm_blockscaled_pair_kernel<KIND, EPI>;
     cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmemBytes);

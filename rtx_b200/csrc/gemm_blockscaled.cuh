@@ -117,7 +117,9 @@ struct GemmParams {
   int a_box_rows;         // streaming kernel (M <= 128): rows of A fetched per K step (M rounded up to 8)
   int slots;              // streaming kernel: ring slots that fit shared memory with that A box
   int ks;                 // streaming kernel: K steps per ring slot
-  int map3d;              // streaming kernel: payload maps are [K/128][rows][128] views (one load per slot)
+  int map3d;              // streaming and pair kernels: payload maps are [K/128][rows][128] views (one load per
+                          // operand brings all K steps of a ring slot / barrier group)
+  int sfb3d;              // pair kernel: the scale map of B is 3-D, third coordinate = half of the 256-wide tile
   int overlap_previous;   // streaming kernel: launched as a programmatic dependent; A / SFA / out_scale may
                           // come from the grid before it, B / SFB do not
   int debug;              // experiments only (results invalid when set): bit0 = copy scale factors on the
@@ -270,20 +272,21 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
 // shared -> TMEM copy of one K step's scale factors into scale set `set`.
 // SFA tile c -> columns sfa + 4c; SFB (row block nb, tile c) -> sfb + 8c + 4nb.
 template <int KIND, bool PAIR>
-__device__ __forceinline__ void issue_scale_copy(uint32_t tmem_base, uint32_t ssfa, uint32_t ssfb, int set) {
+__device__ __forceinline__ void issue_scale_copy(uint32_t tmem_base, uint32_t ssfa, uint32_t ssfb0, uint32_t ssfb1,
+                                                 int set) {
+  // ssfb0 / ssfb1: scale tiles of the B rows behind accumulator columns [0,128) and [128,256)
   using TP = TmemPlan<KIND>;
-  constexpr int kSfaBytes = 512 * TP::kSfChunks;
   const uint32_t ta = tmem_base + TP::sfa_col(set), tb = tmem_base + TP::sfb_col(set);
 #pragma unroll
   for (int c = 0; c < TP::kSfChunks; ++c) {
     if (PAIR) {
       tc_cp_32x128b_warpx4_pair(ta + 4 * c, umma_desc_sf(ssfa + 512 * c));
-      tc_cp_32x128b_warpx4_pair(tb + 8 * c, umma_desc_sf(ssfb + 512 * c));
-      tc_cp_32x128b_warpx4_pair(tb + 8 * c + 4, umma_desc_sf(ssfb + kSfaBytes + 512 * c));
+      tc_cp_32x128b_warpx4_pair(tb + 8 * c, umma_desc_sf(ssfb0 + 512 * c));
+      tc_cp_32x128b_warpx4_pair(tb + 8 * c + 4, umma_desc_sf(ssfb1 + 512 * c));
     } else {
       tc_cp_32x128b_warpx4(ta + 4 * c, umma_desc_sf(ssfa + 512 * c));
-      tc_cp_32x128b_warpx4(tb + 8 * c, umma_desc_sf(ssfb + 512 * c));
-      tc_cp_32x128b_warpx4(tb + 8 * c + 4, umma_desc_sf(ssfb + kSfaBytes + 512 * c));
+      tc_cp_32x128b_warpx4(tb + 8 * c, umma_desc_sf(ssfb0 + 512 * c));
+      tc_cp_32x128b_warpx4(tb + 8 * c + 4, umma_desc_sf(ssfb1 + 512 * c));
     }
   }
 }
@@ -359,9 +362,13 @@ __device__ __forceinline__ void mma_issuer_loop(const GemmParams& p, uint8_t* sm
         for (int sub = 0; sub < KS; ++sub, ++step) {
           const int slot = group * KS + sub;
           const int set = step & 1;
+          // SFB in the ring: per slot [half 0 | half 1] (single-CTA kernel), or per barrier group
+          // [half 0 of its KS steps | half 1 of its KS steps] (pair kernel: one load brings a group's halves)
+          const uint32_t ssfb0 = PAIR ? smem_base + OFF_SFB + group * KS * SFB_BYTES + sub * SFA_BYTES
+                                      : smem_base + OFF_SFB + slot * SFB_BYTES;
+          const uint32_t ssfb1 = ssfb0 + (PAIR ? KS * SFA_BYTES : SFA_BYTES);
           if (!(p.debug & 1) || (kg == 0 && sub == 0))
-            issue_scale_copy<KIND, PAIR>(tmem_base, smem_base + OFF_SFA + slot * SFA_BYTES,
-                                         smem_base + OFF_SFB + slot * SFB_BYTES, set);
+            issue_scale_copy<KIND, PAIR>(tmem_base, smem_base + OFF_SFA + slot * SFA_BYTES, ssfb0, ssfb1, set);
           issue_k_step<KIND, PAIR>(tmem_base, acc_col, smem_base + slot * A_BYTES, smem_base + OFF_B + slot * B_BYTES,
                                    set, idesc, kg == 0 && sub == 0);
         }
@@ -650,21 +657,38 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
             break;
           }
           if (leader) {
+            // One instruction per operand and barrier group where the layout allows it: issuing a TMA
+            // instruction costs the issuing thread on the order of 100 clocks, and one K step of MMAs
+            // lasts 512.  Payloads: [K/128][rows][128] views (KS steps per load) when rows are 128-byte
+            // multiples.  Scale tiles: KS steps of a row block are consecutive rows of the scale maps, and
+            // the two B halves are one 3-D box (third coordinate = half).
             const uint32_t full_addr = mapa_shared(smem_u32(&full_bar[group]), 0);
             if (rank == 0) mbar_expect_tx(&full_bar[group], 2 * KS * T::kTxBytesPerCta);
+            const int slot0 = group * KS;
+            const int kt0 = kg * KS;   // past the end of K: zero payload (TMA fill), any finite scales
+            if (p.map3d) {
+              tma_load_3d_pair(smem + slot0 * T::kABytes, &map_a, full_addr, 0, m_blk * 128, kt0);
+              tma_load_3d_pair(smem + T::kOffB + slot0 * T::kBBytes, &map_b, full_addr, 0, b_mine * 128, kt0);
+            } else {
 #pragma unroll
-            for (int sub = 0; sub < KS; ++sub) {
-              const int slot = group * KS + sub;
-              const int kt = kg * KS + sub;   // past the end of K: zero payload (TMA fill), any finite scales
-              tma_load_2d_pair(smem + slot * T::kABytes, &map_a, full_addr, kt * kBlockKBytes, m_blk * 128);
-              tma_load_2d_pair(smem + T::kOffB + slot * T::kBBytes, &map_b, full_addr, kt * kBlockKBytes, b_mine * 128);
-              // scale tiles: rows of the maps are 512-byte tiles, [row block][K tile]
-              const int sf_col = kt * T::kSfChunks;
-              tma_load_2d_pair(smem + T::kOffSfa + slot * T::kSfaBytes, &map_sfa, full_addr, 0,
-                               m_blk * p.sf_k_chunks + sf_col);
-              tma_load_2d_pair(smem + T::kOffSfb + slot * T::kSfbBytes, &map_sfb, full_addr, 0,
+              for (int sub = 0; sub < KS; ++sub) {
+                tma_load_2d_pair(smem + (slot0 + sub) * T::kABytes, &map_a, full_addr, (kt0 + sub) * kBlockKBytes,
+                                 m_blk * 128);
+                tma_load_2d_pair(smem + T::kOffB + (slot0 + sub) * T::kBBytes, &map_b, full_addr,
+                                 (kt0 + sub) * kBlockKBytes, b_mine * 128);
+              }
+            }
+            // scale tiles: rows of the maps are 512-byte tiles, [row block][K tile]
+            const int sf_col = kt0 * T::kSfChunks;
+            tma_load_2d_pair(smem + T::kOffSfa + slot0 * T::kSfaBytes, &map_sfa, full_addr, 0,
+                             m_blk * p.sf_k_chunks + sf_col);
+            if (p.sfb3d) {
+              tma_load_3d_pair(smem + T::kOffSfb + slot0 * T::kSfbBytes, &map_sfb, full_addr, 0,
+                               b_blk0 * p.sf_k_chunks + sf_col, 0);
+            } else {
+              tma_load_2d_pair(smem + T::kOffSfb + slot0 * T::kSfbBytes, &map_sfb, full_addr, 0,
                                b_blk0 * p.sf_k_chunks + sf_col);
-              tma_load_2d_pair(smem + T::kOffSfb + slot * T::kSfbBytes + T::kSfaBytes, &map_sfb, full_addr, 0,
+              tma_load_2d_pair(smem + T::kOffSfb + slot0 * T::kSfbBytes + KS * T::kSfaBytes, &map_sfb, full_addr, 0,
                                b_blk1 * p.sf_k_chunks + sf_col);
             }
           }
