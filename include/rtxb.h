@@ -59,6 +59,13 @@ const char* rtxb_error_string(int code);
 /* last CUDA/driver error text recorded by this thread's most recent failing call */
 const char* rtxb_last_cuda_error(void);
 
+/* SMs that the persistent kernels of this library leave unused from now on (process-wide; 0 =
+ * use every SM).  No counterpart in the reference (single GPU): the GEMMs here hold every SM for
+ * their whole run, so a collective that should overlap one (the NCCL all-reduce of dW beside the dX
+ * GEMM) only gets to run if some SMs are left to it. */
+int rtxb_set_sm_margin(int sms);
+int rtxb_get_sm_margin(void);
+
 /* ---- sizes ------------------------------------------------------------- */
 
 /* padded K: 32-multiples (rtx/kernels/mxfp8.py:57-66, rtx/configs/nvfp4.py:15-28) */

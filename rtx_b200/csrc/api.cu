@@ -10,6 +10,8 @@
 
 #include "gemm_blockscaled.cuh"
 #include "gemm_skinny.cuh"
+
+#include <atomic>
 #include "quant.cuh"
 
 using namespace rtxb;
@@ -136,16 +138,23 @@ int make_scale_map_halves(CUtensorMap* map, const void* base, int64_t total_tile
   return RTXB_OK;
 }
 
+// SMs the persistent kernels leave free (for a collective that runs beside them); process-wide
+std::atomic<int> g_sm_margin{0};
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+  int n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    if (cached[dev] == 0) {
+      int q = 0;
+      if (cudaDeviceGetAttribute(&q, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || q <= 0) q = 148;
+      cached[dev] = q;
+    }
+    n = cached[dev];
   }
-  return cached[dev];
+  const int usable = n - g_sm_margin.load(std::memory_order_relaxed);
+  return usable < 2 ? 2 : usable;
 }
 
 // launch `kernel` so that it may start while the kernel before it on the stream is still running
@@ -354,6 +363,13 @@ struct Carver {
 extern "C" {
 
 int rtxb_version(void) { return 100; }
+
+int rtxb_set_sm_margin(int sms) {
+  if (sms < 0 || sms > 128) return fail_msg(RTXB_E_INVALID_ARGUMENT, "SM margin must be in [0, 128]");
+  g_sm_margin.store(sms, std::memory_order_relaxed);
+  return RTXB_OK;
+}
+int rtxb_get_sm_margin(void) { return g_sm_margin.load(std::memory_order_relaxed); }
 
 const char* rtxb_error_string(int code) {
   switch (code) {

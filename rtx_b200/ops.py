@@ -215,6 +215,28 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
 
 
 # ---------------------------------------------------------------------------
+# SM margin
+# ---------------------------------------------------------------------------
+
+class sm_margin:
+    """Context manager: the library's persistent kernels launched inside leave `sms` SMs unused, so
+    that a collective running beside them (NCCL all-reduce of dW during the dX GEMM) gets to run.
+    Process-wide setting (one process per GPU); restored on exit."""
+
+    def __init__(self, sms: int):
+        self.sms, self.prev = int(sms), 0
+
+    def __enter__(self):
+        self.prev = N.query("rtxb_get_sm_margin")
+        N.call("rtxb_set_sm_margin", self.sms)
+        return self
+
+    def __exit__(self, *exc):
+        N.call("rtxb_set_sm_margin", self.prev)
+        return False
+
+
+# ---------------------------------------------------------------------------
 # NVFP4
 # ---------------------------------------------------------------------------
 
