@@ -184,6 +184,32 @@ int rtxb_nvfp4_quantize(const void* src_bf16, int64_t rows, int64_t k, int64_t l
 int rtxb_nvfp4_quantize_dynamic(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, int mode, void* q,
                                 void* scales, int scale_layout, float* scale_out, const float* other_scale,
                                 float* out_scale, void* amax_scratch, void* stream);
+/* ---- NVFP4 row-region policy (scaling="jit_row_region", the reference's default) ----------
+ * compile_nvfp4_jit_region_dual_quant(x_rows, weight_rows, k, cfg, x_region_rows, weight_region_rows,
+ * tensor_scale_mode, ...) -> (x, w, qx, qw, sx, sw, region_scales)   rtx/kernels/nvfp4_quant.py:1623-1678,
+ * kernel NVFP4JITRegionDualQuantKernel :667-1000; bound at rtx/fp4.py:817-830.
+ * One FP32 outer scale per `region_rows` consecutive rows, the tensor-scale rule applied to the
+ * region's current |max|.  Here per operand: rtxb_nvfp4_region_scales (one warp per region; a single
+ * region = the whole tensor takes the grid-wide reduction and needs the 4-byte amax_scratch), then
+ * rtxb_nvfp4_quantize_regions.  region_rows must divide rows. */
+int rtxb_nvfp4_region_scales(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, int64_t region_rows, int mode,
+                             void* amax_scratch, float* scales_out, void* stream);
+int rtxb_nvfp4_quantize_regions(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                                int scale_layout, const float* region_scales, int64_t region_rows, void* stream);
+/* compile_nvfp4_jit_region_gemm(problem, cfg, x_region_rows, weight_region_rows) ->
+ * (qx, qw, sx, sw, out bf16, region_scales)   rtx/kernels/nvfp4_gemm.py; epilogue
+ * rtx/kernels/mxfp8_gemm.py:1720-1760: out[m,n] = bf16(acc * (xs[m / Rx] * ws[n / Rw])). */
+int rtxb_nvfp4_gemm_regions(const void* qa, const void* sa, const void* qb, const void* sb, void* out_bf16, int64_t m,
+                            int64_t n, int64_t k, int64_t ldo, const float* x_region_scales, int64_t x_region_rows,
+                            const float* w_region_scales, int64_t w_region_rows, void* stream, int* status);
+/* _JITRegionDynamicRunner (rtx/fp4.py:522-560, built at :758-845).  Region sizes are requests: one
+ * that does not split the operand's rows evenly into more than one region falls back to a single
+ * region over the tensor (rtx/fp4.py:89-94). */
+size_t rtxb_nvfp4_linear_regions_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t x_region_rows,
+                                                 int64_t w_region_rows);
+int rtxb_nvfp4_linear_fwd_regions(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n,
+                                  int64_t k, int64_t x_region_rows, int64_t w_region_rows, int scale_mode,
+                                  void* workspace, size_t workspace_bytes, void* stream, int* status);
 /* compile_nvfp4_gemm(problem, cfg) -> (qx, qw, sx, sw, out bf16, output_scale f32[1])
  *   rtx/kernels/nvfp4_gemm.py:22-64, epilogue rtx/kernels/mxfp8_gemm.py:779-781;
  *   bound at rtx/fp4.py:707, :901, :1734, :2313.  output_scale NULL = 1 (block GEMM). */

@@ -233,11 +233,11 @@ class NVFP4QuantConfig(_Config):
 @dataclass(frozen=True)
 class NVFP4ScaleConfig(_Config):
     """Outer-scale policy (rtx/configs/nvfp4.py `NVFP4ScaleConfig`)."""
-    policy: str = "current"            # current | block   (jit_row_region, delayed: not built)
+    policy: str = "current"            # current | jit_row_region | block   (delayed: not built)
     tensor_scale_mode: str = "power2"  # power2 (dynamic default) | exact (offline weights)
 
     def rejection(self) -> Optional[str]:
-        if self.policy not in ("current", "block"):
+        if self.policy not in ("current", "jit_row_region", "block"):
             return f"NVFP4 scaling policy {self.policy!r} is not built for sm_100a yet"
         if self.tensor_scale_mode not in ("power2", "exact"):
             return f"unknown tensor scale mode {self.tensor_scale_mode!r}"
@@ -265,8 +265,22 @@ class NVFP4DynamicConfig(_Config):
     quant: NVFP4QuantConfig = field(default_factory=NVFP4QuantConfig)
     gemm: NVFP4GemmConfig = field(default_factory=NVFP4GemmConfig)
     scale: NVFP4ScaleConfig = field(default_factory=NVFP4ScaleConfig)
+    # row-region policy: rows per outer scale of each operand; both zero for the other policies
+    # (rtx/configs/nvfp4.py:325-360)
+    x_scale_region_rows: int = 0
+    weight_scale_region_rows: int = 0
+
+    @property
+    def jit_row_region(self) -> bool:
+        return bool(self.x_scale_region_rows or self.weight_scale_region_rows)
 
     def rejection(self, problem: Optional[NVFP4Problem] = None) -> Optional[str]:
+        if bool(self.x_scale_region_rows) != bool(self.weight_scale_region_rows):
+            return "row-region scaling needs a region size for both operands"
+        if self.jit_row_region and (self.x_scale_region_rows < 1 or self.weight_scale_region_rows < 1):
+            return "region rows must be positive"
+        if self.jit_row_region != (self.scale.policy == "jit_row_region"):
+            return "region sizes go with the jit_row_region policy and only with it"
         return self.quant.rejection() or self.scale.rejection() or self.gemm.rejection(problem)
 
 

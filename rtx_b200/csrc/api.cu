@@ -201,11 +201,18 @@ bool use_skinny_kernel(int m_tiles, int64_t n_rows_b) {
   return (n_rows_b + kBlockN - 1) / kBlockN < 74;
 }
 
+// outer scales of the NVFP4 row-region policy (kEpiRegionBf16)
+struct RegionScales {
+  const float* x;
+  const float* w;
+  int x_rows, w_rows;
+};
+
 template <int KIND, int EPI>
 int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
                 int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
                 const float* out_scale, cudaStream_t stream, int* status, void* q_out = nullptr,
-                void* sf_out = nullptr, bool overlap_previous = false) {
+                void* sf_out = nullptr, bool overlap_previous = false, const RegionScales* regions = nullptr) {
   // overlap_previous: B and its scales do not depend on the kernel launched just before this one on
   // the stream, so the streaming kernel may start fetching them while that kernel is still running
   using T = GemmTraits<KIND>;
@@ -230,6 +237,10 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.out_cols = static_cast<int>(out_cols);
   p.out_vec_ok = (aligned(out, 16) && (ldo * (EPI == kEpiF32 ? 4 : 2)) % 16 == 0) ? 1 : 0;
   p.out_scale = out_scale;
+  p.x_region_scales = regions ? regions->x : nullptr;
+  p.w_region_scales = regions ? regions->w : nullptr;
+  p.x_region_rows = regions ? regions->x_rows : 1;
+  p.w_region_rows = regions ? regions->w_rows : 1;
   p.q_out = static_cast<uint8_t*>(q_out);
   p.sf_out = static_cast<uint8_t*>(sf_out);
   p.sf_out_chunks = static_cast<int>((out_cols / 32 + 3) / 4);
@@ -244,7 +255,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     const char* dbg = getenv("RTXB_GEMM_DEBUG");
     p.debug = dbg ? atoi(dbg) : 0;
   }
-  if (use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI)) {
+  if (use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI) && EPI != kEpiRegionBf16) {
     // one 128-row block of A: the bandwidth-shaped 128 x 64 kernel streams B once over all SMs
     using S = SkinnyTraits<KIND>;
     p.a_box_rows = static_cast<int>(round_up(m, 8));
@@ -652,6 +663,8 @@ int rtxb_nvfp4_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, vo
   p.q = static_cast<uint8_t*>(q);
   p.scales = static_cast<uint8_t*>(scales);
   p.tensor_scale = tensor_scale;
+  p.region_scales = nullptr;
+  p.region_rows = 0;
   p.rows = static_cast<int>(rows);
   p.k = static_cast<int>(k);
   p.kp = static_cast<int>(round_up(k, 32));
@@ -695,6 +708,8 @@ int rtxb_nvfp4_quantize_dynamic(const void* src, int64_t rows, int64_t k, int64_
   dp.q.q = static_cast<uint8_t*>(q);
   dp.q.scales = static_cast<uint8_t*>(scales);
   dp.q.tensor_scale = nullptr;
+  dp.q.region_scales = nullptr;
+  dp.q.region_rows = 0;
   dp.q.rows = static_cast<int>(rows);
   dp.q.k = static_cast<int>(k);
   dp.q.kp = static_cast<int>(kp);
@@ -715,6 +730,78 @@ int rtxb_nvfp4_quantize_dynamic(const void* src, int64_t rows, int64_t k, int64_
   e = launch_dependent(quant_nvfp4_dynamic_kernel, static_cast<int>(tiles), kQuantThreads, 0, s, true, dp);
   if (e != cudaSuccess) return fail_cuda(e, "quant_nvfp4_dynamic_kernel launch");
   return RTXB_OK;
+}
+
+int rtxb_nvfp4_region_scales(const void* src, int64_t rows, int64_t k, int64_t ld, int64_t region_rows, int mode,
+                             void* amax_scratch, float* scales_out, void* stream) {
+  if (!src || !scales_out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (region_rows <= 0 || rows % region_rows) return fail_msg(RTXB_E_INVALID_ARGUMENT, "region_rows must divide rows");
+  if (mode != RTXB_TENSOR_SCALE_EXACT && mode != RTXB_TENSOR_SCALE_POWER2)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown tensor scale mode");
+  if (rows > INT32_MAX || k > INT32_MAX) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (region_rows == rows) {
+    // one region = the tensor: the grid-wide reduction
+    if (!amax_scratch) return fail_msg(RTXB_E_INVALID_ARGUMENT, "amax_scratch is needed for a single region");
+    return rtxb_nvfp4_tensor_scale(src, rows, k, ld, mode, amax_scratch, scales_out, nullptr, nullptr, stream);
+  }
+  const int64_t regions = rows / region_rows;
+  const int64_t ctas = (regions + 7) / 8;   // one warp per region, eight warps per CTA
+  const int grid = static_cast<int>(ctas < sm_count() * 8 ? ctas : sm_count() * 8);
+  amax_regions_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), static_cast<int>(rows), static_cast<int>(k), ld,
+      static_cast<int>(region_rows), mode, scales_out);
+  RTXB_CHECK_LAUNCH("amax_regions_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_nvfp4_quantize_regions(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                                int scale_layout, const float* region_scales, int64_t region_rows, void* stream) {
+  if (!src || !q || !scales || !region_scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (region_rows <= 0 || rows % region_rows) return fail_msg(RTXB_E_INVALID_ARGUMENT, "region_rows must divide rows");
+  if (rows > INT32_MAX || k > INT32_MAX - 512) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!aligned(q, 16)) return fail_msg(RTXB_E_ALIGNMENT, "q must be 16-byte aligned");
+  if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  QuantNvParams p;
+  p.src = static_cast<const __nv_bfloat16*>(src);
+  p.q = static_cast<uint8_t*>(q);
+  p.scales = static_cast<uint8_t*>(scales);
+  p.tensor_scale = nullptr;
+  p.region_scales = region_scales;
+  p.region_rows = static_cast<int>(region_rows);
+  p.rows = static_cast<int>(rows);
+  p.k = static_cast<int>(k);
+  p.kp = static_cast<int>(round_up(k, 32));
+  p.ld = ld;
+  p.nb = p.kp / 16;
+  p.sf_chunks = static_cast<int>(round_up((p.nb + 3) / 4, 4));
+  p.layout = scale_layout;
+  const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 255) / 256);
+  quant_nvfp4_regions_kernel<<<quant_grid(tiles, 4), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RTXB_CHECK_LAUNCH("quant_nvfp4_regions_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_nvfp4_gemm_regions(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m,
+                            int64_t n, int64_t k, int64_t ldo, const float* x_region_scales, int64_t x_region_rows,
+                            const float* w_region_scales, int64_t w_region_rows, void* stream, int* status) {
+  int rc = check_gemm_args(qa, sa, qb, sb, out, m, n, k, ldo, n, 2);
+  if (rc) return rc;
+  if (!x_region_scales || !w_region_scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null region scales");
+  if (x_region_rows <= 0 || m % x_region_rows || w_region_rows <= 0 || n % w_region_rows)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "region rows must divide the operand's rows");
+  const int64_t kp = round_up(k, 32);
+  const int64_t chunks = round_up((kp / 16 + 3) / 4, 4);
+  const RegionScales rs{x_region_scales, w_region_scales, static_cast<int>(x_region_rows),
+                        static_cast<int>(w_region_rows)};
+  return launch_gemm<kKindNvfp4, kEpiRegionBf16>(qa, sa, qb, sb, out, m, n, kp / 2, chunks, ldo, n, 0, nullptr,
+                                                 static_cast<cudaStream_t>(stream), status, nullptr, nullptr, false,
+                                                 &rs);
 }
 
 int rtxb_nvfp4_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
@@ -800,6 +887,55 @@ int rtxb_nvfp4_linear_fwd_prequant_w(const void* x, const void* qw, const void* 
   const int64_t chunks = round_up((kp / 16 + 3) / 4, 4);
   return launch_gemm<kKindNvfp4, kEpiBf16>(qx, sx, qw, sw, out, m, n, kp / 2, chunks, n, n, 0, o_scale,
                                            static_cast<cudaStream_t>(stream), status, nullptr, nullptr, true);
+}
+
+namespace {
+// rows per region actually used: the request when it splits the rows evenly into more than one region,
+// else one region over the whole tensor (rtx/fp4.py:89-94)
+int64_t effective_region_rows(int64_t rows, int64_t requested) {
+  if (requested <= 0 || rows <= requested || rows % requested) return rows;
+  return requested;
+}
+}  // namespace
+
+size_t rtxb_nvfp4_linear_regions_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t x_region_rows,
+                                                 int64_t w_region_rows) {
+  Carver c(nullptr);
+  const int64_t kp = round_up(k, 32);
+  c.take(256);
+  c.take(4 * (m / effective_region_rows(m, x_region_rows)));
+  c.take(4 * (n / effective_region_rows(n, w_region_rows)));
+  c.take(m * kp / 2);
+  c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  c.take(n * kp / 2);
+  c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  return c.off;
+}
+
+int rtxb_nvfp4_linear_fwd_regions(const void* x, const void* w, void* out, int64_t m, int64_t n, int64_t k,
+                                  int64_t x_region_rows, int64_t w_region_rows, int scale_mode, void* workspace,
+                                  size_t workspace_bytes, void* stream, int* status) {
+  if (m <= 0 || n <= 0 || k <= 0) return fail_msg(RTXB_E_INVALID_ARGUMENT, "m, n, k must be positive");
+  if (!workspace ||
+      workspace_bytes < rtxb_nvfp4_linear_regions_workspace_bytes(m, n, k, x_region_rows, w_region_rows))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_nvfp4_linear_fwd_regions");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  const int64_t rx = effective_region_rows(m, x_region_rows), rw = effective_region_rows(n, w_region_rows);
+  Carver c(workspace);
+  const int64_t kp = round_up(k, 32);
+  uint8_t* scal = c.take(256);
+  float* xs = reinterpret_cast<float*>(c.take(4 * (m / rx)));
+  float* wsc = reinterpret_cast<float*>(c.take(4 * (n / rw)));
+  uint8_t* qx = c.take(m * kp / 2);
+  uint8_t* sx = c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  uint8_t* qw = c.take(n * kp / 2);
+  uint8_t* sw = c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  int rc;
+  if ((rc = rtxb_nvfp4_region_scales(x, m, k, k, rx, scale_mode, scal, xs, stream))) return rc;
+  if ((rc = rtxb_nvfp4_region_scales(w, n, k, k, rw, scale_mode, scal + 4, wsc, stream))) return rc;
+  if ((rc = rtxb_nvfp4_quantize_regions(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, xs, rx, stream))) return rc;
+  if ((rc = rtxb_nvfp4_quantize_regions(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, wsc, rw, stream))) return rc;
+  return rtxb_nvfp4_gemm_regions(qx, sx, qw, sw, out, m, n, k, n, xs, rx, wsc, rw, stream, status);
 }
 
 #ifdef RTXB_TRACE

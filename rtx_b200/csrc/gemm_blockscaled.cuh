@@ -34,7 +34,8 @@ enum GemmEpilogue : int {
   kEpiBf16 = 0,   // D bf16 = acc * out_scale
   kEpiF32 = 1,    // D f32  = acc * out_scale
   kEpiGluBf16 = 2, // D bf16[M, N/2] = silu(acc[:, gate]) * acc[:, up]
-  kEpiGluMx = 3    // the same H, also (or only) emitted as MXFP8: E4M3 payload + E8M0 scale tiles
+  kEpiGluMx = 3,   // the same H, also (or only) emitted as MXFP8: E4M3 payload + E8M0 scale tiles
+  kEpiRegionBf16 = 4  // D bf16 = acc * (x_region_scale[row / Rx] * w_region_scale[col / Rw])  (NVFP4 row-region policy)
 };
 __host__ __device__ constexpr bool epi_is_glu(int epi) { return epi == kEpiGluBf16 || epi == kEpiGluMx; }
 
@@ -110,6 +111,9 @@ struct GemmParams {
   int out_cols;           // n, or inter for GLU
   int out_vec_ok;         // 1 when out and its row pitch are 16-byte aligned (vector stores allowed)
   const float* out_scale; // device scalar or nullptr (= 1)
+  const float* x_region_scales;  // kEpiRegionBf16: FP32 outer scale per x_region_rows rows of A
+  const float* w_region_scales;  // kEpiRegionBf16: FP32 outer scale per w_region_rows rows of B (output columns)
+  int x_region_rows, w_region_rows;
   uint8_t* q_out;         // kEpiGluMx: E4M3 payload of H, [M, out_cols] (out may then be nullptr)
   uint8_t* sf_out;        // kEpiGluMx: E8M0 scales of H in 128-row tiles, sf_out_chunks tiles per row block
   int sf_out_chunks;
@@ -238,7 +242,35 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
       }
       if (!row_ok) continue;
       const int col = col_base + c;
-      if (EPI == kEpiBf16) {
+      if (EPI == kEpiRegionBf16) {
+        // the product of the row's and the column's region scale is formed first, then applied to the
+        // accumulator (rtx/kernels/mxfp8_gemm.py:1720-1760); `out_scale` carries this row's scale.
+        // Column scales are the same for every thread of the warp (broadcast loads).
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+        const int last_region = (p.out_cols - 1) / p.w_region_rows;
+        int widx = col / p.w_region_rows, wrem = col - widx * p.w_region_rows;
+        float factor = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
+#pragma unroll
+        for (int v = 0; v < 32; v += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float f[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              f[h] = __uint_as_float(r[v + 2 * e + h]) * factor;
+              if (++wrem == p.w_region_rows) {
+                wrem = 0;
+                ++widx;
+                factor = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
+              }
+            }
+            __nv_bfloat162 b = __floats2bfloat162_rn(f[0], f[1]);
+            w[e] = *reinterpret_cast<uint32_t*>(&b);
+          }
+          store_bf16x8(out, col + v, p.out_cols, p.out_vec_ok != 0, w);
+        }
+      } else if (EPI == kEpiBf16) {
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
 #pragma unroll
         for (int v = 0; v < 32; v += 8) {
@@ -531,8 +563,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         break;
       }
       tc_fence_after_sync();
+      // row-region policy: the row's own outer scale takes the place of the launch-wide output scale
+      const float row_scale = (EPI == kEpiRegionBf16 && row_ok) ? __ldg(p.x_region_scales + row / p.x_region_rows)
+                                                                : out_scale;
       epilogue_drain<KIND, EPI>(p, tmem_base + lane_base + acc_col, row, row_ok, n_idx, (local_tile & 1) != 0,
-                                smem_u32(acc_overlap_bar), out_scale, lane);
+                                smem_u32(acc_overlap_bar), row_scale, lane);
     }
   }
 
@@ -725,8 +760,10 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
         break;
       }
       tc_fence_after_sync();
+      const float row_scale = (EPI == kEpiRegionBf16 && row_ok) ? __ldg(p.x_region_scales + row / p.x_region_rows)
+                                                                : out_scale;
       epilogue_drain<KIND, EPI>(p, tmem_base + lane_base + acc_col, row, row_ok, n_idx, (local_tile & 1) != 0,
-                                overlap_addr, out_scale, lane);
+                                overlap_addr, row_scale, lane);
     }
   }
 

@@ -323,6 +323,8 @@ struct QuantNvParams {
   uint8_t* q;
   uint8_t* scales;
   const float* tensor_scale;  // device scalar, nullptr = 1.0 (block policy)
+  const float* region_scales; // row-region policy: outer scale of rows [i * region_rows, (i + 1) * region_rows)
+  int region_rows;            // 0 = one scale for the tensor (tensor_scale)
   int rows, k, kp;
   int64_t ld;
   int nb;         // kp / 16
@@ -351,7 +353,9 @@ __device__ __forceinline__ QuantNvTileCtx quant_nvfp4_ctx(const QuantNvParams& p
   return c;
 }
 
-// one 128 x 256 tile: payload bytes and the tile's scale bytes (block-wide: ends with a barrier)
+// one 128 x 256 tile: payload bytes and the tile's scale bytes (block-wide: ends with a barrier).
+// REGION: the outer scale is looked up per row (row-region policy) instead of being one per tensor.
+template <bool REGION = false>
 __device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const QuantNvTileCtx& c, int tile,
                                                  uint8_t (*tile_scales)[16]) {
   const int row0 = (tile / c.col_tiles) * 128;
@@ -382,10 +386,16 @@ __device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const Q
       float a = fabsf(v[0]);
 #pragma unroll
       for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
-      float rawscale = __fdiv_rn(a, c.six_st);
+      float six_st = c.six_st, inv_st = c.inv_st;
+      if (REGION) {
+        const float st = live ? __ldg(p.region_scales + row / p.region_rows) : 1.0f;
+        six_st = 6.0f * st;
+        inv_st = __fdiv_rn(1.0f, st);
+      }
+      float rawscale = __fdiv_rn(a, six_st);
       rawscale = fmin_nan(fmax_nan(rawscale, 0.015625f), 448.0f);
       const uint32_t sb = cvt_e4m3x2(rawscale, rawscale) & 0xFF;
-      const float recip = __fdiv_rn(c.inv_st, e4m3_to_float(sb));
+      const float recip = __fdiv_rn(inv_st, e4m3_to_float(sb));
       tile_scales[r][c.sub] = live ? static_cast<uint8_t>(sb) : 0;
       if (live) {
         uint32_t w0 = 0, w1 = 0;
@@ -409,6 +419,57 @@ __global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_rows_kernel(cons
   const QuantNvTileCtx c = quant_nvfp4_ctx(p, st);
   const int row_tiles = (p.rows + 127) / 128;
   for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x) quant_nvfp4_tile(p, c, tile, tile_scales);
+}
+
+// ---------------------------------------------------------------------------
+// Row-region policy (the reference's default NVFP4 scaling, NVFP4JITRegionDualQuantKernel,
+// rtx/kernels/nvfp4_quant.py:667-1000): one FP32 outer scale per region of `region_rows` consecutive
+// rows, from the region's current |max|.  Here: one warp reduces a region and applies the scale rule
+// (amax_regions_kernel), then the tiled quantizer looks the scale up per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) amax_regions_kernel(const __nv_bfloat16* src, int rows, int k, int64_t ld,
+                                                           int region_rows, int mode, float* region_scales) {
+  const int regions = rows / region_rows;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const bool vec_ok = (ld % 8 == 0) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (int region = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; region < regions; region += warps) {
+    uint32_t m = 0;
+    for (int r = 0; r < region_rows; ++r) {
+      const __nv_bfloat16* rp = src + static_cast<int64_t>(region * region_rows + r) * ld;
+      if (vec_ok) {
+        const int vecs = k / 8;
+        for (int i0 = lane; i0 < vecs; i0 += 128) {   // four 16-byte loads in flight per lane
+          uint4 raw[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            raw[j] = i0 + 32 * j < vecs ? __ldg(reinterpret_cast<const uint4*>(rp) + i0 + 32 * j) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+              m = max(m, w[e] & 0x7FFF0000u);
+            }
+          }
+        }
+      } else {
+        const uint16_t* sp = reinterpret_cast<const uint16_t*>(rp);
+        for (int i = lane; i < k; i += 32) m = max(m, (static_cast<uint32_t>(sp[i]) << 16) & 0x7FFFFFFFu);
+      }
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if (lane == 0) region_scales[region] = nvfp4_scale_from_amax_bits(m, mode);
+  }
+}
+
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_regions_kernel(const QuantNvParams p) {
+  __shared__ __align__(16) uint8_t tile_scales[128][16];
+  const QuantNvTileCtx c = quant_nvfp4_ctx(p, 1.0f);
+  const int row_tiles = (p.rows + 127) / 128;
+  for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x)
+    quant_nvfp4_tile<true>(p, c, tile, tile_scales);
 }
 
 // ---------------------------------------------------------------------------

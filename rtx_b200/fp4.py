@@ -5,9 +5,11 @@ custom ops, with the reference's signatures (rtx/fp4.py:1501-1540, :1543-1973,
 Numerics (PRECISION_POLICY of the reference): NVFP4 forward — E2M1 payload, E4M3
 scale per 16 values, FP32 per-tensor outer scale — and MXFP8 backward on the saved
 BF16 operands (rtx/fp4.py:1772-1794).  Scaling policies built for sm_100a:
-`current` (outer scale from the tensor's present |max|; power-of-two for dynamic
-operands, exact `amax/2688` for offline weights) and `block` (outer scale 1).
-`jit_row_region` and `delayed` are not built yet and raise NotImplementedError.
+`jit_row_region` (the default for dynamic operands: one outer scale per region of
+rows, from the region's present |max|), `current` (outer scale from the tensor's
+present |max|; power-of-two for dynamic operands, exact `amax/2688` for offline
+weights) and `block` (outer scale 1).  `delayed` is not built yet and raises
+NotImplementedError.
 """
 
 from __future__ import annotations
@@ -197,6 +199,42 @@ def _(x, weight, key, bwd_key):
 nvfp4_linear_block_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
 
 
+def _jit_row_region_forward(x, weight, key):
+    cfg = _resolve_dynamic(key)
+    if not cfg.jit_row_region:
+        raise RuntimeError("the forward schedule carries no region geometry")
+    x = x if x.is_contiguous() else x.contiguous()
+    weight = weight if weight.is_contiguous() else weight.contiguous()
+    return ops.nvfp4_linear_fwd_regions(x, weight, _fp8._workspace(x.device), cfg.x_scale_region_rows,
+                                        cfg.weight_scale_region_rows,
+                                        scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_jit_row_region_fwd", mutates_args=(), device_types="cuda")
+def nvfp4_linear_jit_row_region_fwd(x: torch.Tensor, weight: torch.Tensor, key: str) -> torch.Tensor:
+    """`jit_row_region` policy: per-region outer scales observed and applied inside the call
+    (rtx/fp4.py:1604-1626, _JITRegionDynamicRunner :522-560); region sizes travel in the config key."""
+    return _jit_row_region_forward(x, weight, key)
+
+
+@nvfp4_linear_jit_row_region_fwd.register_fake
+def _(x, weight, key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("rtx::nvfp4_linear_jit_row_region_train", mutates_args=(), device_types="cuda")
+def nvfp4_linear_jit_row_region_train(x: torch.Tensor, weight: torch.Tensor, key: str, bwd_key: str) -> torch.Tensor:
+    return _jit_row_region_forward(x, weight, key)
+
+
+@nvfp4_linear_jit_row_region_train.register_fake
+def _(x, weight, key, bwd_key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+nvfp4_linear_jit_row_region_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
+
+
 @torch.library.custom_op("rtx::nvfp4_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
 def nvfp4_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor, weight_block_scales: torch.Tensor,
                                       x_scale: torch.Tensor, output_scale: torch.Tensor, n: int, k: int, layout: str,
@@ -249,11 +287,26 @@ def _bwd_key(backward_config):
     return (backward_config or MXFP8BwdConfig()).to_key()
 
 
+def _resolve_scale_region_rows(shared, x_rows, weight_rows):
+    """The shared override or the asymmetric defaults X = 5, W = 4 (rtx/fp4.py:61-86)."""
+    if shared is not None and shared <= 0:
+        raise ValueError("scale_region_rows must be positive")
+    rx = x_rows if x_rows is not None else shared if shared is not None else DEFAULT_NVFP4_X_SCALE_REGION_ROWS
+    rw = (weight_rows if weight_rows is not None else shared if shared is not None
+          else DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS)
+    if rx <= 0 or rw <= 0:
+        raise ValueError("X and weight scale-region rows must be positive")
+    return int(rx), int(rw)
+
+
 @torch._dynamo.assume_constant_result
-def _dynamic_key(dynamic_config, scale_config, scaling):
+def _dynamic_key(dynamic_config, scale_config, scaling, region_rows=(0, 0)):
+    region = scaling == "jit_row_region"
     cfg = dynamic_config or NVFP4DynamicConfig(
         scale=scale_config or NVFP4ScaleConfig(policy=scaling,
-                                               tensor_scale_mode="power2" if scaling == "current" else "exact"))
+                                               tensor_scale_mode="exact" if scaling == "block" else "power2"),
+        x_scale_region_rows=region_rows[0] if region else 0,
+        weight_scale_region_rows=region_rows[1] if region else 0)
     rejection = cfg.rejection()
     if rejection is not None:
         raise RuntimeError(f"illegal NVFP4 forward schedule: {rejection}")
@@ -270,18 +323,22 @@ def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
     """Apply NVFP4 forward and MXFP8 backward to BF16 or packed operands (rtx/fp4.py:2676-2942)."""
     w_packed, x_packed = isinstance(weight, NVFP4Tensor), isinstance(x, NVFP4Tensor)
     if scaling is None:
-        # the reference defaults dynamic operands to jit_row_region, which is not built for sm_100a
-        scaling = "current"
+        # dynamic BF16 operands default to the row-region policy; a packed weight to current activation
+        # scaling (rtx/fp4.py:2730-2760: JIT regions need both operands dynamic)
+        scaling = (scale_config.policy if scale_config is not None
+                   else "current" if w_packed else "jit_row_region")
     if scaling not in ("current", "jit_row_region", "block"):
         raise ValueError("functional NVFP4 scaling must be current, jit_row_region, or block")
-    if scaling == "jit_row_region":
-        raise NotImplementedError("NVFP4 jit_row_region scaling is not built for sm_100a yet; use scaling='current'")
+    if scaling == "jit_row_region" and w_packed:
+        raise ValueError("jit_row_region scaling requires dynamic BF16 X and W; a packed weight uses current scaling")
     _fp8._normalize_backend(backend)
     _fp8._autotune_mode(autotune)
     if x_packed and not w_packed:
         raise ValueError("a packed activation requires a packed weight")
     bwd_key = _bwd_key(backward_config)
-    cfg, key = _dynamic_key(dynamic_config, scale_config, scaling)
+    region_rows = (_resolve_scale_region_rows(scale_region_rows, x_scale_region_rows, weight_scale_region_rows)
+                   if scaling == "jit_row_region" else (0, 0))
+    cfg, key = _dynamic_key(dynamic_config, scale_config, scaling, region_rows)
     if w_packed:
         n, k = nvfp4_matrix_shape(weight)
         wq, wscales = nvfp4_qdata_2d(weight), nvfp4_scales_for_kernel(weight)
@@ -315,6 +372,9 @@ def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
     if cfg.scale.policy == "block":
         out = (torch.ops.rtx.nvfp4_linear_block_train(x2d, weight, key, bwd_key) if train
                else torch.ops.rtx.nvfp4_linear_block_fwd(x2d, weight, key))
+    elif cfg.scale.policy == "jit_row_region":
+        out = (torch.ops.rtx.nvfp4_linear_jit_row_region_train(x2d, weight, key, bwd_key) if train
+               else torch.ops.rtx.nvfp4_linear_jit_row_region_fwd(x2d, weight, key))
     else:
         mode = cfg.scale.tensor_scale_mode
         x_scale = _outer_tensor_scale(x2d.detach(), mode)
@@ -350,11 +410,17 @@ class NVFP4Linear(nn.Module):
         if dtype is not torch.bfloat16:
             raise TypeError(f"NVFP4Linear parameters must be BF16, got {dtype}")
         if scaling is None:
-            scaling = "current"
-        if scaling in ("jit_row_region", "delayed"):
-            raise NotImplementedError(f"NVFP4 {scaling} scaling is not built for sm_100a yet; use 'current' or 'block'")
-        if scaling not in ("current", "block"):
+            # rtx/fp4.py:3010-3040: dynamic BF16 operands default to the row-region policy, a packed weight to
+            # current activation scaling (JIT regions need both operands dynamic)
+            scaling = (scale_config.policy if scale_config is not None
+                       else "current" if packed_weight is not None else "jit_row_region")
+        if scaling == "delayed":
+            raise NotImplementedError("NVFP4 delayed scaling is not built for sm_100a yet; "
+                                      "use 'jit_row_region', 'current' or 'block'")
+        if scaling not in ("current", "jit_row_region", "block"):
             raise ValueError(f"unknown NVFP4 scaling {scaling!r}")
+        if scaling == "jit_row_region" and packed_weight is not None:
+            raise ValueError("jit_row_region scaling requires dynamic BF16 X and W; a packed weight uses current scaling")
         self.in_features, self.out_features = int(in_features), int(out_features)
         self.scaling = scaling
         self.scale_config = scale_config
@@ -364,11 +430,11 @@ class NVFP4Linear(nn.Module):
         self.tuning_policy = tuning_policy
         self.autotune_cache_dir = autotune_cache_dir
         self.dynamic_config = dynamic_config
-        self.x_scale_region_rows = x_scale_region_rows or scale_region_rows or DEFAULT_NVFP4_X_SCALE_REGION_ROWS
-        self.weight_scale_region_rows = (weight_scale_region_rows or scale_region_rows
-                                         or DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS)
+        self.x_scale_region_rows, self.weight_scale_region_rows = _resolve_scale_region_rows(
+            scale_region_rows, x_scale_region_rows, weight_scale_region_rows)
         self.weight_mode = "prequantized" if packed_weight is not None else "dynamic"
-        self._dynamic_config, self._forward_key = _dynamic_key(dynamic_config, scale_config, scaling)
+        self._dynamic_config, self._forward_key = _dynamic_key(
+            dynamic_config, scale_config, scaling, (self.x_scale_region_rows, self.weight_scale_region_rows))
         self._backward_key = _bwd_key(backward_config)
         if packed_weight is None:
             self.weight = nn.Parameter(torch.empty(self.out_features, self.in_features, device=device,
@@ -416,7 +482,9 @@ class NVFP4Linear(nn.Module):
 
     def explain(self) -> dict:
         return {"format": "nvfp4", "weight_mode": self.weight_mode, "scaling": self.scaling,
-                "pipeline": "outer scale + quantize once + tcgen05 mxf4nvf4 GEMM (sm_100a)", "backward": "mxfp8"}
+                "x_scale_region_rows": self.x_scale_region_rows if self.scaling == "jit_row_region" else 0,
+                "weight_scale_region_rows": self.weight_scale_region_rows if self.scaling == "jit_row_region" else 0,
+                "pipeline": "outer scale(s) + quantize once + tcgen05 mxf4nvf4 GEMM (sm_100a)", "backward": "mxfp8"}
 
     def to(self, *args, **kwargs):
         if self.weight_mode == "prequantized":
@@ -447,6 +515,9 @@ class NVFP4Linear(nn.Module):
         if self._dynamic_config.scale.policy == "block":
             out = (torch.ops.rtx.nvfp4_linear_block_train(x2d, self.weight, key, bwd_key) if train
                    else torch.ops.rtx.nvfp4_linear_block_fwd(x2d, self.weight, key))
+        elif self._dynamic_config.scale.policy == "jit_row_region":
+            out = (torch.ops.rtx.nvfp4_linear_jit_row_region_train(x2d, self.weight, key, bwd_key) if train
+                   else torch.ops.rtx.nvfp4_linear_jit_row_region_fwd(x2d, self.weight, key))
         else:
             mode = self._dynamic_config.scale.tensor_scale_mode
             x_scale = torch.ops.rtx.nvfp4_outer_scale(x2d.detach(), mode)

@@ -305,6 +305,74 @@ def nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n: int, ws: Workspace, out: 
     return out
 
 
+def nvfp4_effective_region_rows(rows: int, requested: int) -> int:
+    """The reference's `_effective_scale_region_rows` (rtx/fp4.py:89-94) with "one region" spelled as
+    `rows`: a request that does not split the rows evenly into more than one region covers the tensor."""
+    if requested <= 0 or rows <= requested or rows % requested:
+        return rows
+    return requested
+
+
+def nvfp4_region_scales(src: torch.Tensor, region_rows: int, mode: int = N.TENSOR_SCALE_POWER2) -> torch.Tensor:
+    """FP32 outer scale of every region of `region_rows` consecutive rows (must divide the rows)."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    scales = torch.empty(rows // max(region_rows, 1), dtype=torch.float32, device=src.device)
+    scratch = torch.empty(1, dtype=torch.int32, device=src.device)
+    with torch.cuda.device(src.device):
+        N.call("rtxb_nvfp4_region_scales", src.data_ptr(), rows, k, k, region_rows, mode, scratch.data_ptr(),
+               scales.data_ptr(), _stream_ptr())
+    return scales
+
+
+def nvfp4_quantize_regions(src: torch.Tensor, region_scales: torch.Tensor, region_rows: int, *,
+                           layout: int = N.SCALE_MMA128):
+    """Every region of rows quantized with its own outer scale -> (q, block scales)."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    kp = mx_storage_k(k)
+    q = torch.empty(rows, kp // 2, dtype=torch.uint8, device=src.device)
+    scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        N.call("rtxb_nvfp4_quantize_regions", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout,
+               region_scales.data_ptr(), region_rows, _stream_ptr())
+    return q, scales
+
+
+def nvfp4_gemm_regions(qa, sa, qb, sb, m: int, n: int, k: int, x_region_scales, x_region_rows: int,
+                       w_region_scales, w_region_rows: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m, n] = bf16(acc * (xs[m / Rx] * ws[n / Rw]))."""
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=qa.device)
+    with torch.cuda.device(qa.device):
+        N.call("rtxb_nvfp4_gemm_regions", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(),
+               m, n, k, out.stride(0), x_region_scales.data_ptr(), x_region_rows, w_region_scales.data_ptr(),
+               w_region_rows, _stream_ptr(), status_word(qa.device).data_ptr())
+    return out
+
+
+def nvfp4_linear_fwd_regions(x, w, ws: Workspace, x_region_rows: int, w_region_rows: int,
+                             out: Optional[torch.Tensor] = None,
+                             scale_mode: int = N.TENSOR_SCALE_POWER2) -> torch.Tensor:
+    """NVFP4 forward with the row-region outer scales (region sizes are requests, see
+    nvfp4_effective_region_rows): two region-|max| launches, two quantizers, the GEMM."""
+    _require(x, torch.bfloat16, "x")
+    _require(w, torch.bfloat16, "weight")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError("x and weight disagree on K")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    nbytes = N.query("rtxb_nvfp4_linear_regions_workspace_bytes", m, n, k, x_region_rows, w_region_rows)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_nvfp4_linear_fwd_regions", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x_region_rows,
+               w_region_rows, scale_mode, buf.data_ptr(), buf.numel(), _stream_ptr(),
+               status_word(x.device).data_ptr())
+    return out
+
+
 def nvfp4_gemm(qa, sa, qb, sb, m: int, n: int, k: int, output_scale: Optional[torch.Tensor], *,
                out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if out is None:

@@ -50,7 +50,17 @@ def test_configs_round_trip_and_reject_explicitly():
     assert C.MXFP8GemmConfig(tile_m=256, cta_group=2, stages=6).rejection() is None
     assert C.MXFP8GemmConfig().rejection(C.MXFP8Problem(0, 1, 1)) == "m, n and k must be positive"
     assert C.MXFP8FwdConfig(pipeline="fused").rejection() == "forward pipeline 'fused' is not built"
-    assert "not built" in C.NVFP4ScaleConfig(policy="jit_row_region").rejection()
+    assert "not built" in C.NVFP4ScaleConfig(policy="delayed").rejection()
+    assert C.NVFP4ScaleConfig(policy="jit_row_region").rejection() is None
+    # region sizes travel in the forward schedule and go with the jit_row_region policy only
+    region = C.NVFP4DynamicConfig(scale=C.NVFP4ScaleConfig(policy="jit_row_region"), x_scale_region_rows=5,
+                                  weight_scale_region_rows=4)
+    assert region.rejection() is None and region.jit_row_region
+    assert C.config_from_key(region.to_key()) == region
+    assert "both operands" in C.NVFP4DynamicConfig(scale=C.NVFP4ScaleConfig(policy="jit_row_region"),
+                                                   x_scale_region_rows=5).rejection()
+    assert "only with it" in C.NVFP4DynamicConfig(x_scale_region_rows=5, weight_scale_region_rows=4).rejection()
+    assert "only with it" in C.NVFP4DynamicConfig(scale=C.NVFP4ScaleConfig(policy="jit_row_region")).rejection()
     assert C.NVFP4QuantConfig(scale_reciprocal="rcp_approx").rejection() is not None
     assert C.MXFP8Problem(3, 5, 1).storage_k == 32 and C.NVFP4Problem(1, 1, 129).storage_k == 160
     assert C.MXFP8GemmConfig().smem_bytes() <= C.SMEM_CAPACITY_BYTES
@@ -116,9 +126,15 @@ def test_module_constructors_and_state_dict_schema():
     with pytest.raises(NotImplementedError):
         MXFP8Linear.from_float(torch.nn.Linear(4, 4, bias=True))
     nv = NVFP4Linear(64, 32)
-    assert list(nv.state_dict()) == ["weight"] and nv.scaling == "current"
-    with pytest.raises(NotImplementedError, match="jit_row_region"):
-        NVFP4Linear(8, 8, scaling="jit_row_region")
+    # dynamic operands default to the row-region policy with the asymmetric X = 5, W = 4 regions
+    assert list(nv.state_dict()) == ["weight"] and nv.scaling == "jit_row_region"
+    assert (nv.x_scale_region_rows, nv.weight_scale_region_rows) == (5, 4)
+    assert nv._dynamic_config.x_scale_region_rows == 5 and nv.explain()["weight_scale_region_rows"] == 4
+    shared = NVFP4Linear(8, 8, scale_region_rows=4, x_scale_region_rows=8)
+    assert (shared.x_scale_region_rows, shared.weight_scale_region_rows) == (8, 4)
+    assert NVFP4Linear(8, 8, scaling="current")._dynamic_config.x_scale_region_rows == 0
+    with pytest.raises(ValueError, match="positive"):
+        NVFP4Linear(8, 8, scale_region_rows=0)
     with pytest.raises(NotImplementedError, match="delayed"):
         NVFP4Linear(8, 8, scaling="delayed")
     with pytest.raises(ValueError):
@@ -142,7 +158,7 @@ def test_functional_argument_errors_before_any_launch():
         quantize_mxfp8(x)
     with pytest.raises(TypeError):
         quantize_nvfp4(x.float())
-    with pytest.raises(NotImplementedError, match="jit_row_region"):
+    with pytest.raises(ValueError, match="CUDA"):
         nvfp4_linear(x, w, scaling="jit_row_region")
     with pytest.raises(ValueError, match="scaling must be"):
         nvfp4_linear(x, w, scaling="nope")

@@ -133,10 +133,17 @@ def test_nvfp4_linear_module_and_packed_weight(dev):
 
     torch.manual_seed(1905)
     layer = rtx.NVFP4Linear(256, 192, device=dev)
+    assert layer.scaling == "jit_row_region"          # the reference's default for dynamic operands
     x = torch.randn(3, 50, 256).bfloat16().to(dev).requires_grad_(True)
     y = layer(x)
     w_cpu, x_cpu = layer.weight.detach().cpu(), x.detach().cpu()
-    _close(y, O.nvfp4_linear(x_cpu, w_cpu, mode="power2"))
+    _close(y, O.nvfp4_linear_regions(x_cpu, w_cpu))    # 150 rows / 5, 192 rows / 4
+    cur = rtx.NVFP4Linear(256, 192, device=dev, scaling="current")
+    with torch.no_grad():
+        cur.weight.copy_(layer.weight)
+        _close(cur(x.detach()), O.nvfp4_linear(x_cpu, w_cpu, mode="power2"))
+        _close(rtx.nvfp4_linear(x.detach(), layer.weight.detach(), scale_region_rows=6),
+               O.nvfp4_linear_regions(x_cpu, w_cpu, 6, 6))
     g = (torch.randn(3, 50, 192) * 0.1).bfloat16().to(dev)
     y.backward(g)
     _done(dev)

@@ -376,6 +376,54 @@ def test_nvfp4_quantize_dynamic_equals_two_pass(gpu, shape, mode):
     assert torch.equal(s_rm.cpu().view(rows, -1)[:, :so.shape[1]], so)
 
 
+@pytest.mark.parametrize("shape_r", [((40, 256), 5), ((128, 1024), 4), ((300, 1000), 5), ((512, 4096), 8),
+                                     ((37, 64), 37), ((6, 33), 1)])
+@pytest.mark.parametrize("mode", ["power2", "exact"])
+def test_nvfp4_row_region_scales_and_payload(gpu, shape_r, mode):
+    """Row-region policy: one outer scale per region of rows from the region's |max| (bit equal to the
+    oracle), and payload / block scales of every row quantized with its region's scale."""
+    ops, N, dev, _ = gpu
+    (rows, k), r = shape_r
+    torch.manual_seed(rows * 7 + k)
+    x = (torch.randn(rows, k) * torch.logspace(-2, 2, rows).unsqueeze(1)).bfloat16()   # regions differ in range
+    code = N.TENSOR_SCALE_EXACT if mode == "exact" else N.TENSOR_SCALE_POWER2
+    xd = x.to(dev)
+    scales = ops.nvfp4_region_scales(xd, r, code)
+    want_scales = O.nvfp4_region_scales(x, r, mode)
+    _ok(ops, dev)
+    assert torch.equal(scales.cpu(), want_scales)
+    q, s = ops.nvfp4_quantize_regions(xd, scales, r, layout=N.SCALE_ROW_MAJOR)
+    q2, s2 = ops.nvfp4_quantize_regions(xd, scales, r)
+    _ok(ops, dev)
+    qo, so = O.nvfp4_quantize_regions(x, want_scales, r)
+    assert torch.equal(q.cpu(), qo) and torch.equal(q2.cpu(), qo)
+    assert torch.equal(s.cpu().view(rows, -1)[:, :so.shape[1]], so)
+    nb = so.shape[1]
+    chunks = (nb + 3) // 4
+    chunks = (chunks + 3) // 4 * 4
+    assert torch.equal(O.scales_from_mma128(s2.cpu().view(-1, chunks, 512), rows, nb), so)
+
+
+@pytest.mark.parametrize("mnk_r", [((40, 64, 128), 5, 4), ((260, 384, 512), 5, 4), ((257, 385, 256), 5, 4),
+                                   ((1000, 3000, 2048), 5, 4), ((128, 8192, 1024), 8, 8), ((64, 512, 256), 1, 1)])
+def test_nvfp4_row_region_linear(gpu, mnk_r):
+    """Forward with row-region outer scales against the oracle: out = bf16(acc * (xs[m / Rx] * ws[n / Rw])).
+    (257, 385) does not split into regions of 5 / 4 rows: both operands fall back to one region, which
+    must equal the `current` policy bit for bit."""
+    ops, N, dev, ws = gpu
+    (m, n, k), rx, rw = mnk_r
+    torch.manual_seed(m + n + k)
+    x = (torch.randn(m, k) * torch.logspace(-1, 1, m).unsqueeze(1)).bfloat16()
+    w = (torch.randn(n, k) / k ** 0.5 * torch.logspace(-1, 1, n).unsqueeze(1)).bfloat16()
+    y = ops.nvfp4_linear_fwd_regions(x.to(dev), w.to(dev), ws, rx, rw)
+    _ok(ops, dev)
+    _assert_output(y, O.nvfp4_linear_regions(x, w, rx, rw))
+    if (m, n) == (257, 385):
+        y_cur = ops.nvfp4_linear_fwd(x.to(dev), w.to(dev), ws)
+        _ok(ops, dev)
+        assert torch.equal(y, y_cur)
+
+
 @pytest.mark.parametrize("m", [1, 8, 16, 64, 128])
 @pytest.mark.parametrize("n", [1536, 19456])
 def test_nvfp4_linear_fwd_prequant_w(gpu, m, n):

@@ -180,3 +180,26 @@ def test_cpu_baseline_path_equals_oracle():
     h, y = C.mx_glu_mlp(x, wgu, wd)
     ho, yo = O.mxfp8_glu_mlp(x, wgu, wd)
     assert torch.equal(h, ho) and torch.equal(y, yo)
+
+
+def test_nvfp4_row_region_oracle_is_consistent():
+    """Row-region policy restated from the reference (unpinned like the rest of NVFP4): a single region
+    over the tensor is the `current` policy, regions are quantized independently, and the region-size
+    fallback follows rtx/fp4.py:89-94."""
+    torch.manual_seed(11)
+    x = (torch.randn(40, 128) * torch.logspace(-2, 2, 40).unsqueeze(1)).bfloat16()
+    w = torch.randn(32, 128).bfloat16()
+    assert O.nvfp4_effective_region_rows(40, 5) == 5 and O.nvfp4_effective_region_rows(16384, 5) == 16384
+    assert O.nvfp4_effective_region_rows(4, 4) == 4 and O.nvfp4_effective_region_rows(28672, 4) == 4
+    assert torch.equal(O.nvfp4_linear_regions(x, w, 40, 32), O.nvfp4_linear(x, w))
+    scales = O.nvfp4_region_scales(x, 5)
+    assert scales.shape == (8,) and scales[0] < scales[-1]
+    assert torch.equal(scales[3:4], O.nvfp4_tensor_scale(x[15:20]))
+    q, s = O.nvfp4_quantize_regions(x, scales, 5)
+    q3, s3 = O.nvfp4_quantize(x[15:20], scales[3:4])
+    assert torch.equal(q[15:20], q3) and torch.equal(s[15:20], s3)
+    # regional scales track the local range: closer to the FP32 product than one scale for the tensor
+    ref = x.float() @ w.float().t()
+    err_region = (O.nvfp4_linear_regions(x, w, 5, 4).float() - ref).norm()
+    err_tensor = (O.nvfp4_linear(x, w).float() - ref).norm()
+    assert err_region <= err_tensor
