@@ -746,7 +746,16 @@ int rtxb_nvfp4_region_scales(const void* src, int64_t rows, int64_t k, int64_t l
     return rtxb_nvfp4_tensor_scale(src, rows, k, ld, mode, amax_scratch, scales_out, nullptr, nullptr, stream);
   }
   const int64_t regions = rows / region_rows;
-  const int64_t ctas = (regions + 7) / 8;   // one warp per region, eight warps per CTA
+  if (region_rows * k * 2 >= 32768) {
+    // a whole CTA per region: enough bytes per region to keep 256 threads' loads in flight
+    const int grid = static_cast<int>(regions < sm_count() * 8 ? regions : sm_count() * 8);
+    amax_regions_cta_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(src), static_cast<int>(rows), static_cast<int>(k), ld,
+        static_cast<int>(region_rows), mode, scales_out);
+    RTXB_CHECK_LAUNCH("amax_regions_cta_kernel");
+    return RTXB_OK;
+  }
+  const int64_t ctas = (regions + 7) / 8;   // small regions: one warp per region, eight warps per CTA
   const int grid = static_cast<int>(ctas < sm_count() * 8 ? ctas : sm_count() * 8);
   amax_regions_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(src), static_cast<int>(rows), static_cast<int>(k), ld,

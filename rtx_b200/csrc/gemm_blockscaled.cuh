@@ -248,6 +248,24 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
         // Column scales are the same for every thread of the warp (broadcast loads).
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
         const int last_region = (p.out_cols - 1) / p.w_region_rows;
+        if (p.w_region_rows == 4) {
+          // the default geometry: these 32 columns are exactly eight regions
+          float fac[8];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) fac[g] = out_scale * __ldg(p.w_region_scales + min((col >> 2) + g, last_region));
+#pragma unroll
+          for (int v = 0; v < 32; v += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[v + 2 * e]) * fac[(v + 2 * e) >> 2],
+                                                       __uint_as_float(r[v + 2 * e + 1]) * fac[(v + 2 * e + 1) >> 2]);
+              w[e] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            store_bf16x8(out, col + v, p.out_cols, p.out_vec_ok != 0, w);
+          }
+          continue;
+        }
         int widx = col / p.w_region_rows, wrem = col - widx * p.w_region_rows;
         float factor = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
 #pragma unroll

@@ -357,7 +357,8 @@ __device__ __forceinline__ QuantNvTileCtx quant_nvfp4_ctx(const QuantNvParams& p
 // REGION: the outer scale is looked up per row (row-region policy) instead of being one per tensor.
 template <bool REGION = false>
 __device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const QuantNvTileCtx& c, int tile,
-                                                 uint8_t (*tile_scales)[16]) {
+                                                 uint8_t (*tile_scales)[16], const float2* row_factors = nullptr) {
+  // row_factors (REGION): per row of the tile {6 * scale, 1 / scale} of the row's region, in shared memory
   const int row0 = (tile / c.col_tiles) * 128;
   const int col = (tile % c.col_tiles) * 256 + c.sub * 16;
   const bool col_ok = col < p.kp;
@@ -388,9 +389,9 @@ __device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const Q
       for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
       float six_st = c.six_st, inv_st = c.inv_st;
       if (REGION) {
-        const float st = live ? __ldg(p.region_scales + row / p.region_rows) : 1.0f;
-        six_st = 6.0f * st;
-        inv_st = __fdiv_rn(1.0f, st);
+        const float2 f = row_factors[r];
+        six_st = f.x;
+        inv_st = f.y;
       }
       float rawscale = __fdiv_rn(a, six_st);
       rawscale = fmin_nan(fmax_nan(rawscale, 0.015625f), 448.0f);
@@ -464,12 +465,72 @@ __global__ void __launch_bounds__(256) amax_regions_kernel(const __nv_bfloat16* 
   }
 }
 
+// The same reduction with a whole CTA per region, for regions large enough to keep 256 threads busy
+// (a region is contiguous when ld == k: the threads then stride over it as one flat range).
+__global__ void __launch_bounds__(256) amax_regions_cta_kernel(const __nv_bfloat16* src, int rows, int k, int64_t ld,
+                                                               int region_rows, int mode, float* region_scales) {
+  __shared__ uint32_t warp_max[8];
+  const int regions = rows / region_rows;
+  const bool flat = (ld == k) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (int region = blockIdx.x; region < regions; region += gridDim.x) {
+    uint32_t m = 0;
+    if (flat) {
+      const uint4* base = reinterpret_cast<const uint4*>(src + static_cast<int64_t>(region) * region_rows * ld);
+      const int vecs = region_rows * (k / 8);
+      for (int i0 = threadIdx.x; i0 < vecs; i0 += 4 * 256) {
+        uint4 raw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) raw[j] = i0 + 256 * j < vecs ? __ldg(base + i0 + 256 * j) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+            m = max(m, w[e] & 0x7FFF0000u);
+          }
+        }
+      }
+    } else {
+      const uint16_t* sp = reinterpret_cast<const uint16_t*>(src);
+      const int64_t total = static_cast<int64_t>(region_rows) * k;
+      for (int64_t i = threadIdx.x; i < total; i += 256) {
+        const int64_t row = region * static_cast<int64_t>(region_rows) + i / k;
+        m = max(m, (static_cast<uint32_t>(sp[row * ld + i % k]) << 16) & 0x7FFFFFFFu);
+      }
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      uint32_t v = threadIdx.x < 8 ? warp_max[threadIdx.x] : 0u;
+      v = __reduce_max_sync(0xffffffffu, v);
+      if (threadIdx.x == 0) region_scales[region] = nvfp4_scale_from_amax_bits(v, mode);
+    }
+    __syncthreads();
+  }
+}
+
 __global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_regions_kernel(const QuantNvParams p) {
   __shared__ __align__(16) uint8_t tile_scales[128][16];
+  __shared__ float2 row_factors[128];
   const QuantNvTileCtx c = quant_nvfp4_ctx(p, 1.0f);
   const int row_tiles = (p.rows + 127) / 128;
-  for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x)
-    quant_nvfp4_tile<true>(p, c, tile, tile_scales);
+  int table_row0 = -1;
+  for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x) {
+    const int row0 = (tile / c.col_tiles) * 128;
+    if (row0 != table_row0) {
+      // the 128 rows of this tile: look the region scale up once per row, not once per block of 16 values
+      if (threadIdx.x < 128) {
+        const int row = row0 + threadIdx.x;
+        const float st = row < p.rows ? __ldg(p.region_scales + row / p.region_rows) : 1.0f;
+        row_factors[threadIdx.x] = make_float2(6.0f * st, __fdiv_rn(1.0f, st));
+      }
+      table_row0 = row0;
+      __syncthreads();
+    }
+    quant_nvfp4_tile<true>(p, c, tile, tile_scales, row_factors);   // ends with a block-wide barrier
+  }
 }
 
 // ---------------------------------------------------------------------------

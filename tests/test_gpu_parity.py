@@ -377,7 +377,7 @@ def test_nvfp4_quantize_dynamic_equals_two_pass(gpu, shape, mode):
 
 
 @pytest.mark.parametrize("shape_r", [((40, 256), 5), ((128, 1024), 4), ((300, 1000), 5), ((512, 4096), 8),
-                                     ((37, 64), 37), ((6, 33), 1)])
+                                     ((48, 2052), 8), ((37, 64), 37), ((6, 33), 1)])
 @pytest.mark.parametrize("mode", ["power2", "exact"])
 def test_nvfp4_row_region_scales_and_payload(gpu, shape_r, mode):
     """Row-region policy: one outer scale per region of rows from the region's |max| (bit equal to the
