@@ -184,6 +184,25 @@ int rtxb_nvfp4_quantize(const void* src_bf16, int64_t rows, int64_t k, int64_t l
 int rtxb_nvfp4_quantize_dynamic(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, int mode, void* q,
                                 void* scales, int scale_layout, float* scale_out, const float* other_scale,
                                 float* out_scale, void* amax_scratch, void* stream);
+/* ---- NVFP4 delayed policy (scaling="delayed") --------------------------------------------
+ * compile_nvfp4_delayed_dual_quant(...) -> (x, w, qx, qw, sx, sw, x_history, weight_history,
+ * next_x_history, next_weight_history, output_scale); kernel NVFP4DelayedDualQuantKernel,
+ * rtx/kernels/nvfp4_quant.py:473-664; bound at rtx/fp4.py:736; runner _DelayedDynamicRunner
+ * rtx/fp4.py:462-517.  Per operand here: the outer scale is the tensor-scale rule applied to
+ * max(history[0 .. len)) (window_max != 0) or to history[0] (most recent); the tensor is quantized
+ * with it in the same single read that observes its |max|; next_history[0] = observed |max|,
+ * next_history[i] = history[i - 1].  history_len is 1, 4, 16 or 64; the two generations must not
+ * alias.  scale_out[0] = the scale used; with other_scale / out_scale also the product. */
+int rtxb_nvfp4_quantize_delayed(const void* src_bf16, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                                int scale_layout, const float* history, float* next_history, int history_len,
+                                int window_max, int mode, float* scale_out, const float* other_scale, float* out_scale,
+                                void* stream);
+/* Both operands + GEMM; workspace as rtxb_nvfp4_linear_workspace_bytes(m, n, k). */
+int rtxb_nvfp4_linear_fwd_delayed(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n,
+                                  int64_t k, const float* x_history, const float* w_history, float* next_x_history,
+                                  float* next_w_history, int history_len, int window_max, int scale_mode,
+                                  void* workspace, size_t workspace_bytes, void* stream, int* status);
+
 /* ---- NVFP4 row-region policy (scaling="jit_row_region", the reference's default) ----------
  * compile_nvfp4_jit_region_dual_quant(x_rows, weight_rows, k, cfg, x_region_rows, weight_region_rows,
  * tensor_scale_mode, ...) -> (x, w, qx, qw, sx, sw, region_scales)   rtx/kernels/nvfp4_quant.py:1623-1678,

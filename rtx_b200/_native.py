@@ -60,6 +60,8 @@ SIGNATURES = {
     "rtxb_nvfp4_gemm": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P, _P]),
     "rtxb_nvfp4_linear_workspace_bytes": (_Z, [_L, _L, _L]),
     "rtxb_nvfp4_linear_fwd": (_I, [_P, _P, _P, _L, _L, _L, _I, _P, _Z, _P, _P]),
+    "rtxb_nvfp4_quantize_delayed": (_I, [_P, _L, _L, _L, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
+    "rtxb_nvfp4_linear_fwd_delayed": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P, _P]),
     "rtxb_nvfp4_region_scales": (_I, [_P, _L, _L, _L, _L, _I, _P, _P, _P]),
     "rtxb_nvfp4_quantize_regions": (_I, [_P, _L, _L, _L, _P, _P, _I, _P, _L, _P]),
     "rtxb_nvfp4_gemm_regions": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _L, _P, _L, _P, _P]),

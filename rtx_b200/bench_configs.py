@@ -119,7 +119,32 @@ def config3(args, rank, world, dev):
                      "frac": flops / (region_gemm_ms * 1e-3) / 1e12 / peak, "ms_per_launch": region_gemm_ms,
                      "traffic": None},
     }
-    return [region_line, {
+    # delayed policy: the outer scales come from the |max| history, no reduction before the quantizers
+    hx = x.float().abs().amax().reshape(1).expand(16).clone()
+    hw = w.float().abs().amax().reshape(1).expand(16).clone()
+    hist = {"x": [hx, torch.empty_like(hx)], "w": [hw, torch.empty_like(hw)]}
+
+    def delayed_step():
+        ops.nvfp4_linear_fwd_delayed(x, w, ws, hist["x"][0], hist["w"][0], hist["x"][1], hist["w"][1], out=out)
+        hist["x"].reverse()
+        hist["w"].reverse()
+
+    delayed_ms = _time(delayed_step, args.steps, args.warmup, world, dev)
+    delayed_line = {
+        "metric": "fused quant+GEMM TFLOPS (NVFP4 linear forward, delayed outer scales, quantization + |max| "
+                  "observation included)",
+        "value": flops * world / (delayed_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        "ms_per_step": delayed_ms, "scaling": "weak", "dtype": "nvfp4 (e2m1 x e4m3 x f32), fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "nvfp4_linear_fwd_m16384_n28672_k8192", "m_per_gpu": m,
+                   "scaling_policy": "delayed/power2, history 16, window max"},
+        "pct_of_nominal_fp4_peak": 100.0 * flops / (delayed_ms * 1e-3) / 1e12 / NOMINAL["fp4"],
+        "gpu_launches_per_step": 3,
+        "roofline": {"kernel": "gemm_blockscaled_pair_kernel<nvfp4, bf16>", "bound": "tensor",
+                     "achieved": flops / (gemm_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                     "frac": flops / (gemm_ms * 1e-3) / 1e12 / peak, "ms_per_launch": gemm_ms, "traffic": None},
+    }
+    return [region_line, delayed_line, {
         "metric": "fused quant+GEMM TFLOPS (NVFP4 linear forward, outer scales + quantization included)",
         "value": flops * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "ms_per_step": ms,
         "scaling": "weak", "dtype": "nvfp4 (e2m1 x e4m3 x f32), fp32 accumulate", "data": "synthetic",

@@ -233,14 +233,20 @@ class NVFP4QuantConfig(_Config):
 @dataclass(frozen=True)
 class NVFP4ScaleConfig(_Config):
     """Outer-scale policy (rtx/configs/nvfp4.py `NVFP4ScaleConfig`)."""
-    policy: str = "current"            # current | jit_row_region | block   (delayed: not built)
+    policy: str = "current"            # current | jit_row_region | delayed | block
     tensor_scale_mode: str = "power2"  # power2 (dynamic default) | exact (offline weights)
+    amax_history_len: int = 16         # delayed: |max| values kept per operand (1, 4, 16 or 64)
+    amax_history_algo: str = "window_max"   # delayed: window_max | most_recent
 
     def rejection(self) -> Optional[str]:
-        if self.policy not in ("current", "jit_row_region", "block"):
-            return f"NVFP4 scaling policy {self.policy!r} is not built for sm_100a yet"
+        if self.policy not in ("current", "jit_row_region", "delayed", "block"):
+            return f"unknown NVFP4 scaling policy {self.policy!r}"
         if self.tensor_scale_mode not in ("power2", "exact"):
             return f"unknown tensor scale mode {self.tensor_scale_mode!r}"
+        if self.amax_history_len not in (1, 4, 16, 64):
+            return "amax_history_len must be 1, 4, 16, or 64"
+        if self.amax_history_algo not in ("most_recent", "window_max"):
+            return "amax_history_algo must be most_recent or window_max"
         return None
 
 

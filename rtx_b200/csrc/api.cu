@@ -732,6 +732,58 @@ int rtxb_nvfp4_quantize_dynamic(const void* src, int64_t rows, int64_t k, int64_
   return RTXB_OK;
 }
 
+int rtxb_nvfp4_quantize_delayed(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                                int scale_layout, const float* history, float* next_history, int history_len,
+                                int window_max, int mode, float* scale_out, const float* other_scale, float* out_scale,
+                                void* stream) {
+  if (!src || !q || !scales || !history || !next_history || !scale_out)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (history_len != 1 && history_len != 4 && history_len != 16 && history_len != 64)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "amax history must have 1, 4, 16 or 64 values");
+  if (history == next_history) return fail_msg(RTXB_E_INVALID_ARGUMENT, "amax history generations must not alias");
+  if (mode != RTXB_TENSOR_SCALE_EXACT && mode != RTXB_TENSOR_SCALE_POWER2)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown tensor scale mode");
+  if ((out_scale == nullptr) != (other_scale == nullptr))
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "other_scale and out_scale go together");
+  if (rows > INT32_MAX || k > INT32_MAX - 512) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!aligned(q, 16)) return fail_msg(RTXB_E_ALIGNMENT, "q must be 16-byte aligned");
+  if (scale_layout == RTXB_SCALE_MMA128 && !aligned(scales, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(next_history, 0, 4, s);   // the observed |max| is accumulated with an atomic max
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(next history)");
+  QuantNvDelayedParams dp;
+  dp.q.src = static_cast<const __nv_bfloat16*>(src);
+  dp.q.q = static_cast<uint8_t*>(q);
+  dp.q.scales = static_cast<uint8_t*>(scales);
+  dp.q.tensor_scale = nullptr;
+  dp.q.region_scales = nullptr;
+  dp.q.region_rows = 0;
+  dp.q.rows = static_cast<int>(rows);
+  dp.q.k = static_cast<int>(k);
+  dp.q.kp = static_cast<int>(round_up(k, 32));
+  dp.q.ld = ld;
+  dp.q.nb = dp.q.kp / 16;
+  dp.q.sf_chunks = static_cast<int>(round_up((dp.q.nb + 3) / 4, 4));
+  dp.q.layout = scale_layout;
+  dp.history = history;
+  dp.next_history = next_history;
+  dp.history_len = history_len;
+  dp.entries = window_max ? history_len : 1;
+  dp.mode = mode;
+  dp.scale_out = scale_out;
+  dp.other_scale = other_scale;
+  dp.out_scale = out_scale;
+  const int64_t tiles = ((rows + 127) / 128) * ((dp.q.kp + 255) / 256);
+  quant_nvfp4_delayed_kernel<<<quant_grid(tiles, 4), kQuantThreads, 0, s>>>(dp);
+  RTXB_CHECK_LAUNCH("quant_nvfp4_delayed_kernel");
+  return RTXB_OK;
+}
+
 int rtxb_nvfp4_region_scales(const void* src, int64_t rows, int64_t k, int64_t ld, int64_t region_rows, int mode,
                              void* amax_scratch, float* scales_out, void* stream) {
   if (!src || !scales_out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
@@ -945,6 +997,34 @@ int rtxb_nvfp4_linear_fwd_regions(const void* x, const void* w, void* out, int64
   if ((rc = rtxb_nvfp4_quantize_regions(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, xs, rx, stream))) return rc;
   if ((rc = rtxb_nvfp4_quantize_regions(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, wsc, rw, stream))) return rc;
   return rtxb_nvfp4_gemm_regions(qx, sx, qw, sw, out, m, n, k, n, xs, rx, wsc, rw, stream, status);
+}
+
+int rtxb_nvfp4_linear_fwd_delayed(const void* x, const void* w, void* out, int64_t m, int64_t n, int64_t k,
+                                  const float* x_history, const float* w_history, float* next_x_history,
+                                  float* next_w_history, int history_len, int window_max, int scale_mode,
+                                  void* workspace, size_t workspace_bytes, void* stream, int* status) {
+  if (m <= 0 || n <= 0 || k <= 0) return fail_msg(RTXB_E_INVALID_ARGUMENT, "m, n, k must be positive");
+  if (!workspace || workspace_bytes < rtxb_nvfp4_linear_workspace_bytes(m, n, k))
+    return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_nvfp4_linear_fwd_delayed");
+  if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
+  Carver c(workspace);
+  const int64_t kp = round_up(k, 32);
+  uint8_t* scal = c.take(256);
+  uint8_t* qx = c.take(m * kp / 2);
+  uint8_t* sx = c.take(rtxb_nvfp4_scale_bytes(m, k, RTXB_SCALE_MMA128));
+  uint8_t* qw = c.take(n * kp / 2);
+  uint8_t* sw = c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
+  float* x_scale = reinterpret_cast<float*>(scal + 16);
+  float* w_scale = reinterpret_cast<float*>(scal + 20);
+  float* o_scale = reinterpret_cast<float*>(scal + 24);
+  int rc;
+  if ((rc = rtxb_nvfp4_quantize_delayed(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, x_history, next_x_history, history_len,
+                                        window_max, scale_mode, x_scale, nullptr, nullptr, stream)))
+    return rc;
+  if ((rc = rtxb_nvfp4_quantize_delayed(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, w_history, next_w_history, history_len,
+                                        window_max, scale_mode, w_scale, x_scale, o_scale, stream)))
+    return rc;
+  return rtxb_nvfp4_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, o_scale, stream, status);
 }
 
 #ifdef RTXB_TRACE

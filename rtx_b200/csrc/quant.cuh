@@ -355,9 +355,11 @@ __device__ __forceinline__ QuantNvTileCtx quant_nvfp4_ctx(const QuantNvParams& p
 
 // one 128 x 256 tile: payload bytes and the tile's scale bytes (block-wide: ends with a barrier).
 // REGION: the outer scale is looked up per row (row-region policy) instead of being one per tensor.
-template <bool REGION = false>
+template <bool REGION = false, bool OBSERVE = false>
 __device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const QuantNvTileCtx& c, int tile,
-                                                 uint8_t (*tile_scales)[16], const float2* row_factors = nullptr) {
+                                                 uint8_t (*tile_scales)[16], const float2* row_factors = nullptr,
+                                                 float* observed = nullptr) {
+  // OBSERVE: *observed accumulates the |max| of everything this thread quantizes (delayed policy)
   // row_factors (REGION): per row of the tile {6 * scale, 1 / scale} of the row's region, in shared memory
   const int row0 = (tile / c.col_tiles) * 128;
   const int col = (tile % c.col_tiles) * 256 + c.sub * 16;
@@ -387,6 +389,7 @@ __device__ __forceinline__ void quant_nvfp4_tile(const QuantNvParams& p, const Q
       float a = fabsf(v[0]);
 #pragma unroll
       for (int e = 1; e < 16; ++e) a = fmax_nan(a, fabsf(v[e]));
+      if (OBSERVE) *observed = fmax_nan(*observed, a);
       float six_st = c.six_st, inv_st = c.inv_st;
       if (REGION) {
         const float2 f = row_factors[r];
@@ -420,6 +423,54 @@ __global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_rows_kernel(cons
   const QuantNvTileCtx c = quant_nvfp4_ctx(p, st);
   const int row_tiles = (p.rows + 127) / 128;
   for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x) quant_nvfp4_tile(p, c, tile, tile_scales);
+}
+
+// ---------------------------------------------------------------------------
+// Delayed policy (NVFP4DelayedDualQuantKernel, rtx/kernels/nvfp4_quant.py:473-664): the outer scale
+// comes from the |max| history of earlier steps (history[0] = most recent; the window maximum or only
+// the most recent entry), and the same single read of the tensor both quantizes it with that scale
+// and observes its |max|, published as next_history[0]; next_history[i] = history[i - 1].  No
+// reduction over the current tensor stands before the quantization.  next_history[0] must be zero
+// when the kernel starts (the entry point clears it).
+// ---------------------------------------------------------------------------
+struct QuantNvDelayedParams {
+  QuantNvParams q;            // q.tensor_scale / region fields are not read
+  const float* history;       // [history_len]
+  float* next_history;        // [history_len]
+  int history_len, entries;   // entries read for the scale: history_len (window_max) or 1 (most_recent)
+  int mode;
+  float* scale_out;           // [1] the scale used
+  const float* other_scale;   // nullptr or [1]
+  float* out_scale;           // nullptr or [1] = scale * other_scale
+};
+
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_delayed_kernel(const QuantNvDelayedParams dp) {
+  __shared__ __align__(16) uint8_t tile_scales[128][16];
+  __shared__ uint32_t prior_bits;
+  const QuantNvParams& p = dp.q;
+  if (threadIdx.x < 32) {
+    uint32_t m = 0;
+    for (int i = threadIdx.x; i < dp.entries; i += 32) m = max(m, __float_as_uint(__ldg(dp.history + i)) & 0x7FFFFFFFu);
+    m = __reduce_max_sync(0xffffffffu, m);
+    if (threadIdx.x == 0) prior_bits = m;
+    if (blockIdx.x == 0) {
+      for (int i = threadIdx.x + 1; i < dp.history_len; i += 32) dp.next_history[i] = __ldg(dp.history + i - 1);
+    }
+  }
+  __syncthreads();
+  const float st = nvfp4_scale_from_amax_bits(prior_bits, dp.mode);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *dp.scale_out = st;
+    if (dp.out_scale) *dp.out_scale = st * *dp.other_scale;
+  }
+  const QuantNvTileCtx c = quant_nvfp4_ctx(p, st);
+  const int row_tiles = (p.rows + 127) / 128;
+  float observed = 0.0f;
+  for (int tile = blockIdx.x; tile < c.col_tiles * row_tiles; tile += gridDim.x)
+    quant_nvfp4_tile<false, true>(p, c, tile, tile_scales, nullptr, &observed);
+  uint32_t obs = __float_as_uint(observed) & 0x7FFFFFFFu;   // NaN keeps a pattern above infinity
+  obs = __reduce_max_sync(0xffffffffu, obs);
+  if ((threadIdx.x & 31) == 0 && obs != 0) atomicMax(reinterpret_cast<uint32_t*>(dp.next_history), obs);
 }
 
 // ---------------------------------------------------------------------------

@@ -8,8 +8,9 @@ BF16 operands (rtx/fp4.py:1772-1794).  Scaling policies built for sm_100a:
 `jit_row_region` (the default for dynamic operands: one outer scale per region of
 rows, from the region's present |max|), `current` (outer scale from the tensor's
 present |max|; power-of-two for dynamic operands, exact `amax/2688` for offline
-weights) and `block` (outer scale 1).  `delayed` is not built yet and raises
-NotImplementedError.
+weights), `delayed` (outer scale from the |max| history of earlier steps; the
+current |max| is only observed, in the same pass that quantizes) and `block`
+(outer scale 1).
 """
 
 from __future__ import annotations
@@ -235,6 +236,56 @@ def _(x, weight, key, bwd_key):
 nvfp4_linear_jit_row_region_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
 
 
+@torch.library.custom_op("rtx::nvfp4_linear_train_delayed",
+                         mutates_args=("next_x_amax_state", "next_weight_amax_state"), device_types="cuda")
+def nvfp4_linear_train_delayed(x: torch.Tensor, weight: torch.Tensor, x_amax_state: torch.Tensor,
+                               weight_amax_state: torch.Tensor, next_x_amax_state: torch.Tensor,
+                               next_weight_amax_state: torch.Tensor, forward_config_key: str,
+                               materialized_config_key: str, backward_config_key: str) -> torch.Tensor:
+    """`delayed` policy (rtx/fp4.py:1931-1957, _DelayedDynamicRunner :462-517): outer scales from the prior
+    |max| histories, successor histories written into the `next_*` tensors (index 0 = this call's |max|)."""
+    cfg = _resolve_dynamic(forward_config_key)
+    if x_amax_state.data_ptr() == next_x_amax_state.data_ptr():
+        raise ValueError("delayed x amax generations must not alias")
+    if weight_amax_state.data_ptr() == next_weight_amax_state.data_ptr():
+        raise ValueError("delayed weight amax generations must not alias")
+    x = x if x.is_contiguous() else x.contiguous()
+    weight = weight if weight.is_contiguous() else weight.contiguous()
+    return ops.nvfp4_linear_fwd_delayed(x, weight, _fp8._workspace(x.device), x_amax_state, weight_amax_state,
+                                        next_x_amax_state, next_weight_amax_state,
+                                        window_max=cfg.scale.amax_history_algo == "window_max",
+                                        scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
+
+
+@nvfp4_linear_train_delayed.register_fake
+def _(x, weight, x_amax_state, weight_amax_state, next_x_amax_state, next_weight_amax_state, forward_config_key,
+      materialized_config_key, backward_config_key):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
+
+
+class _NVFP4DelayedAutograd(torch.autograd.Function):
+    """Autograd shell around the state-mutating delayed forward (rtx/fp4.py:2635-2673): the histories are
+    plain buffers, gradients flow to x and weight through the MXFP8 backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, x_state, w_state, next_x_state, next_w_state, key, materialized_key, bwd_key):
+        ctx.save_for_backward(x, weight)
+        ctx.bwd_key = bwd_key
+        ctx.n_inputs = 9
+        return torch.ops.rtx.nvfp4_linear_train_delayed(x, weight, x_state, w_state, next_x_state, next_w_state, key,
+                                                        materialized_key, bwd_key)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _nv_train_backward(ctx, grad_output)
+
+
+def _delayed_amax_state(tensor: torch.Tensor, values: int) -> torch.Tensor:
+    """History bootstrapped from the tensor's present |max|, no host synchronisation (rtx/fp4.py:368-373)."""
+    amax = torch.amax(torch.abs(tensor.detach().float())).reshape(1)
+    return amax.expand(values).clone()
+
+
 @torch.library.custom_op("rtx::nvfp4_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
 def nvfp4_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor, weight_block_scales: torch.Tensor,
                                       x_scale: torch.Tensor, output_scale: torch.Tensor, n: int, k: int, layout: str,
@@ -302,6 +353,10 @@ def _resolve_scale_region_rows(shared, x_rows, weight_rows):
 @torch._dynamo.assume_constant_result
 def _dynamic_key(dynamic_config, scale_config, scaling, region_rows=(0, 0)):
     region = scaling == "jit_row_region"
+    if scale_config is not None and scale_config.policy != scaling:
+        # the policy is chosen by `scaling`; a scale_config contributes the scale mode and history settings
+        import dataclasses
+        scale_config = dataclasses.replace(scale_config, policy=scaling)
     cfg = dynamic_config or NVFP4DynamicConfig(
         scale=scale_config or NVFP4ScaleConfig(policy=scaling,
                                                tensor_scale_mode="exact" if scaling == "block" else "power2"),
@@ -414,13 +469,10 @@ class NVFP4Linear(nn.Module):
             # current activation scaling (JIT regions need both operands dynamic)
             scaling = (scale_config.policy if scale_config is not None
                        else "current" if packed_weight is not None else "jit_row_region")
-        if scaling == "delayed":
-            raise NotImplementedError("NVFP4 delayed scaling is not built for sm_100a yet; "
-                                      "use 'jit_row_region', 'current' or 'block'")
-        if scaling not in ("current", "jit_row_region", "block"):
-            raise ValueError(f"unknown NVFP4 scaling {scaling!r}")
-        if scaling == "jit_row_region" and packed_weight is not None:
-            raise ValueError("jit_row_region scaling requires dynamic BF16 X and W; a packed weight uses current scaling")
+        if scaling not in ("delayed", "current", "jit_row_region", "block"):
+            raise ValueError("NVFP4 scaling must be delayed, current, jit_row_region, or block")
+        if scaling in ("jit_row_region", "delayed") and packed_weight is not None:
+            raise ValueError(f"{scaling} scaling requires dynamic BF16 X and W; a packed weight uses current scaling")
         self.in_features, self.out_features = int(in_features), int(out_features)
         self.scaling = scaling
         self.scale_config = scale_config
@@ -436,6 +488,10 @@ class NVFP4Linear(nn.Module):
         self._dynamic_config, self._forward_key = _dynamic_key(
             dynamic_config, scale_config, scaling, (self.x_scale_region_rows, self.weight_scale_region_rows))
         self._backward_key = _bwd_key(backward_config)
+        self._delayed_initialized = False
+        self._delayed_problem = None
+        self._x_amax_state = self._weight_amax_state = None
+        self._next_x_amax_state = self._next_weight_amax_state = None
         if packed_weight is None:
             self.weight = nn.Parameter(torch.empty(self.out_features, self.in_features, device=device,
                                                    dtype=torch.bfloat16))
@@ -478,7 +534,44 @@ class NVFP4Linear(nn.Module):
                                  (self.out_features, self.in_features), layout)
 
     def reset_delayed_scales(self) -> None:
-        """Delayed scaling keeps an amax history in the reference; nothing to reset for `current`/`block`."""
+        """Drop the |max| histories of the delayed policy; the next forward re-initialises them from its
+        own operands (rtx/fp4.py:3269-3283).  Called after state loading and when training is re-entered."""
+        self._delayed_initialized = False
+        self._delayed_problem = None
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self.reset_delayed_scales()
+
+    def train(self, mode: bool = True):
+        if mode and not self.training:
+            self.reset_delayed_scales()
+        return super().train(mode)
+
+    def _forward_delayed(self, x2d: torch.Tensor) -> torch.Tensor:
+        """History handling of the delayed policy (rtx/fp4.py:3452-3535): (re)initialise from current data when
+        the problem (device, stream, shape) changes, run, then swap the two generations.  The policy is a
+        forward one: eval / no_grad consume and publish histories exactly like training."""
+        problem = (x2d.device.type, x2d.device.index, torch.cuda.current_stream(x2d.device).cuda_stream,
+                   int(x2d.shape[0]), self.out_features, self.in_features)
+        if not self._delayed_initialized or self._delayed_problem != problem:
+            with torch.no_grad():
+                values = self._dynamic_config.scale.amax_history_len
+                self._x_amax_state = _delayed_amax_state(x2d, values)
+                self._weight_amax_state = _delayed_amax_state(self.weight, values)
+                self._next_x_amax_state = torch.empty_like(self._x_amax_state)
+                self._next_weight_amax_state = torch.empty_like(self._weight_amax_state)
+            self._delayed_initialized, self._delayed_problem = True, problem
+        args = (x2d, self.weight, self._x_amax_state, self._weight_amax_state, self._next_x_amax_state,
+                self._next_weight_amax_state, self._forward_key, self._forward_key, self._backward_key)
+        if torch.is_grad_enabled() and (x2d.requires_grad or self.weight.requires_grad):
+            from . import fp8_bwd  # noqa: F401  (registers the backward ops)
+            out = _NVFP4DelayedAutograd.apply(*args)
+        else:
+            out = torch.ops.rtx.nvfp4_linear_train_delayed(*args)
+        self._x_amax_state, self._next_x_amax_state = self._next_x_amax_state, self._x_amax_state
+        self._weight_amax_state, self._next_weight_amax_state = self._next_weight_amax_state, self._weight_amax_state
+        return out
 
     def explain(self) -> dict:
         return {"format": "nvfp4", "weight_mode": self.weight_mode, "scaling": self.scaling,
@@ -509,6 +602,8 @@ class NVFP4Linear(nn.Module):
                 x2d, self.weight_data, self.weight_block_scales, x_scale, x_scale * self.weight_tensor_scale, n, k,
                 self._weight_scale_layout, key)
             return out.reshape(*x.shape[:-1], n)
+        if self._dynamic_config.scale.policy == "delayed":
+            return self._forward_delayed(x2d).reshape(*x.shape[:-1], n)
         train = torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad)
         if train:
             from . import fp8_bwd  # noqa: F401  (registers the backward ops)

@@ -305,6 +305,52 @@ def nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n: int, ws: Workspace, out: 
     return out
 
 
+def nvfp4_quantize_delayed(src: torch.Tensor, history: torch.Tensor, next_history: torch.Tensor, *,
+                           window_max: bool = True, mode: int = N.TENSOR_SCALE_POWER2,
+                           other_scale: Optional[torch.Tensor] = None, layout: int = N.SCALE_MMA128):
+    """Delayed policy for one operand: quantize with the scale of the |max| history, observe the current
+    |max| in the same pass, write the successor history.  Returns (q, scales, scale f32[1], product | None)."""
+    _require(src, torch.bfloat16, "src")
+    rows, k = src.shape
+    kp = mx_storage_k(k)
+    q = torch.empty(rows, kp // 2, dtype=torch.uint8, device=src.device)
+    scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
+    scale = torch.empty(1, dtype=torch.float32, device=src.device)
+    prod = torch.empty(1, dtype=torch.float32, device=src.device) if other_scale is not None else None
+    with torch.cuda.device(src.device):
+        N.call("rtxb_nvfp4_quantize_delayed", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout,
+               history.data_ptr(), next_history.data_ptr(), history.numel(), int(window_max), mode, scale.data_ptr(),
+               other_scale.data_ptr() if other_scale is not None else None,
+               prod.data_ptr() if prod is not None else None, _stream_ptr())
+    return q, scales, scale, prod
+
+
+def nvfp4_linear_fwd_delayed(x, w, ws: Workspace, x_history, w_history, next_x_history, next_w_history, *,
+                             window_max: bool = True, scale_mode: int = N.TENSOR_SCALE_POWER2,
+                             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """NVFP4 forward under the delayed policy: two quantizer launches (each also observes its operand's
+    |max| for the next step) and the GEMM; no reduction over the current tensors before the quantization."""
+    _require(x, torch.bfloat16, "x")
+    _require(w, torch.bfloat16, "weight")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError("x and weight disagree on K")
+    for t in (x_history, w_history, next_x_history, next_w_history):
+        if t.dtype is not torch.float32 or not t.is_contiguous() or t.numel() != x_history.numel():
+            raise ValueError("amax histories must be contiguous FP32 vectors of one length")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    nbytes = N.query("rtxb_nvfp4_linear_workspace_bytes", m, n, k)
+    buf = ws.get(nbytes)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_nvfp4_linear_fwd_delayed", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
+               x_history.data_ptr(), w_history.data_ptr(), next_x_history.data_ptr(), next_w_history.data_ptr(),
+               x_history.numel(), int(window_max), scale_mode, buf.data_ptr(), buf.numel(), _stream_ptr(),
+               status_word(x.device).data_ptr())
+    return out
+
+
 def nvfp4_effective_region_rows(rows: int, requested: int) -> int:
     """The reference's `_effective_scale_region_rows` (rtx/fp4.py:89-94) with "one region" spelled as
     `rows`: a request that does not split the rows evenly into more than one region covers the tensor."""

@@ -50,7 +50,10 @@ def test_configs_round_trip_and_reject_explicitly():
     assert C.MXFP8GemmConfig(tile_m=256, cta_group=2, stages=6).rejection() is None
     assert C.MXFP8GemmConfig().rejection(C.MXFP8Problem(0, 1, 1)) == "m, n and k must be positive"
     assert C.MXFP8FwdConfig(pipeline="fused").rejection() == "forward pipeline 'fused' is not built"
-    assert "not built" in C.NVFP4ScaleConfig(policy="delayed").rejection()
+    assert C.NVFP4ScaleConfig(policy="delayed").rejection() is None
+    assert "history_len" in C.NVFP4ScaleConfig(policy="delayed", amax_history_len=3).rejection()
+    assert "history_algo" in C.NVFP4ScaleConfig(policy="delayed", amax_history_algo="mean").rejection()
+    assert "unknown NVFP4 scaling policy" in C.NVFP4ScaleConfig(policy="per_channel").rejection()
     assert C.NVFP4ScaleConfig(policy="jit_row_region").rejection() is None
     # region sizes travel in the forward schedule and go with the jit_row_region policy only
     region = C.NVFP4DynamicConfig(scale=C.NVFP4ScaleConfig(policy="jit_row_region"), x_scale_region_rows=5,
@@ -111,7 +114,7 @@ def test_module_constructors_and_state_dict_schema():
         MXFP8Linear(8, 8, dtype=torch.float16)
     with pytest.raises(ValueError, match="unknown MXFP8 backend"):
         MXFP8Linear(8, 8, backend="cutlass")
-    from rtx_b200.configs import MXFP8FwdConfig, MXFP8PrequantConfig
+    from rtx_b200.configs import MXFP8FwdConfig, MXFP8PrequantConfig, NVFP4ScaleConfig
 
     with pytest.raises(ValueError, match="both config aliases"):
         MXFP8Linear(8, 8, config=MXFP8FwdConfig(), forward_config=MXFP8FwdConfig())
@@ -135,8 +138,16 @@ def test_module_constructors_and_state_dict_schema():
     assert NVFP4Linear(8, 8, scaling="current")._dynamic_config.x_scale_region_rows == 0
     with pytest.raises(ValueError, match="positive"):
         NVFP4Linear(8, 8, scale_region_rows=0)
-    with pytest.raises(NotImplementedError, match="delayed"):
-        NVFP4Linear(8, 8, scaling="delayed")
+    delayed = NVFP4Linear(8, 8, scaling="delayed", scale_config=NVFP4ScaleConfig(amax_history_len=4))
+    assert delayed._dynamic_config.scale.policy == "delayed" and delayed._dynamic_config.scale.amax_history_len == 4
+    assert not delayed._delayed_initialized and list(delayed.state_dict()) == ["weight"]   # histories are not state
+    delayed._delayed_initialized = True
+    delayed.load_state_dict(nv.state_dict() if nv.weight.shape == delayed.weight.shape else delayed.state_dict())
+    assert not delayed._delayed_initialized          # loading a checkpoint drops the histories
+    delayed._delayed_initialized = True
+    delayed.eval()
+    delayed.train()
+    assert not delayed._delayed_initialized          # so does re-entering training
     with pytest.raises(ValueError):
         NVFP4Linear(8, 8, scaling="per_channel")
     # BF16 / MXFP8 / NVFP4 dynamic modules share checkpoints

@@ -150,6 +150,26 @@ def test_nvfp4_linear_module_and_packed_weight(dev):
     dx, dw = O.mxfp8_backward(x_cpu.reshape(-1, 256), w_cpu, g.cpu().reshape(-1, 192), dw_dtype=torch.float32)
     _close(x.grad.reshape(-1, 256), dx)          # NVFP4 forward, MXFP8 backward
     _close(layer.weight.grad, dw.bfloat16())
+    # delayed policy: the first call bootstraps the histories from its own operands (= current scaling, power
+    # of two); the second call still uses the first call's |max| although its activations are 4x larger
+    dly = rtx.NVFP4Linear(256, 192, device=dev, scaling="delayed")
+    with torch.no_grad():
+        dly.weight.copy_(layer.weight)
+    xg = x.detach().clone().requires_grad_(True)
+    y1 = dly(xg)
+    _close(y1, O.nvfp4_linear(x_cpu, w_cpu, mode="power2"))
+    y1.backward(g)
+    _close(xg.grad.reshape(-1, 256), dx)
+    x4 = (x_cpu * 4).bfloat16()
+    with torch.no_grad():
+        y2 = dly(x4.to(dev))
+    _done(dev)
+    h_x = x_cpu.float().abs().amax().reshape(1).expand(16).clone()
+    h_w = w_cpu.float().abs().amax().reshape(1).expand(16).clone()
+    _, h_x, h_w = O.nvfp4_linear_delayed(x_cpu.reshape(-1, 256), w_cpu, h_x, h_w)
+    want2, h_x, h_w = O.nvfp4_linear_delayed(x4.reshape(-1, 256), w_cpu, h_x, h_w)
+    _close(y2.reshape(-1, 192), want2)
+    assert torch.equal(dly._x_amax_state.cpu(), h_x) and float(h_x[0]) == float(x4.float().abs().amax())
     # block policy: outer scales are 1
     blk = rtx.NVFP4Linear(256, 192, device=dev, scaling="block")
     with torch.no_grad():

@@ -424,6 +424,54 @@ def test_nvfp4_row_region_linear(gpu, mnk_r):
         assert torch.equal(y, y_cur)
 
 
+@pytest.mark.parametrize("hist", [(1, True), (4, True), (16, False), (64, True)])
+@pytest.mark.parametrize("mode", ["power2", "exact"])
+def test_nvfp4_delayed_operand(gpu, hist, mode):
+    """Delayed policy, one operand: quantized with the scale of the |max| history (window maximum or most
+    recent entry), current |max| observed in the same pass and published as next_history[0], history
+    rotated by one."""
+    ops, N, dev, _ = gpu
+    length, window = hist
+    torch.manual_seed(length * 3 + int(window))
+    x = (torch.randn(300, 1000) * 2).bfloat16()
+    history = (torch.rand(length) * 6 + 0.5).float()
+    nxt = torch.full((length,), -1.0)
+    code = N.TENSOR_SCALE_EXACT if mode == "exact" else N.TENSOR_SCALE_POWER2
+    other = torch.tensor([0.25], device=dev)
+    hd, nd = history.to(dev), nxt.to(dev)
+    q, s, scale, prod = ops.nvfp4_quantize_delayed(x.to(dev), hd, nd, window_max=window, mode=code, other_scale=other,
+                                                   layout=N.SCALE_ROW_MAJOR)
+    _ok(ops, dev)
+    qo, so, scale_o, next_o = O.nvfp4_delayed_operand(x, history, "window_max" if window else "most_recent", mode)
+    assert torch.equal(scale.cpu(), scale_o) and float(prod.cpu()) == float(scale_o) * 0.25
+    assert torch.equal(q.cpu(), qo)
+    assert torch.equal(s.cpu().view(300, -1)[:, :so.shape[1]], so)
+    assert torch.equal(nd.cpu(), next_o)
+    assert torch.equal(hd.cpu(), history)          # the prior generation is read only
+
+
+def test_nvfp4_delayed_linear_steps(gpu):
+    """Three steps of the delayed forward with drifting activations: every step equals the oracle fed with
+    the same histories, and the histories evolve as the oracle's do."""
+    ops, N, dev, ws = gpu
+    m, n, k = 260, 384, 512
+    torch.manual_seed(5)
+    w = (torch.randn(n, k) / k ** 0.5).bfloat16()
+    xh = torch.full((4,), 3.0)
+    wh = w.float().abs().amax().reshape(1).expand(4).clone()
+    xd_h, wd_h = xh.to(dev), wh.to(dev)
+    xd_n, wd_n = torch.empty_like(xd_h), torch.empty_like(wd_h)
+    for step in range(3):
+        x = (torch.randn(m, k) * (1.0 + 2.0 * step)).bfloat16()     # the range drifts: the scale lags one step
+        y = ops.nvfp4_linear_fwd_delayed(x.to(dev), w.to(dev), ws, xd_h, wd_h, xd_n, wd_n)
+        _ok(ops, dev)
+        want, xh, wh = O.nvfp4_linear_delayed(x, w, xh, wh)
+        _assert_output(y, want)
+        assert torch.equal(xd_n.cpu(), xh) and torch.equal(wd_n.cpu(), wh)
+        xd_h, xd_n = xd_n, xd_h
+        wd_h, wd_n = wd_n, wd_h
+
+
 @pytest.mark.parametrize("m", [1, 8, 16, 64, 128])
 @pytest.mark.parametrize("n", [1536, 19456])
 def test_nvfp4_linear_fwd_prequant_w(gpu, m, n):
