@@ -48,6 +48,13 @@ _LAZY_EXPORTS = {
     "mxfp8_linear_backward": ("fp8_bwd", "mxfp8_linear_backward"),
     "clear_runtime_caches": ("runtime", "clear_runtime_caches"),
     "validate_runtime_environment": ("runtime", "validate_runtime_environment"),
+    "MXFP8TrainingConfig": ("ptq", "MXFP8TrainingConfig"),
+    "NVFP4TrainingConfig": ("ptq", "NVFP4TrainingConfig"),
+    "MXFP8WeightOnlyConfig": ("ptq", "MXFP8WeightOnlyConfig"),
+    "NVFP4WeightOnlyConfig": ("ptq", "NVFP4WeightOnlyConfig"),
+    "convert_to_mxfp8_training": ("ptq", "convert_to_mxfp8_training"),
+    "convert_to_nvfp4_training": ("ptq", "convert_to_nvfp4_training"),
+    "quantize_": ("ptq", "quantize_"),
     # sm_100a additions
     "mxfp8_glu_mlp": ("glu", "mxfp8_glu_mlp"),
     "KernelAdapter": ("autotune", "KernelAdapter"),

@@ -276,3 +276,48 @@ def test_autotune_adapter_and_winner_cache(tmp_path):
     failing = A.pick(A.KernelContext("mxfp8_prequant_fwd", 1, 1, 1), adapter,
                      lambda c: A.TrialOutcome("failed", detail="x"), mode="balanced", cache_dir=tmp_path)
     assert failing == adapter.default(ctx)
+
+
+def test_model_conversion_keeps_parameters_and_is_all_or_nothing():
+    """rtx/ptq.py semantics: training conversion keeps the Parameter objects (optimizer references, sharing,
+    state-dict keys), shared modules are replaced at every alias, and nothing is touched when a selected
+    layer is invalid."""
+    import rtx_b200 as rtx
+    from torch import nn
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up = nn.Linear(32, 64, bias=False, dtype=torch.bfloat16)
+            self.down = nn.Linear(64, 32, bias=False, dtype=torch.bfloat16)
+            self.tied = self.up                      # an alias of a shared module
+            self.head = nn.Linear(32, 8, bias=True, dtype=torch.bfloat16)
+
+    model = Block()
+    params = {n: p for n, p in model.named_parameters()}
+    keys = list(model.state_dict())
+    no_head = lambda m, fqn: isinstance(m, nn.Linear) and fqn != "head"
+    out = rtx.convert_to_mxfp8_training(model, module_filter_fn=no_head)
+    assert out is model and isinstance(model.up, rtx.MXFP8Linear) and model.tied is model.up
+    assert isinstance(model.head, nn.Linear) and list(model.state_dict()) == keys
+    assert all(params[n] is p for n, p in model.named_parameters())
+    # the default filter reaches the biased head: refused before anything changes
+    model2 = Block()
+    with pytest.raises(NotImplementedError, match="bias"):
+        rtx.convert_to_nvfp4_training(model2)
+    assert type(model2.up) is nn.Linear
+    with pytest.raises(ValueError, match="only some aliases"):
+        rtx.convert_to_nvfp4_training(model2, module_filter_fn=lambda m, fqn: fqn == "up")
+    nv = rtx.convert_to_nvfp4_training(model2, module_filter_fn=no_head,
+                                       config=rtx.NVFP4TrainingConfig(scaling="delayed", scale_region_rows=None))
+    assert isinstance(nv.down, rtx.NVFP4Linear) and nv.down.scaling == "delayed" and nv.down.weight is not None
+    # PTQ needs CUDA weights and one of the two weight-only policies
+    with pytest.raises(ValueError, match="CUDA"):
+        rtx.quantize_(Block(), rtx.MXFP8WeightOnlyConfig(), filter_fn=no_head)
+    with pytest.raises(TypeError, match="WeightOnlyConfig"):
+        rtx.quantize_(Block(), object())
+    with pytest.raises(ValueError, match="current or block"):
+        rtx.NVFP4WeightOnlyConfig(scaling="delayed")
+    # a root that is itself a linear is returned replaced
+    root = nn.Linear(32, 32, bias=False, dtype=torch.bfloat16)
+    assert isinstance(rtx.convert_to_mxfp8_training(root), rtx.MXFP8Linear)

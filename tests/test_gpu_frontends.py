@@ -244,3 +244,26 @@ def test_runtime_caches_clear(dev):
     released = rtx.clear_runtime_caches()
     assert released["fp8"]["workspaces"]["entries"] >= 1
     assert rtx.validate_runtime_environment(require_device=True)["capability"][0] == 10
+
+
+def test_quantize_model_in_place(dev):
+    """`quantize_` (rtx/ptq.py:292-384): packed inference modules replace the BF16 linears, the packed
+    forward equals the oracle with exact outer scales, and the BF16 masters are gone."""
+    import rtx_b200 as rtx
+    from torch import nn
+
+    torch.manual_seed(3)
+    model = nn.Sequential(nn.Linear(256, 192, bias=False, dtype=torch.bfloat16),
+                          nn.Linear(192, 128, bias=False, dtype=torch.bfloat16)).to(dev)
+    w0 = model[0].weight.detach().cpu()
+    x = torch.randn(40, 256).bfloat16()
+    fp4 = rtx.quantize_(nn.Sequential(*[nn.Linear(l.in_features, l.out_features, bias=False, dtype=torch.bfloat16,
+                                                   device=dev) for l in model]), rtx.NVFP4WeightOnlyConfig())
+    assert all(isinstance(l, rtx.NVFP4Linear) and l.weight is None for l in fp4)
+    mx = rtx.quantize_(model, rtx.MXFP8WeightOnlyConfig(), filter_fn=lambda m, fqn: fqn == "0")
+    assert isinstance(mx[0], rtx.MXFP8Linear) and mx[0].weight_mode == "prequantized" and type(mx[1]) is nn.Linear
+    assert "0.weight" not in mx.state_dict() and "0.weight_data" in mx.state_dict()
+    with torch.no_grad():
+        y = mx[0](x.to(dev))
+    _done(dev)
+    _close(y, O.mxfp8_linear(x, w0))
