@@ -630,3 +630,9 @@ def _clear_runtime_caches() -> dict:
 
 __all__ = ["NVFP4Linear", "nvfp4_linear", "quantize_nvfp4", "DEFAULT_NVFP4_X_SCALE_REGION_ROWS",
            "DEFAULT_NVFP4_WEIGHT_SCALE_REGION_ROWS"]
+
+
+# Inductor lowerings of the ops above (skipped quietly when Inductor's internals are unavailable)
+from . import inductor as _inductor  # noqa: E402
+
+_inductor.register_nvfp4_lowerings()

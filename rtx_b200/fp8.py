@@ -389,3 +389,9 @@ class MXFP8Linear(nn.Module):
 
 __all__ = ["MXFP8Linear", "mxfp8_linear", "quantize_mxfp8", "MXFP8PrequantConfig", "DEFAULT_MXFP8_PREQUANT_CONFIG",
            "DEFAULT_MXFP8_INFERENCE_CONFIG"]
+
+
+# Inductor lowerings of the ops above (skipped quietly when Inductor's internals are unavailable)
+from . import inductor as _inductor  # noqa: E402
+
+_inductor.register_mxfp8_lowerings()

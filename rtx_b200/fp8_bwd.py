@@ -197,3 +197,9 @@ DEFAULT_MXFP8_BWD_CONFIG = MXFP8BwdConfig()
 DEFAULT_FUSED_MXFP8_BWD_CONFIG = MXFP8BwdConfig()
 
 __all__ = ["mxfp8_linear_backward", "MXFP8BwdConfig", "DEFAULT_MXFP8_BWD_CONFIG", "DEFAULT_FUSED_MXFP8_BWD_CONFIG"]
+
+
+# Inductor lowerings of the ops above (skipped quietly when Inductor's internals are unavailable)
+from . import inductor as _inductor  # noqa: E402
+
+_inductor.register_mxfp8_train_lowering()
