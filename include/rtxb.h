@@ -85,6 +85,12 @@ int rtxb_mxfp8_quantize(const void* src_bf16, int64_t rows, int64_t k, int64_t l
 int rtxb_mxfp8_quantize_transposed(const void* src_bf16_k_by_rows, int64_t rows, int64_t k, int64_t ld, void* q,
                                    void* scales, int scale_layout, int rounding, void* stream);
 
+/* compile_mxfp8_backward_quad_quant(..., shared_g=True) reads the gradient once for its two
+ * quantizations (rtx/kernels/mxfp8_quant.py:1400-1763; bound at rtx/fp8_bwd.py:545-555).  Here:
+ * src [m, n] -> q_rows [m, np] with scales along n (= rtxb_mxfp8_quantize) AND q_t [n, mp] with
+ * scales along m (= rtxb_mxfp8_quantize_transposed), both from one staged read of src. */
+int rtxb_mxfp8_quantize_dual(const void* src_bf16, int64_t m, int64_t n, int64_t ld, void* q_rows, void* s_rows,
+                             void* q_t, void* s_t, int scale_layout, int rounding, void* stream);
 /* ---- MXFP8 GEMM on packed operands ---------------------------------------
  * compile_mxfp8_gemm(problem, cfg, ...) -> (qx, qw, sx, sw, out)
  *   rtx/kernels/mxfp8_gemm.py:2048-2151; bound at rtx/fp8.py:932, :1260, :1338 and

@@ -467,9 +467,54 @@ int rtxb_mxfp8_quantize_transposed(const void* src, int64_t rows, int64_t k, int
   p.sf_chunks = (p.nb + 3) / 4;
   p.layout = scale_layout;
   p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
+  p.q_rows = nullptr;
+  p.s_rows = nullptr;
+  p.np = p.nb_rows = p.chunks_rows = 0;
   const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 127) / 128);
-  quant_mxfp8_transposed_kernel<<<quant_grid(tiles, 4), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t ae = cudaFuncSetAttribute(quant_mxfp8_transposed_kernel<false>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kQtSmemBytes);
+  if (ae != cudaSuccess) return fail_cuda(ae, "cudaFuncSetAttribute(transposed quantizer)");
+  quant_mxfp8_transposed_kernel<false><<<quant_grid(tiles, RTXB_QT_OCC), kQuantThreads, kQtSmemBytes,
+                                         static_cast<cudaStream_t>(stream)>>>(p);
   RTXB_CHECK_LAUNCH("quant_mxfp8_transposed_kernel");
+  return RTXB_OK;
+}
+
+int rtxb_mxfp8_quantize_dual(const void* src, int64_t m, int64_t n, int64_t ld, void* q_rows, void* s_rows, void* q_t,
+                             void* s_t, int scale_layout, int rounding, void* stream) {
+  if (!src || !q_rows || !s_rows || !q_t || !s_t) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || n <= 0 || ld < n) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (m > INT32_MAX - 256 || n > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
+  if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
+  if (!aligned(q_rows, 16) || !aligned(q_t, 16)) return fail_msg(RTXB_E_ALIGNMENT, "payloads must be 16-byte aligned");
+  if (scale_layout == RTXB_SCALE_MMA128 && (!aligned(s_rows, 16) || !aligned(s_t, 16)))
+    return fail_msg(RTXB_E_ALIGNMENT, "mma128 scale tiles must be 16-byte aligned");
+  QuantMxTParams p;
+  p.src = static_cast<const __nv_bfloat16*>(src);
+  p.q = static_cast<uint8_t*>(q_t);          // transposed: [n, mp], blocks along m
+  p.scales = static_cast<uint8_t*>(s_t);
+  p.rows = static_cast<int>(n);
+  p.k = static_cast<int>(m);
+  p.kp = static_cast<int>(round_up(m, 32));
+  p.ld = ld;
+  p.nb = p.kp / 32;
+  p.sf_chunks = (p.nb + 3) / 4;
+  p.layout = scale_layout;
+  p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
+  p.q_rows = static_cast<uint8_t*>(q_rows);  // rows: [m, np], blocks along n
+  p.s_rows = static_cast<uint8_t*>(s_rows);
+  p.np = static_cast<int>(round_up(n, 32));
+  p.nb_rows = p.np / 32;
+  p.chunks_rows = (p.nb_rows + 3) / 4;
+  const int64_t tiles = ((n + 127) / 128) * ((p.kp + 127) / 128);
+  cudaError_t ae = cudaFuncSetAttribute(quant_mxfp8_transposed_kernel<true>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kQtSmemBytes);
+  if (ae != cudaSuccess) return fail_cuda(ae, "cudaFuncSetAttribute(dual quantizer)");
+  quant_mxfp8_transposed_kernel<true><<<quant_grid(tiles, RTXB_QT_OCC), kQuantThreads, kQtSmemBytes,
+                                        static_cast<cudaStream_t>(stream)>>>(p);
+  RTXB_CHECK_LAUNCH("quant_mxfp8_transposed_kernel<dual>");
   return RTXB_OK;
 }
 
@@ -605,10 +650,16 @@ int rtxb_mxfp8_linear_bwd(const void* dy, const void* x, const void* w, void* dx
   uint8_t* qc = c.take(n * mp);  uint8_t* sc = c.take(rtxb_mxfp8_scale_bytes(n, m, RTXB_SCALE_MMA128));
   uint8_t* qd = c.take(k * mp);  uint8_t* sd = c.take(rtxb_mxfp8_scale_bytes(k, m, RTXB_SCALE_MMA128));
   int rc;
+  const bool shared_dy = dx && dw;   // both products: dY is read once for its row and its transposed quantization
+  if (shared_dy &&
+      (rc = rtxb_mxfp8_quantize_dual(dy, m, n, n, qa, sa, qc, sc, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+    return rc;
   if (dx) {
     if (!w) return fail_msg(RTXB_E_INVALID_ARGUMENT, "dx needs w");
     // A = dY [M, N] blocks along N; B = W^T as [K rows, N] blocks along N (W stored [N, K])
-    if ((rc = rtxb_mxfp8_quantize(dy, m, n, n, qa, sa, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+    if (!shared_dy &&
+        (rc = rtxb_mxfp8_quantize(dy, m, n, n, qa, sa, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+      return rc;
     if ((rc = rtxb_mxfp8_quantize_transposed(w, k, n, k, qb, sb, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
       return rc;
     if ((rc = rtxb_mxfp8_gemm(qa, sa, qb, sb, dx, m, k, n, k, RTXB_OUT_BF16, stream, status))) return rc;
@@ -616,7 +667,8 @@ int rtxb_mxfp8_linear_bwd(const void* dy, const void* x, const void* w, void* dx
   if (dw) {
     if (!x) return fail_msg(RTXB_E_INVALID_ARGUMENT, "dw needs x");
     // A = dY^T as [N rows, M] blocks along M (dY stored [M, N]); B = X^T as [K rows, M] (X stored [M, K])
-    if ((rc = rtxb_mxfp8_quantize_transposed(dy, n, m, n, qc, sc, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+    if (!shared_dy &&
+        (rc = rtxb_mxfp8_quantize_transposed(dy, n, m, n, qc, sc, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
       return rc;
     if ((rc = rtxb_mxfp8_quantize_transposed(x, k, m, k, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
       return rc;

@@ -167,80 +167,170 @@ struct QuantMxTParams {
   int rows, k, kp;
   int64_t ld;
   int nb, sf_chunks, layout, round_to_infinity;
+  // dual form: the same staged tile is also quantized along the source rows (blocks of 32 source columns),
+  // i.e. the plain row quantization of src, so that src is read from memory once for both
+  uint8_t* q_rows;           // [k, np], np = source columns rounded up to 32
+  uint8_t* s_rows;
+  int np, nb_rows, chunks_rows;
 };
 
-__global__ void __launch_bounds__(kQuantThreads) quant_mxfp8_transposed_kernel(const QuantMxTParams p) {
-  // [k_local][row_local] BF16 bits; pitch 130 halfwords = 65 words (odd) so a warp reading
-  // one k with 32 consecutive rows, or one row with consecutive k, stays conflict free
-  __shared__ uint16_t tile[128][130];
+// Staged tile: [k_local][row_local] BF16 bits, pitch 136 halfwords (272 bytes: 16-byte aligned rows for the
+// asynchronous 16-byte copies; a warp reading one k with 32 consecutive row pairs is conflict free).
+constexpr int kQtPitch = 136;
+constexpr int kQtTileBytes = 128 * kQtPitch * 2;
+constexpr int kQtSmemBytes = 2 * kQtTileBytes;   // two tiles: the next one is fetched while this one is quantized
+
+// Column pass over a staged 128 x 128 tile `tile[k_local][row_local]` (BF16 bits, pitch kQtPitch halfwords):
+// thread -> two adjacent output rows (source columns) x one block of 32 along k, so every
+// shared-memory read is one 32-bit word holding both rows' values; consecutive lanes read consecutive
+// words (conflict free).  Writes the E4M3 payload of rows row0 + r to `q` (pitch kp, columns from k0) and
+// the 128 x 4 scale codes to `tile_scales`.
+__device__ __forceinline__ void quant_mxfp8_tile_columns(const uint16_t (*tile)[kQtPitch], uint8_t (*tile_scales)[4],
+                                                         uint8_t* q, int kp, int rows, int row0, int k0,
+                                                         bool round_to_infinity) {
+  const int rp = threadIdx.x & 63, j = threadIdx.x >> 6;   // 64 row pairs x 4 blocks = 256 threads
+  uint32_t w[32];
+#pragma unroll
+  for (int e = 0; e < 32; ++e) w[e] = *reinterpret_cast<const uint32_t*>(&tile[j * 32 + e][2 * rp]);
+  const int kcol = k0 + j * 32;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float a = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) a = fmax_nan(a, fabsf(h ? bf16_hi(w[e]) : bf16_lo(w[e])));
+    const uint32_t code = e8m0_from_amax(a, round_to_infinity);
+    const float recip = e8m0_reciprocal(code);
+    const int r = 2 * rp + h, row = row0 + r;
+    const bool live = row < rows && kcol < kp;
+    tile_scales[r][j] = live ? static_cast<uint8_t>(code) : 0;
+    if (live) {
+      uint32_t o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float v0 = h ? bf16_hi(w[4 * e]) : bf16_lo(w[4 * e]), v1 = h ? bf16_hi(w[4 * e + 1]) : bf16_lo(w[4 * e + 1]);
+        const float v2 = h ? bf16_hi(w[4 * e + 2]) : bf16_lo(w[4 * e + 2]), v3 = h ? bf16_hi(w[4 * e + 3]) : bf16_lo(w[4 * e + 3]);
+        o[e] = cvt_e4m3x2(v0 * recip, v1 * recip) | (cvt_e4m3x2(v2 * recip, v3 * recip) << 16);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * kp + kcol);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
+// Row pass over the same staged tile: thread -> one source row (k_local) x two blocks of 32 source columns.
+__device__ __forceinline__ void quant_mxfp8_tile_rows(const uint16_t (*tile)[kQtPitch], uint8_t (*tile_scales)[4],
+                                                      uint8_t* q, int np, int k_rows, int cols, int k0, int col0,
+                                                      bool round_to_infinity) {
+  const int r = threadIdx.x & 127;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int jb = (threadIdx.x >> 7) + 2 * i;
+    // 16-byte reads: the row pitch is 17 chunks of 16 bytes (odd), so the eight lanes of a quarter warp --
+    // eight consecutive rows, same chunk -- fall into eight different bank groups
+    uint32_t w[16];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 v = *reinterpret_cast<const uint4*>(&tile[r][jb * 32 + 8 * c]);
+      w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) a = fmax_nan(a, fmax_nan(fabsf(bf16_lo(w[e])), fabsf(bf16_hi(w[e]))));
+    const uint32_t code = e8m0_from_amax(a, round_to_infinity);
+    const float recip = e8m0_reciprocal(code);
+    const int row = k0 + r, col = col0 + jb * 32;
+    const bool live = row < k_rows && col < np;
+    tile_scales[r][jb] = live ? static_cast<uint8_t>(code) : 0;
+    if (live) {
+      uint32_t o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        o[e] = cvt_e4m3x2(bf16_lo(w[2 * e]) * recip, bf16_hi(w[2 * e]) * recip) |
+               (cvt_e4m3x2(bf16_lo(w[2 * e + 1]) * recip, bf16_hi(w[2 * e + 1]) * recip) << 16);
+      uint4* dst = reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * np + col);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
+#ifndef RTXB_QT_OCC
+#define RTXB_QT_OCC 3   // resident CTAs per SM the transposed quantizer is compiled for (registers, 70 KB of tiles)
+#endif
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+  // copies 16 bytes, or writes 16 zero bytes when !valid (source size 0)
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src),
+               "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// fetch tile t (128 source rows x 128 source columns) into `tile`; aligned full-width tiles asynchronously
+__device__ __forceinline__ void quant_mxfp8_t_fetch(const QuantMxTParams& p, uint16_t (*tile)[kQtPitch], int row0, int k0,
+                                                    bool vec_ok) {
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(p.src);
+  if (vec_ok && row0 + 128 <= p.rows) {
+    const int c8 = (threadIdx.x & 15) * 8, kr = threadIdx.x >> 4;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gk = k0 + kr + 16 * j;
+      const bool valid = gk < p.k;
+      cp_async_16(&tile[kr + 16 * j][c8], src + static_cast<int64_t>(valid ? gk : 0) * p.ld + row0 + c8, valid);
+    }
+  } else {
+    for (int i = threadIdx.x; i < 128 * 64; i += kQuantThreads) {
+      const int kk = i >> 6, c2 = (i & 63) * 2;
+      const int gk = k0 + kk, gc = row0 + c2;
+      uint16_t a = 0, b = 0;
+      if (gk < p.k) {
+        const uint16_t* rp = src + static_cast<int64_t>(gk) * p.ld;
+        if (gc < p.rows) a = rp[gc];
+        if (gc + 1 < p.rows) b = rp[gc + 1];
+      }
+      tile[kk][c2] = a;
+      tile[kk][c2 + 1] = b;
+    }
+  }
+  cp_async_commit();
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(kQuantThreads, RTXB_QT_OCC) quant_mxfp8_transposed_kernel(const QuantMxTParams p) {
+  extern __shared__ __align__(16) uint8_t qt_smem[];
+  uint16_t (*tiles[2])[kQtPitch] = {reinterpret_cast<uint16_t (*)[kQtPitch]>(qt_smem),
+                                    reinterpret_cast<uint16_t (*)[kQtPitch]>(qt_smem + kQtTileBytes)};
   __shared__ __align__(16) uint8_t tile_scales[128][4];
+  __shared__ __align__(16) uint8_t tile_scales_rows[DUAL ? 128 : 1][4];
   const int row_tiles = (p.rows + 127) / 128;
   const int k_tiles = (p.kp + 127) / 128;
-  const uint16_t* src = reinterpret_cast<const uint16_t*>(p.src);
+  const int total = row_tiles * k_tiles;
   const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
-  for (int t = blockIdx.x; t < row_tiles * k_tiles; t += gridDim.x) {
+  int buf = 0;
+  if (static_cast<int>(blockIdx.x) < total)
+    quant_mxfp8_t_fetch(p, tiles[0], (blockIdx.x % row_tiles) * 128, (blockIdx.x / row_tiles) * 128, vec_ok);
+  for (int t = blockIdx.x; t < total; t += gridDim.x) {
     const int row0 = (t % row_tiles) * 128;  // output rows = source columns
     const int k0 = (t / row_tiles) * 128;
-    // load: 128 source rows (k) x 128 source columns.  Aligned case: eight 16-byte loads per
-    // thread, all issued before the first shared-memory store.
-    if (vec_ok && row0 + 128 <= p.rows) {
-      uint4 raw[8];
-      const int c8 = (threadIdx.x & 15) * 8, kr = threadIdx.x >> 4;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int gk = k0 + kr + 16 * j;
-        raw[j] = gk < p.k ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<int64_t>(gk) * p.ld + row0 + c8))
-                          : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[kr + 16 * j][c8]);
-        dst[0] = raw[j].x; dst[1] = raw[j].y; dst[2] = raw[j].z; dst[3] = raw[j].w;
-      }
+    const int tn = t + gridDim.x;
+    if (tn < total) {
+      quant_mxfp8_t_fetch(p, tiles[buf ^ 1], (tn % row_tiles) * 128, (tn / row_tiles) * 128, vec_ok);
+      cp_async_wait<1>();   // everything but the newest group (the next tile) has landed
     } else {
-      for (int i = threadIdx.x; i < 128 * 64; i += kQuantThreads) {
-        const int kk = i >> 6, c2 = (i & 63) * 2;
-        const int gk = k0 + kk, gc = row0 + c2;
-        uint16_t a = 0, b = 0;
-        if (gk < p.k) {
-          const uint16_t* rp = src + static_cast<int64_t>(gk) * p.ld;
-          if (gc < p.rows) a = rp[gc];
-          if (gc + 1 < p.rows) b = rp[gc + 1];
-        }
-        tile[kk][c2] = a;
-        tile[kk][c2 + 1] = b;
-      }
+      cp_async_wait<0>();
     }
     __syncthreads();
-    // quantise: thread -> (output row r, block j of 32 along k); 128 rows x 4 blocks = 512 items
-    for (int item = threadIdx.x; item < 512; item += kQuantThreads) {
-      const int r = item & 127, j = item >> 7;
-      float v[32];
-      float a = 0.0f;
-#pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        v[e] = __uint_as_float(static_cast<uint32_t>(tile[j * 32 + e][r]) << 16);
-        a = fmax_nan(a, fabsf(v[e]));
-      }
-      const uint32_t code = e8m0_from_amax(a, p.round_to_infinity != 0);
-      const float recip = e8m0_reciprocal(code);
-      const int row = row0 + r, kcol = k0 + j * 32;
-      const bool live = row < p.rows && kcol < p.kp;
-      tile_scales[r][j] = live ? static_cast<uint8_t>(code) : 0;
-      if (live) {
-        uint32_t w[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          w[e] = cvt_e4m3x2(v[4 * e] * recip, v[4 * e + 1] * recip) |
-                 (cvt_e4m3x2(v[4 * e + 2] * recip, v[4 * e + 3] * recip) << 16);
-        uint4* dst = reinterpret_cast<uint4*>(p.q + static_cast<int64_t>(row) * p.kp + kcol);
-        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-      }
-    }
+    quant_mxfp8_tile_columns(tiles[buf], tile_scales, p.q, p.kp, p.rows, row0, k0, p.round_to_infinity != 0);
+    if (DUAL)
+      quant_mxfp8_tile_rows(tiles[buf], tile_scales_rows, p.q_rows, p.np, p.k, p.rows, k0, row0,
+                            p.round_to_infinity != 0);
     __syncthreads();
     store_scale_tile<4>(tile_scales, p.scales, p.layout, row0, k0 / 32, p.rows, p.nb, p.sf_chunks);
-    __syncthreads();
+    if (DUAL) store_scale_tile<4>(tile_scales_rows, p.s_rows, p.layout, k0, row0 / 32, p.k, p.nb_rows, p.chunks_rows);
+    __syncthreads();   // the scale tiles and this buffer are free again
+    buf ^= 1;
   }
 }
 

@@ -102,6 +102,22 @@ def mxfp8_quantize_transposed(src: torch.Tensor, *, layout: int = N.SCALE_MMA128
     return q, scales
 
 
+def mxfp8_quantize_dual(src: torch.Tensor, *, layout: int = N.SCALE_MMA128, rounding: int = N.ROUND_INFINITY):
+    """src bf16 [M, N] -> (q_rows [M, Np], s_rows, q_t [N, Mp], s_t): the row quantization and the
+    quantization of the transpose from one read of src (the backward's gradient operand)."""
+    _require(src, torch.bfloat16, "src")
+    m, n = src.shape
+    np_, mp = mx_storage_k(n), mx_storage_k(m)
+    q_rows = torch.empty(m, np_, dtype=torch.uint8, device=src.device)
+    s_rows = torch.empty(mxfp8_scale_numel(m, n, layout), dtype=torch.uint8, device=src.device)
+    q_t = torch.empty(n, mp, dtype=torch.uint8, device=src.device)
+    s_t = torch.empty(mxfp8_scale_numel(n, m, layout), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        N.call("rtxb_mxfp8_quantize_dual", src.data_ptr(), m, n, n, q_rows.data_ptr(), s_rows.data_ptr(), q_t.data_ptr(),
+               s_t.data_ptr(), layout, rounding, _stream_ptr())
+    return q_rows, s_rows, q_t, s_t
+
+
 def mxfp8_gemm(qa, sa, qb, sb, m: int, n: int, k: int, *, out_dtype: torch.dtype = torch.bfloat16,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """(qx, qw, sx, sw) -> out[m,n]; scales in the mma128 layout."""

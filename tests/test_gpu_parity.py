@@ -496,6 +496,24 @@ def test_nvfp4_linear_fwd_prequant_w(gpu, m, n):
     _assert_output(y, want)
 
 
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (300, 1000), (33, 65), (1, 32), (1000, 72)])
+@pytest.mark.parametrize("layout", ["mma128", "row_major"])
+def test_mxfp8_quantize_dual_equals_separate_passes(gpu, shape, layout):
+    """The dual quantizer (gradient read once for the dX and the dW operand) gives the bytes of the row
+    quantizer and of the transposed quantizer, scale buffers included."""
+    ops, N, dev, _ = gpu
+    m, n = shape
+    torch.manual_seed(m * 3 + n)
+    g = (torch.randn(m, n) * 0.1).bfloat16().to(dev)
+    code = N.SCALE_MMA128 if layout == "mma128" else N.SCALE_ROW_MAJOR
+    q_rows, s_rows, q_t, s_t = ops.mxfp8_quantize_dual(g, layout=code)
+    q1, s1 = ops.mxfp8_quantize(g, layout=code)
+    q2, s2 = ops.mxfp8_quantize_transposed(g, layout=code)
+    _ok(ops, dev)
+    assert torch.equal(q_rows, q1) and torch.equal(s_rows, s1)
+    assert torch.equal(q_t, q2) and torch.equal(s_t, s2)
+
+
 @pytest.mark.parametrize("mnk", [(1, 64, 32), (128, 8192, 512), (100, 4100, 1000), (17, 63, 4096), (16, 19456, 256)])
 def test_mxfp8_skinny_shapes(gpu, mnk):
     ops, N, dev, ws = gpu
