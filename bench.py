@@ -250,7 +250,7 @@ def run_own_arm(args) -> None:
 
     # end to end through host buffers (rtx_b200.host.GluMlpHostSession): every step copies that step's X
     # from pinned host memory to the device and its Y back to pinned host memory; copy-in of step i+1 and
-    # copy-out of step i-1 overlap the compute of step i (three streams, two buffer sets)
+    # copy-out of step i-1 overlap the compute of step i (three streams, three device buffer sets)
     from rtx_b200.host import GluMlpHostSession
 
     session = GluMlpHostSession(wgu, wd, m_local)

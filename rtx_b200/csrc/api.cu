@@ -250,11 +250,8 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.ks = 1;
   p.map3d = 0;
   p.sfb3d = 0;
+  p.b_box256 = 0;
   p.overlap_previous = overlap_previous ? 1 : 0;
-  {
-    const char* dbg = getenv("RTXB_GEMM_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-  }
   if (use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI) && EPI != kEpiRegionBf16) {
     // one 128-row block of A: the bandwidth-shaped 128 x 64 kernel streams B once over all SMs
     using S = SkinnyTraits<KIND>;
@@ -330,6 +327,18 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, p);
     RTXB_CHECK_LAUNCH("gemm_blockscaled_pair_kernel");
     return RTXB_OK;
+  }
+  if (p.m_tiles == 1) {
+    // one row block: fetch only the live rows of A
+    p.a_box_rows = static_cast<int>(round_up(m, 8));
+    rc = make_payload_map(&map_a, qa, m, row_bytes, p.a_box_rows);
+    if (rc) return rc;
+  }
+  if (!epi_is_glu(EPI)) {
+    // plain tiles: the two 128-row halves of B are consecutive rows, one 256-row box brings both
+    p.b_box256 = 1;
+    rc = make_payload_map(&map_b, qb, n_rows_b, row_bytes, 256);
+    if (rc) return rc;
   }
   auto kernel = gemm_blockscaled_kernel<KIND, EPI>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);

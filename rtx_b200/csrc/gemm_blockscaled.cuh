@@ -118,17 +118,15 @@ struct GemmParams {
   uint8_t* sf_out;        // kEpiGluMx: E8M0 scales of H in 128-row tiles, sf_out_chunks tiles per row block
   int sf_out_chunks;
   int* status;            // device status word or nullptr
-  int a_box_rows;         // streaming kernel (M <= 128): rows of A fetched per K step (M rounded up to 8)
+  int a_box_rows;         // kernels for one row block (M <= 128): rows of A fetched per K step (M rounded up to 8)
   int slots;              // streaming kernel: ring slots that fit shared memory with that A box
   int ks;                 // streaming kernel: K steps per ring slot
   int map3d;              // streaming and pair kernels: payload maps are [K/128][rows][128] views (one load per
                           // operand brings all K steps of a ring slot / barrier group)
+  int b_box256;           // single-CTA kernel: the map of B has 256-row boxes (both halves of a tile in one load)
   int sfb3d;              // pair kernel: the scale map of B is 3-D, third coordinate = half of the 256-wide tile
   int overlap_previous;   // streaming kernel: launched as a programmatic dependent; A / SFA / out_scale may
                           // come from the grid before it, B / SFB do not
-  int debug;              // experiments only (results invalid when set): bit0 = copy scale factors on the
-                          // first K step only, bit1 = stop loading once the ring is filled,
-                          // bit2 = issue the scale copy of step i+1 before the MMAs of step i
 };
 
 // Tile order: groups of `group_m` M blocks; inside a group M runs fastest, then N.  CTAs that run at
@@ -417,8 +415,7 @@ __device__ __forceinline__ void mma_issuer_loop(const GemmParams& p, uint8_t* sm
           const uint32_t ssfb0 = PAIR ? smem_base + OFF_SFB + group * KS * SFB_BYTES + sub * SFA_BYTES
                                       : smem_base + OFF_SFB + slot * SFB_BYTES;
           const uint32_t ssfb1 = ssfb0 + (PAIR ? KS * SFA_BYTES : SFA_BYTES);
-          if (!(p.debug & 1) || (kg == 0 && sub == 0))
-            issue_scale_copy<KIND, PAIR>(tmem_base, smem_base + OFF_SFA + slot * SFA_BYTES, ssfb0, ssfb1, set);
+          issue_scale_copy<KIND, PAIR>(tmem_base, smem_base + OFF_SFA + slot * SFA_BYTES, ssfb0, ssfb1, set);
           issue_k_step<KIND, PAIR>(tmem_base, acc_col, smem_base + slot * A_BYTES, smem_base + OFF_B + slot * B_BYTES,
                                    set, idesc, kg == 0 && sub == 0);
         }
@@ -521,30 +518,33 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             break;
           }
           if (leader) {
-            if ((p.debug & 2) && (kg * KS >= kStages || tile != static_cast<int>(blockIdx.x))) {
-              mbar_arrive(&full_bar[group]);  // experiment: reuse whatever the slots hold, no loads
-            } else {
-              // K steps past the end of K fetch zero payload (TMA fill) and no scale tiles
-              const int live = min(KS, p.k_tiles - kg * KS);
-              mbar_expect_tx(&full_bar[group], KS * (T::kABytes + T::kBBytes) +
-                                                   live * (T::kSfaBytes + (b1_valid ? T::kSfbBytes : T::kSfaBytes)));
+            // K steps past the end of K fetch zero payload (TMA fill) and no scale tiles
+            const int live = min(KS, p.k_tiles - kg * KS);
+            // A: only the live rows are fetched when there is a single row block (box of a_box_rows rows; the
+            // MMA reads 128 rows of the slot, the rest only reaches accumulator rows that are never stored)
+            mbar_expect_tx(&full_bar[group], KS * (p.a_box_rows * kBlockKBytes + T::kBBytes) +
+                                                 live * (T::kSfaBytes + (b1_valid ? T::kSfbBytes : T::kSfaBytes)));
 #pragma unroll
-              for (int sub = 0; sub < KS; ++sub) {
-                const int slot = group * KS + sub;
-                const int kt = kg * KS + sub;
-                uint8_t* sa = smem + slot * T::kABytes;
-                uint8_t* sb = smem + T::kOffB + slot * T::kBBytes;
-                uint8_t* ssfa = smem + T::kOffSfa + slot * T::kSfaBytes;
-                uint8_t* ssfb = smem + T::kOffSfb + slot * T::kSfbBytes;
-                tma_load_2d(sa, &map_a, &full_bar[group], kt * kBlockKBytes, m0);
+            for (int sub = 0; sub < KS; ++sub) {
+              const int slot = group * KS + sub;
+              const int kt = kg * KS + sub;
+              uint8_t* sa = smem + slot * T::kABytes;
+              uint8_t* sb = smem + T::kOffB + slot * T::kBBytes;
+              uint8_t* ssfa = smem + T::kOffSfa + slot * T::kSfaBytes;
+              uint8_t* ssfb = smem + T::kOffSfb + slot * T::kSfbBytes;
+              tma_load_2d(sa, &map_a, &full_bar[group], kt * kBlockKBytes, m0);
+              if (p.b_box256) {
+                // the two halves are 256 consecutive rows of B: one box
+                tma_load_2d(sb, &map_b, &full_bar[group], kt * kBlockKBytes, b_row0);
+              } else {
                 tma_load_2d(sb, &map_b, &full_bar[group], kt * kBlockKBytes, b_row0);
                 tma_load_2d(sb + 128 * kBlockKBytes, &map_b, &full_bar[group], kt * kBlockKBytes, b_row1);
-                if (sub < live) {
-                  const size_t sf_off = static_cast<size_t>(kt) * T::kSfaBytes;
-                  bulk_load_1d(ssfa, sfa_src + sf_off, T::kSfaBytes, &full_bar[group]);
-                  bulk_load_1d(ssfb, sfb_src0 + sf_off, T::kSfaBytes, &full_bar[group]);
-                  if (b1_valid) bulk_load_1d(ssfb + T::kSfaBytes, sfb_src1 + sf_off, T::kSfaBytes, &full_bar[group]);
-                }
+              }
+              if (sub < live) {
+                const size_t sf_off = static_cast<size_t>(kt) * T::kSfaBytes;
+                bulk_load_1d(ssfa, sfa_src + sf_off, T::kSfaBytes, &full_bar[group]);
+                bulk_load_1d(ssfb, sfb_src0 + sf_off, T::kSfaBytes, &full_bar[group]);
+                if (b1_valid) bulk_load_1d(ssfb + T::kSfaBytes, sfb_src1 + sf_off, T::kSfaBytes, &full_bar[group]);
               }
             }
           }

@@ -1,9 +1,10 @@
 """Host-buffer entry point for the SwiGLU MLP: the call a user with activations in
 host memory makes.  Each `submit` copies X from pinned host memory to the device,
 runs the MXFP8 MLP (quantize, gate/up GEMM with fused SiLU*up, quantize, down GEMM)
-and copies Y back to pinned host memory.  Three streams and two device buffer sets
+and copies Y back to pinned host memory.  Three streams and three device buffer sets
 let the copy-in of step i+1 and the copy-out of step i-1 overlap the compute of
-step i; `drain()` waits for everything submitted.
+step i (a buffer set's X is free again as soon as its previous compute has finished,
+its Y once the previous copy-out has); `drain()` waits for everything submitted.
 """
 
 from __future__ import annotations
@@ -16,7 +17,7 @@ from . import ops
 
 
 class GluMlpHostSession:
-    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, max_rows: int, depth: int = 2):
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, max_rows: int, depth: int = 3):
         if w_gate_up.device.type != "cuda":
             raise ValueError("weights must already be resident on the GPU")
         self.device = w_gate_up.device
@@ -45,9 +46,11 @@ class GluMlpHostSession:
             raise ValueError("activation shape does not fit this session")
         b = self._step % self.depth
         with torch.cuda.device(self.device):
-            # the buffer set is free once its previous occupant has been copied out
+            # x[b] is free once the previous occupant's kernels have read it; y[b] once it has been copied out
+            if self._compute_done[b] is not None:
+                self.copy_in.wait_event(self._compute_done[b])
             if self._out_done[b] is not None:
-                self.copy_in.wait_event(self._out_done[b])
+                self.compute.wait_event(self._out_done[b])
             with torch.cuda.stream(self.copy_in):
                 self.x[b][:m].copy_(x_host, non_blocking=True)
                 self._in_done[b] = torch.cuda.Event()
