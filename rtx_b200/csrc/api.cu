@@ -13,6 +13,7 @@
 
 #include <atomic>
 #include "quant.cuh"
+#include "gemm_decode_fused.cuh"
 
 using namespace rtxb;
 
@@ -347,6 +348,67 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   e = launch_dependent(kernel, grid, kGemmThreads, T::kSmemBytes, stream, overlap_previous, map_a, map_b, p);
   if (e != cudaSuccess) return fail_cuda(e, "gemm_blockscaled_kernel launch");
+  return RTXB_OK;
+}
+
+// The one-kernel decode forward: up to four rows (every CTA re-quantizes all of X, which costs about
+// 0.9 us per row even with twelve quantizer warps: measured 12.7 us at M = 1 and 18.7 us at M = 8 against
+// 16.1 us for the three chained launches), K a multiple of 256 values whose quantized form (A tiles +
+// scale tiles for every K step) leaves room for at least three ring slots of weights, and few enough
+// 256-wide column tiles that the 64-wide streaming tiling is the right one.
+// RTXB_DECODE_FUSED=0/1 forces the choice where the shape allows it (up to kFusedMaxRows rows).
+bool decode_fused_eligible(const void* x, int64_t m, int64_t n, int64_t k) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* v = getenv("RTXB_DECODE_FUSED");
+    forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
+  }
+  if (forced == 0) return false;
+  if (m > kFusedMaxRows || k % 256 != 0 || !aligned(x, 16)) return false;
+  const int k_tiles = static_cast<int>(k / 256);
+  if (k_tiles < 2 || fused_slots_for(k_tiles, 2) < 3) return false;
+  return forced == 1 || (m <= 4 && use_skinny_kernel(1, n));
+}
+
+int launch_decode_fused(const void* x, const void* qw, const void* sw, const float* w_scale, void* out, int64_t m,
+                        int64_t n, int64_t k, int scale_mode, float* x_scale_out, cudaStream_t stream, int* status) {
+  using S = SkinnyTraits<kKindNvfp4>;
+  const int64_t row_bytes = k / 2;
+  GemmParams p = {};
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k_tiles = static_cast<int>(k / 256);
+  p.m_tiles = 1;
+  p.n_tiles = static_cast<int>((n + kSkinnyN - 1) / kSkinnyN);
+  p.sfb = static_cast<const uint8_t*>(sw);
+  p.sf_k_chunks = static_cast<int>(round_up((k / 16 + 3) / 4, 4));
+  p.out = out;
+  p.ldo = n;
+  p.out_cols = static_cast<int>(n);
+  p.out_vec_ok = (aligned(out, 16) && (n * 2) % 16 == 0) ? 1 : 0;
+  p.status = status;
+  p.ks = fused_slots_for(p.k_tiles, 4) >= 4 && p.k_tiles >= 4 ? 4 : 2;
+  p.slots = fused_slots_for(p.k_tiles, p.ks);
+  p.map3d = 1;
+  CUtensorMap map_b;
+  int rc = make_payload_map_ksteps(&map_b, qw, n, row_bytes, kSkinnyN, p.ks);
+  if (rc) return rc;
+  FusedXParams fx;
+  fx.x = static_cast<const __nv_bfloat16*>(x);
+  fx.ldx = k;
+  fx.k = static_cast<int>(k);
+  fx.mode = scale_mode;
+  fx.w_scale = w_scale;
+  fx.x_scale_out = x_scale_out;
+  cudaError_t e = cudaFuncSetAttribute(gemm_decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSkinnySmemBudget);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(decode fused)");
+  // quantizer warps: 4 (they are also the epilogue warps) for one or two rows, 12 above
+  const int threads = m <= 2 ? kGemmThreads : kFusedMaxThreads;
+  e = launch_dependent(gemm_decode_fused_kernel, p.n_tiles < sm_count() ? p.n_tiles : sm_count(), threads,
+                       fused_smem_bytes(p.k_tiles, p.ks, p.slots), stream, true, map_b, p, fx);
+  if (e != cudaSuccess) return fail_cuda(e, "gemm_decode_fused_kernel launch");
+  (void)S::kSfBytes;
   return RTXB_OK;
 }
 
@@ -1001,6 +1063,12 @@ int rtxb_nvfp4_linear_fwd_prequant_w(const void* x, const void* qw, const void* 
   // scalar block: [0, 256) |max| partials, [256] x scale, [264] output scale
   float* x_scale = reinterpret_cast<float*>(scal + 256);
   float* o_scale = reinterpret_cast<float*>(scal + 264);
+  if (decode_fused_eligible(x, m, n, k)) {
+    // a handful of rows: one kernel quantizes them in every CTA while the weight already streams
+    rc = launch_decode_fused(x, qw, sw, w_scale, out, m, n, k, scale_mode, x_scale, static_cast<cudaStream_t>(stream),
+                             status);
+    return rc;
+  }
   rc = rtxb_nvfp4_quantize_dynamic(x, m, k, k, scale_mode, qx, sx, RTXB_SCALE_MMA128, x_scale, w_scale, o_scale, scal,
                                    stream);
   if (rc) return rc;

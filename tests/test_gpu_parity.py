@@ -514,6 +514,32 @@ def test_mxfp8_quantize_dual_equals_separate_passes(gpu, shape, layout):
     assert torch.equal(q_t, q2) and torch.equal(s_t, s2)
 
 
+@pytest.mark.parametrize("mnk", [(1, 64, 512), (3, 1000, 768), (4, 130, 2048), (4, 8192, 8192), (2, 4096, 4096)])
+@pytest.mark.parametrize("mode", ["power2", "exact"])
+def test_nvfp4_decode_one_kernel_equals_the_chain(gpu, mnk, mode):
+    """M <= 4 and K a multiple of 256: the activations are quantized inside the GEMM kernel (every CTA
+    reduces |max| of X, applies the scale rule and writes the swizzled A tiles itself).  Bit equal to the
+    separate |max| / quantize / GEMM launches, and within tolerance of the oracle."""
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    torch.manual_seed(m * 5 + n + k)
+    x = (torch.randn(m, k) * 1.7).bfloat16()
+    w = (torch.randn(n, k) / k ** 0.5).bfloat16()
+    code = N.TENSOR_SCALE_EXACT if mode == "exact" else N.TENSOR_SCALE_POWER2
+    wd, xd = w.to(dev), x.to(dev)
+    w_scale = ops.nvfp4_tensor_scale(wd, N.TENSOR_SCALE_EXACT)
+    qw, sw = ops.nvfp4_quantize(wd, w_scale)
+    for _ in range(2):
+        y = ops.nvfp4_linear_fwd_prequant_w(xd, qw, sw, w_scale, n, ws, scale_mode=code)
+    x_scale, o_scale = ops.nvfp4_tensor_scale(xd, code, other_scale=w_scale)
+    qx, sx = ops.nvfp4_quantize(xd, x_scale)
+    y2 = ops.nvfp4_gemm(qx, sx, qw, sw, m, n, k, o_scale)
+    _ok(ops, dev)
+    assert torch.equal(y, y2)
+    want = O.nvfp4_linear(x, w, x_scale=O.nvfp4_tensor_scale(x, mode), w_scale=O.nvfp4_tensor_scale(w, "exact"))
+    _assert_output(y, want)
+
+
 @pytest.mark.parametrize("mnk", [(1, 64, 32), (128, 8192, 512), (100, 4100, 1000), (17, 63, 4096), (16, 19456, 256)])
 def test_mxfp8_skinny_shapes(gpu, mnk):
     ops, N, dev, ws = gpu
