@@ -304,6 +304,27 @@ def _(x, weight_data, weight_block_scales, x_scale, output_scale, n, k, layout, 
     return x.new_empty((x.shape[0], n), dtype=torch.bfloat16)
 
 
+@torch.library.custom_op("rtx::nvfp4_linear_prequant_w_current", mutates_args=(), device_types="cuda")
+def nvfp4_linear_prequant_w_current(x: torch.Tensor, weight_data: torch.Tensor, weight_block_scales: torch.Tensor,
+                                    weight_tensor_scale: torch.Tensor, n: int, k: int, layout: str,
+                                    key: str) -> torch.Tensor:
+    """Packed weight, BF16 activations with their exact current outer scale, all inside one call: what
+    `NVFP4Linear.forward` does for a packed weight (rtx/fp4.py:3421-3446 `_current_tensor_scale` followed by
+    `nvfp4_linear_dynamic_x_prequant_w`), without the separate scale op and product.  Decode-sized inputs
+    take one kernel (M <= 4) or three chained launches; the bits equal the two-op route."""
+    if x.dtype is not torch.bfloat16 or x.ndim != 2 or x.shape[1] != k:
+        raise TypeError("x must be BF16 [M, K]")
+    x = x if x.is_contiguous() else x.contiguous()
+    sw = _kernel_block_scales(weight_block_scales, n, k, layout)
+    return ops.nvfp4_linear_fwd_prequant_w(x, weight_data.view(torch.uint8), sw, weight_tensor_scale, n,
+                                           _fp8._workspace(x.device), scale_mode=N.TENSOR_SCALE_EXACT)
+
+
+@nvfp4_linear_prequant_w_current.register_fake
+def _(x, weight_data, weight_block_scales, weight_tensor_scale, n, k, layout, key):
+    return x.new_empty((x.shape[0], n), dtype=torch.bfloat16)
+
+
 @torch.library.custom_op("rtx::nvfp4_linear_prequantized", mutates_args=(), device_types="cuda")
 def nvfp4_linear_prequantized(x_data: torch.Tensor, weight_data: torch.Tensor, x_block_scales: torch.Tensor,
                               weight_block_scales: torch.Tensor, output_scale: torch.Tensor, m: int, n: int, k: int,
@@ -412,9 +433,8 @@ def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
         if x.requires_grad:
             raise RuntimeError("a prequantized NVFP4 weight is inference-only; keep the BF16 master weight to train")
         x2d = x.reshape(-1, k)
-        x_scale = _current_tensor_scale(x2d)            # rtx/fp4.py:3421-3446: exact scale for packed weights
-        out = torch.ops.rtx.nvfp4_linear_dynamic_x_prequant_w(x2d, wq, wscales, x_scale, x_scale * w_scale, n, k,
-                                                              "mma128", key)
+        # rtx/fp4.py:3421-3446: exact current scale of the activations for packed weights
+        out = torch.ops.rtx.nvfp4_linear_prequant_w_current(x2d, wq, wscales, w_scale, n, k, "mma128", key)
         return out.reshape(*x.shape[:-1], n)
     _check_bf16_cuda(x, "activation")
     _check_bf16_cuda(weight, "weight")
@@ -597,9 +617,9 @@ class NVFP4Linear(nn.Module):
         if self.weight_mode == "prequantized":
             if x.requires_grad and torch.is_grad_enabled():
                 raise RuntimeError("a prequantized NVFP4 weight is inference-only; keep the BF16 master weight to train")
-            x_scale = torch.ops.rtx.nvfp4_outer_scale(x2d.detach(), "exact")   # rtx/fp4.py:3421-3446
-            out = torch.ops.rtx.nvfp4_linear_dynamic_x_prequant_w(
-                x2d, self.weight_data, self.weight_block_scales, x_scale, x_scale * self.weight_tensor_scale, n, k,
+            # exact current outer scale of the activations (rtx/fp4.py:3421-3446), computed inside the call
+            out = torch.ops.rtx.nvfp4_linear_prequant_w_current(
+                x2d, self.weight_data, self.weight_block_scales, self.weight_tensor_scale, n, k,
                 self._weight_scale_layout, key)
             return out.reshape(*x.shape[:-1], n)
         if self._dynamic_config.scale.policy == "delayed":

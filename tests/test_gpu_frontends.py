@@ -187,6 +187,15 @@ def test_nvfp4_linear_module_and_packed_weight(dev):
     x2 = x_cpu.reshape(-1, 256)
     want = O.nvfp4_linear(x2, w_cpu, x_scale=O.nvfp4_tensor_scale(x2, "exact"), w_scale=O.nvfp4_tensor_scale(w_cpu, "exact"))
     _close(yp.reshape(-1, 192), want)
+    # decode-sized call through the packed module: one kernel quantizes the two rows and runs the GEMM
+    base = rtx.NVFP4Linear(512, 192, device=dev, scaling="current")
+    dec = base.to_quantized_weight()
+    xs, wb = torch.randn(2, 512).bfloat16(), base.weight.detach().cpu()
+    with torch.no_grad():
+        yd = dec(xs.to(dev))
+    _done(dev)
+    _close(yd, O.nvfp4_linear(xs, wb, x_scale=O.nvfp4_tensor_scale(xs, "exact"),
+                              w_scale=O.nvfp4_tensor_scale(wb, "exact")))
     t = rtx.quantize_nvfp4(layer.weight.detach())
     qo, so = O.nvfp4_quantize(w_cpu, O.nvfp4_tensor_scale(w_cpu, "exact"))
     assert torch.equal(t.qdata.view(torch.uint8).cpu().reshape(192, 128), qo)
