@@ -45,6 +45,47 @@ def test_queries_and_argument_checks(native_lib):
         N.call("rtxb_mxfp8_linear_fwd", None, None, None, 8, 8, 32, 1, None, 0, None, None)
 
 
+def test_newer_entry_points_reject_bad_arguments_before_any_launch(native_lib):
+    """Decode, row-region, delayed, dual-quantize and SM-margin entry points: every rejection below happens
+    in host code, so it can be checked without a GPU."""
+    import ctypes
+
+    from rtx_b200 import _native as N
+
+    L = native_lib
+    buf = (ctypes.c_uint8 * 4096)()
+    p = ctypes.addressof(buf) + (16 - ctypes.addressof(buf) % 16) % 16      # any 16-byte aligned non-null address
+    assert L.rtxb_nvfp4_quantize_dynamic(None, 1, 32, 32, 1, None, None, 2, None, None, None, None, None) == -1
+    assert L.rtxb_nvfp4_quantize_dynamic(p, 1, 32, 16, 1, p, p, 2, p, None, None, p, None) == -1      # ld < k
+    assert L.rtxb_nvfp4_quantize_dynamic(p, 1, 32, 32, 7, p, p, 2, p, None, None, p, None) == -1      # scale mode
+    assert L.rtxb_nvfp4_quantize_dynamic(p, 1, 32, 32, 1, p, p, 2, p, p, None, p, None) == -1         # scales go together
+    assert L.rtxb_nvfp4_linear_fwd_prequant_w(p, p, p, None, p, 1, 64, 256, 0, p, 1 << 20, None, None) == -1
+    assert L.rtxb_nvfp4_linear_fwd_prequant_w(p, p, p, p, p, 1, 64, 256, 0, None, 0, None, None) == -4
+    assert N.query("rtxb_nvfp4_linear_prequant_w_workspace_bytes", 8, 8192) >= 8 * 4096
+    # regions must divide the rows; a single region needs the scratch word
+    assert L.rtxb_nvfp4_region_scales(p, 10, 32, 32, 4, 1, p, p, None) == -1
+    assert L.rtxb_nvfp4_region_scales(p, 10, 32, 32, 10, 1, None, p, None) == -1
+    assert L.rtxb_nvfp4_quantize_regions(p, 10, 32, 32, p, p, 2, None, 5, None) == -1
+    assert L.rtxb_nvfp4_quantize_regions(p, 10, 32, 32, p, p, N.SCALE_MMA64, p, 5, None) == -2
+    assert L.rtxb_nvfp4_gemm_regions(p, p, p, p, p, 10, 8, 32, 8, p, 3, p, 4, None, None) == -1      # 3 does not divide 10
+    ws = N.query("rtxb_nvfp4_linear_regions_workspace_bytes", 256, 512, 256, 5, 4)
+    assert ws >= 256 * 128 + 512 * 128
+    assert L.rtxb_nvfp4_linear_fwd_regions(p, p, p, 256, 512, 256, 5, 4, 1, p, ws - 1, None, None) == -4
+    # delayed: history length 1/4/16/64, two distinct generations
+    assert L.rtxb_nvfp4_quantize_delayed(p, 1, 32, 32, p, p, 2, p, p + 256, 5, 1, 1, p, None, None, None) == -1
+    assert L.rtxb_nvfp4_quantize_delayed(p, 1, 32, 32, p, p, 2, p, p, 4, 1, 1, p, None, None, None) == -1
+    assert L.rtxb_nvfp4_linear_fwd_delayed(p, p, p, 8, 8, 32, p, p, p, p, 4, 1, 1, None, 0, None, None) == -4
+    # dual quantizer
+    assert L.rtxb_mxfp8_quantize_dual(p, 4, 32, 32, p, p, None, p, 2, 1, None) == -1
+    assert L.rtxb_mxfp8_quantize_dual(p, 4, 32, 16, p, p, p, p, 2, 1, None) == -1
+    assert L.rtxb_mxfp8_quantize_dual(p, 4, 32, 32, p, p, p, p, N.SCALE_MMA64, 1, None) == -2
+    # SM margin: process-wide setting with a sane range
+    assert L.rtxb_get_sm_margin() == 0
+    assert L.rtxb_set_sm_margin(32) == 0 and L.rtxb_get_sm_margin() == 32
+    assert L.rtxb_set_sm_margin(-1) == -1 and L.rtxb_set_sm_margin(1000) == -1 and L.rtxb_get_sm_margin() == 32
+    assert L.rtxb_set_sm_margin(0) == 0
+
+
 def test_missing_library_is_loud(monkeypatch, tmp_path):
     from rtx_b200 import _native as N
 
