@@ -165,9 +165,9 @@ def _nv_train_backward(ctx, grad_output):
     if need_dx and need_dw:
         dx, dw = torch.ops.rtx.mxfp8_linear_bwd(grad_output, x, weight, ctx.bwd_key)
     elif need_dx:
-        dx = torch.ops.rtx.mxfp8_linear_dx(grad_output, weight, ctx.bwd_key)
+        dx = torch.ops.rtx.mxfp8_linear_dx(grad_output, x, weight, ctx.bwd_key)
     elif need_dw:
-        dw = torch.ops.rtx.mxfp8_linear_dw(grad_output, x, ctx.bwd_key)
+        dw = torch.ops.rtx.mxfp8_linear_dw(grad_output, x, weight, ctx.bwd_key)
     return (dx, dw) + (None,) * (ctx.n_inputs - 2)
 
 

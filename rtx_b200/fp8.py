@@ -164,6 +164,39 @@ def _kernel_scales(scales: torch.Tensor, rows: int, k: int, layout: str) -> torc
     raise RuntimeError(f"MXFP8 scale layout {layout!r} cannot feed the sm_100a GEMM")
 
 
+# Launch-only variants writing into a caller-provided [M, N] BF16 tensor (rtx/fp8.py:648-680, :1043-1075)
+_OUT_LIBRARY = torch.library.Library("rtx", "FRAGMENT")
+_OUT_LIBRARY.define("mxfp8_linear_fwd_out(Tensor x, Tensor weight, str config_key, Tensor(a!) out) -> ()")
+_OUT_LIBRARY.define("mxfp8_linear_prequant_out(Tensor x, Tensor weight, str config_key, Tensor(a!) out) -> ()")
+
+
+def _fwd_out(x, weight, config_key, out):
+    _check_inputs(x, weight)
+    cfg = _resolve_prequant(config_key)
+    rejection = cfg.rejection(MXFP8Problem(int(x.shape[0]), int(weight.shape[0]), int(x.shape[1])))
+    if rejection is not None:
+        raise RuntimeError(f"illegal MXFP8 forward schedule: {rejection}")
+    if tuple(out.shape) != (x.shape[0], weight.shape[0]) or out.dtype is not torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous BF16 [M, N] tensor")
+    ops.mxfp8_linear_fwd(x if x.is_contiguous() else x.contiguous(),
+                         weight if weight.is_contiguous() else weight.contiguous(), _workspace(x.device), out=out,
+                         rounding=_rounding(cfg))
+
+
+torch.library.impl("rtx::mxfp8_linear_fwd_out", "cuda")(_fwd_out)
+torch.library.impl("rtx::mxfp8_linear_prequant_out", "cuda")(_fwd_out)
+
+
+@torch.library.register_fake("rtx::mxfp8_linear_fwd_out")
+def _(x, weight, config_key, out):
+    return None
+
+
+@torch.library.register_fake("rtx::mxfp8_linear_prequant_out")
+def _(x, weight, config_key, out):
+    return None
+
+
 @torch.library.custom_op("rtx::mxfp8_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
 def mxfp8_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor, weight_scales: torch.Tensor, n: int,
                                       k: int, weight_scale_layout: str, config_key: str) -> torch.Tensor:

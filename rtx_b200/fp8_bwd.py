@@ -103,25 +103,83 @@ def unpack_bwd(flat: torch.Tensor, x_shape, w_shape):
 
 
 @torch.library.custom_op("rtx::mxfp8_linear_dx", mutates_args=(), device_types="cuda")
-def mxfp8_linear_dx(grad_output: torch.Tensor, weight: torch.Tensor, config_key: str) -> torch.Tensor:
+def mxfp8_linear_dx(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                    config_key: str) -> torch.Tensor:
+    """dX only; `x` gives the result's shape, as in the reference (rtx/fp8_bwd.py:1097-1118)."""
     _bwd_config(config_key)
     return _run(grad_output, None, weight, True, False)[0]
 
 
 @mxfp8_linear_dx.register_fake
-def _(grad_output, weight, config_key):
-    return grad_output.new_empty((grad_output.shape[0], weight.shape[1]), dtype=torch.bfloat16)
+def _(grad_output, x, weight, config_key):
+    return torch.empty_like(x)
 
 
 @torch.library.custom_op("rtx::mxfp8_linear_dw", mutates_args=(), device_types="cuda")
-def mxfp8_linear_dw(grad_output: torch.Tensor, x: torch.Tensor, config_key: str) -> torch.Tensor:
+def mxfp8_linear_dw(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                    config_key: str) -> torch.Tensor:
+    """dW only; `weight` gives the result's shape (rtx/fp8_bwd.py:1121-1142)."""
     _bwd_config(config_key)
     return _run(grad_output, x, None, False, True)[1]
 
 
 @mxfp8_linear_dw.register_fake
-def _(grad_output, x, config_key):
-    return grad_output.new_empty((grad_output.shape[1], x.shape[1]), dtype=torch.bfloat16)
+def _(grad_output, x, weight, config_key):
+    return torch.empty_like(weight)
+
+
+# Launch-only overloads writing into caller-provided tensors (rtx/fp8_bwd.py:1145-1248): compiled graphs
+# allocate the results in their memory planner and call these.
+_OUT_LIBRARY = torch.library.Library("rtx", "FRAGMENT")
+_OUT_TAGS = (torch.Tag.out,) if hasattr(torch.Tag, "out") else ()
+_OUT_LIBRARY.define("mxfp8_linear_bwd.out(Tensor grad_output, Tensor x, Tensor weight, str config_key, *, "
+                    "Tensor(a!) grad_x, Tensor(b!) grad_weight) -> (Tensor(a!), Tensor(b!))", tags=_OUT_TAGS)
+_OUT_LIBRARY.define("mxfp8_linear_dx.out(Tensor grad_output, Tensor x, Tensor weight, str config_key, *, "
+                    "Tensor(a!) grad_x) -> Tensor(a!)", tags=_OUT_TAGS)
+_OUT_LIBRARY.define("mxfp8_linear_dw.out(Tensor grad_output, Tensor x, Tensor weight, str config_key, *, "
+                    "Tensor(a!) grad_weight) -> Tensor(a!)", tags=_OUT_TAGS)
+
+
+def _run_out(grad_output, x, weight, need_dx, need_dw, grad_x=None, grad_weight=None):
+    ops.mxfp8_linear_bwd(_contig(grad_output), _contig(x) if need_dw else None, _contig(weight) if need_dx else None,
+                         _fp8._workspace(grad_output.device), need_dx=need_dx, need_dw=need_dw, dx_out=grad_x,
+                         dw_out=grad_weight)
+
+
+@torch.library.impl("rtx::mxfp8_linear_bwd.out", "cuda")
+def _bwd_out(grad_output, x, weight, config_key, *, grad_x, grad_weight):
+    _bwd_config(config_key)
+    _run_out(grad_output, x, weight, True, True, grad_x, grad_weight)
+    return grad_x, grad_weight
+
+
+@torch.library.impl("rtx::mxfp8_linear_dx.out", "cuda")
+def _dx_out(grad_output, x, weight, config_key, *, grad_x):
+    _bwd_config(config_key)
+    _run_out(grad_output, x, weight, True, False, grad_x=grad_x)
+    return grad_x
+
+
+@torch.library.impl("rtx::mxfp8_linear_dw.out", "cuda")
+def _dw_out(grad_output, x, weight, config_key, *, grad_weight):
+    _bwd_config(config_key)
+    _run_out(grad_output, x, weight, False, True, grad_weight=grad_weight)
+    return grad_weight
+
+
+@torch.library.register_fake("rtx::mxfp8_linear_bwd.out")
+def _(grad_output, x, weight, config_key, *, grad_x, grad_weight):
+    return grad_x, grad_weight
+
+
+@torch.library.register_fake("rtx::mxfp8_linear_dx.out")
+def _(grad_output, x, weight, config_key, *, grad_x):
+    return grad_x
+
+
+@torch.library.register_fake("rtx::mxfp8_linear_dw.out")
+def _(grad_output, x, weight, config_key, *, grad_weight):
+    return grad_weight
 
 
 @torch.library.custom_op("rtx::mxfp8_linear_dw_f32", mutates_args=(), device_types="cuda")
@@ -164,9 +222,9 @@ def _train_backward(ctx, grad_output):
         dx, dw = torch.ops.rtx.mxfp8_linear_bwd(grad_output, x, weight, ctx.bwd_key)
         return dx, dw, None, None
     if need_dx:
-        return torch.ops.rtx.mxfp8_linear_dx(grad_output, weight, ctx.bwd_key), None, None, None
+        return torch.ops.rtx.mxfp8_linear_dx(grad_output, x, weight, ctx.bwd_key), None, None, None
     if need_dw:
-        return None, torch.ops.rtx.mxfp8_linear_dw(grad_output, x, ctx.bwd_key), None, None
+        return None, torch.ops.rtx.mxfp8_linear_dw(grad_output, x, weight, ctx.bwd_key), None, None
     return None, None, None, None
 
 

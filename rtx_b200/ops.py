@@ -209,13 +209,23 @@ def mxfp8_glu_mlp_fwd(x, w_gate_up, w_down, ws: Workspace, h: Optional[torch.Ten
 
 
 def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: bool = True,
-                     dw_dtype: torch.dtype = torch.bfloat16):
-    """(dY [M,N], X [M,K], W [N,K]) -> (dX bf16 [M,K] | None, dW [N,K] | None)."""
+                     dw_dtype: torch.dtype = torch.bfloat16, dx_out: Optional[torch.Tensor] = None,
+                     dw_out: Optional[torch.Tensor] = None):
+    """(dY [M,N], X [M,K], W [N,K]) -> (dX bf16 [M,K] | None, dW [N,K] | None); results go into
+    `dx_out` / `dw_out` (contiguous, right shape and dtype) when given."""
     _require(dy, torch.bfloat16, "grad_output")
     m, n = dy.shape
     k = w.shape[1] if w is not None else x.shape[1]
-    dx = torch.empty(m, k, dtype=torch.bfloat16, device=dy.device) if need_dx else None
-    dw = torch.empty(n, k, dtype=dw_dtype, device=dy.device) if need_dw else None
+    dx = dw = None
+    if need_dx:
+        dx = dx_out if dx_out is not None else torch.empty(m, k, dtype=torch.bfloat16, device=dy.device)
+        if tuple(dx.shape) != (m, k) or dx.dtype is not torch.bfloat16 or not dx.is_contiguous():
+            raise ValueError("dx_out must be a contiguous BF16 [M, K] tensor")
+    if need_dw:
+        dw_dtype = dw_out.dtype if dw_out is not None else dw_dtype
+        dw = dw_out if dw_out is not None else torch.empty(n, k, dtype=dw_dtype, device=dy.device)
+        if tuple(dw.shape) != (n, k) or dw.dtype not in (torch.bfloat16, torch.float32) or not dw.is_contiguous():
+            raise ValueError("dw_out must be a contiguous BF16 or FP32 [N, K] tensor")
     if need_dx:
         _require(w, torch.bfloat16, "weight")
     if need_dw:

@@ -198,8 +198,15 @@ def test_custom_ops_dispatch_on_fake_cuda_tensors():
         dx, dw = ops.mxfp8_linear_bwd(g, x, w, bk)
         assert dx.shape == x.shape and dw.shape == w.shape and dw.dtype is torch.bfloat16
         assert ops.mxfp8_linear_bwd_packed(g, x, w, bk).numel() == 48 * 96 + 80 * 96
-        assert ops.mxfp8_linear_dx(g, w, bk).shape == (48, 96)
-        assert ops.mxfp8_linear_dw(g, x, bk).shape == (80, 96)
+        assert ops.mxfp8_linear_dx(g, x, w, bk).shape == (48, 96)
+        assert ops.mxfp8_linear_dw(g, x, w, bk).shape == (80, 96)
+        dx_buf, dw_buf = torch.empty_like(x), torch.empty_like(w)
+        got = torch.ops.rtx.mxfp8_linear_bwd.out(g, x, w, bk, grad_x=dx_buf, grad_weight=dw_buf)
+        assert got[0] is dx_buf and got[1] is dw_buf
+        assert torch.ops.rtx.mxfp8_linear_dx.out(g, x, w, bk, grad_x=dx_buf) is dx_buf
+        assert torch.ops.rtx.mxfp8_linear_dw.out(g, x, w, bk, grad_weight=dw_buf) is dw_buf
+        assert torch.ops.rtx.mxfp8_linear_fwd_out(x, w, fk, torch.empty(48, 80, dtype=torch.bfloat16, device="cuda")) is None
+        assert torch.ops.rtx.mxfp8_linear_prequant_out(x, w, fk, torch.empty(48, 80, dtype=torch.bfloat16, device="cuda")) is None
         assert ops.mxfp8_linear_dw_f32(g, x, bk).dtype is torch.float32
         q = torch.empty(80, 96, dtype=torch.uint8, device="cuda")
         sc = torch.empty(512 * 1, dtype=torch.uint8, device="cuda")

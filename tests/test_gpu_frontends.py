@@ -297,3 +297,32 @@ def test_quantize_model_in_place(dev):
         y = mx[0](x.to(dev))
     _done(dev)
     _close(y, O.mxfp8_linear(x, w0))
+
+
+def test_out_overloads_write_into_given_tensors(dev):
+    """Launch-only variants (rtx/fp8.py:648-680, rtx/fp8_bwd.py:1145-1248): same bits as the functional ops,
+    written into tensors the caller owns."""
+    import rtx_b200 as rtx  # noqa: F401  (registers the ops)
+    from rtx_b200 import fp8_bwd  # noqa: F401
+    from rtx_b200.configs import MXFP8BwdConfig, MXFP8PrequantConfig
+
+    torch.manual_seed(21)
+    fk, bk = MXFP8PrequantConfig().to_key(), MXFP8BwdConfig().to_key()
+    x = torch.randn(96, 160).bfloat16().to(dev)
+    w = (torch.randn(128, 160) / 12).bfloat16().to(dev)
+    g = (torch.randn(96, 128) * 0.1).bfloat16().to(dev)
+    y = torch.ops.rtx.mxfp8_linear_fwd(x, w, fk)
+    y_buf = torch.zeros_like(y)
+    torch.ops.rtx.mxfp8_linear_fwd_out(x, w, fk, y_buf)
+    dx, dw = torch.ops.rtx.mxfp8_linear_bwd(g, x, w, bk)
+    dx_buf, dw_buf = torch.zeros_like(x), torch.zeros_like(w)
+    torch.ops.rtx.mxfp8_linear_bwd.out(g, x, w, bk, grad_x=dx_buf, grad_weight=dw_buf)
+    dx2, dw2 = torch.zeros_like(x), torch.zeros_like(w)
+    torch.ops.rtx.mxfp8_linear_dx.out(g, x, w, bk, grad_x=dx2)
+    torch.ops.rtx.mxfp8_linear_dw.out(g, x, w, bk, grad_weight=dw2)
+    _done(dev)
+    assert torch.equal(y, y_buf)
+    assert torch.equal(dx, dx_buf) and torch.equal(dw, dw_buf)
+    assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
+    assert torch.equal(dx, torch.ops.rtx.mxfp8_linear_dx(g, x, w, bk))
+    assert torch.equal(dw, torch.ops.rtx.mxfp8_linear_dw(g, x, w, bk))
