@@ -57,6 +57,7 @@ _LAZY_EXPORTS = {
     "quantize_": ("ptq", "quantize_"),
     # sm_100a additions
     "mxfp8_glu_mlp": ("glu", "mxfp8_glu_mlp"),
+    "SwiGLU": ("glu", "SwiGLU"),
     "KernelAdapter": ("autotune", "KernelAdapter"),
     "data_parallel_linear_backward": ("parallel", "data_parallel_linear_backward"),
 }

@@ -1053,8 +1053,12 @@ int rtxb_nvfp4_linear_fwd_prequant_w(const void* x, const void* qw, const void* 
   if (!workspace || workspace_bytes < rtxb_nvfp4_linear_prequant_w_workspace_bytes(m, k))
     return fail_msg(RTXB_E_WORKSPACE, "workspace too small for rtxb_nvfp4_linear_fwd_prequant_w");
   if (!aligned(workspace, 256)) return fail_msg(RTXB_E_ALIGNMENT, "workspace must be 256-byte aligned");
-  int rc = check_gemm_args(x, sw, qw, sw, out, m, n, k, n, n, 2);
-  if (rc) return rc;
+  if (!x || !qw || !sw || !out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || n <= 0 || k <= 0) return fail_msg(RTXB_E_INVALID_ARGUMENT, "m, n, k must be positive");
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX - 512) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (!aligned(sw, 16)) return fail_msg(RTXB_E_ALIGNMENT, "scale tiles must be 16-byte aligned");
+  if (!aligned(out, 2)) return fail_msg(RTXB_E_ALIGNMENT, "output pointer is not element aligned");
+  int rc;
   Carver c(workspace);
   const int64_t kp = round_up(k, 32);
   uint8_t* scal = c.take(512);

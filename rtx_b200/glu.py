@@ -11,9 +11,73 @@ activation-recompute use); training modules use `MXFP8Linear` for both projectio
 from __future__ import annotations
 
 import torch
+from torch import nn
 
 from . import fp8 as _fp8
 from . import ops
+
+
+@torch.library.custom_op("rtx::mxfp8_glu_mlp_fwd", mutates_args=(), device_types="cuda")
+def mxfp8_glu_mlp_fwd(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """x [M, K], w_gate_up [2*I, K] (gate rows first, I a multiple of 128), w_down [N, I] -> y [M, N]:
+    three quantizer launches, the gate/up GEMM whose epilogue emits H = silu(g) * u already MXFP8-encoded,
+    the down GEMM.  Forward only (no sm_120 counterpart: the reference applies SiLU * up in PyTorch,
+    rtx/models/decoder.py:382-384)."""
+    _fp8._check_inputs(x, w_gate_up)
+    inter = w_gate_up.shape[0] // 2
+    if w_gate_up.shape[0] != 2 * inter or inter % 128 or w_down.shape[1] != inter:
+        raise ValueError("w_gate_up must be [2*I, K] with I a multiple of 128, w_down [N, I]")
+    _, y = ops.mxfp8_glu_mlp_fwd(x if x.is_contiguous() else x.contiguous(), w_gate_up.contiguous(),
+                                 w_down.contiguous(), _fp8._workspace(x.device), want_hidden=False)
+    return y
+
+
+@mxfp8_glu_mlp_fwd.register_fake
+def _(x, w_gate_up, w_down):
+    return x.new_empty((x.shape[0], w_down.shape[0]), dtype=torch.bfloat16)
+
+
+class SwiGLU(nn.Module):
+    """SwiGLU feed-forward block with a fused gate/up projection, the caller of the hot path in the
+    reference's decoder (rtx/models/decoder.py:349-384: `gate_up_proj` [2*I, H], `down_proj` [H, I], both
+    no-bias low-precision linears; forward `down(silu(gate) * up)`).  Parameter names and shapes match, so
+    checkpoints interchange.  `linear` picks the projection modules: "mxfp8", "nvfp4" or "bf16".
+
+    With MXFP8 projections and no gradient required the forward is the fused pipeline above (the BF16
+    gate/up output and the BF16 H never reach memory); training, NVFP4 and BF16 run the two projections
+    as modules with SiLU * up between them, as the reference does."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, *, linear: str = "mxfp8", device=None, **linear_kwargs):
+        super().__init__()
+        if linear not in ("mxfp8", "nvfp4", "bf16"):
+            raise ValueError("linear must be mxfp8, nvfp4 or bf16")
+        self.hidden_size, self.intermediate_size, self.linear = int(hidden_size), int(intermediate_size), linear
+        if linear == "mxfp8":
+            make = lambda i, o: _fp8.MXFP8Linear(i, o, device=device, **linear_kwargs)
+        elif linear == "nvfp4":
+            from .fp4 import NVFP4Linear
+            make = lambda i, o: NVFP4Linear(i, o, device=device, **linear_kwargs)
+        else:
+            make = lambda i, o: nn.Linear(i, o, bias=False, device=device, dtype=torch.bfloat16)
+        self.gate_up_proj = make(self.hidden_size, 2 * self.intermediate_size)
+        self.down_proj = make(self.intermediate_size, self.hidden_size)
+
+    def _fused_ok(self, x: torch.Tensor) -> bool:
+        if self.linear != "mxfp8" or self.intermediate_size % 128:
+            return False
+        if getattr(self.gate_up_proj, "weight_mode", "") != "dynamic" or self.down_proj.weight_mode != "dynamic":
+            return False
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.gate_up_proj.weight.requires_grad
+                                                  or self.down_proj.weight.requires_grad)
+        return not needs_grad
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self._fused_ok(x):
+            y = torch.ops.rtx.mxfp8_glu_mlp_fwd(x.reshape(-1, self.hidden_size), self.gate_up_proj.weight,
+                                                self.down_proj.weight)
+            return y.reshape(*x.shape[:-1], self.hidden_size)
+        gate, up = self.gate_up_proj(x).chunk(2, dim=-1)
+        return self.down_proj(torch.nn.functional.silu(gate) * up)
 
 
 def mxfp8_glu_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, *, return_hidden: bool = False):

@@ -326,3 +326,37 @@ def test_out_overloads_write_into_given_tensors(dev):
     assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
     assert torch.equal(dx, torch.ops.rtx.mxfp8_linear_dx(g, x, w, bk))
     assert torch.equal(dw, torch.ops.rtx.mxfp8_linear_dw(g, x, w, bk))
+
+
+def test_swiglu_block_fused_inference_and_training(dev):
+    """The decoder's feed-forward block (rtx/models/decoder.py:349-384): inference takes the fused pipeline
+    (also under torch.compile), training the two modules with SiLU * up between them; same parameters."""
+    import rtx_b200 as rtx
+
+    torch.manual_seed(31)
+    blk = rtx.SwiGLU(256, 384, device=dev)
+    assert list(blk.state_dict()) == ["gate_up_proj.weight", "down_proj.weight"]
+    assert blk.gate_up_proj.weight.shape == (768, 256) and blk.down_proj.weight.shape == (256, 384)
+    x = torch.randn(2, 70, 256).bfloat16().to(dev)
+    with torch.no_grad():
+        y = blk(x)
+        y_c = torch.compile(blk, fullgraph=True, dynamic=False)(x)
+    _done(dev)
+    want = O.mxfp8_glu_mlp(x.cpu().reshape(-1, 256), blk.gate_up_proj.weight.detach().cpu(),
+                           blk.down_proj.weight.detach().cpu())
+    want = want[1] if isinstance(want, tuple) else want
+    _close(y.reshape(-1, 256), want)
+    assert torch.equal(y, y_c)
+    # training: unfused composition, gradients reach both projections
+    xg = x.clone().requires_grad_(True)
+    blk(xg).float().square().mean().backward()
+    _done(dev)
+    assert xg.grad is not None and blk.gate_up_proj.weight.grad is not None and blk.down_proj.weight.grad is not None
+    assert torch.isfinite(blk.down_proj.weight.grad.float()).all()
+    # the other projection kinds share the parameter layout
+    nv = rtx.SwiGLU(256, 384, linear="nvfp4", device=dev)
+    nv.load_state_dict(blk.state_dict())
+    with torch.no_grad():
+        yn = nv(x)
+    _done(dev)
+    assert yn.shape == y.shape and torch.isfinite(yn.float()).all()
