@@ -66,6 +66,19 @@ const char* rtxb_last_cuda_error(void);
 int rtxb_set_sm_margin(int sms);
 int rtxb_get_sm_margin(void);
 
+/* GEMM schedule used by the calls this thread makes from now on.  The reference selects a schedule per
+ * call through the config object given to its compile_* factories (tile shape, stages, persistence:
+ * rtx/configs/mxfp8.py:110-343, chosen by rtx/autotune); here the built schedules are an enumeration:
+ * AUTO (the library picks by shape), SINGLE (one CTA per 128 x 256 tile, 4 stages), PAIR (two CTAs per
+ * 256 x 256 tile, cta_group::2), STREAM (128 x 64 tiles for M <= 128; ignored for larger M).  All give
+ * the same bits.  Thread-local. */
+#define RTXB_SCHEDULE_AUTO 0
+#define RTXB_SCHEDULE_SINGLE 1
+#define RTXB_SCHEDULE_PAIR 2
+#define RTXB_SCHEDULE_STREAM 3
+int rtxb_set_gemm_schedule(int schedule);
+int rtxb_get_gemm_schedule(void);
+
 /* ---- sizes ------------------------------------------------------------- */
 
 /* padded K: 32-multiples (rtx/kernels/mxfp8.py:57-66, rtx/configs/nvfp4.py:15-28) */

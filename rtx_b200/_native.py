@@ -37,6 +37,8 @@ SIGNATURES = {
     "rtxb_version": (_I, []),
     "rtxb_error_string": (c_char_p, [_I]),
     "rtxb_last_cuda_error": (c_char_p, []),
+    "rtxb_set_gemm_schedule": (_I, [_I]),
+    "rtxb_get_gemm_schedule": (_I, []),
     "rtxb_set_sm_margin": (_I, [_I]),
     "rtxb_get_sm_margin": (_I, []),
     "rtxb_mxfp8_storage_k": (_L, [_L]),

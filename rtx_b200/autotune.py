@@ -93,8 +93,13 @@ class DiscreteKernelAdapter:
 
 
 def _gemm_space():
-    # schedules the library is built with; the pair schedule is selected at run time with RTXB_GEMM_PAIR
-    return (MXFP8GemmConfig(), MXFP8GemmConfig(tile_m=256, cta_group=2, stages=6))
+    # one candidate per built kernel; the frontends select it for the call with the library's per-thread
+    # schedule switch, so a stored winner changes which kernel runs
+    return tuple(MXFP8GemmConfig.for_schedule(name) for name in MXFP8GemmConfig.SCHEDULES)
+
+
+def _nvfp4_gemm_space():
+    return tuple(NVFP4GemmConfig.for_schedule(name) for name in NVFP4GemmConfig.SCHEDULES)
 
 
 def make_mxfp8_prequant_fwd_adapter() -> DiscreteKernelAdapter:
@@ -113,7 +118,8 @@ def make_mxfp8_bwd_adapter() -> DiscreteKernelAdapter:
 
 
 def make_nvfp4_dynamic_fwd_adapter() -> DiscreteKernelAdapter:
-    return DiscreteKernelAdapter("nvfp4_dynamic_fwd", NVFP4DynamicConfig(), (NVFP4DynamicConfig(gemm=NVFP4GemmConfig()),),
+    return DiscreteKernelAdapter("nvfp4_dynamic_fwd", NVFP4DynamicConfig(),
+                                 tuple(NVFP4DynamicConfig(gemm=g) for g in _nvfp4_gemm_space()),
                                  problem_type=NVFP4Problem)
 
 

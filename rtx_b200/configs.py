@@ -106,20 +106,39 @@ class MXFP8GemmConfig(_Config):
     tile_k_bytes: int = 128
     stages: int = 4
     cta_group: int = 1
-    accumulator_windows: int = 2       # overlapping TMEM windows [0,256) and [192,448)
+    accumulator_windows: int = 2       # overlapping TMEM windows [0,256) and [224,480)
     epilogue: str = "direct"           # direct vectorised stores
     raster: str = "m_fastest"
+    # which built kernel runs: "auto" (the library picks by shape) or one of SCHEDULES, whose tile shape the
+    # other fields must then state
+    schedule: str = "auto"
 
-    BUILT: ClassVar[tuple] = ((128, 256, 128, 4, 1), (256, 256, 128, 6, 2))
+    # (tile_m, tile_n, tile_k_bytes, stages, cta_group); stages 0 = ring depth chosen at launch
+    SCHEDULES: ClassVar[dict] = {"single": (128, 256, 128, 4, 1), "pair": (256, 256, 128, 6, 2),
+                                 "stream": (128, 64, 128, 0, 1)}
+    BUILT: ClassVar[tuple] = tuple(SCHEDULES.values())
+
+    @classmethod
+    def for_schedule(cls, name: str) -> "MXFP8GemmConfig":
+        tm, tn, tk, st, cg = cls.SCHEDULES[name]
+        return cls(tile_m=tm, tile_n=tn, tile_k_bytes=tk, stages=st, cta_group=cg, schedule=name)
 
     def smem_bytes(self, sf_bytes_per_stage: int = 1536) -> int:
         rows = self.tile_m // self.cta_group + self.tile_n // self.cta_group   # per CTA
         return self.stages * (rows * self.tile_k_bytes + sf_bytes_per_stage) + 1280
 
     def rejection(self, problem: Optional[MXFP8Problem] = None) -> Optional[str]:
-        if (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group) not in self.BUILT:
+        shape = (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group)
+        if shape not in self.BUILT:
             return ("no kernel is built for this tile/stage/cta_group combination; built: "
                     + ", ".join(map(str, self.BUILT)))
+        if self.schedule != "auto":
+            if self.schedule not in self.SCHEDULES:
+                return f"unknown GEMM schedule {self.schedule!r}; built: auto, " + ", ".join(self.SCHEDULES)
+            if self.SCHEDULES[self.schedule] != shape:
+                return f"schedule {self.schedule!r} has the tile shape {self.SCHEDULES[self.schedule]}, not {shape}"
+            if self.schedule == "stream" and problem is not None and problem.m > 128:
+                return "the streaming schedule serves M <= 128"
         if self.smem_bytes() > SMEM_CAPACITY_BYTES:
             return "pipeline does not fit 227 KB of shared memory"
         if problem is not None:
@@ -258,10 +277,27 @@ class NVFP4GemmConfig(_Config):
     tile_k_bytes: int = 128            # 256 E2M1 values
     stages: int = 4
     cta_group: int = 1
+    schedule: str = "auto"             # as MXFP8GemmConfig.schedule
+
+    SCHEDULES: ClassVar[dict] = {"single": (128, 256, 128, 4, 1), "pair": (256, 256, 128, 5, 2),
+                                 "stream": (128, 64, 128, 0, 1)}
+
+    @classmethod
+    def for_schedule(cls, name: str) -> "NVFP4GemmConfig":
+        tm, tn, tk, st, cg = cls.SCHEDULES[name]
+        return cls(tile_m=tm, tile_n=tn, tile_k_bytes=tk, stages=st, cta_group=cg, schedule=name)
 
     def rejection(self, problem: Optional[NVFP4Problem] = None) -> Optional[str]:
-        if (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group) != (128, 256, 128, 4, 1):
+        shape = (self.tile_m, self.tile_n, self.tile_k_bytes, self.stages, self.cta_group)
+        if shape not in self.SCHEDULES.values():
             return "no kernel is built for this tile/stage/cta_group combination"
+        if self.schedule != "auto":
+            if self.schedule not in self.SCHEDULES:
+                return f"unknown GEMM schedule {self.schedule!r}; built: auto, " + ", ".join(self.SCHEDULES)
+            if self.SCHEDULES[self.schedule] != shape:
+                return f"schedule {self.schedule!r} has the tile shape {self.SCHEDULES[self.schedule]}, not {shape}"
+            if self.schedule == "stream" and problem is not None and problem.m > 128:
+                return "the streaming schedule serves M <= 128"
         return problem.rejection() if problem is not None else None
 
 

@@ -176,9 +176,15 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, size
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Caller-selected GEMM schedule of this thread (0 = the library chooses): 1 single-CTA 128 x 256 tiles,
+// 2 CTA pairs with 256 x 256 tiles, 3 streaming 128 x 64 tiles (only for M <= 128, else ignored).
+thread_local int t_gemm_schedule = 0;
+
 // Schedule choice: the CTA-pair kernel (256 x 256 pair tiles) unless the problem has a single
 // 128-row block of A, where half of every pair would idle.  RTXB_GEMM_PAIR=0/1 forces one.
 bool use_pair_kernel(int m_tiles) {
+  if (t_gemm_schedule == 1 || t_gemm_schedule == 3) return false;
+  if (t_gemm_schedule == 2) return true;
   static int forced = -2;
   if (forced == -2) {
     const char* v = getenv("RTXB_GEMM_PAIR");
@@ -198,6 +204,8 @@ bool use_skinny_kernel(int m_tiles, int64_t n_rows_b) {
     forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
   }
   if (m_tiles != 1) return false;
+  if (t_gemm_schedule == 3) return true;
+  if (t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
   if (forced >= 0) return forced == 1;
   return (n_rows_b + kBlockN - 1) / kBlockN < 74;
 }
@@ -363,7 +371,7 @@ bool decode_fused_eligible(const void* x, int64_t m, int64_t n, int64_t k) {
     const char* v = getenv("RTXB_DECODE_FUSED");
     forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
   }
-  if (forced == 0) return false;
+  if (forced == 0 || t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
   if (m > kFusedMaxRows || k % 256 != 0 || !aligned(x, 16)) return false;
   const int k_tiles = static_cast<int>(k / 256);
   if (k_tiles < 2 || fused_slots_for(k_tiles, 2) < 3) return false;
@@ -452,6 +460,14 @@ int rtxb_set_sm_margin(int sms) {
   return RTXB_OK;
 }
 int rtxb_get_sm_margin(void) { return g_sm_margin.load(std::memory_order_relaxed); }
+
+int rtxb_set_gemm_schedule(int schedule) {
+  if (schedule < RTXB_SCHEDULE_AUTO || schedule > RTXB_SCHEDULE_STREAM)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown GEMM schedule");
+  t_gemm_schedule = schedule;
+  return RTXB_OK;
+}
+int rtxb_get_gemm_schedule(void) { return t_gemm_schedule; }
 
 const char* rtxb_error_string(int code) {
   switch (code) {

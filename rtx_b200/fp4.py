@@ -126,8 +126,8 @@ def nvfp4_linear_materialized_fwd(x: torch.Tensor, weight: torch.Tensor, x_scale
                                   weight_scale: torch.Tensor, output_scale: torch.Tensor, key: str) -> torch.Tensor:
     """`current` policy: outer scales computed by the caller, dual quantize, GEMM x output_scale
     (rtx/fp4.py:1260-1313, _DynamicRunner :404-454)."""
-    _resolve_dynamic(key)
-    return _materialized_forward(x, weight, x_scale, weight_scale, output_scale)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return _materialized_forward(x, weight, x_scale, weight_scale, output_scale)
 
 
 @nvfp4_linear_materialized_fwd.register_fake
@@ -139,8 +139,8 @@ def _(x, weight, x_scale, weight_scale, output_scale, key):
 def nvfp4_linear_materialized_train(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor,
                                     weight_scale: torch.Tensor, output_scale: torch.Tensor, key: str,
                                     bwd_key: str) -> torch.Tensor:
-    _resolve_dynamic(key)
-    return _materialized_forward(x, weight, x_scale, weight_scale, output_scale)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return _materialized_forward(x, weight, x_scale, weight_scale, output_scale)
 
 
 @nvfp4_linear_materialized_train.register_fake
@@ -177,8 +177,8 @@ nvfp4_linear_materialized_train.register_autograd(_nv_train_backward, setup_cont
 @torch.library.custom_op("rtx::nvfp4_linear_block_fwd", mutates_args=(), device_types="cuda")
 def nvfp4_linear_block_fwd(x: torch.Tensor, weight: torch.Tensor, key: str) -> torch.Tensor:
     """`block` policy: outer scale 1 folded out of both kernels (rtx/fp4.py:859-875)."""
-    _resolve_dynamic(key)
-    return _materialized_forward(x, weight, None, None, None)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return _materialized_forward(x, weight, None, None, None)
 
 
 @nvfp4_linear_block_fwd.register_fake
@@ -188,8 +188,8 @@ def _(x, weight, key):
 
 @torch.library.custom_op("rtx::nvfp4_linear_block_train", mutates_args=(), device_types="cuda")
 def nvfp4_linear_block_train(x: torch.Tensor, weight: torch.Tensor, key: str, bwd_key: str) -> torch.Tensor:
-    _resolve_dynamic(key)
-    return _materialized_forward(x, weight, None, None, None)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return _materialized_forward(x, weight, None, None, None)
 
 
 @nvfp4_linear_block_train.register_fake
@@ -206,9 +206,10 @@ def _jit_row_region_forward(x, weight, key):
         raise RuntimeError("the forward schedule carries no region geometry")
     x = x if x.is_contiguous() else x.contiguous()
     weight = weight if weight.is_contiguous() else weight.contiguous()
-    return ops.nvfp4_linear_fwd_regions(x, weight, _fp8._workspace(x.device), cfg.x_scale_region_rows,
-                                        cfg.weight_scale_region_rows,
-                                        scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
+    with ops.schedule_of(cfg.gemm):
+        return ops.nvfp4_linear_fwd_regions(x, weight, _fp8._workspace(x.device), cfg.x_scale_region_rows,
+                                            cfg.weight_scale_region_rows,
+                                            scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
 
 
 @torch.library.custom_op("rtx::nvfp4_linear_jit_row_region_fwd", mutates_args=(), device_types="cuda")
@@ -251,10 +252,11 @@ def nvfp4_linear_train_delayed(x: torch.Tensor, weight: torch.Tensor, x_amax_sta
         raise ValueError("delayed weight amax generations must not alias")
     x = x if x.is_contiguous() else x.contiguous()
     weight = weight if weight.is_contiguous() else weight.contiguous()
-    return ops.nvfp4_linear_fwd_delayed(x, weight, _fp8._workspace(x.device), x_amax_state, weight_amax_state,
-                                        next_x_amax_state, next_weight_amax_state,
-                                        window_max=cfg.scale.amax_history_algo == "window_max",
-                                        scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
+    with ops.schedule_of(cfg.gemm):
+        return ops.nvfp4_linear_fwd_delayed(x, weight, _fp8._workspace(x.device), x_amax_state, weight_amax_state,
+                                            next_x_amax_state, next_weight_amax_state,
+                                            window_max=cfg.scale.amax_history_algo == "window_max",
+                                            scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
 
 
 @nvfp4_linear_train_delayed.register_fake
@@ -296,7 +298,8 @@ def nvfp4_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor
     x = x if x.is_contiguous() else x.contiguous()
     qx, sx = ops.nvfp4_quantize(x, x_scale)
     sw = _kernel_block_scales(weight_block_scales, n, k, layout)
-    return ops.nvfp4_gemm(qx, sx, weight_data.view(torch.uint8), sw, int(x.shape[0]), n, k, output_scale)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return ops.nvfp4_gemm(qx, sx, weight_data.view(torch.uint8), sw, int(x.shape[0]), n, k, output_scale)
 
 
 @nvfp4_linear_dynamic_x_prequant_w.register_fake
@@ -316,8 +319,9 @@ def nvfp4_linear_prequant_w_current(x: torch.Tensor, weight_data: torch.Tensor, 
         raise TypeError("x must be BF16 [M, K]")
     x = x if x.is_contiguous() else x.contiguous()
     sw = _kernel_block_scales(weight_block_scales, n, k, layout)
-    return ops.nvfp4_linear_fwd_prequant_w(x, weight_data.view(torch.uint8), sw, weight_tensor_scale, n,
-                                           _fp8._workspace(x.device), scale_mode=N.TENSOR_SCALE_EXACT)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return ops.nvfp4_linear_fwd_prequant_w(x, weight_data.view(torch.uint8), sw, weight_tensor_scale, n,
+                                               _fp8._workspace(x.device), scale_mode=N.TENSOR_SCALE_EXACT)
 
 
 @nvfp4_linear_prequant_w_current.register_fake
@@ -332,7 +336,8 @@ def nvfp4_linear_prequantized(x_data: torch.Tensor, weight_data: torch.Tensor, x
     """Both operands packed (rtx/fp4.py:1689-1760)."""
     sx = _kernel_block_scales(x_block_scales, m, k, x_layout)
     sw = _kernel_block_scales(weight_block_scales, n, k, weight_layout)
-    return ops.nvfp4_gemm(x_data.view(torch.uint8), sx, weight_data.view(torch.uint8), sw, m, n, k, output_scale)
+    with ops.schedule_of(_resolve_dynamic(key).gemm):
+        return ops.nvfp4_gemm(x_data.view(torch.uint8), sx, weight_data.view(torch.uint8), sw, m, n, k, output_scale)
 
 
 @nvfp4_linear_prequantized.register_fake

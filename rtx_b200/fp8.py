@@ -136,7 +136,8 @@ def mxfp8_linear_fwd(x: torch.Tensor, weight: torch.Tensor, config_key: str) -> 
         raise RuntimeError(f"illegal MXFP8 forward schedule: {rejection}")
     x = x if x.is_contiguous() else x.contiguous()
     weight = weight if weight.is_contiguous() else weight.contiguous()
-    return ops.mxfp8_linear_fwd(x, weight, _workspace(x.device), rounding=_rounding(cfg))
+    with ops.schedule_of(cfg.gemm):
+        return ops.mxfp8_linear_fwd(x, weight, _workspace(x.device), rounding=_rounding(cfg))
 
 
 @mxfp8_linear_fwd.register_fake
@@ -178,9 +179,10 @@ def _fwd_out(x, weight, config_key, out):
         raise RuntimeError(f"illegal MXFP8 forward schedule: {rejection}")
     if tuple(out.shape) != (x.shape[0], weight.shape[0]) or out.dtype is not torch.bfloat16 or not out.is_contiguous():
         raise ValueError("out must be a contiguous BF16 [M, N] tensor")
-    ops.mxfp8_linear_fwd(x if x.is_contiguous() else x.contiguous(),
-                         weight if weight.is_contiguous() else weight.contiguous(), _workspace(x.device), out=out,
-                         rounding=_rounding(cfg))
+    with ops.schedule_of(cfg.gemm):
+        ops.mxfp8_linear_fwd(x if x.is_contiguous() else x.contiguous(),
+                             weight if weight.is_contiguous() else weight.contiguous(), _workspace(x.device), out=out,
+                             rounding=_rounding(cfg))
 
 
 torch.library.impl("rtx::mxfp8_linear_fwd_out", "cuda")(_fwd_out)
@@ -207,7 +209,8 @@ def mxfp8_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor
     x = x if x.is_contiguous() else x.contiguous()
     qx, sx = ops.mxfp8_quantize(x, rounding=_rounding(cfg))
     sw = _kernel_scales(weight_scales, n, k, weight_scale_layout)
-    return ops.mxfp8_gemm(qx, sx, weight_data.view(torch.uint8), sw, int(x.shape[0]), n, k)
+    with ops.schedule_of(cfg.gemm):
+        return ops.mxfp8_gemm(qx, sx, weight_data.view(torch.uint8), sw, int(x.shape[0]), n, k)
 
 
 @mxfp8_linear_dynamic_x_prequant_w.register_fake
@@ -222,7 +225,8 @@ def mxfp8_linear_prequantized(x_data: torch.Tensor, weight_data: torch.Tensor, x
     """Both operands packed (rtx/fp8.py:1305-1366)."""
     sx = _kernel_scales(x_scales, m, k, x_scale_layout)
     sw = _kernel_scales(weight_scales, n, k, weight_scale_layout)
-    return ops.mxfp8_gemm(x_data.view(torch.uint8), sx, weight_data.view(torch.uint8), sw, m, n, k)
+    with ops.schedule_of(_resolve_prequant(config_key).gemm):
+        return ops.mxfp8_gemm(x_data.view(torch.uint8), sx, weight_data.view(torch.uint8), sw, m, n, k)
 
 
 @mxfp8_linear_prequantized.register_fake

@@ -51,7 +51,8 @@ def _mxfp8_fwd_launcher(key: str):
 
     def launch(x, weight, *, out):
         _count("mxfp8_fwd")
-        ops.mxfp8_linear_fwd(x, weight, fp8._workspace(x.device), out=out, rounding=rounding)
+        with ops.schedule_of(cfg.gemm):
+            ops.mxfp8_linear_fwd(x, weight, fp8._workspace(x.device), out=out, rounding=rounding)
 
     return launch
 
@@ -64,8 +65,9 @@ def _nvfp4_region_launcher(key: str):
 
     def launch(x, weight, *, out):
         _count("nvfp4_jit_row_region_fwd")
-        ops.nvfp4_linear_fwd_regions(x, weight, fp8._workspace(x.device), cfg.x_scale_region_rows,
-                                     cfg.weight_scale_region_rows, out=out, scale_mode=mode)
+        with ops.schedule_of(cfg.gemm):
+            ops.nvfp4_linear_fwd_regions(x, weight, fp8._workspace(x.device), cfg.x_scale_region_rows,
+                                         cfg.weight_scale_region_rows, out=out, scale_mode=mode)
 
     return launch
 
@@ -73,13 +75,14 @@ def _nvfp4_region_launcher(key: str):
 def _nvfp4_block_launcher(key: str):
     from . import fp4, ops
 
-    fp4._resolve_dynamic(key)
+    cfg = fp4._resolve_dynamic(key)
 
     def launch(x, weight, *, out):
         _count("nvfp4_block_fwd")
         qx, sx = ops.nvfp4_quantize(x, None)
         qw, sw = ops.nvfp4_quantize(weight, None)
-        ops.nvfp4_gemm(qx, sx, qw, sw, int(x.shape[0]), int(weight.shape[0]), int(x.shape[1]), None, out=out)
+        with ops.schedule_of(cfg.gemm):
+            ops.nvfp4_gemm(qx, sx, qw, sw, int(x.shape[0]), int(weight.shape[0]), int(x.shape[1]), None, out=out)
 
     return launch
 
@@ -87,13 +90,15 @@ def _nvfp4_block_launcher(key: str):
 def _nvfp4_materialized_launcher(key: str):
     from . import fp4, ops
 
-    fp4._resolve_dynamic(key)
+    cfg = fp4._resolve_dynamic(key)
 
     def launch(x, weight, x_scale, weight_scale, output_scale, *, out):
         _count("nvfp4_materialized_fwd")
         qx, sx = ops.nvfp4_quantize(x, x_scale)
         qw, sw = ops.nvfp4_quantize(weight, weight_scale)
-        ops.nvfp4_gemm(qx, sx, qw, sw, int(x.shape[0]), int(weight.shape[0]), int(x.shape[1]), output_scale, out=out)
+        with ops.schedule_of(cfg.gemm):
+            ops.nvfp4_gemm(qx, sx, qw, sw, int(x.shape[0]), int(weight.shape[0]), int(x.shape[1]), output_scale,
+                           out=out)
 
     return launch
 

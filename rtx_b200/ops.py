@@ -244,6 +244,45 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
 # SM margin
 # ---------------------------------------------------------------------------
 
+GEMM_SCHEDULES = {"auto": 0, "single": 1, "pair": 2, "stream": 3}
+
+
+class gemm_schedule:
+    """Context manager: GEMMs launched by this thread inside use the named schedule ("auto", "single",
+    "pair", "stream"); restored on exit.  All schedules give the same bits."""
+
+    def __init__(self, name: str):
+        if name not in GEMM_SCHEDULES:
+            raise ValueError(f"unknown GEMM schedule {name!r}; built: {', '.join(GEMM_SCHEDULES)}")
+        self.code, self.prev = GEMM_SCHEDULES[name], 0
+
+    def __enter__(self):
+        self.prev = N.query("rtxb_get_gemm_schedule")
+        N.call("rtxb_set_gemm_schedule", self.code)
+        return self
+
+    def __exit__(self, *exc):
+        N.call("rtxb_set_gemm_schedule", self.prev)
+        return False
+
+
+class _NoSchedule:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SCHEDULE = _NoSchedule()
+
+
+def schedule_of(gemm_config):
+    """The context manager for a GEMM config's schedule ("auto" costs nothing)."""
+    name = getattr(gemm_config, "schedule", "auto")
+    return _NO_SCHEDULE if name == "auto" else gemm_schedule(name)
+
+
 class sm_margin:
     """Context manager: the library's persistent kernels launched inside leave `sms` SMs unused, so
     that a collective running beside them (NCCL all-reduce of dW during the dX GEMM) gets to run.

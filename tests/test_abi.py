@@ -84,6 +84,19 @@ def test_newer_entry_points_reject_bad_arguments_before_any_launch(native_lib):
     assert L.rtxb_set_sm_margin(32) == 0 and L.rtxb_get_sm_margin() == 32
     assert L.rtxb_set_sm_margin(-1) == -1 and L.rtxb_set_sm_margin(1000) == -1 and L.rtxb_get_sm_margin() == 32
     assert L.rtxb_set_sm_margin(0) == 0
+    # the GEMM schedule switch is per thread and refuses unknown schedules
+    assert L.rtxb_get_gemm_schedule() == 0
+    for code in (1, 2, 3):
+        assert L.rtxb_set_gemm_schedule(code) == 0 and L.rtxb_get_gemm_schedule() == code
+    assert L.rtxb_set_gemm_schedule(4) == -1 and L.rtxb_set_gemm_schedule(-1) == -1
+    assert L.rtxb_get_gemm_schedule() == 3
+    import threading
+    seen = []
+    worker = threading.Thread(target=lambda: seen.append(L.rtxb_get_gemm_schedule()))
+    worker.start()
+    worker.join()
+    assert seen == [0]
+    assert L.rtxb_set_gemm_schedule(0) == 0
 
 
 def test_missing_library_is_loud(monkeypatch, tmp_path):

@@ -49,6 +49,15 @@ def test_configs_round_trip_and_reject_explicitly():
     assert "no kernel is built" in C.MXFP8GemmConfig(tile_n=128).rejection()
     assert C.MXFP8GemmConfig(tile_m=256, cta_group=2, stages=6).rejection() is None
     assert C.MXFP8GemmConfig().rejection(C.MXFP8Problem(0, 1, 1)) == "m, n and k must be positive"
+    # a named schedule selects one built kernel and must state that kernel's tile shape
+    for name in ("single", "pair", "stream"):
+        assert C.MXFP8GemmConfig.for_schedule(name).rejection() is None
+        assert C.NVFP4GemmConfig.for_schedule(name).rejection() is None
+        assert C.config_from_key(C.MXFP8GemmConfig.for_schedule(name).to_key()).schedule == name
+    assert "unknown GEMM schedule" in C.MXFP8GemmConfig(schedule="wide").rejection()
+    assert "tile shape" in C.MXFP8GemmConfig(schedule="pair").rejection()
+    assert "M <= 128" in C.MXFP8GemmConfig.for_schedule("stream").rejection(C.MXFP8Problem(256, 64, 64))
+    assert "M <= 128" in C.NVFP4GemmConfig.for_schedule("stream").rejection(C.NVFP4Problem(256, 64, 64))
     assert C.MXFP8FwdConfig(pipeline="fused").rejection() == "forward pipeline 'fused' is not built"
     assert C.NVFP4ScaleConfig(policy="delayed").rejection() is None
     assert "history_len" in C.NVFP4ScaleConfig(policy="delayed", amax_history_len=3).rejection()
@@ -263,11 +272,18 @@ def test_autotune_adapter_and_winner_cache(tmp_path):
     assert isinstance(adapter, A.KernelAdapter)
     ctx = A.KernelContext("mxfp8_prequant_fwd", 8192, 28672, 4096)
     cands = adapter.candidates(ctx)
-    assert len(cands) == 2 and all(adapter.rejection(c, ctx) is None for c in cands)
+    # the library's own choice plus one candidate per built kernel that serves the shape
+    assert [c.gemm.schedule for c in cands] == ["auto", "single", "pair"]
+    assert all(adapter.rejection(c, ctx) is None for c in cands)
+    small = adapter.candidates(A.KernelContext("mxfp8_prequant_fwd", 64, 8192, 4096))
+    assert [c.gemm.schedule for c in small] == ["auto", "single", "pair", "stream"]
+    nv = A.make_nvfp4_dynamic_fwd_adapter()
+    assert [c.gemm.schedule for c in nv.candidates(A.KernelContext("nvfp4_dynamic_fwd", 8, 8192, 8192))] == [
+        "auto", "single", "pair", "stream"]
     assert adapter.decode(adapter.encode(cands[1])) == cands[1]
     assert A.pick(ctx, adapter, None, mode="off") == adapter.default(ctx)
     assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == adapter.default(ctx)
-    times = {adapter.encode(cands[0]): 2.0, adapter.encode(cands[1]): 1.0}
+    times = {adapter.encode(cands[0]): 2.0, adapter.encode(cands[1]): 1.0, adapter.encode(cands[2]): 1.5}
     calls = []
 
     def evaluate(cfg):
@@ -275,7 +291,7 @@ def test_autotune_adapter_and_winner_cache(tmp_path):
         return A.TrialOutcome("ok", median_ms=times[adapter.encode(cfg)])
 
     best = A.pick(ctx, adapter, evaluate, mode="balanced", cache_dir=tmp_path)
-    assert best == cands[1] and len(calls) == 2
+    assert best == cands[1] and len(calls) == 3
     path = A.runtime_winner_path(ctx, tmp_path)
     assert path.name == "m8192_n28672_k4096_hot_default_rev1.json" and path.parent.name == "b200"
     assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == cands[1]

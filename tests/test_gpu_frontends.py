@@ -360,3 +360,50 @@ def test_swiglu_block_fused_inference_and_training(dev):
         yn = nv(x)
     _done(dev)
     assert yn.shape == y.shape and torch.isfinite(yn.float()).all()
+
+
+def test_autotune_picks_among_the_built_kernels(dev, tmp_path):
+    """The schedule in a config selects the kernel that runs: every candidate of the adapter, passed through
+    the functional API, returns the same bits; `pick` times them on the device, stores the winner under the
+    reference's key scheme and a later `cache` lookup returns it (rtx/autotune/core.py:167-293,
+    rtx/autotune/winners.py:26-45)."""
+    import rtx_b200 as rtx
+    from rtx_b200 import autotune as A
+
+    m, n, k = 96, 2048, 1024
+    torch.manual_seed(5)
+    x = torch.randn(m, k).bfloat16().to(dev)
+    w = (torch.randn(n, k) / k ** 0.5).bfloat16().to(dev)
+    adapter = A.make_mxfp8_prequant_fwd_adapter()
+    ctx = A.KernelContext("mxfp8_prequant_fwd", m, n, k)
+    cands = adapter.candidates(ctx)
+    assert [c.gemm.schedule for c in cands] == ["auto", "single", "pair", "stream"]
+    outs = {}
+
+    def evaluate(cfg):
+        with torch.no_grad():
+            outs[cfg.gemm.schedule] = rtx.mxfp8_linear(x, w, dynamic_config=cfg).clone()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(5):
+                rtx.mxfp8_linear(x, w, dynamic_config=cfg)
+            stop.record()
+        stop.synchronize()
+        return A.TrialOutcome("ok", median_ms=start.elapsed_time(stop) / 5)
+
+    best = A.pick(ctx, adapter, evaluate, mode="balanced", cache_dir=tmp_path)
+    _done(dev)
+    assert set(outs) == {"auto", "single", "pair", "stream"}
+    for name, out in outs.items():
+        assert torch.equal(out, outs["auto"]), name
+    _close(outs["auto"], O.mxfp8_linear(x.cpu(), w.cpu()))
+    assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == best
+    # NVFP4: the three policies accept a schedule through their forward config
+    nv = A.make_nvfp4_dynamic_fwd_adapter()
+    ref = None
+    for cfg in nv.candidates(A.KernelContext("nvfp4_dynamic_fwd", m, n, k)):
+        with torch.no_grad():
+            y = rtx.nvfp4_linear(x, w, scaling="current", dynamic_config=cfg)
+        _done(dev)
+        ref = y if ref is None else ref
+        assert torch.equal(y, ref), cfg.gemm.schedule

@@ -552,6 +552,55 @@ def test_mxfp8_skinny_shapes(gpu, mnk):
     _assert_output(y, O.mxfp8_linear(x, w))
 
 
+@pytest.mark.parametrize("mnk", [(64, 512, 1024), (128, 8192, 512), (100, 4100, 1000), (300, 640, 512), (1, 64, 32)])
+def test_gemm_schedules_give_the_same_bits(gpu, mnk):
+    """Every built GEMM kernel, forced for the call with the per-thread schedule switch, returns the bits the
+    library's own choice returns (K is accumulated in the same order by all of them); the switch is restored
+    on exit and refuses unknown names."""
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    torch.manual_seed(4242)
+    x = torch.randn(m, k).bfloat16().to(dev)
+    w = (torch.randn(n, k) / k ** 0.5).bfloat16().to(dev)
+    auto = ops.mxfp8_linear_fwd(x, w, ws).clone()
+    xs, wsc = ops.nvfp4_tensor_scale(x, N.TENSOR_SCALE_POWER2), ops.nvfp4_tensor_scale(w, N.TENSOR_SCALE_POWER2)
+    qx, sx = ops.nvfp4_quantize(x, xs)
+    qw, sw = ops.nvfp4_quantize(w, wsc)
+    out_scale = xs * wsc
+    auto4 = ops.nvfp4_gemm(qx, sx, qw, sw, m, n, k, out_scale).clone()
+    _ok(ops, dev)
+    for name in ("single", "pair", "stream"):
+        with ops.gemm_schedule(name):
+            assert N.query("rtxb_get_gemm_schedule") == ops.GEMM_SCHEDULES[name]
+            got = ops.mxfp8_linear_fwd(x, w, ws).clone()
+            got4 = ops.nvfp4_gemm(qx, sx, qw, sw, m, n, k, out_scale).clone()
+        _ok(ops, dev)
+        assert N.query("rtxb_get_gemm_schedule") == 0
+        assert torch.equal(got.view(torch.int16), auto.view(torch.int16)), name
+        assert torch.equal(got4.view(torch.int16), auto4.view(torch.int16)), name
+    with pytest.raises(ValueError):
+        ops.gemm_schedule("wide")
+
+
+def test_decode_entry_honours_the_schedule(gpu):
+    """M <= 4 with a packed weight takes one kernel by default; a forced large-tile schedule takes the
+    three-launch chain with that GEMM instead and returns the same bits."""
+    ops, N, dev, ws = gpu
+    m, n, k = 2, 1024, 2048
+    torch.manual_seed(99)
+    x = torch.randn(m, k).bfloat16().to(dev)
+    w = (torch.randn(n, k) / k ** 0.5).bfloat16().to(dev)
+    w_scale = ops.nvfp4_tensor_scale(w, N.TENSOR_SCALE_POWER2)
+    qw, sw = ops.nvfp4_quantize(w, w_scale)
+    auto = ops.nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n, ws).clone()
+    _ok(ops, dev)
+    for name in ("single", "pair", "stream"):
+        with ops.gemm_schedule(name):
+            got = ops.nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n, ws).clone()
+        _ok(ops, dev)
+        assert torch.equal(got.view(torch.int16), auto.view(torch.int16)), name
+
+
 # ----------------------------------------------------------------------------- full-size properties
 
 def _deq_mx_gpu(q, s_tiles, rows, k):
