@@ -58,6 +58,7 @@ _LAZY_EXPORTS = {
     # sm_100a additions
     "mxfp8_glu_mlp": ("glu", "mxfp8_glu_mlp"),
     "SwiGLU": ("glu", "SwiGLU"),
+    "quantized_weight_cache": ("weight_cache", "quantized_weight_cache"),
     "KernelAdapter": ("autotune", "KernelAdapter"),
     "data_parallel_linear_backward": ("parallel", "data_parallel_linear_backward"),
 }

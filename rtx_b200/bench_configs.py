@@ -3,6 +3,7 @@
     python -m rtx_b200.bench_configs --config 3            # NVFP4 forward 16384 x 28672 x 8192
     python -m rtx_b200.bench_configs --config 4            # MXFP8 backward dX + dW, 16384 x 4096 x 4096
     python -m rtx_b200.bench_configs --config 5            # NVFP4 decode, packed weights, M in {1, 8, 16, 64}
+    python -m rtx_b200.bench_configs --config 6            # configuration 2's shapes with the step-scoped weight cache
     python -m torch.distributed.run --nproc-per-node N ... -m rtx_b200.bench_configs --config 4
 
 One JSON line per measured case (rank 0).  Token rows are sharded over ranks (weak scaling: the
@@ -255,9 +256,76 @@ def config5(args, rank, world, dev):
     return lines
 
 
+def config6(args, rank, world, dev):
+    """Step-scoped quantized-weight cache on the shapes of configuration 2: (a) the SwiGLU block's fused
+    inference forward, (b) a training step of the gate/up projection with four micro-batches (forward,
+    dX, dW each).  Every case is timed without and inside `quantized_weight_cache()`; the outputs of the
+    two are bit-identical.  The cached numbers skip work the uncached path does, so they are reported
+    beside configuration 2's metric, never as it."""
+    import rtx_b200 as rtx
+
+    m, k, inter = 8192, 4096, 14336
+    inp = make_inputs(2)
+    x = inp["x"].to(dev)
+    blk = rtx.SwiGLU(k, inter, device=dev)
+    with torch.no_grad():
+        blk.gate_up_proj.weight.copy_(inp["w_gate_up"].to(dev))
+        blk.down_proj.weight.copy_(inp["w_down"].to(dev))
+    lin = blk.gate_up_proj
+    micro = 4
+    xg = x.clone().requires_grad_(True)
+    dy = (torch.randn(m, 2 * inter, device=dev) * 0.1).bfloat16()
+
+    def infer():
+        with torch.no_grad():
+            return blk(x)
+
+    def train_step():
+        lin.weight.grad = None
+        xg.grad = None
+        for _ in range(micro):
+            lin(xg).backward(dy)
+
+    def scoped(fn):
+        def run():
+            with rtx.quantized_weight_cache():
+                fn()
+        return run
+
+    lines = []
+    with torch.no_grad():
+        want = infer().clone()
+    with rtx.quantized_weight_cache() as cache:
+        same = torch.equal(infer(), want)
+        t_inf_cached = _time(infer, args.steps, args.warmup, world, dev)      # warm cache: weights unchanged
+    t_inf = _time(infer, args.steps, args.warmup, world, dev)
+    flops_inf = 2.0 * m * (2 * inter) * k + 2.0 * m * k * inter
+    lines.append({
+        "metric": "fused quant+GEMM TFLOPS (MXFP8 SwiGLU block forward; weights quantized once per scope)",
+        "value": flops_inf * world / (t_inf_cached * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        "ms_per_step": t_inf_cached, "scaling": "weak", "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "mxfp8_glu_mlp_fwd_m8192_k4096_i14336", "weights": "cached in scope (3 launches)",
+                   "uncached_ms_per_step": t_inf, "uncached_tflops": flops_inf / (t_inf * 1e-3) / 1e12,
+                   "bit_identical_to_uncached": bool(same)},
+        "gpu_launches_per_step": 3})
+    t_train = _time(train_step, max(args.steps // 4, 3), args.warmup, world, dev)
+    t_train_cached = _time(scoped(train_step), max(args.steps // 4, 3), args.warmup, world, dev)
+    flops_train = micro * 3 * 2.0 * m * (2 * inter) * k
+    lines.append({
+        "metric": "fused quant+GEMM TFLOPS (MXFP8 gate/up projection, forward + dX + dW, 4 micro-batches per step)",
+        "value": flops_train * world / (t_train_cached * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        "ms_per_step": t_train_cached, "scaling": "weak", "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "mxfp8_linear_train_m8192_n28672_k4096_x4_microbatches",
+                   "weights": "quantized once per step (row-wise and transposed), scope closed before the update",
+                   "uncached_ms_per_step": t_train, "uncached_tflops": flops_train / (t_train * 1e-3) / 1e12}})
+    return lines
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5))
+    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5, 6))
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -270,7 +338,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    lines = {3: config3, 4: config4, 5: config5}[args.config](args, rank, world, dev)
+    lines = {3: config3, 4: config4, 5: config5, 6: config6}[args.config](args, rank, world, dev)
     if rank == 0:
         for line in lines:
             line.update({"steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True})

@@ -24,6 +24,7 @@ from torch import nn
 from . import _native as N
 from . import fp8 as _fp8
 from . import ops
+from . import weight_cache as _weight_cache
 from .configs import (DEFAULT_NVFP4_QUANT_CONFIG, MXFP8BwdConfig, NVFP4DynamicConfig, NVFP4Problem, NVFP4QuantConfig,
                       NVFP4ScaleConfig, config_from_key)
 from .formats import (PACKED_OPERAND_SCHEMA_VERSION, SCALE_LAYOUT_CODES, SCALE_LAYOUT_NAMES, NVFP4Tensor,
@@ -636,8 +637,17 @@ class NVFP4Linear(nn.Module):
             out = (torch.ops.rtx.nvfp4_linear_block_train(x2d, self.weight, key, bwd_key) if train
                    else torch.ops.rtx.nvfp4_linear_block_fwd(x2d, self.weight, key))
         elif self._dynamic_config.scale.policy == "jit_row_region":
-            out = (torch.ops.rtx.nvfp4_linear_jit_row_region_train(x2d, self.weight, key, bwd_key) if train
-                   else torch.ops.rtx.nvfp4_linear_jit_row_region_fwd(x2d, self.weight, key))
+            cache = _weight_cache.active()
+            if cache is not None:
+                # inside a quantized_weight_cache() scope: weight payload, block and region scales are reused
+                _check_bf16_cuda(x2d, "activation")
+                cfg = self._dynamic_config
+                args = (cfg.x_scale_region_rows, cfg.weight_scale_region_rows, _SCALE_MODE[cfg.scale.tensor_scale_mode])
+                out = (_weight_cache.NVFP4CachedRegionLinearFunction.apply(x2d, self.weight, cache, *args) if train
+                       else _weight_cache.nvfp4_linear_regions_cached(cache, x2d, self.weight, *args))
+            else:
+                out = (torch.ops.rtx.nvfp4_linear_jit_row_region_train(x2d, self.weight, key, bwd_key) if train
+                       else torch.ops.rtx.nvfp4_linear_jit_row_region_fwd(x2d, self.weight, key))
         else:
             mode = self._dynamic_config.scale.tensor_scale_mode
             x_scale = torch.ops.rtx.nvfp4_outer_scale(x2d.detach(), mode)

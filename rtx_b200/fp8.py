@@ -21,6 +21,7 @@ from torch import nn
 
 from . import _native as N
 from . import ops
+from . import weight_cache as _weight_cache
 from .configs import (DEFAULT_MXFP8_INFERENCE_CONFIG, DEFAULT_MXFP8_PREQUANT_CONFIG, MXFP8BwdConfig, MXFP8FwdConfig,
                       MXFP8PrequantConfig, MXFP8Problem, MXFP8QuantConfig, config_from_key)
 from .formats import (PACKED_OPERAND_SCHEMA_VERSION, SCALE_LAYOUT_CODES, SCALE_LAYOUT_NAMES, MXFP8Tensor,
@@ -414,6 +415,17 @@ class MXFP8Linear(nn.Module):
                 raise RuntimeError("a prequantized MXFP8 weight is inference-only; keep the BF16 master weight to train")
             out = torch.ops.rtx.mxfp8_linear_dynamic_x_prequant_w(x2d, self.weight_data, self.weight_scales, n, k,
                                                                   self._weight_scale_layout, self._forward_config_key)
+        elif (cache := _weight_cache.active()) is not None:
+            # inside a quantized_weight_cache() scope: the weight operands come from the step's cache
+            _check_inputs(x2d, self.weight)
+            rounding = _rounding(_resolve_prequant(self._forward_config_key))
+            if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
+                out = _weight_cache.MXFP8CachedLinearFunction.apply(x2d, self.weight, cache, rounding)
+            else:
+                qw, sw = _weight_cache.mxfp8_rows(cache, self.weight, rounding)
+                x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
+                qx, sx = ops.mxfp8_quantize(x2d, rounding=rounding)
+                out = ops.mxfp8_gemm(qx, sx, qw, sw, int(x2d.shape[0]), n, k)
         elif torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
             from . import fp8_bwd  # noqa: F401  (registers rtx::mxfp8_linear_train)
 

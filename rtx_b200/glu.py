@@ -15,6 +15,7 @@ from torch import nn
 
 from . import fp8 as _fp8
 from . import ops
+from . import weight_cache as _weight_cache
 
 
 @torch.library.custom_op("rtx::mxfp8_glu_mlp_fwd", mutates_args=(), device_types="cuda")
@@ -73,6 +74,12 @@ class SwiGLU(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self._fused_ok(x):
+            cache = _weight_cache.active()
+            if cache is not None:
+                x2d = x.reshape(-1, self.hidden_size)
+                _fp8._check_inputs(x2d, self.gate_up_proj.weight)
+                y = _weight_cache.mxfp8_glu_mlp_cached(cache, x2d, self.gate_up_proj.weight, self.down_proj.weight)
+                return y.reshape(*x.shape[:-1], self.hidden_size)
             y = torch.ops.rtx.mxfp8_glu_mlp_fwd(x.reshape(-1, self.hidden_size), self.gate_up_proj.weight,
                                                 self.down_proj.weight)
             return y.reshape(*x.shape[:-1], self.hidden_size)

@@ -344,3 +344,42 @@ def test_model_conversion_keeps_parameters_and_is_all_or_nothing():
     # a root that is itself a linear is returned replaced
     root = nn.Linear(32, 32, bias=False, dtype=torch.bfloat16)
     assert isinstance(rtx.convert_to_mxfp8_training(root), rtx.MXFP8Linear)
+
+
+def test_quantized_weight_cache_scope_and_invalidation():
+    """Host logic of the step-scoped weight cache: entries follow the parameter's storage and autograd
+    version, scopes nest onto the outermost cache, the scope is per thread and empties on exit."""
+    import threading
+
+    import rtx_b200 as rtx
+    from rtx_b200 import weight_cache as W
+
+    assert W.active() is None
+    w = torch.nn.Parameter(torch.zeros(4, 4))
+    other = torch.nn.Parameter(torch.zeros(4, 4))
+    made = []
+
+    def make(tag):
+        return lambda: made.append(tag) or [tag]
+
+    with rtx.quantized_weight_cache() as cache:
+        assert W.active() is cache and cache.alive
+        assert cache.get(w, "rows", make("a")) is cache.get(w, "rows", make("b"))
+        assert cache.get(w, "transposed", make("c")) == ["c"]          # parts are independent
+        assert cache.get(other, "rows", make("d")) == ["d"]            # so are parameters
+        assert cache.get(w.detach(), "rows", make("e")) == ["a"]       # same storage and version: same entry
+        with torch.no_grad():
+            w.add_(1)                                                  # what an optimizer does
+        assert cache.get(w, "rows", make("f")) == ["f"]
+        assert cache.get(w, "transposed", make("g")) == ["g"]
+        with rtx.quantized_weight_cache() as inner:
+            assert inner is cache
+        assert W.active() is cache
+        seen = []
+        t = threading.Thread(target=lambda: seen.append(W.active()))
+        t.start()
+        t.join()
+        assert seen == [None]
+        assert cache.stats == {"hits": 2, "misses": 5}
+    assert made == ["a", "c", "d", "f", "g"]
+    assert W.active() is None and not cache.alive and not cache.entries

@@ -407,3 +407,70 @@ def test_autotune_picks_among_the_built_kernels(dev, tmp_path):
         _done(dev)
         ref = y if ref is None else ref
         assert torch.equal(y, ref), cfg.gemm.schedule
+
+
+def test_quantized_weight_cache_is_bit_identical(dev):
+    """Inside `quantized_weight_cache()` modules reuse the quantized weight across micro-batches; outputs,
+    dX and accumulated dW equal the uncached run bit for bit, an in-place weight update is seen, and the
+    scope saves exactly the weight quantizer launches."""
+    import rtx_b200 as rtx
+
+    torch.manual_seed(77)
+    xs = [torch.randn(3, 50, 256).bfloat16().to(dev) for _ in range(3)]
+
+    def run(module, cached):
+        module.zero_grad(set_to_none=True)
+        outs, dxs = [], []
+        scope = rtx.quantized_weight_cache() if cached else None
+        cache = scope.__enter__() if cached else None
+        try:
+            for x in xs:
+                xg = x.clone().requires_grad_(True)
+                y = module(xg)
+                y.float().square().mean().backward()
+                outs.append(y.detach().clone())
+                dxs.append(xg.grad.clone())
+            with torch.no_grad():
+                outs.append(module(xs[0]).clone())
+        finally:
+            if cached:
+                scope.__exit__(None, None, None)
+        _done(dev)
+        return outs, dxs, module.weight.grad.clone(), (cache.stats.copy() if cached else None)
+
+    for make in (lambda: rtx.MXFP8Linear(256, 384, device=dev), lambda: rtx.NVFP4Linear(256, 384, device=dev)):
+        module = make()
+        outs0, dxs0, dw0, _ = run(module, False)
+        outs1, dxs1, dw1, stats = run(module, True)
+        for a, b in zip(outs0 + dxs0 + [dw0], outs1 + dxs1 + [dw1]):
+            assert torch.equal(a, b)
+        # forward operand: 1 miss + 3 hits; dX operand: 1 miss + 2 hits
+        assert stats == {"hits": 5, "misses": 2}, stats
+        # an optimizer-style update inside a scope is seen through the version counter
+        with rtx.quantized_weight_cache() as cache:
+            with torch.no_grad():
+                before = module(xs[0]).clone()
+                module.weight.mul_(0.5)
+                after = module(xs[0]).clone()
+            assert cache.stats["misses"] == 2
+        with torch.no_grad():
+            want = module(xs[0])
+        _done(dev)
+        assert torch.equal(after, want) and not torch.equal(before, after)
+
+    # the fused SwiGLU inference path
+    blk = rtx.SwiGLU(256, 384, device=dev)
+    with torch.no_grad():
+        want = blk(xs[0])
+        with rtx.quantized_weight_cache() as cache:
+            got = [blk(xs[0]).clone() for _ in range(2)]
+        assert cache.stats == {"hits": 2, "misses": 2}
+    _done(dev)
+    assert torch.equal(got[0], want) and torch.equal(got[1], want)
+    # under torch.compile the scope is ignored, not traced
+    lin = rtx.MXFP8Linear(256, 384, device=dev)
+    with torch.no_grad(), rtx.quantized_weight_cache() as cache:
+        y_c = torch.compile(lin, fullgraph=True, dynamic=False)(xs[0])
+        y_e = lin(xs[0])
+    _done(dev)
+    assert torch.equal(y_c, y_e)
