@@ -212,6 +212,10 @@ def run_own_arm(args) -> None:
     rows_global = M * world if args.scaling == "weak" else M
     inp = make_inputs(2, m=rows_global)
     per = rows_global // world
+    # host buffers on the NUMA node of this rank's GPU (affinity restored before the CPU baseline runs)
+    from rtx_b200.host import numa_local
+    numa = numa_local(dev)
+    numa.__enter__()
     x_host = inp["x"][rank * per:(rank + 1) * per].contiguous().pin_memory()
     x = x_host.to(dev, non_blocking=True)
     wgu = inp["w_gate_up"].to(dev)
@@ -270,6 +274,24 @@ def run_own_arm(args) -> None:
     sampler.mark(w0, time.time())
     barrier()
 
+    # the copies of the end-to-end step alone (X in and Y out at the same time, no compute): the PCIe
+    # floor of the end-to-end number
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    c0, c1, c2, c3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s_in):
+        c0.record()
+        for i in range(args.steps):
+            x.copy_(x_hosts[i % 2], non_blocking=True)
+        c1.record()
+    with torch.cuda.stream(s_out):
+        c2.record()
+        for i in range(args.steps):
+            y_hosts[i % 2].copy_(y, non_blocking=True)
+        c3.record()
+    torch.cuda.synchronize()
+    copy_ms = max(c0.elapsed_time(c1), c2.elapsed_time(c3)) / args.steps
+
     # dominant kernel alone: the gate/up GEMM with the fused SwiGLU epilogue
     qx, sx = ops.mxfp8_quantize(x)
     qg, sg = ops.mxfp8_quantize(wgu)
@@ -284,6 +306,7 @@ def run_own_arm(args) -> None:
     torch.cuda.synchronize()
     sampler.mark(w0, time.time())
     clocks = sampler.stop()
+    numa.__exit__(None, None, None)
     gemm_ms = ev0.elapsed_time(ev1) / args.steps
     ops.check_device_status(dev)
 
@@ -318,7 +341,10 @@ def run_own_arm(args) -> None:
             "pct_of_measured_fp8_proxy": 100.0 * value / world / fp8_peak,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": e2e_ms_total / args.steps,
-                    "api": "rtx_b200.host.GluMlpHostSession.submit/drain (copies overlapped with compute)"},
+                    "api": "rtx_b200.host.GluMlpHostSession.submit/drain (copies overlapped with compute)",
+                    "host_cpus": f"{len(numa.cpus)} CPUs next to the GPU" if numa.cpus else "unbound",
+                    "copies_alone_ms_per_step": copy_ms,
+                    "copies_alone_gbs_each_way": x_host.numel() * 2 / (copy_ms * 1e-3) / 1e9},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, glu_mx> (gate/up GEMM + SiLU*up + MXFP8 encode of H)", "bound": "tensor",

@@ -16,6 +16,56 @@ import torch
 from . import ops
 
 
+def gpu_local_cpus(device: torch.device) -> Optional[List[int]]:
+    """CPUs of this process's allowed set that sit on the NUMA node of `device` (NVML's CPU affinity of the
+    GPU, looked up by UUID so that CUDA_VISIBLE_DEVICES does not matter); None when NVML, the UUID or an
+    overlap with the allowed set is missing."""
+    import os
+
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device).uuid)
+        handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        words = (os.cpu_count() or 64) // 64 + 1
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+    except Exception:
+        return None
+    local = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+    cpus = sorted(local & os.sched_getaffinity(0))
+    return cpus or None
+
+
+class numa_local:
+    """Context manager: run the calling thread on the CPUs next to `device` while pinned host buffers are
+    allocated (first touch puts their pages on that NUMA node) and copies are submitted; the previous
+    affinity is restored on exit.  With eight GPUs behind two sockets, host buffers on the far socket send
+    every host-device copy across the socket interconnect."""
+
+    def __init__(self, device: torch.device):
+        import os
+
+        # RTXB_HOST_NUMA=0 leaves the affinity alone
+        self.cpus = None if os.environ.get("RTXB_HOST_NUMA") == "0" else gpu_local_cpus(device)
+        self.prev = None
+
+    def __enter__(self):
+        import os
+
+        if self.cpus:
+            self.prev = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, self.cpus)
+        return self
+
+    def __exit__(self, *exc):
+        import os
+
+        if self.prev is not None:
+            os.sched_setaffinity(0, self.prev)
+        return False
+
+
 class GluMlpHostSession:
     def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, max_rows: int, depth: int = 3):
         if w_gate_up.device.type != "cuda":
