@@ -383,3 +383,24 @@ def test_quantized_weight_cache_scope_and_invalidation():
         assert cache.stats == {"hits": 2, "misses": 5}
     assert made == ["a", "c", "d", "f", "g"]
     assert W.active() is None and not cache.alive and not cache.entries
+
+
+def test_numa_local_is_a_no_op_without_a_gpu(monkeypatch):
+    """`numa_local` narrows the thread's CPU affinity only when NVML names CPUs next to the GPU that the
+    process may use; otherwise, and with RTXB_HOST_NUMA=0, the affinity is left alone.  It is restored on exit."""
+    import os
+
+    from rtx_b200 import host
+
+    before = os.sched_getaffinity(0)
+    with host.numa_local(torch.device("cuda", 0)) as scope:
+        assert scope.cpus is None or set(scope.cpus) <= before
+    assert os.sched_getaffinity(0) == before
+    one = sorted(before)[:1]
+    monkeypatch.setattr(host, "gpu_local_cpus", lambda device: one)
+    with host.numa_local(torch.device("cuda", 0)) as scope:
+        assert scope.cpus == one and os.sched_getaffinity(0) == set(one)
+    assert os.sched_getaffinity(0) == before
+    monkeypatch.setenv("RTXB_HOST_NUMA", "0")
+    with host.numa_local(torch.device("cuda", 0)) as scope:
+        assert scope.cpus is None and os.sched_getaffinity(0) == before
