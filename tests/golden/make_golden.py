@@ -1,9 +1,9 @@
 """Generate the golden fixtures of tests/golden/ by EXECUTING the reference.
 
-Run in a container that has the reference checkout (read-only) at
-$RTX_REFERENCE (default /root/reference):
+Run where the reference checkout (read-only) is available and name it in
+$RTX_REFERENCE:
 
-    python tests/golden/make_golden.py
+    RTX_REFERENCE=<reference checkout> python tests/golden/make_golden.py
 
 What it executes (nothing is copied into this repository):
   * rtx.autotune.legacy._torch_mxfp8_reference (rtx/autotune/legacy.py:783-806),
@@ -29,7 +29,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("RTX_REFERENCE", "/root/reference")
+REF = os.environ.get("RTX_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set RTX_REFERENCE to the reference checkout")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
