@@ -241,7 +241,7 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
 
 
 # ---------------------------------------------------------------------------
-# SM margin
+# Launch controls: GEMM schedule of the calling thread, SM margin of the process
 # ---------------------------------------------------------------------------
 
 GEMM_SCHEDULES = {"auto": 0, "single": 1, "pair": 2, "stream": 3}
