@@ -4,12 +4,20 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl own|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (N=1 and per rank): the MXFP8 SwiGLU MLP forward of the benchmark
-configuration — X bf16 [8192, 4096] (N(0,1), 0.1 % of entries x50), W_gate|W_up
-bf16 [28672, 4096], W_down bf16 [4096, 14336]; every step quantizes X, both
-weights and H to MXFP8 and runs the two block-scaled GEMMs (SiLU*up fused into
-the first epilogue).  Token rows are sharded over ranks, weights replicated, no
-collective on the forward path.  One JSON line is printed by rank 0.
+Headline workload: the MXFP8 SwiGLU MLP forward of benchmark configuration 2 — ONE batch
+X bf16 [8192, 4096] (N(0,1), 0.1 % of entries x50), W_gate|W_up bf16 [28672, 4096], W_down bf16
+[4096, 14336] — whose token rows are sharded over the ranks (strong scaling: 8192 / N rows per GPU),
+weights replicated, no collective.  Every step quantizes X, both weights and H to MXFP8 and runs
+the two block-scaled GEMMs (SiLU*up fused into the first epilogue).
+
+The one JSON line rank 0 prints also carries, as named sub-records:
+  weak       the same forward with 8192 rows PER GPU (per-GPU work fixed);
+  sustained  the headline step looped for at least two seconds (clock and power under the cap);
+  backward   configuration 4 (MXFP8 dX + dW, 16384 x 4096 x 4096) through
+             rtx_b200.parallel.data_parallel_linear_backward, the FP32 dW all-reduced with NCCL
+             inside the timed region, strong (16384 rows split) and weak (16384 rows per GPU),
+             with a parity check of the sharded result against the unsharded one;
+  configs    (1 GPU only) configurations 3 and 5 measured as bench_configs.py does.
 """
 
 from __future__ import annotations
@@ -19,7 +27,6 @@ import json
 import os
 import statistics
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -27,7 +34,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 M, K, INTER, N_OUT = 8192, 4096, 14336, 4096
+BWD_M, BWD_N, BWD_K = 16384, 4096, 4096
 NOMINAL_FP8_TFLOPS = 4500.0
+SUSTAINED_SECONDS = 2.2
 METRIC = "fused quant+GEMM TFLOPS (MXFP8 SwiGLU MLP forward, quantization included)"
 
 
@@ -47,7 +56,8 @@ def measured_peaks() -> dict:
 
 class ClockSampler:
     """Samples SM clock, power and throttle reasons with `nvidia-smi -lms` (read-only) in a child process
-    while the timed loops run; samples are kept only if their timestamp falls inside a marked region."""
+    while the timed loops run; a sample counts for a label if its timestamp falls inside a region marked
+    with that label."""
 
     FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -71,27 +81,31 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def mark(self, t0: float, t1: float):
-        self.regions.append((t0, t1))
+    def mark(self, label: str, t0: float, t1: float):
+        self.regions.append((label, t0, t1))
 
     def stop(self) -> dict:
+        """{label: {sm_mhz, sm_max_mhz, power_w, reasons, samples}}"""
         import datetime
 
+        labels = sorted({r[0] for r in self.regions})
+        empty = {"sm_mhz": None, "sm_max_mhz": None, "power_w": None, "reasons": [], "samples": 0}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {label: dict(empty) for label in labels}
         time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        clocks, powers, reasons, max_mhz, total = [], [], set(), None, 0
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         try:
             lines = open(self.path).read().splitlines()
             os.unlink(self.path)
         except OSError:
             lines = []
+        acc = {label: {"clocks": [], "powers": [], "reasons": set()} for label in labels}
+        max_mhz, total = None, 0
         for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
@@ -103,17 +117,18 @@ class ClockSampler:
                 continue
             total += 1
             max_mhz = mx
-            if not any(t0 - 0.005 <= ts <= t1 + 0.005 for t0, t1 in self.regions):
-                continue
-            clocks.append(mhz)
-            powers.append(watts)
-            for name, flag in zip(names, parts[4:8]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_mhz,
-                "power_w": statistics.median(powers) if powers else None, "reasons": sorted(reasons),
-                "samples": len(clocks), "samples_total": total,
-                "regions": "timed steps, end-to-end steps and the dominant-kernel loop"}
+            for label, t0, t1 in self.regions:
+                if t0 - 0.005 <= ts <= t1 + 0.005:
+                    a = acc[label]
+                    a["clocks"].append(mhz)
+                    a["powers"].append(watts)
+                    a["reasons"].update(n for n, flag in zip(names, parts[4:8]) if flag.lower().startswith("active"))
+        out = {}
+        for label, a in acc.items():
+            out[label] = {"sm_mhz": statistics.median(a["clocks"]) if a["clocks"] else None, "sm_max_mhz": max_mhz,
+                          "power_w": statistics.median(a["powers"]) if a["powers"] else None,
+                          "reasons": sorted(a["reasons"]), "samples": len(a["clocks"]), "samples_total": total}
+        return out
 
 
 def physical_gpu_index(local_rank: int) -> int:
@@ -130,18 +145,17 @@ def physical_gpu_index(local_rank: int) -> int:
 # reference arm and CPU baseline: the reference's CPU path (oracle/cpu_path.py)
 # --------------------------------------------------------------------------
 
-def cpu_sample_run(m_s: int, inter_s: int, threads: int, repeats: int, warmup: int):
-    """Times the CPU path on a sample: the first m_s token rows, gate/up rows [0, inter_s) of each
-    half and the matching inter_s columns of W_down.  Returns (seconds per run list, flops per run)."""
+def cpu_workload_run(m_rows: int, threads: int, repeats: int, warmup: int):
+    """Times the reference's CPU formulation (encode + FP32 dequantized matmul) of the MLP forward on the
+    first m_rows token rows of configuration 2 with the full weights.  -> (seconds per run, flop per run)"""
     import torch
 
     from oracle import cpu_path as C
     from rtx_b200.workloads import make_inputs
 
     torch.set_num_threads(threads)
-    inp = make_inputs(2, m=m_s, inter=inter_s)
+    inp = make_inputs(2, m=m_rows, inter=INTER)
     x, wgu, wd = inp["x"], inp["w_gate_up"], inp["w_down"]
-    flops = 2.0 * m_s * (2 * inter_s) * K + 2.0 * m_s * N_OUT * inter_s
     times = []
     for i in range(warmup + repeats):
         t0 = time.perf_counter()
@@ -149,27 +163,29 @@ def cpu_sample_run(m_s: int, inter_s: int, threads: int, repeats: int, warmup: i
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
-    return times, flops
+    return times, mlp_flops(m_rows)
 
 
 def run_reference_arm(args) -> None:
+    """The reference's own CPU path on the host cores, all threads, every step the WHOLE configuration-2
+    batch (8192 rows, full weights): the same work per step as the own arm's global step at any N."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    m_s, inter_s = 2048, 2048
-    times, flops = cpu_sample_run(m_s, inter_s, threads, args.steps, max(args.warmup, 1))
+    times, flops = cpu_workload_run(M, threads, args.steps, max(min(args.warmup, 2), 1))
     total = sum(times)
     value = flops * len(times) / total / 1e12
-    sample = (f"per step: X[:{m_s}] of {M} rows, gate/up rows [0,{inter_s}) of {INTER} each, "
-              f"W_down[:, :{inter_s}]; K={K} and n_out={N_OUT} full; {flops:.3e} flop/step")
+    sample = (f"every step = the whole workload: X {M} rows, W_gate|W_up [{2 * INTER}, {K}], W_down [{N_OUT}, {INTER}], "
+              f"{flops:.3e} flop; {len(times)} steps in {total:.1f} s")
     line = {
         "impl": "reference",
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "mxfp8_glu_mlp_fwd_m8192_k4096_i14336", "sample": sample,
-                   "path": "reference CPU path: torch encode + FP32 dequantized matmul (oracle/cpu_path.py port)"},
+        "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"mxfp8_glu_mlp_fwd_m{M}_k{K}_i{INTER}", "sample": sample,
+                   "path": "reference CPU path: torch encode + FP32 dequantized matmul (oracle/cpu_path.py, pinned bit "
+                           "for bit to the reference's rtx.autotune.legacy._torch_mxfp8_reference)"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -181,12 +197,53 @@ def run_reference_arm(args) -> None:
 # own arm
 # --------------------------------------------------------------------------
 
+class Timer:
+    """CUDA-event timing on the current stream between barriers; results are reduced (max over ranks)
+    together at the end."""
+
+    def __init__(self, torch, dist, world, local_rank, sampler):
+        self.torch, self.dist, self.world, self.local_rank, self.sampler = torch, dist, world, local_rank, sampler
+        self.results = {}
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier(device_ids=[self.local_rank])
+
+    def run(self, name, fn, steps, warmup, label="burst"):
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        torch.cuda.synchronize()
+        w0 = time.time()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        self.sampler.mark(label, w0, time.time())
+        self.barrier()
+        self.results[name] = ev0.elapsed_time(ev1) / steps
+        return self.results[name]
+
+    def reduce(self, dev):
+        names = sorted(self.results)
+        t = self.torch.tensor([self.results[n] for n in names], dtype=self.torch.float64, device=dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        self.results = dict(zip(names, (float(v) for v in t.tolist())))
+        return self.results
+
+
 def run_own_arm(args) -> None:
     import torch
     import torch.distributed as dist
 
     from rtx_b200 import _native as N
-    from rtx_b200 import build, ops
+    from rtx_b200 import build, ops, parallel
+    from rtx_b200.host import GluMlpHostSession, numa_local
     from rtx_b200.workloads import make_inputs
 
     rank = int(os.environ.get("RANK", "0"))
@@ -201,166 +258,218 @@ def run_own_arm(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, pg_options=parallel.nccl_options())
+    if M % (world * 128) or BWD_M % (world * 128):
+        raise SystemExit(f"{M} and {BWD_M} token rows must split into whole 128-row tiles over {world} ranks")
+    steps, warmup = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    timer = Timer(torch, dist, world, local_rank, sampler)
+    ws = ops.Workspace(dev)
 
-    def barrier():
-        if world > 1:
-            dist.barrier(device_ids=[local_rank])
-
-    # identical global tensors on every rank; each rank keeps its own M rows (weak scaling:
-    # M rows per GPU whatever the GPU count)
-    rows_global = M * world if args.scaling == "weak" else M
-    inp = make_inputs(2, m=rows_global)
-    per = rows_global // world
-    # host buffers on the NUMA node of this rank's GPU (affinity restored before the CPU baseline runs)
-    from rtx_b200.host import numa_local
+    # ---------------- forward inputs: one global draw, every rank slices its rows ----------------
+    inp = make_inputs(2, m=M)             # the same batch and weights at every N
     numa = numa_local(dev)
-    numa.__enter__()
+    numa.__enter__()                       # host buffers next to this rank's GPU; restored before the CPU baseline
+    per = M // world
     x_host = inp["x"][rank * per:(rank + 1) * per].contiguous().pin_memory()
     x = x_host.to(dev, non_blocking=True)
+    # weak sub-record: M rows per GPU out of a global draw of M * world rows
+    x_weak = make_inputs(2, m=M * world)["x"][rank * M:(rank + 1) * M].to(dev) if world > 1 else x
     wgu = inp["w_gate_up"].to(dev)
     wd = inp["w_down"].to(dev)
     del inp
-    m_local = per
-    y = torch.empty(m_local, N_OUT, dtype=torch.bfloat16, device=dev)
-    y_host = torch.empty(m_local, N_OUT, dtype=torch.bfloat16).pin_memory()
-    ws = ops.Workspace(dev)
+    y = torch.empty(per, N_OUT, dtype=torch.bfloat16, device=dev)
+    y_weak = torch.empty(M, N_OUT, dtype=torch.bfloat16, device=dev) if world > 1 else y
+    y_host = torch.empty(per, N_OUT, dtype=torch.bfloat16).pin_memory()
     launches_per_step = 5  # quantize X, W_gate_up, W_down + gate/up GEMM (SiLU*up and H quantization fused) + down GEMM
 
     def step():
         ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, None, y, want_hidden=False)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-    ops.check_device_status(dev)
+    def step_weak():
+        ops.mxfp8_glu_mlp_fwd(x_weak, wgu, wd, ws, None, y_weak, want_hidden=False)
 
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    torch.cuda.synchronize()
     sampler.start()
-    torch.cuda.synchronize()
-    w0 = time.time()
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    torch.cuda.synchronize()
-    sampler.mark(w0, time.time())
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
+    timer.run("fwd", step, steps, warmup)
     ops.check_device_status(dev)
+    if world > 1:
+        timer.run("fwd_weak", step_weak, steps, warmup)
+        ops.check_device_status(dev)
 
-    # end to end through host buffers (rtx_b200.host.GluMlpHostSession): every step copies that step's X
-    # from pinned host memory to the device and its Y back to pinned host memory; copy-in of step i+1 and
-    # copy-out of step i-1 overlap the compute of step i (three streams, three device buffer sets)
-    from rtx_b200.host import GluMlpHostSession
-
-    session = GluMlpHostSession(wgu, wd, m_local)
+    # ---------------- end to end through host buffers (rtx_b200.host.GluMlpHostSession) ----------------
+    # every step copies that step's X from pinned host memory to the device and its Y back; copy-in of step
+    # i+1 and copy-out of step i-1 overlap the compute of step i (three streams, three device buffer sets)
+    session = GluMlpHostSession(wgu, wd, per)
     x_hosts = [x_host, x_host.clone().pin_memory()]
     y_hosts = [y_host, torch.empty_like(y_host).pin_memory()]
     for i in range(3):
         session.submit(x_hosts[i % 2], y_hosts[i % 2])
     session.drain()
-    barrier()
+    timer.barrier()
     torch.cuda.synchronize()
     w0 = time.time()
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(steps):
         session.submit(x_hosts[i % 2], y_hosts[i % 2])
     session.drain()
-    e2e_ms_total = (time.perf_counter() - t0) * 1e3   # spans three streams: host clock around submit..drain
-    sampler.mark(w0, time.time())
-    barrier()
+    timer.results["e2e"] = (time.perf_counter() - t0) * 1e3 / steps   # spans three streams: host clock, submit..drain
+    sampler.mark("burst", w0, time.time())
+    timer.barrier()
+    del session
 
-    # the copies of the end-to-end step alone (X in and Y out at the same time, no compute): the PCIe
-    # floor of the end-to-end number
+    # the copies of the end-to-end step alone (X in and Y out at the same time, no compute): its PCIe floor
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     c0, c1, c2, c3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
     torch.cuda.synchronize()
     with torch.cuda.stream(s_in):
         c0.record()
-        for i in range(args.steps):
+        for i in range(steps):
             x.copy_(x_hosts[i % 2], non_blocking=True)
         c1.record()
     with torch.cuda.stream(s_out):
         c2.record()
-        for i in range(args.steps):
+        for i in range(steps):
             y_hosts[i % 2].copy_(y, non_blocking=True)
         c3.record()
     torch.cuda.synchronize()
-    copy_ms = max(c0.elapsed_time(c1), c2.elapsed_time(c3)) / args.steps
+    timer.results["copies"] = max(c0.elapsed_time(c1), c2.elapsed_time(c3)) / steps
+    numa.__exit__(None, None, None)
 
-    # dominant kernel alone: the gate/up GEMM with the fused SwiGLU epilogue
+    # ---------------- dominant kernel alone: the gate/up GEMM with the fused SwiGLU epilogue ----------------
     qx, sx = ops.mxfp8_quantize(x)
     qg, sg = ops.mxfp8_quantize(wgu)
-    for _ in range(3):
-        ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, m_local, INTER, K)
-    torch.cuda.synchronize()
-    w0 = time.time()
-    ev0.record()
-    for _ in range(args.steps):
-        ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, m_local, INTER, K)
-    ev1.record()
-    torch.cuda.synchronize()
-    sampler.mark(w0, time.time())
-    clocks = sampler.stop()
-    numa.__exit__(None, None, None)
-    gemm_ms = ev0.elapsed_time(ev1) / args.steps
+    timer.run("gemm", lambda: ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, per, INTER, K), steps, 3)
     ops.check_device_status(dev)
+    del qx, sx, qg, sg
 
-    t = torch.tensor([ms_total, e2e_ms_total, gemm_ms], dtype=torch.float64, device=dev)
+    # ---------------- sustained: the headline step for >= 2 s ----------------
+    t = torch.tensor([timer.results["fwd"]], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_total, gemm_ms = (float(v) for v in t.tolist())
+    sustained_steps = int(SUSTAINED_SECONDS * 1e3 / float(t.item())) + 1
+    timer.run("sustained", step, sustained_steps, 0, label="sustained")
+    ops.check_device_status(dev)
+    del x_weak, y_weak
+
+    # ---------------- backward (configuration 4): dX local, FP32 dW all-reduced inside the timed region ----------------
+    bwd = make_inputs(4, m=BWD_M * world)
+    bper = BWD_M // world
+    w_b = bwd["w"].to(dev)
+    shards = {"strong": (bwd["x"][rank * bper:(rank + 1) * bper].to(dev), bwd["dy"][rank * bper:(rank + 1) * bper].to(dev))}
+    if world > 1:
+        shards["weak"] = (bwd["x"][rank * BWD_M:(rank + 1) * BWD_M].to(dev),
+                          bwd["dy"][rank * BWD_M:(rank + 1) * BWD_M].to(dev))
+    bwd_parity = None
+    for mode, (xb, dyb) in shards.items():
+        timer.run(f"bwd_{mode}", lambda: parallel.data_parallel_linear_backward(dyb, xb, w_b), steps, warmup)
+        ops.check_device_status(dev)
+    if world > 1:
+        # parity of the sharded step: dX rows bit-equal to the unsharded rows, all-reduced dW within the
+        # output bar of the unsharded dW (only the FP32 summation order differs)
+        from oracle.mx_oracle import parity_report
+
+        xb, dyb = shards["strong"]
+        dx_r, dw_r = parallel.data_parallel_linear_backward(dyb, xb, w_b)
+        x_all, dy_all = bwd["x"][:BWD_M].to(dev), bwd["dy"][:BWD_M].to(dev)
+        dx_1, dw_1 = ops.mxfp8_linear_bwd(dy_all, x_all, w_b, ws)
+        torch.cuda.synchronize()
+        rep = parity_report(dw_r.cpu(), dw_1.cpu())
+        bwd_parity = {"dx_rows_bit_equal": bool(torch.equal(dx_r, dx_1[rank * bper:(rank + 1) * bper])),
+                      "dw_rel_fro": rep["rel_fro"], "dw_frac_le_1ulp": rep["frac_le_1ulp"],
+                      "against": "the unsharded rtxb_mxfp8_linear_bwd on the same 16384 rows (rank 0's comparison)"}
+        del x_all, dy_all, dx_1, dw_1, dx_r, dw_r
+    del bwd, shards
+
+    clocks = sampler.stop()
+    res = timer.reduce(dev)
+
+    # ---------------- other configurations, one GPU only ----------------
+    others = None
+    if world == 1 and not args.no_other_configs:
+        import bench_configs as BC
+
+        sub = argparse.Namespace(steps=steps, warmup=3)
+        keep = ("metric", "value", "unit", "ms_per_step", "config", "roofline", "gpu_launches_per_step")
+        others = {"c3_nvfp4_forward": [{k: ln.get(k) for k in keep} for ln in BC.config3(sub, 0, 1, dev)],
+                  "c5_nvfp4_decode": [{k: ln.get(k) for k in keep} for ln in BC.config5(sub, 0, 1, dev)]}
 
     if rank == 0:
         peaks = measured_peaks()
-        flops_step_global = mlp_flops(m_local) * world
-        value = flops_step_global * args.steps / (ms_total * 1e-3) / 1e12
-        e2e_value = flops_step_global * args.steps / (e2e_ms_total * 1e-3) / 1e12
-        gemm_tflops = 2.0 * m_local * (2 * INTER) * K / (gemm_ms * 1e-3) / 1e12
         fp8_peak = 2.0 * peaks["bf16_tflops"]
+        flops_global = mlp_flops(M)                       # strong scaling: the global batch is fixed
+        value = flops_global / (res["fwd"] * 1e-3) / 1e12
+        e2e_value = flops_global / (res["e2e"] * 1e-3) / 1e12
+        gemm_tflops = 2.0 * per * (2 * INTER) * K / (res["gemm"] * 1e-3) / 1e12
+        sus = clocks.get("sustained", {})
+        sus_value = flops_global / (res["sustained"] * 1e-3) / 1e12
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
-        if os.path.exists(tpath):
+        if os.path.exists(tpath) and world == 1:
             with open(tpath) as f:
                 traffic = json.load(f).get("gemm_glu_mxfp8_c2_dram_bytes_per_launch")
+        bwd_flops = 4.0 * BWD_M * BWD_N * BWD_K
+        backward = {
+            "metric": "fused quant+GEMM TFLOPS (MXFP8 backward dX + dW, operand quantizations and the dW all-reduce included)",
+            "workload": f"mxfp8_linear_bwd_m{BWD_M}_n{BWD_N}_k{BWD_K}",
+            "api": "rtx_b200.parallel.data_parallel_linear_backward",
+            "collective": (f"NCCL all-reduce(sum) of the FP32 dW ({BWD_N * BWD_K * 4 / 1e6:.0f} MB), issued per band of dW "
+                           f"rows as the dW GEMM finishes it, beside the rest of the step" if world > 1 else "none (1 GPU)"),
+            "strong": {"rows_per_gpu": bper, "ms_per_step": res["bwd_strong"],
+                       "value": bwd_flops / (res["bwd_strong"] * 1e-3) / 1e12, "unit": "TFLOP/s"},
+        }
+        if world > 1:
+            backward["weak"] = {"rows_per_gpu": BWD_M, "ms_per_step": res["bwd_weak"],
+                                "value": bwd_flops * world / (res["bwd_weak"] * 1e-3) / 1e12, "unit": "TFLOP/s"}
+            backward["parity"] = bwd_parity
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate",
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": res["fwd"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate",
             "data": "synthetic",
-            "config": {"workload": f"mxfp8_glu_mlp_fwd_m{M}_k{K}_i{INTER}", "m_per_gpu": m_local, "k": K,
-                       "inter": INTER, "n_out": N_OUT, "parallelism": f"dp{world} (token rows sharded, weights replicated)",
-                       "l2": "inputs exceed L2 (X 67 MB + weights 352 MB bf16 re-read every step)",
+            "config": {"workload": f"mxfp8_glu_mlp_fwd_m{M}_k{K}_i{INTER}", "m_global": M, "m_per_gpu": per, "k": K,
+                       "inter": INTER, "n_out": N_OUT,
+                       "parallelism": f"dp{world} (one {M}-row batch, token rows sharded, weights replicated, no collective)",
+                       "l2": "inputs exceed L2 (352 MB of bf16 weights + X re-read and re-quantized every step)",
                        "hidden": "H leaves the gate/up epilogue already MXFP8-encoded; no BF16 H is materialized"},
             "tflops_per_gpu": value / world,
             "pct_of_nominal_fp8_peak": 100.0 * value / world / NOMINAL_FP8_TFLOPS,
             "pct_of_measured_fp8_proxy": 100.0 * value / world / fp8_peak,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2 * world,
-                    "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": e2e_ms_total / args.steps,
+                    "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": res["e2e"],
                     "api": "rtx_b200.host.GluMlpHostSession.submit/drain (copies overlapped with compute)",
                     "host_cpus": f"{len(numa.cpus)} CPUs next to the GPU" if numa.cpus else "unbound",
-                    "copies_alone_ms_per_step": copy_ms,
-                    "copies_alone_gbs_each_way": x_host.numel() * 2 / (copy_ms * 1e-3) / 1e9},
-            "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks,
-            "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, glu_mx> (gate/up GEMM + SiLU*up + MXFP8 encode of H)", "bound": "tensor",
-                         "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
-                         "traffic": traffic, "ms_per_launch": gemm_ms,
+                    "copies_alone_ms_per_step": res["copies"],
+                    "copies_alone_gbs_each_way": x_host.numel() * 2 / (res["copies"] * 1e-3) / 1e9},
+            "gpu_launches": launches_per_step * steps,
+            "clocks": clocks.get("burst"),
+            "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, glu_mx> (gate/up GEMM + SiLU*up + MXFP8 encode of H)",
+                         "bound": "tensor", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": gemm_tflops / fp8_peak, "frac_of_nominal": gemm_tflops / NOMINAL_FP8_TFLOPS,
+                         "traffic": traffic, "ms_per_launch": res["gemm"], "rows": per,
                          "peak_note": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s) as the "
-                                      f"dense FP8 proxy; nominal dense FP8 is {NOMINAL_FP8_TFLOPS} TFLOP/s"},
+                                      f"dense FP8 proxy (of measured); nominal dense FP8 is {NOMINAL_FP8_TFLOPS} TFLOP/s"},
+            "sustained": {"value": sus_value, "unit": "TFLOP/s", "steps": sustained_steps, "ms_per_step": res["sustained"],
+                          "seconds": res["sustained"] * sustained_steps * 1e-3, "sm_mhz": sus.get("sm_mhz"),
+                          "power_w": sus.get("power_w"), "reasons": sus.get("reasons"), "samples": sus.get("samples"),
+                          "ms_times_mhz": (res["sustained"] * sus["sm_mhz"]) if sus.get("sm_mhz") else None,
+                          "burst_ms_times_mhz": (res["fwd"] * clocks["burst"]["sm_mhz"])
+                          if clocks.get("burst", {}).get("sm_mhz") else None,
+                          "pct_of_nominal_fp8_peak": 100.0 * sus_value / world / NOMINAL_FP8_TFLOPS},
+            "backward": backward,
         }
+        if world > 1:
+            weak_value = mlp_flops(M) * world / (res["fwd_weak"] * 1e-3) / 1e12
+            line["weak"] = {"value": weak_value, "unit": "TFLOP/s", "rows_per_gpu": M, "ms_per_step": res["fwd_weak"],
+                            "tflops_per_gpu": weak_value / world}
+        if others is not None:
+            line["configs"] = others
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            m_s = M
-            times, flops = cpu_sample_run(m_s, INTER, threads, 3, 1)
+            times, flops = cpu_workload_run(M, threads, 3, 1)
             line["cpu_baseline"] = {
                 "value": flops * len(times) / sum(times) / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                 "sample": f"{len(times)} runs (after 1 warm-up) of the reference CPU path on the whole workload: "
-                          f"X {m_s} rows, full weights, {flops:.3e} flop per run, {sum(times):.1f} s in total"}
+                          f"X {M} rows, full weights, {flops:.3e} flop per run, {sum(times):.1f} s in total"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -372,9 +481,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--m", type=int, default=M, help="token rows per GPU (smaller values give profiler-sized cases)")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip configurations 3 and 5 (1-GPU runs)")
+    ap.add_argument("--m", type=int, default=M, help="token rows of the batch (smaller values give profiler-sized cases)")
     ap.add_argument("--inter", type=int, default=INTER, help="SwiGLU intermediate width")
     args = ap.parse_args()
     globals()["M"], globals()["INTER"] = args.m, args.inter

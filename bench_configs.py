@@ -1,10 +1,10 @@
 """Device-timed measurements of benchmark configurations 3, 4 and 5 (configuration 2 is `bench.py`).
 
-    python -m rtx_b200.bench_configs --config 3            # NVFP4 forward 16384 x 28672 x 8192
-    python -m rtx_b200.bench_configs --config 4            # MXFP8 backward dX + dW, 16384 x 4096 x 4096
-    python -m rtx_b200.bench_configs --config 5            # NVFP4 decode, packed weights, M in {1, 8, 16, 64}
-    python -m rtx_b200.bench_configs --config 6            # configuration 2's shapes with the step-scoped weight cache
-    python -m torch.distributed.run --nproc-per-node N ... -m rtx_b200.bench_configs --config 4
+    python bench_configs.py --config 3            # NVFP4 forward 16384 x 28672 x 8192
+    python bench_configs.py --config 4            # MXFP8 backward dX + dW, 16384 x 4096 x 4096
+    python bench_configs.py --config 5            # NVFP4 decode, packed weights, M in {1, 8, 16, 64}
+    python bench_configs.py --config 6            # configuration 2's shapes with the step-scoped weight cache
+    python -m torch.distributed.run --nproc-per-node N ... bench_configs.py --config 4
 
 One JSON line per measured case (rank 0).  Token rows are sharded over ranks (weak scaling: the
 configuration's M per GPU); configuration 4 all-reduces the FP32 dW with NCCL inside the timed
@@ -18,19 +18,24 @@ import argparse
 import json
 import os
 
+import sys
+
 import torch
 import torch.distributed as dist
 
-from . import _native as N
-from . import ops, parallel
-from .workloads import make_inputs
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from rtx_b200 import _native as N  # noqa: E402
+from rtx_b200 import ops, parallel  # noqa: E402
+from rtx_b200.workloads import make_inputs  # noqa: E402
 
 NOMINAL = {"fp8": 4500.0, "fp4": 9000.0, "hbm": 8000.0}
 
 
 def _peaks():
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    path = os.path.join(root, "MEASURED_PEAKS.json")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
@@ -165,18 +170,9 @@ def config4(args, rank, world, dev):
     ws = ops.Workspace(dev)
 
     def step():
-        if world == 1:
-            # one call for both products: dY is read once for its two quantizations; dW accumulates in FP32
-            # in TMEM and leaves the epilogue as BF16, the reference's dW dtype
-            return ops.mxfp8_linear_bwd(dy, x, w, ws)
-        # dW first so that its all-reduce overlaps the dX quantize + GEMM
-        _, dw = ops.mxfp8_linear_bwd(dy, x, None, ws, need_dx=False, dw_dtype=torch.float32)
-        handle = parallel.all_reduce_dw(dw, async_op=True) if world > 1 else None
-        with ops.sm_margin(parallel.OVERLAP_SM_MARGIN if handle is not None else 0):
-            dx, _ = ops.mxfp8_linear_bwd(dy, None, w, ws, need_dw=False)
-        if handle is not None:
-            handle.wait()
-        return dx, dw.to(torch.bfloat16)
+        # one rank: one call for both products (dY read once for its two quantizations, dW rounded to BF16 in
+        # the epilogue); more: FP32 dW all-reduced band by band beside the rest of the step
+        return parallel.data_parallel_linear_backward(dy, x, w)
 
     ms = _time(step, args.steps, args.warmup, world, dev)
     qc, sc = ops.mxfp8_quantize_transposed(dy)
@@ -190,8 +186,8 @@ def config4(args, rank, world, dev):
         "value": flops * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "ms_per_step": ms,
         "scaling": "weak", "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate", "data": "synthetic",
         "config": {"workload": "mxfp8_linear_bwd_m16384_n4096_k4096", "m_per_gpu": m,
-                   "collective": (f"NCCL all-reduce(sum) of FP32 dW (67 MB) beside dX, which leaves "
-                                  f"{parallel.OVERLAP_SM_MARGIN} SMs to it") if world > 1 else "none"},
+                   "collective": (f"NCCL all-reduce(sum) of FP32 dW (67 MB) in bands of rows behind the dW GEMM, "
+                                  f"{parallel.OVERLAP_SM_MARGIN} SMs left to it") if world > 1 else "none"},
         "pct_of_nominal_fp8_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / NOMINAL["fp8"],
         "gpu_launches_per_step": 5 if world == 1 else 7,
         "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, f32> (dW, K = 16384)", "bound": "tensor",
@@ -337,7 +333,7 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, pg_options=parallel.nccl_options())
     lines = {3: config3, 4: config4, 5: config5, 6: config6}[args.config](args, rank, world, dev)
     if rank == 0:
         for line in lines:

@@ -46,8 +46,6 @@ def build(force: bool = False, verbose: bool = False, out: str = OUT) -> str:
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
     cmd = [_nvcc(), *NVCC_FLAGS]
-    # schedule tunables (see gemm_blockscaled.cuh), e.g. RTXB_DEFINES="RTXB_PAIR_KS_MX=3"
-    cmd += [f"-D{d}" for d in os.environ.get("RTXB_DEFINES", "").split()]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", out, *[os.path.join(CSRC, s) for s in SOURCES]]

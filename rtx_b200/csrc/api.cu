@@ -7,6 +7,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "gemm_blockscaled.cuh"
 #include "gemm_skinny.cuh"
@@ -36,6 +37,16 @@ int fail_msg(int code, const char* msg) {
     if (e__ != cudaSuccess) return fail_cuda(e__, where);       \
   } while (0)
 
+}  // namespace
+
+namespace rtxb {
+// Records `msg` as this thread's error detail (what rtxb_last_cuda_error() returns) and hands `code`
+// back; for the library's other translation units.
+int set_last_error(int code, const char* msg) { return fail_msg(code, msg); }
+}  // namespace rtxb
+
+namespace {
+
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
@@ -57,24 +68,77 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// ---- tensor maps --------------------------------------------------------------------------------
+// A tensor map is a pure function of the base address, extents, strides and box, so encoded maps are
+// kept in a small per-thread table and re-used by later launches on the same buffers (a decode step
+// launches in microseconds; two to four driver encodes per launch were a visible part of that).
+struct MapKey {
+  const void* base;
+  uint64_t dim[3];
+  uint64_t stride[2];   // bytes, dimensions 1 and 2
+  uint32_t box[3];
+  uint32_t rank;        // 2 or 3
+  uint32_t words;       // 0: bytes with the 128-byte swizzle (payload); 1: 32-bit words, no swizzle (scale tiles)
+};
+
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+
+constexpr int kMapSlots = 64;
+thread_local MapSlot t_map_cache[kMapSlots];
+
+int encode_map(CUtensorMap* out, const MapKey& key, const char* what) {
+  uint64_t h = reinterpret_cast<uintptr_t>(key.base) >> 4;
+  h = h * 0x9E3779B97F4A7C15ull + key.dim[1] * 31 + key.dim[2] * 7 + key.box[1] * 131 + key.box[2] * 17 + key.rank +
+      key.words * 3 + key.stride[1];
+  MapSlot& slot = t_map_cache[(h >> 17) % kMapSlots];
+  if (slot.valid && memcmp(&slot.key, &key, sizeof(MapKey)) == 0) {
+    *out = slot.map;
+    return RTXB_OK;
+  }
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[3] = {key.dim[0], key.dim[1], key.dim[2]};
+  cuuint64_t gstride[2] = {key.stride[0], key.stride[1]};
+  cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(out, key.words ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, key.rank,
+                  const_cast<void*>(key.base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  key.words ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what,
+             static_cast<int>(r));
+    return RTXB_E_DRIVER;
+  }
+  slot.key = key;
+  slot.map = *out;
+  slot.valid = true;
+  return RTXB_OK;
+}
+
+MapKey blank_key(const void* base) {
+  MapKey k;
+  memset(&k, 0, sizeof(k));   // padding bytes too: keys are compared with memcmp
+  k.base = base;
+  return k;
+}
+
 // byte matrix [rows, row_bytes] (pitch row_bytes), boxes of 128 bytes x box_rows, 128-byte swizzle,
 // out-of-range elements read as zero
 int make_payload_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
   if (!aligned(base, 16) || row_bytes % 16 != 0) return fail_msg(RTXB_E_ALIGNMENT, "payload must be 16-byte aligned");
-  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
-  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_bytes)};
-  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
-    return RTXB_E_DRIVER;
-  }
-  return RTXB_OK;
+  MapKey k = blank_key(base);
+  k.rank = 2;
+  k.dim[0] = static_cast<uint64_t>(row_bytes);
+  k.dim[1] = static_cast<uint64_t>(rows);
+  k.stride[0] = static_cast<uint64_t>(row_bytes);
+  k.box[0] = 128u;
+  k.box[1] = static_cast<uint32_t>(box_rows);
+  return encode_map(map, k, "payload");
 }
 
 // the same byte matrix viewed as [row_bytes / 128][rows][128]: boxes of `box_k` consecutive 128-byte
@@ -82,61 +146,74 @@ int make_payload_map(CUtensorMap* map, const void* base, int64_t rows, int64_t r
 // (otherwise the last chunk of a row would run into the next row instead of reading zeros).
 int make_payload_map_ksteps(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows,
                             int box_k) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
   if (!aligned(base, 16) || row_bytes % 128 != 0) return fail_msg(RTXB_E_ALIGNMENT, "payload rows must be 128-byte multiples");
-  cuuint64_t gdim[3] = {128u, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(row_bytes / 128)};
-  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(row_bytes), 128u};
-  cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_k)};
-  cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(3d) failed with CUresult %d", static_cast<int>(r));
-    return RTXB_E_DRIVER;
-  }
-  return RTXB_OK;
+  MapKey k = blank_key(base);
+  k.rank = 3;
+  k.dim[0] = 128u;
+  k.dim[1] = static_cast<uint64_t>(rows);
+  k.dim[2] = static_cast<uint64_t>(row_bytes / 128);
+  k.stride[0] = static_cast<uint64_t>(row_bytes);
+  k.stride[1] = 128u;
+  k.box[0] = 128u;
+  k.box[1] = static_cast<uint32_t>(box_rows);
+  k.box[2] = static_cast<uint32_t>(box_k);
+  return encode_map(map, k, "payload K steps");
 }
 
 // scale tiles as a matrix of 512-byte rows (128 x uint32), boxes of `box_rows` consecutive tiles
 int make_scale_map(CUtensorMap* map, const void* base, int64_t total_tiles, int box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
-  cuuint64_t gdim[2] = {128u, static_cast<cuuint64_t>(total_tiles)};
-  cuuint64_t gstride[1] = {512u};
-  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(scales) failed with CUresult %d",
-             static_cast<int>(r));
-    return RTXB_E_DRIVER;
-  }
-  return RTXB_OK;
+  MapKey k = blank_key(base);
+  k.rank = 2;
+  k.words = 1;
+  k.dim[0] = 128u;
+  k.dim[1] = static_cast<uint64_t>(total_tiles);
+  k.stride[0] = 512u;
+  k.box[0] = 128u;
+  k.box[1] = static_cast<uint32_t>(box_rows);
+  return encode_map(map, k, "scales");
 }
 
 // scale tiles of B for the pair kernel: [2 halves][rows = 512-byte tiles][128 words], the second half
 // `delta_tiles` tiles after the first, so one box brings the tiles of both 128-row blocks behind a
 // 256-wide accumulator tile.  Rows are limited to those whose second half lies inside the buffer.
 int make_scale_map_halves(CUtensorMap* map, const void* base, int64_t total_tiles, int box_rows, int64_t delta_tiles) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail_msg(RTXB_E_DRIVER, "cuTensorMapEncodeTiled entry point not available");
-  cuuint64_t gdim[3] = {128u, static_cast<cuuint64_t>(total_tiles - delta_tiles), 2u};
-  cuuint64_t gstride[2] = {512u, static_cast<cuuint64_t>(delta_tiles) * 512u};
-  cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), 2u};
-  cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(scale halves) failed with CUresult %d",
-             static_cast<int>(r));
-    return RTXB_E_DRIVER;
+  MapKey k = blank_key(base);
+  k.rank = 3;
+  k.words = 1;
+  k.dim[0] = 128u;
+  k.dim[1] = static_cast<uint64_t>(total_tiles - delta_tiles);
+  k.dim[2] = 2u;
+  k.stride[0] = 512u;
+  k.stride[1] = static_cast<uint64_t>(delta_tiles) * 512u;
+  k.box[0] = 128u;
+  k.box[1] = static_cast<uint32_t>(box_rows);
+  k.box[2] = 2u;
+  return encode_map(map, k, "scale halves");
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of per launch
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Done { const void* kernel; int device; int bytes; };
+  static std::mutex mu;
+  static std::vector<Done> done;
+  thread_local Done last = {nullptr, -1, 0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (last.kernel == kernel && last.device == dev && last.bytes >= bytes) return cudaSuccess;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Done& d : done)
+      if (d.kernel == kernel && d.device == dev && d.bytes >= bytes) {
+        last = d;
+        return cudaSuccess;
+      }
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    done.push_back({kernel, dev, bytes});
+    last = done.back();
   }
-  return RTXB_OK;
+  return cudaSuccess;
 }
 
 // SMs the persistent kernels leave free (for a collective that runs beside them); process-wide
@@ -181,32 +258,20 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, size
 thread_local int t_gemm_schedule = 0;
 
 // Schedule choice: the CTA-pair kernel (256 x 256 pair tiles) unless the problem has a single
-// 128-row block of A, where half of every pair would idle.  RTXB_GEMM_PAIR=0/1 forces one.
+// 128-row block of A, where half of every pair would idle.
 bool use_pair_kernel(int m_tiles) {
   if (t_gemm_schedule == 1 || t_gemm_schedule == 3) return false;
   if (t_gemm_schedule == 2) return true;
-  static int forced = -2;
-  if (forced == -2) {
-    const char* v = getenv("RTXB_GEMM_PAIR");
-    forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
-  }
-  if (forced >= 0) return forced == 1;
   return m_tiles >= 2;
 }
 
 // M <= 128 and too few 256-wide tiles to occupy the SMs: the 128 x 64 skinny kernel.  With many
 // 256-wide tiles (N >= ~19k) the large-tile kernel already keeps more bytes in flight per SM and
-// streams faster.  RTXB_GEMM_SKINNY=0/1 forces the choice.
+// streams faster.
 bool use_skinny_kernel(int m_tiles, int64_t n_rows_b) {
-  static int forced = -2;
-  if (forced == -2) {
-    const char* v = getenv("RTXB_GEMM_SKINNY");
-    forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
-  }
   if (m_tiles != 1) return false;
   if (t_gemm_schedule == 3) return true;
   if (t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
-  if (forced >= 0) return forced == 1;
   return (n_rows_b + kBlockN - 1) / kBlockN < 74;
 }
 
@@ -272,10 +337,6 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
       for (int ks = 4; ks >= 2; ks >>= 1)
         if (S::slots_for(p.a_box_rows, ks) >= 4 && p.k_tiles >= ks) { p.ks = ks; break; }
     }
-    if (const char* v = getenv("RTXB_SKINNY_KS")) {
-      const int ks = atoi(v);
-      if (ks >= 1 && ks <= 8 && (ks == 1 || p.map3d) && S::slots_for(p.a_box_rows, ks) >= 2) p.ks = ks;
-    }
     p.slots = S::slots_for(p.a_box_rows, p.ks);
     if (p.map3d) {
       rc = make_payload_map_ksteps(&map_a, qa, m, row_bytes, p.a_box_rows, p.ks);
@@ -290,7 +351,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     }
     p.n_tiles = static_cast<int>((n_rows_b + kSkinnyN - 1) / kSkinnyN);
     auto sk = gemm_skinny_kernel<KIND, EPI == kEpiF32 ? kEpiF32 : kEpiBf16>;
-    cudaError_t se = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnySmemBudget);
+    cudaError_t se = ensure_dynamic_smem(reinterpret_cast<const void*>(sk), kSkinnySmemBudget);
     if (se != cudaSuccess) return fail_cuda(se, "cudaFuncSetAttribute(skinny gemm)");
     se = launch_dependent(sk, p.n_tiles < sm_count() ? p.n_tiles : sm_count(), kGemmThreads,
                           S::smem_bytes(p.a_box_rows, p.ks, p.slots), stream, overlap_previous, map_a, map_b, p);
@@ -321,13 +382,12 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
       rc = make_scale_map(&map_sfb, sb, b_blocks * sf_k_chunks, KS * P::kSfChunks);
     if (rc) return rc;
     auto pk = gemm_blockscaled_pair_kernel<KIND, EPI>;
-    cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmemBytes);
+    cudaError_t pe = ensure_dynamic_smem(reinterpret_cast<const void*>(pk), P::kSmemBytes);
     if (pe != cudaSuccess) return fail_cuda(pe, "cudaFuncSetAttribute(pair gemm)");
     {
       // A panel of a raster group: about 32 MB (group_m pairs x 256 rows x row_bytes) so that it stays in L2
       const int m_pairs = (p.m_tiles + 1) / 2;
       int64_t g = (32ll << 20) / (256 * row_bytes);
-      if (const char* v = getenv("RTXB_GEMM_GROUP_M")) g = atoi(v);
       p.group_m = static_cast<int>(g < 4 ? 4 : (g > m_pairs ? m_pairs : g));
     }
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles;
@@ -350,7 +410,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     if (rc) return rc;
   }
   auto kernel = gemm_blockscaled_kernel<KIND, EPI>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), T::kSmemBytes);
   if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(gemm)");
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
@@ -364,18 +424,12 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
 // 16.1 us for the three chained launches), K a multiple of 256 values whose quantized form (A tiles +
 // scale tiles for every K step) leaves room for at least three ring slots of weights, and few enough
 // 256-wide column tiles that the 64-wide streaming tiling is the right one.
-// RTXB_DECODE_FUSED=0/1 forces the choice where the shape allows it (up to kFusedMaxRows rows).
 bool decode_fused_eligible(const void* x, int64_t m, int64_t n, int64_t k) {
-  static int forced = -2;
-  if (forced == -2) {
-    const char* v = getenv("RTXB_DECODE_FUSED");
-    forced = (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
-  }
-  if (forced == 0 || t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
-  if (m > kFusedMaxRows || k % 256 != 0 || !aligned(x, 16)) return false;
+  if (t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
+  if (m > 4 || k % 256 != 0 || !aligned(x, 16)) return false;
   const int k_tiles = static_cast<int>(k / 256);
   if (k_tiles < 2 || fused_slots_for(k_tiles, 2) < 3) return false;
-  return forced == 1 || (m <= 4 && use_skinny_kernel(1, n));
+  return use_skinny_kernel(1, n);
 }
 
 int launch_decode_fused(const void* x, const void* qw, const void* sw, const float* w_scale, void* out, int64_t m,
@@ -408,8 +462,7 @@ int launch_decode_fused(const void* x, const void* qw, const void* sw, const flo
   fx.mode = scale_mode;
   fx.w_scale = w_scale;
   fx.x_scale_out = x_scale_out;
-  cudaError_t e = cudaFuncSetAttribute(gemm_decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSkinnySmemBudget);
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_decode_fused_kernel), kSkinnySmemBudget);
   if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(decode fused)");
   // quantizer warps: 4 (they are also the epilogue warps) for one or two rows, 12 above
   const int threads = m <= 2 ? kGemmThreads : kFusedMaxThreads;
@@ -558,10 +611,9 @@ int rtxb_mxfp8_quantize_transposed(const void* src, int64_t rows, int64_t k, int
   p.s_rows = nullptr;
   p.np = p.nb_rows = p.chunks_rows = 0;
   const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 127) / 128);
-  cudaError_t ae = cudaFuncSetAttribute(quant_mxfp8_transposed_kernel<false>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kQtSmemBytes);
+  cudaError_t ae = ensure_dynamic_smem(reinterpret_cast<const void*>(quant_mxfp8_transposed_kernel<false>), kQtSmemBytes);
   if (ae != cudaSuccess) return fail_cuda(ae, "cudaFuncSetAttribute(transposed quantizer)");
-  quant_mxfp8_transposed_kernel<false><<<quant_grid(tiles, RTXB_QT_OCC), kQuantThreads, kQtSmemBytes,
+  quant_mxfp8_transposed_kernel<false><<<quant_grid(tiles, kQtOccupancy), kQuantThreads, kQtSmemBytes,
                                          static_cast<cudaStream_t>(stream)>>>(p);
   RTXB_CHECK_LAUNCH("quant_mxfp8_transposed_kernel");
   return RTXB_OK;
@@ -596,10 +648,9 @@ int rtxb_mxfp8_quantize_dual(const void* src, int64_t m, int64_t n, int64_t ld, 
   p.nb_rows = p.np / 32;
   p.chunks_rows = (p.nb_rows + 3) / 4;
   const int64_t tiles = ((n + 127) / 128) * ((p.kp + 127) / 128);
-  cudaError_t ae = cudaFuncSetAttribute(quant_mxfp8_transposed_kernel<true>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kQtSmemBytes);
+  cudaError_t ae = ensure_dynamic_smem(reinterpret_cast<const void*>(quant_mxfp8_transposed_kernel<true>), kQtSmemBytes);
   if (ae != cudaSuccess) return fail_cuda(ae, "cudaFuncSetAttribute(dual quantizer)");
-  quant_mxfp8_transposed_kernel<true><<<quant_grid(tiles, RTXB_QT_OCC), kQuantThreads, kQtSmemBytes,
+  quant_mxfp8_transposed_kernel<true><<<quant_grid(tiles, kQtOccupancy), kQuantThreads, kQtSmemBytes,
                                         static_cast<cudaStream_t>(stream)>>>(p);
   RTXB_CHECK_LAUNCH("quant_mxfp8_transposed_kernel<dual>");
   return RTXB_OK;
@@ -764,8 +815,11 @@ int rtxb_mxfp8_linear_bwd(const void* dy, const void* x, const void* w, void* dx
   return RTXB_OK;
 }
 
-int rtxb_nvfp4_tensor_scale(const void* src, int64_t rows, int64_t k, int64_t ld, int mode, void* amax_scratch,
-                            float* scale_out, const float* other_scale, float* out_scale, void* stream) {
+namespace {
+// |max| over the tensor, then the outer-scale rule; kernel_form selects how the reference forms
+// amax / 2688 (see nvfp4_scale_from_amax_bits)
+int tensor_scale_impl(const void* src, int64_t rows, int64_t k, int64_t ld, int mode, void* amax_scratch,
+                      float* scale_out, const float* other_scale, float* out_scale, void* stream, bool kernel_form) {
   if (!src || !amax_scratch || !scale_out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
   if (rows <= 0 || k <= 0 || ld < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
   if (mode != RTXB_TENSOR_SCALE_EXACT && mode != RTXB_TENSOR_SCALE_POWER2)
@@ -781,9 +835,15 @@ int rtxb_nvfp4_tensor_scale(const void* src, int64_t rows, int64_t k, int64_t ld
                                         static_cast<uint32_t*>(amax_scratch));
   RTXB_CHECK_LAUNCH("amax_bf16_kernel");
   nvfp4_tensor_scale_kernel<<<1, 1, 0, s>>>(static_cast<const uint32_t*>(amax_scratch), mode, scale_out, other_scale,
-                                            out_scale);
+                                            out_scale, kernel_form);
   RTXB_CHECK_LAUNCH("nvfp4_tensor_scale_kernel");
   return RTXB_OK;
+}
+}  // namespace
+
+int rtxb_nvfp4_tensor_scale(const void* src, int64_t rows, int64_t k, int64_t ld, int mode, void* amax_scratch,
+                            float* scale_out, const float* other_scale, float* out_scale, void* stream) {
+  return tensor_scale_impl(src, rows, k, ld, mode, amax_scratch, scale_out, other_scale, out_scale, stream, false);
 }
 
 int rtxb_nvfp4_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales, int scale_layout,
@@ -934,7 +994,7 @@ int rtxb_nvfp4_region_scales(const void* src, int64_t rows, int64_t k, int64_t l
   if (region_rows == rows) {
     // one region = the tensor: the grid-wide reduction
     if (!amax_scratch) return fail_msg(RTXB_E_INVALID_ARGUMENT, "amax_scratch is needed for a single region");
-    return rtxb_nvfp4_tensor_scale(src, rows, k, ld, mode, amax_scratch, scales_out, nullptr, nullptr, stream);
+    return tensor_scale_impl(src, rows, k, ld, mode, amax_scratch, scales_out, nullptr, nullptr, stream, true);
   }
   const int64_t regions = rows / region_rows;
   if (region_rows * k * 2 >= 32768) {
@@ -1175,13 +1235,5 @@ int rtxb_nvfp4_linear_fwd_delayed(const void* x, const void* w, void* out, int64
     return rc;
   return rtxb_nvfp4_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, o_scale, stream, status);
 }
-
-#ifdef RTXB_TRACE
-// development builds only: copy the streaming kernel's timeline probe to the host
-int rtxb_debug_skinny_trace(unsigned long long* host_out) {
-  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_skinny_trace, sizeof(unsigned long long) * 160 * 16);
-  return e == cudaSuccess ? 0 : -1;
-}
-#endif
 
 }  // extern "C"

@@ -43,25 +43,10 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockKBytes = 128;  // one swizzle row: 128 E4M3 values or 256 E2M1 values
 constexpr int kStages = 4;        // ring slots (one K step each) of the single-CTA kernel
-// K steps handed over per full/empty barrier (compile-time tunables)
-#ifndef RTXB_SINGLE_KS_MX
-#define RTXB_SINGLE_KS_MX 2
-#endif
-#ifndef RTXB_SINGLE_KS_NV
-#define RTXB_SINGLE_KS_NV 1
-#endif
-#ifndef RTXB_PAIR_KS_MX
-#define RTXB_PAIR_KS_MX 2
-#endif
-#ifndef RTXB_PAIR_KS_NV
-#define RTXB_PAIR_KS_NV 1
-#endif
-#ifndef RTXB_PAIR_SLOTS_MX
-#define RTXB_PAIR_SLOTS_MX 6
-#endif
-#ifndef RTXB_PAIR_SLOTS_NV
-#define RTXB_PAIR_SLOTS_NV 5
-#endif
+// K steps handed over per full/empty barrier and ring slots of the pair kernel, per operand format
+constexpr int kSingleStepsMx = 2, kSingleStepsNv = 1;
+constexpr int kPairStepsMx = 2, kPairStepsNv = 1;
+constexpr int kPairSlotsMx = 6, kPairSlotsNv = 5;
 constexpr int kGemmThreads = 192;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
@@ -92,7 +77,7 @@ struct GemmTraits {
   static constexpr int kOffSfb = kOffSfa + kStages * kSfaBytes;
   static constexpr int kOffBars = kOffSfb + kStages * kSfbBytes;
   static constexpr int kSmemBytes = kOffBars + 1024 /*align slack*/ + 256 /*barriers*/;
-  static constexpr int kStepsPerBarrier = KIND == kKindMxfp8 ? RTXB_SINGLE_KS_MX : RTXB_SINGLE_KS_NV;
+  static constexpr int kStepsPerBarrier = KIND == kKindMxfp8 ? kSingleStepsMx : kSingleStepsNv;
   static constexpr uint32_t kIdesc =
       idesc_block_scaled(kBlockM, kBlockN, KIND == kKindMxfp8 ? 0u : 1u, KIND == kKindMxfp8 ? 1u : 0u);
 };
@@ -407,9 +392,14 @@ __device__ __forceinline__ void mma_issuer_loop(const GemmParams& p, uint8_t* sm
       }
       if (leader) {
 #pragma unroll
-        for (int sub = 0; sub < KS; ++sub, ++step) {
+        for (int sub = 0; sub < KS; ++sub) {
+          // A barrier group may reach past the end of K.  Those steps are loaded (zero payload) but
+          // never issued: the scale bytes beside them belong to the next row block or to an earlier
+          // use of the slot, and a NaN scale (E8M0 0xFF) against a zero payload would still give NaN.
+          if (kg * KS + sub >= p.k_tiles) break;
           const int slot = group * KS + sub;
           const int set = step & 1;
+          ++step;
           // SFB in the ring: per slot [half 0 | half 1] (single-CTA kernel), or per barrier group
           // [half 0 of its KS steps | half 1 of its KS steps] (pair kernel: one load brings a group's halves)
           const uint32_t ssfb0 = PAIR ? smem_base + OFF_SFB + group * KS * SFB_BYTES + sub * SFA_BYTES
@@ -464,11 +454,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     *abort_flag = 0;
     fence_barrier_init();
   }
-  // scale slots start as zeros: a K step past the end of K reuses whatever its slot holds, and
-  // that must never decode to NaN (its payload is zero, so any finite scale contributes nothing)
-  for (int i = threadIdx.x; i < (T::kOffBars - T::kOffSfa) / 4; i += kGemmThreads)
-    reinterpret_cast<uint32_t*>(smem + T::kOffSfa)[i] = 0u;
-  fence_proxy_async_smem();
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -611,8 +596,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 // ===========================================================================
 template <int KIND>
 struct PairTraits {
-  static constexpr int kStagesP = KIND == kKindMxfp8 ? RTXB_PAIR_SLOTS_MX : RTXB_PAIR_SLOTS_NV;   // ring slots
-  static constexpr int kStepsPerBarrierP = KIND == kKindMxfp8 ? RTXB_PAIR_KS_MX : RTXB_PAIR_KS_NV;
+  static constexpr int kStagesP = KIND == kKindMxfp8 ? kPairSlotsMx : kPairSlotsNv;   // ring slots
+  static constexpr int kStepsPerBarrierP = KIND == kKindMxfp8 ? kPairStepsMx : kPairStepsNv;
   static constexpr int kSfChunks = TmemPlan<KIND>::kSfChunks;
   static constexpr int kSfaBytes = 512 * kSfChunks;
   static constexpr int kSfbBytes = 2 * kSfaBytes;
@@ -718,7 +703,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
             const uint32_t full_addr = mapa_shared(smem_u32(&full_bar[group]), 0);
             if (rank == 0) mbar_expect_tx(&full_bar[group], 2 * KS * T::kTxBytesPerCta);
             const int slot0 = group * KS;
-            const int kt0 = kg * KS;   // past the end of K: zero payload (TMA fill), any finite scales
+            const int kt0 = kg * KS;   // steps past the end of K are loaded (zero fill) but never issued
             if (p.map3d) {
               tma_load_3d_pair(smem + slot0 * T::kABytes, &map_a, full_addr, 0, m_blk * 128, kt0);
               tma_load_3d_pair(smem + T::kOffB + slot0 * T::kBBytes, &map_b, full_addr, 0, b_mine * 128, kt0);

@@ -52,14 +52,6 @@ struct SkinnyTraits {
   }
 };
 
-// Timeline probe for development builds (-DRTXB_TRACE): per CTA, %globaltimer at a few points.
-#ifdef RTXB_TRACE
-__device__ unsigned long long g_skinny_trace[160 * 16];
-#define RTXB_TRACE_POINT(i) (g_skinny_trace[blockIdx.x * 16 + (i)] = global_timer_ns())
-#else
-#define RTXB_TRACE_POINT(i) ((void)0)
-#endif
-
 // Loads of one ring slot.  With a 3-D tensor map one instruction fetches all `ks` K steps of an
 // operand (issuing a TMA instruction costs the issuing thread on the order of 100 clocks, which at
 // four instructions per 8 KB K step is what bounded the streaming rate); payloads whose rows are not
@@ -149,7 +141,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int first_pass = total_groups < S ? total_groups : S;
   if (warp == 0) {
     if (lane == 0) {
-      RTXB_TRACE_POINT(0);
       prefetch_tensormap(&map_a);
       prefetch_tensormap(&map_b);
       for (int s = 0; s < S; ++s) {
@@ -167,12 +158,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (!p.overlap_previous) loader.activations(i, kg, &full_bar[i]);
         if (++kg == k_groups) { kg = 0; tile += gridDim.x; }
       }
-      RTXB_TRACE_POINT(2);
     }
     __syncwarp();
     if (p.overlap_previous) griddep_wait();
     if (lane == 0) {
-      RTXB_TRACE_POINT(3);
       if (p.overlap_previous) {
         int kg = 0;
         for (int i = 0; i < first_pass; ++i) {
@@ -199,7 +188,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) RTXB_TRACE_POINT(1);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -254,7 +242,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           break;
         }
         if (leader) {
-          if (step == 0) RTXB_TRACE_POINT(4);
           const int live = min(KS, p.k_tiles - kg * KS);
           for (int sub = 0; sub < live; ++sub, ++step) {
             const int set = step & 1;
@@ -281,7 +268,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
           }
           tc_commit(&empty_bar[slot]);
-          if (kg == k_groups - 1) RTXB_TRACE_POINT(6);
         }
         __syncwarp();
         if (++slot == S) { slot = 0; phase ^= 1; }
@@ -308,7 +294,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         break;
       }
       tc_fence_after_sync();
-      if (threadIdx.x == 64) RTXB_TRACE_POINT(7);
       uint32_t r0[32], r1[32];
       tmem_ld_32x32(tmem_base + lane_base + win * kSkinnyN, r0);
       tmem_ld_32x32(tmem_base + lane_base + win * kSkinnyN + 32, r1);
@@ -345,7 +330,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) RTXB_TRACE_POINT(8);
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, T::kTmemColsS);

@@ -15,7 +15,12 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <mutex>
+
+namespace rtxb {
+int set_last_error(int code, const char* msg);   // api.cu: text behind rtxb_last_cuda_error()
+}
 
 namespace {
 
@@ -28,19 +33,30 @@ constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 void* g_scratch_address[kMaxDevices] = {nullptr};
 
-thread_local char g_noalloc_error[192] = "";
-
 // First call on a device: resolve that device's address of the array, with the
 // device current.  Later calls on the same device reuse it.
 int scratch_for_current_device(void** out) {
+  char msg[192];
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return RTXB_E_CUDA;
+  if (e != cudaSuccess) {
+    snprintf(msg, sizeof(msg), "cudaGetDevice: %s", cudaGetErrorString(e));
+    return rtxb::set_last_error(RTXB_E_CUDA, msg);
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    snprintf(msg, sizeof(msg), "device index %d is outside the %d devices the no-allocation entry point tracks", dev,
+             kMaxDevices);
+    return rtxb::set_last_error(RTXB_E_UNSUPPORTED, msg);
+  }
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (g_scratch_address[dev] == nullptr) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (e != cudaSuccess || ptr == nullptr) return RTXB_E_CUDA;
+    if (e != cudaSuccess || ptr == nullptr) {
+      snprintf(msg, sizeof(msg), "cudaGetSymbolAddress(scratch array) on device %d: %s", dev,
+               e != cudaSuccess ? cudaGetErrorString(e) : "null address");
+      return rtxb::set_last_error(RTXB_E_CUDA, msg);
+    }
     g_scratch_address[dev] = ptr;
   }
   *out = g_scratch_address[dev];
@@ -51,11 +67,16 @@ int scratch_for_current_device(void** out) {
 
 extern "C" int rtxb_mxfp8_linear_fwd_noalloc(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m,
                                              int64_t n, int64_t k, int rounding, void* stream, int* status) {
-  if (!x_bf16 || !w_bf16 || !out_bf16) return RTXB_E_INVALID_ARGUMENT;
-  if (m <= 0 || n <= 0 || k <= 0) return RTXB_E_INVALID_ARGUMENT;
+  if (!x_bf16 || !w_bf16 || !out_bf16) return rtxb::set_last_error(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || n <= 0 || k <= 0) return rtxb::set_last_error(RTXB_E_INVALID_ARGUMENT, "m, n, k must be positive");
   // The operands of this shape must fit the fixed array; nothing is launched otherwise.
   const size_t need = rtxb_mxfp8_linear_workspace_bytes(m, n, k);
-  if (need > static_cast<size_t>(RTXB_NOALLOC_SCRATCH_BYTES)) return RTXB_E_SCRATCH_CAPACITY;
+  if (need > static_cast<size_t>(RTXB_NOALLOC_SCRATCH_BYTES)) {
+    char msg[192];
+    snprintf(msg, sizeof(msg), "this shape needs %zu bytes of quantized operands, the built-in array holds %d", need,
+             RTXB_NOALLOC_SCRATCH_BYTES);
+    return rtxb::set_last_error(RTXB_E_SCRATCH_CAPACITY, msg);
+  }
   void* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != RTXB_OK) return rc;

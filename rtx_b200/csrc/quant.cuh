@@ -255,9 +255,7 @@ __device__ __forceinline__ void quant_mxfp8_tile_rows(const uint16_t (*tile)[kQt
   }
 }
 
-#ifndef RTXB_QT_OCC
-#define RTXB_QT_OCC 3   // resident CTAs per SM the transposed quantizer is compiled for (registers, 70 KB of tiles)
-#endif
+constexpr int kQtOccupancy = 3;   // resident CTAs per SM the transposed quantizer is compiled for (registers, 70 KB of tiles)
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
   // copies 16 bytes, or writes 16 zero bytes when !valid (source size 0)
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src),
@@ -298,7 +296,7 @@ __device__ __forceinline__ void quant_mxfp8_t_fetch(const QuantMxTParams& p, uin
 }
 
 template <bool DUAL>
-__global__ void __launch_bounds__(kQuantThreads, RTXB_QT_OCC) quant_mxfp8_transposed_kernel(const QuantMxTParams p) {
+__global__ void __launch_bounds__(kQuantThreads, kQtOccupancy) quant_mxfp8_transposed_kernel(const QuantMxTParams p) {
   extern __shared__ __align__(16) uint8_t qt_smem[];
   uint16_t (*tiles[2])[kQtPitch] = {reinterpret_cast<uint16_t (*)[kQtPitch]>(qt_smem),
                                     reinterpret_cast<uint16_t (*)[kQtPitch]>(qt_smem + kQtTileBytes)};
@@ -378,27 +376,36 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const __nv_bfloat16* src
   if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(amax_bits, m);
 }
 
-// mode 0: exact amax/(448*6); mode 1: power of two 2^ceil(log2(max(amax/2688, 2^-126)));
-// 1.0 when amax == 0.  Optionally also publishes out_scale = scale * other_scale[0].
-__device__ __forceinline__ float nvfp4_scale_from_amax_bits(uint32_t amax_bits, int mode) {
+// Outer (per tensor / per region) decode scale from a |max| given as FP32 bits.
+// mode 0: exact amax / (448 * 6); mode 1: the power of two 2^ceil(log2(max(amax / 2688, 2^-126))).
+// 1.0 when amax is zero or NaN (the reference selects with `amax > 0`, rtx/fp4.py:343-365).
+// The reference forms the quotient in two ways and both are kept bit for bit:
+//   kernel_form = false  division, as its PyTorch functions do for the `current` policy and for
+//                        quantize_nvfp4 (rtx/fp4.py:346, 361);
+//   kernel_form = true   multiplication by the FP32 constant 1/2688, as its quantizer kernels do for
+//                        the delayed and row-region policies (rtx/kernels/nvfp4_quant.py:117-143).
+// The power of two comes from the exponent-bump rule of those kernels; on every BF16 magnitude it
+// equals the PyTorch exp2(ceil(log2(t))) form (checked exhaustively against the reference's function).
+__device__ __forceinline__ float nvfp4_scale_from_amax_bits(uint32_t amax_bits, int mode, bool kernel_form = false) {
   const float amax = __uint_as_float(amax_bits);
+  const float quotient = kernel_form ? __fmul_rn(amax, 1.0f / 2688.0f) : __fdiv_rn(amax, 2688.0f);
   float s;
   if (mode == 0) {
-    s = __fdiv_rn(amax, 2688.0f);
+    s = quotient;
   } else {
-    const float target = fmax_nan(__fdiv_rn(amax, 2688.0f), 1.17549435e-38f);
+    const float target = fmax_nan(quotient, 1.17549435e-38f);
     const uint32_t bits = __float_as_uint(target);
     uint32_t ebits = bits & 0x7F800000u;
     if (bits & 0x007FFFFFu) ebits += 1u << 23;
     s = __uint_as_float(ebits);
   }
-  if (amax == 0.0f) s = 1.0f;
+  if (!(amax > 0.0f)) s = 1.0f;
   return s;
 }
 
 __global__ void nvfp4_tensor_scale_kernel(const uint32_t* amax_bits, int mode, float* scale, const float* other_scale,
-                                          float* out_scale) {
-  const float s = nvfp4_scale_from_amax_bits(*amax_bits, mode);
+                                          float* out_scale, bool kernel_form) {
+  const float s = nvfp4_scale_from_amax_bits(*amax_bits, mode, kernel_form);
   *scale = s;
   if (out_scale) *out_scale = s * *other_scale;
 }
@@ -548,7 +555,7 @@ __global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_delayed_kernel(c
     }
   }
   __syncthreads();
-  const float st = nvfp4_scale_from_amax_bits(prior_bits, dp.mode);
+  const float st = nvfp4_scale_from_amax_bits(prior_bits, dp.mode, true);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     *dp.scale_out = st;
     if (dp.out_scale) *dp.out_scale = st * *dp.other_scale;
@@ -602,7 +609,7 @@ __global__ void __launch_bounds__(256) amax_regions_kernel(const __nv_bfloat16* 
       }
     }
     m = __reduce_max_sync(0xffffffffu, m);
-    if (lane == 0) region_scales[region] = nvfp4_scale_from_amax_bits(m, mode);
+    if (lane == 0) region_scales[region] = nvfp4_scale_from_amax_bits(m, mode, true);
   }
 }
 
@@ -646,7 +653,7 @@ __global__ void __launch_bounds__(256) amax_regions_cta_kernel(const __nv_bfloat
     if (threadIdx.x < 32) {
       uint32_t v = threadIdx.x < 8 ? warp_max[threadIdx.x] : 0u;
       v = __reduce_max_sync(0xffffffffu, v);
-      if (threadIdx.x == 0) region_scales[region] = nvfp4_scale_from_amax_bits(v, mode);
+      if (threadIdx.x == 0) region_scales[region] = nvfp4_scale_from_amax_bits(v, mode, true);
     }
     __syncthreads();
   }

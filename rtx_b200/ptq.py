@@ -18,8 +18,6 @@ import torch
 from torch import nn
 
 ModuleFilter = Callable[[nn.Module, str], bool]
-# (parent or None for the root, attribute name, module, fully qualified name)
-_Site = Tuple[Optional[nn.Module], Optional[str], nn.Module, str]
 
 
 @dataclass(frozen=True)
@@ -76,69 +74,72 @@ class NVFP4WeightOnlyConfig:
             raise ValueError("packed NVFP4 PTQ scaling must be current or block")
 
 
-def _is_linear(module: nn.Module, fqn: str) -> bool:
-    return isinstance(module, nn.Linear)
+class _Swap:
+    """One conversion, planned before anything is touched: which modules are replaced and under which
+    qualified names each of them hangs in the tree (a shared module hangs under several)."""
 
-
-def _sites(root: nn.Module) -> List[_Site]:
-    """Every place a module is referenced from, aliases of shared modules included; a shared
-    module's children are walked once."""
-    found: List[_Site] = [(None, None, root, "")]
-    seen = {id(root)}
-    stack = [(root, "")]
-    while stack:
-        parent, prefix = stack.pop()
-        for name, child in list(parent._modules.items()):
-            if child is None:
+    def __init__(self, model: nn.Module, wanted: Optional[ModuleFilter], device, needs_cuda: bool):
+        if not isinstance(model, nn.Module):
+            raise TypeError(f"model must be an nn.Module, got {type(model).__name__}")
+        if device is not None:
+            model.to(device=device)
+        self.model = model
+        # torch walks the tree for us; with remove_duplicate=False every alias path is reported
+        paths: Dict[int, List[str]] = {}
+        modules: Dict[int, nn.Module] = {}
+        for path, module in model.named_modules(remove_duplicate=False):
+            modules[id(module)] = module
+            paths.setdefault(id(module), []).append(path)
+        self.targets: List[Tuple[nn.Module, List[str]]] = []
+        for key, module in modules.items():
+            where = paths[key]
+            if wanted is None:
+                picked = [isinstance(module, nn.Linear)] * len(where)
+            else:
+                picked = [bool(wanted(module, path)) for path in where]
+            if True not in picked:
                 continue
-            fqn = f"{prefix}.{name}" if prefix else name
-            found.append((parent, name, child, fqn))
-            if id(child) not in seen:
-                seen.add(id(child))
-                stack.append((child, fqn))
-    return found
+            shown = [path if path else "<root>" for path in where]
+            if False in picked:
+                raise ValueError("filter selected only some aliases of one shared module: " + ", ".join(shown))
+            self._check(module, shown[0], needs_cuda)
+            self.targets.append((module, where))
 
-
-def _select(model: nn.Module, filter_fn: Optional[ModuleFilter], require_cuda: bool):
-    """[(linear, its sites)] for the layers the filter picks, validated."""
-    keep = filter_fn or _is_linear
-    by_module: Dict[int, List[_Site]] = {}
-    for site in _sites(model):
-        by_module.setdefault(id(site[2]), []).append(site)
-    chosen = []
-    for sites in by_module.values():
-        votes = [bool(keep(module, fqn)) for _, _, module, fqn in sites]
-        if not any(votes):
-            continue
-        names = [fqn or "<root>" for _, _, _, fqn in sites]
-        if not all(votes):
-            raise ValueError("filter selected only some aliases of one shared module: " + ", ".join(names))
-        module = sites[0][2]
+    @staticmethod
+    def _check(module: nn.Module, shown: str, needs_cuda: bool) -> None:
         if not isinstance(module, nn.Linear):
             raise TypeError(f"RTX conversion can only replace nn.Linear modules; filter selected {type(module).__name__}")
         if module.bias is not None:
-            raise NotImplementedError(f"RTX linear layers do not support bias; selected {names[0]} has bias")
-        if module.weight.dtype is not torch.bfloat16:
-            raise TypeError(f"RTX conversion requires a BF16 weight; {names[0]} has {module.weight.dtype}")
-        if require_cuda and module.weight.device.type != "cuda":
-            raise ValueError(f"RTX PTQ requires CUDA weights; {names[0]} is on {module.weight.device}")
-        chosen.append((module, sites))
-    return chosen
+            raise NotImplementedError(f"RTX linear layers do not support bias; selected {shown} has bias")
+        weight = module.weight
+        if weight.dtype is not torch.bfloat16:
+            raise TypeError(f"RTX conversion requires a BF16 weight; {shown} has {weight.dtype}")
+        if needs_cuda and not weight.is_cuda:
+            raise ValueError(f"RTX PTQ requires CUDA weights; {shown} is on {weight.device}")
+
+    def apply(self, make: Callable[[nn.Linear], nn.Module]) -> nn.Module:
+        """Build every replacement (any failure leaves the model untouched), then hang each one under
+        every path of the module it replaces.  Returns the root, which may itself have been replaced."""
+        replacements = [(make(module), where) for module, where in self.targets]
+        root = self.model
+        for new, where in replacements:
+            for path in where:
+                if not path:
+                    root = new
+                    continue
+                owner_path, _, leaf = path.rpartition(".")
+                self.model.get_submodule(owner_path)._modules[leaf] = new
+        return root
+
+    def cuda_devices(self):
+        return {module.weight.device for module, _ in self.targets if module.weight.is_cuda}
 
 
-def _install(model: nn.Module, chosen, built: Dict[int, nn.Module]) -> nn.Module:
-    for module, sites in chosen:
-        for parent, name, _, _ in sites:
-            if parent is not None:
-                parent._modules[name] = built[id(module)]
-    return built.get(id(model), model)
-
-
-def _prepare(model: nn.Module, device) -> None:
-    if not isinstance(model, nn.Module):
-        raise TypeError(f"model must be an nn.Module, got {type(model).__name__}")
-    if device is not None:
-        model.to(device=device)
+def _adopt(new: nn.Module, old: nn.Linear) -> nn.Module:
+    """Training swap: the replacement takes over the very `Parameter` object and the mode flag."""
+    new.weight = old.weight
+    new.train(old.training)
+    return new
 
 
 def convert_to_mxfp8_training(model: nn.Module, *, module_filter_fn: Optional[ModuleFilter] = None,
@@ -147,20 +148,16 @@ def convert_to_mxfp8_training(model: nn.Module, *, module_filter_fn: Optional[Mo
     optimizer references, weight sharing, state-dict keys and `requires_grad` carry over."""
     from .fp8 import MXFP8Linear
 
-    _prepare(model, device)
-    chosen = _select(model, module_filter_fn, require_cuda=False)
-    policy = config or MXFP8TrainingConfig()
-    built: Dict[int, nn.Module] = {}
-    for module, _ in chosen:
-        new = MXFP8Linear(module.in_features, module.out_features, bias=False, device=module.weight.device,
-                          dtype=torch.bfloat16, forward_config=policy.forward_config,
-                          dynamic_config=policy.dynamic_config, backward_config=policy.backward_config,
-                          backend=policy.backend, autotune=policy.autotune, tuning_policy=policy.tuning_policy,
-                          autotune_cache_dir=policy.autotune_cache_dir)
-        new.weight = module.weight
-        new.train(module.training)
-        built[id(module)] = new
-    return _install(model, chosen, built)
+    policy = config if config is not None else MXFP8TrainingConfig()
+    options = dict(forward_config=policy.forward_config, dynamic_config=policy.dynamic_config,
+                   backward_config=policy.backward_config, backend=policy.backend, autotune=policy.autotune,
+                   tuning_policy=policy.tuning_policy, autotune_cache_dir=policy.autotune_cache_dir)
+
+    def make(old: nn.Linear) -> nn.Module:
+        return _adopt(MXFP8Linear(old.in_features, old.out_features, bias=False, device=old.weight.device,
+                                  dtype=torch.bfloat16, **options), old)
+
+    return _Swap(model, module_filter_fn, device, needs_cuda=False).apply(make)
 
 
 def convert_to_nvfp4_training(model: nn.Module, *, module_filter_fn: Optional[ModuleFilter] = None,
@@ -168,64 +165,55 @@ def convert_to_nvfp4_training(model: nn.Module, *, module_filter_fn: Optional[Mo
     """BF16 linears -> `NVFP4Linear` (NVFP4 forward, MXFP8 backward), parameters kept as above."""
     from .fp4 import NVFP4Linear
 
-    _prepare(model, device)
-    chosen = _select(model, module_filter_fn, require_cuda=False)
-    policy = config or NVFP4TrainingConfig()
-    built: Dict[int, nn.Module] = {}
-    for module, _ in chosen:
-        new = NVFP4Linear(module.in_features, module.out_features, bias=False, device=module.weight.device,
-                          dtype=torch.bfloat16, scale_config=policy.scale_config,
-                          backward_config=policy.backward_config, scaling=policy.scaling,
-                          scale_region_rows=policy.scale_region_rows,
-                          x_scale_region_rows=policy.x_scale_region_rows,
-                          weight_scale_region_rows=policy.weight_scale_region_rows, backend=policy.backend,
-                          autotune=policy.autotune, tuning_policy=policy.tuning_policy,
-                          autotune_cache_dir=policy.autotune_cache_dir, dynamic_config=policy.dynamic_config)
-        new.weight = module.weight
-        new.train(module.training)
-        built[id(module)] = new
-    return _install(model, chosen, built)
+    policy = config if config is not None else NVFP4TrainingConfig()
+    options = dict(scale_config=policy.scale_config, backward_config=policy.backward_config, scaling=policy.scaling,
+                   scale_region_rows=policy.scale_region_rows, x_scale_region_rows=policy.x_scale_region_rows,
+                   weight_scale_region_rows=policy.weight_scale_region_rows, backend=policy.backend,
+                   autotune=policy.autotune, tuning_policy=policy.tuning_policy,
+                   autotune_cache_dir=policy.autotune_cache_dir, dynamic_config=policy.dynamic_config)
+
+    def make(old: nn.Linear) -> nn.Module:
+        return _adopt(NVFP4Linear(old.in_features, old.out_features, bias=False, device=old.weight.device,
+                                  dtype=torch.bfloat16, **options), old)
+
+    return _Swap(model, module_filter_fn, device, needs_cuda=False).apply(make)
 
 
 def quantize_(model: nn.Module, config, filter_fn: Optional[ModuleFilter] = None, device=None) -> nn.Module:
     """Post-training quantization: pack the weights of the selected no-bias BF16 linears (which must be on a
     CUDA device) and replace the layers by inference-only packed modules.  Children are replaced in place;
     the (possibly replaced) root is returned."""
-    _prepare(model, device)
-    if not isinstance(config, (MXFP8WeightOnlyConfig, NVFP4WeightOnlyConfig)):
-        raise TypeError("rtx.quantize_ requires MXFP8WeightOnlyConfig or NVFP4WeightOnlyConfig; "
-                        f"got {type(config).__name__}")
-    chosen = _select(model, filter_fn, require_cuda=True)
-    built: Dict[int, nn.Module] = {}
     if isinstance(config, MXFP8WeightOnlyConfig):
         from .fp8 import MXFP8Linear, quantize_mxfp8
 
-        for module, _ in chosen:
-            packed = quantize_mxfp8(module.weight.detach())
-            built[id(module)] = MXFP8Linear(module.in_features, module.out_features, bias=False,
-                                            device=module.weight.device, dtype=torch.bfloat16,
-                                            dynamic_config=config.dynamic_config, autotune=config.autotune,
-                                            tuning_policy=config.tuning_policy,
-                                            autotune_cache_dir=config.autotune_cache_dir, packed_weight=packed)
-    else:
+        def make(old: nn.Linear) -> nn.Module:
+            return MXFP8Linear(old.in_features, old.out_features, bias=False, device=old.weight.device,
+                               dtype=torch.bfloat16, dynamic_config=config.dynamic_config, autotune=config.autotune,
+                               tuning_policy=config.tuning_policy, autotune_cache_dir=config.autotune_cache_dir,
+                               packed_weight=quantize_mxfp8(old.weight.detach()))
+    elif isinstance(config, NVFP4WeightOnlyConfig):
         from .fp4 import NVFP4Linear, quantize_nvfp4
 
-        for module, _ in chosen:
-            scale = (torch.ones((), dtype=torch.float32, device=module.weight.device)
-                     if config.scaling == "block" else None)
-            packed = quantize_nvfp4(module.weight.detach(), tensor_scale=scale, config=config.quant_config)
-            built[id(module)] = NVFP4Linear(module.in_features, module.out_features, bias=False,
-                                            device=module.weight.device, dtype=torch.bfloat16,
-                                            scaling=config.scaling, autotune=config.autotune,
-                                            tuning_policy=config.tuning_policy,
-                                            autotune_cache_dir=config.autotune_cache_dir,
-                                            weight_prequant_config=config.weight_prequant_config,
-                                            fully_prequant_config=config.fully_prequant_config,
-                                            packed_weight=packed)
-    # the packing launches are asynchronous: finish them before the BF16 masters can be freed
-    for dev in {m.weight.device for m, _ in chosen if m.weight.device.type == "cuda"}:
+        def make(old: nn.Linear) -> nn.Module:
+            # the block policy has no outer scale: its tensor scale is exactly one
+            unit = torch.ones((), dtype=torch.float32, device=old.weight.device) if config.scaling == "block" else None
+            packed = quantize_nvfp4(old.weight.detach(), tensor_scale=unit, config=config.quant_config)
+            return NVFP4Linear(old.in_features, old.out_features, bias=False, device=old.weight.device,
+                               dtype=torch.bfloat16, scaling=config.scaling, autotune=config.autotune,
+                               tuning_policy=config.tuning_policy, autotune_cache_dir=config.autotune_cache_dir,
+                               weight_prequant_config=config.weight_prequant_config,
+                               fully_prequant_config=config.fully_prequant_config, packed_weight=packed)
+    else:
+        if not isinstance(model, nn.Module):
+            raise TypeError(f"model must be an nn.Module, got {type(model).__name__}")
+        raise TypeError("rtx.quantize_ requires MXFP8WeightOnlyConfig or NVFP4WeightOnlyConfig; "
+                        f"got {type(config).__name__}")
+    swap = _Swap(model, filter_fn, device, needs_cuda=True)
+    root = swap.apply(make)
+    # packing was only enqueued: let it finish before the caller drops the BF16 masters
+    for dev in swap.cuda_devices():
         torch.cuda.current_stream(dev).synchronize()
-    return _install(model, chosen, built)
+    return root
 
 
 __all__ = ["MXFP8TrainingConfig", "MXFP8WeightOnlyConfig", "ModuleFilter", "NVFP4TrainingConfig",

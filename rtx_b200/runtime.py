@@ -5,7 +5,6 @@ environment, and cache release."""
 from __future__ import annotations
 
 import os
-from collections import OrderedDict
 from collections.abc import MutableMapping
 from importlib import import_module
 from threading import RLock
@@ -37,95 +36,122 @@ def validate_runtime_environment(*, require_device: bool = False) -> dict[str, o
 
 
 class BoundedCache(MutableMapping):
-    """Small thread-safe LRU for launchers that retain GPU workspaces.  A size of
-    zero keeps nothing (the value stays alive for the caller's invocation only)."""
+    """LRU table for the launch objects that own GPU workspaces (same name, mapping protocol and
+    `stats()` keys as the reference's runner cache, rtx/runtime.py:134-206).
+
+    Built on the insertion order of a plain dict: the first key is always the least recently used,
+    a lookup re-inserts its key at the end.  `max_entries == 0` stores nothing, so a value lives only
+    as long as the caller's own reference.  Counters: `hits` / `misses` count `cache[key]` lookups,
+    `evictions` counts values dropped for space (a value refused by a zero-sized cache counts)."""
 
     def __init__(self, max_entries: int) -> None:
-        if max_entries < 0:
+        capacity = int(max_entries)
+        if capacity < 0:
             raise ValueError("cache size cannot be negative")
-        self.max_entries = int(max_entries)
-        self._values: OrderedDict = OrderedDict()
-        self._lock = RLock()
-        self.hits = self.misses = self.evictions = 0
+        self.max_entries = capacity
+        self.hits = 0
+        self.misses = 0
+        self.evictions = 0
+        self._table: dict = {}
+        self._guard = RLock()
+
+    def _touch(self, key):
+        """Value of `key`, made the most recent entry; KeyError if absent.  Caller holds the lock."""
+        value = self._table.pop(key)
+        self._table[key] = value
+        return value
 
     def __getitem__(self, key):
-        with self._lock:
-            try:
-                value = self._values.pop(key)
-            except KeyError:
-                self.misses += 1
-                raise
-            self._values[key] = value
-            self.hits += 1
-            return value
+        with self._guard:
+            if key in self._table:
+                self.hits += 1
+                return self._touch(key)
+            self.misses += 1
+        raise KeyError(key)
+
+    def __contains__(self, key) -> bool:       # membership tests do not count as lookups
+        with self._guard:
+            return key in self._table
 
     def get(self, key, default=None):
-        try:
-            return self[key]
-        except KeyError:
+        with self._guard:
+            if key in self._table:
+                self.hits += 1
+                return self._touch(key)
+            self.misses += 1
             return default
 
     def __setitem__(self, key, value) -> None:
-        with self._lock:
-            self._values.pop(key, None)
+        with self._guard:
             if self.max_entries == 0:
                 self.evictions += 1
                 return
-            self._values[key] = value
-            while len(self._values) > self.max_entries:
-                self._values.popitem(last=False)
+            self._table.pop(key, None)
+            self._table[key] = value
+            overflow = len(self._table) - self.max_entries
+            for oldest in list(self._table)[:max(overflow, 0)]:
+                del self._table[oldest]
                 self.evictions += 1
 
     def __delitem__(self, key) -> None:
-        with self._lock:
-            del self._values[key]
+        with self._guard:
+            del self._table[key]
 
     def __iter__(self):
-        with self._lock:
-            return iter(tuple(self._values))
+        with self._guard:
+            snapshot = list(self._table)
+        return iter(snapshot)
 
     def __len__(self) -> int:
-        with self._lock:
-            return len(self._values)
+        with self._guard:
+            return len(self._table)
 
     def clear(self) -> None:
-        with self._lock:
-            self._values.clear()
+        with self._guard:
+            self._table = {}
 
     def stats(self) -> dict[str, int]:
-        with self._lock:
-            return {"entries": len(self._values), "max_entries": self.max_entries, "hits": self.hits,
-                    "misses": self.misses, "evictions": self.evictions}
+        with self._guard:
+            return dict(entries=len(self._table), max_entries=self.max_entries, hits=self.hits,
+                        misses=self.misses, evictions=self.evictions)
 
 
 def runner_cache_limit(kind: str, default: int = 8, *, namespace: str = "MXFP8") -> int:
-    """RTX_<NAMESPACE>_<KIND>_CACHE_ENTRIES, else RTX_<NAMESPACE>_RUNNER_CACHE_ENTRIES, else `default`."""
-    specific = f"RTX_{namespace}_{kind.upper()}_CACHE_ENTRIES"
-    raw = os.getenv(specific, os.getenv(f"RTX_{namespace}_RUNNER_CACHE_ENTRIES", str(default)))
-    try:
-        value = int(raw)
-    except ValueError as exc:
-        raise ValueError(f"{specific} must be an integer, got {raw!r}") from exc
-    if value < 0:
-        raise ValueError(f"{specific} cannot be negative")
-    return value
+    """Entries a frontend's cache may hold: the environment's RTX_<NAMESPACE>_<KIND>_CACHE_ENTRIES if
+    set, else RTX_<NAMESPACE>_RUNNER_CACHE_ENTRIES, else `default` (the reference's variable names,
+    rtx/runtime.py:209-225).  Non-integers and negative values are refused."""
+    names = (f"RTX_{namespace}_{kind.upper()}_CACHE_ENTRIES", f"RTX_{namespace}_RUNNER_CACHE_ENTRIES")
+    for name in names:
+        text = os.environ.get(name)
+        if text is None:
+            continue
+        try:
+            limit = int(text)
+        except ValueError:
+            raise ValueError(f"{name} must be an integer, got {text!r}") from None
+        if limit < 0:
+            raise ValueError(f"{name} cannot be negative")
+        return limit
+    return default
+
+
+_CACHING_FRONTENDS = ("fp8", "fp8_bwd", "fp4")
 
 
 def clear_runtime_caches(*, synchronize: bool = True, device=None) -> dict[str, object]:
-    """Release the workspaces the frontends cache; launches are asynchronous, so the
-    default synchronises first."""
-    if synchronize:
-        import torch
+    """Drop every workspace the frontends hold (rtx/runtime.py:250-269).  Kernels may still be reading
+    those buffers, so by default the device is synchronised first.  Returns what each frontend
+    reported releasing."""
+    import torch
 
-        if torch.cuda.is_available():
-            torch.cuda.synchronize(device)
-    released: dict[str, object] = {}
-    for name in ("fp8", "fp8_bwd", "fp4"):
-        module = import_module(f".{name}", __package__)
-        clear = getattr(module, "_clear_runtime_caches", None)
-        if clear is not None:
-            released[name] = clear()
-    return released
+    if synchronize and torch.cuda.is_available():
+        torch.cuda.synchronize(device)
+    report: dict[str, object] = {}
+    for name in _CACHING_FRONTENDS:
+        hook = getattr(import_module(f"{__package__}.{name}"), "_clear_runtime_caches", None)
+        if callable(hook):
+            report[name] = hook()
+    return report
 
 
 __all__ = ["BoundedCache", "clear_runtime_caches", "runner_cache_limit", "validate_runtime_environment"]

@@ -16,8 +16,16 @@ Outputs: mxfp8_golden.npz (small arrays: inputs as BF16 bit patterns, payload
 codes, scale codes, BF16 output bits) and mxfp8_golden.json (SHA-256 digests of
 larger cases whose inputs are regenerated from the recorded seeds).
 
-The reference holds no NVFP4 golden bytes and pins NVFP4 only against TorchAO
-(not installed), so there is no NVFP4 fixture.
+NVFP4: the reference holds no golden payload bytes and pins payloads only against
+TorchAO (not installed), so there is no NVFP4 payload fixture.  Its OUTER scale
+is pure PyTorch, though: `_current_tensor_scale` / `_outer_tensor_scale`
+(rtx/fp4.py:343-365) are exec'd from the file's text and evaluated on every
+non-negative BF16 magnitude (zero, subnormals, infinity) and NaN, for both modes
+-> nvfp4_outer_scale.npz.  The same sweep records where the integer exponent
+rule of the reference's kernels (rtx/kernels/nvfp4_quant.py:117-143) differs
+from the PyTorch `exp2(ceil(log2(t)))` form: on BF16 magnitudes (count stored in
+nvfp4_outer_scale.json, expected 0) and on FP32 probes one ulp either side of
+2688 * 2^e (listed there input by input).
 """
 from __future__ import annotations
 
@@ -50,6 +58,62 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 def digest(t: torch.Tensor) -> str:
     return hashlib.sha256(bits(t).tobytes()).hexdigest()
+
+
+def integer_power2_rule(amax: np.ndarray) -> np.ndarray:
+    """The exponent-bump rule of rtx/kernels/nvfp4_quant.py:117-143 on FP32 amax values, with the
+    quotient formed by division as rtx/fp4.py:361 does (bit patterns of the scale)."""
+    with np.errstate(invalid="ignore", over="ignore"):
+        t = np.maximum((amax / np.float32(2688.0)).astype(np.float32), np.float32(2.0 ** -126))
+    b = t.view(np.uint32)
+    e = b & np.uint32(0x7F800000)
+    e = np.where((b & np.uint32(0x007FFFFF)) != 0, e + np.uint32(1 << 23), e).astype(np.uint32)
+    return np.where(amax > 0, e, np.float32(1.0).view(np.uint32)).astype(np.uint32)
+
+
+def nvfp4_outer_scale_fixture() -> None:
+    fp4 = _exec_defs(os.path.join(REF, "rtx/fp4.py"), "def _current_tensor_scale", "def _delayed_amax_state")
+    outer = fp4["_outer_tensor_scale"]
+
+    def run(values: np.ndarray, mode: str) -> np.ndarray:
+        out = np.empty(len(values), dtype=np.uint32)
+        for i, v in enumerate(values):
+            out[i] = outer(torch.from_numpy(np.array([[v]], dtype=np.float32)), mode).view(torch.int32).item() & 0xFFFFFFFF
+        return out
+
+    # every non-negative BF16 bit pattern up to +inf, then one NaN
+    bf16_bits = np.concatenate([np.arange(0, 0x7F81, dtype=np.uint32), np.array([0x7FC0], dtype=np.uint32)])
+    amax = (bf16_bits << 16).astype(np.uint32).view(np.float32)
+    exact = run(amax, "exact")
+    power2 = run(amax, "power2")
+    finite = np.isfinite(amax)
+    rule = integer_power2_rule(amax)
+    bf16_disagree = [int(b) for b in bf16_bits[finite][rule[finite] != power2[finite]]]
+
+    # FP32 probes that no BF16 tensor produces: one ulp either side of 2688 * 2^e (quotient next to a power of two)
+    probes = []
+    for e in range(-120, 110, 1):
+        c = np.float32(2688.0 * 2.0 ** e) if -149 <= e + 11 <= 127 else None
+        if c is None or not np.isfinite(c) or c == 0:
+            continue
+        probes += [np.nextafter(c, np.float32(0)), c, np.nextafter(c, np.float32(np.inf))]
+    probes = np.array(probes, dtype=np.float32)
+    probe_ref = run(probes, "power2")
+    probe_rule = integer_power2_rule(probes)
+    listed = [{"amax_bits": int(a.view(np.uint32)), "amax": float(a), "reference_scale_bits": int(r),
+               "integer_rule_scale_bits": int(g)}
+              for a, r, g in zip(probes, probe_ref, probe_rule) if r != g]
+    np.savez_compressed(os.path.join(HERE, "nvfp4_outer_scale.npz"), bf16_bits=bf16_bits.astype(np.uint16),
+                        exact_scale_bits=exact, power2_scale_bits=power2, fp32_probe_bits=probes.view(np.uint32),
+                        fp32_probe_power2_scale_bits=probe_ref)
+    with open(os.path.join(HERE, "nvfp4_outer_scale.json"), "w") as f:
+        json.dump({"source": "rtx/fp4.py:343-365 exec'd on CPU (torch %s)" % torch.__version__,
+                   "bf16_magnitudes": int(len(bf16_bits)),
+                   "bf16_inputs_where_integer_rule_differs": bf16_disagree,
+                   "fp32_probes": int(len(probes)),
+                   "fp32_probes_where_integer_rule_differs": listed}, f, indent=1)
+    print("nvfp4 outer scale:", len(bf16_bits), "BF16 magnitudes,", len(bf16_disagree), "disagree;",
+          len(probes), "FP32 probes,", len(listed), "disagree")
 
 
 def main() -> None:
@@ -125,6 +189,8 @@ def main() -> None:
     manifest["config1"] = {"seed": 0, "m": 256, "n": 1024, "k": 1024, "sha256_y": digest(y),
                            "draw": "g=Generator().manual_seed(0); x=randn(256,1024,generator=g).bfloat16(); w=(randn(1024,1024,generator=g)/32).bfloat16()"}
     arrays["config1_y_corner"] = bits(y[:16, :16].contiguous())
+
+    nvfp4_outer_scale_fixture()
 
     np.savez_compressed(os.path.join(HERE, "mxfp8_golden.npz"), **arrays)
     with open(os.path.join(HERE, "mxfp8_golden.json"), "w") as f:

@@ -28,14 +28,15 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    try:
-        from rtx_b200 import ops, parallel
+    from rtx_b200 import ops, parallel
 
-        inp = O.make_inputs(4, m=512, n=256, k=384)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, pg_options=parallel.nccl_options())
+    try:
+        inp = O.make_inputs(4, m=512, n=1024, k=384)
         x, w, dy = inp["x"], inp["w"], inp["dy"]
         xs = parallel.shard_rows(x, rank, world).to(dev)
         gs = parallel.shard_rows(dy, rank, world).to(dev)
+        parallel.DW_BAND_ROWS = 256          # four bands of dW, four all-reduces
         dx, dw = parallel.data_parallel_linear_backward(gs, xs, w.to(dev))
         torch.cuda.synchronize()
         ops.check_device_status(dev)
@@ -51,7 +52,7 @@ def test_dw_all_reduce_matches_single_gpu_two_ranks(tmp_path):
     world = 2
     mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True,
                        start_method="spawn")
-    inp = O.make_inputs(4, m=512, n=256, k=384)
+    inp = O.make_inputs(4, m=512, n=1024, k=384)    # dW [1024, 384]: several bands, each with its own all-reduce
     x, w, dy = inp["x"], inp["w"], inp["dy"]
     want_dx, want_dw = O.mxfp8_backward(x, w, dy)
     parts = [torch.load(os.path.join(str(tmp_path), f"rank{r}.pt")) for r in range(world)]

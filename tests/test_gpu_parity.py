@@ -216,6 +216,44 @@ def test_mxfp8_prequantized_gemm_f32_and_repeatability(gpu):
         assert torch.equal(got, first)
 
 
+@pytest.mark.parametrize("schedule", ["pair", "single"])
+@pytest.mark.parametrize("operand", ["a", "b"])
+def test_odd_k_tiles_with_nan_in_the_next_row_block(gpu, schedule, operand):
+    """K = 384 is three 128-byte K steps: kernels that hand over two K steps per barrier load a
+    fourth step past the end of K.  Its scale bytes are those of the NEXT 128-row block; a NaN
+    there (E8M0 0xFF) must not reach this block's outputs.  The reference keeps unrelated rows
+    and columns finite, and so must the product: everything outside the poisoned row / column
+    is bit-equal to the result without the NaN."""
+    ops, N, dev, _ = gpu
+    m, n, k = 384, 512, 384
+    torch.manual_seed(77)
+    x, w = torch.randn(m, k).bfloat16(), torch.randn(n, k).bfloat16()
+    qa0, sa0 = ops.mxfp8_quantize(x.to(dev))
+    qb0, sb0 = ops.mxfp8_quantize(w.to(dev))
+    want_clean = O.mxfp8_linear(x, w)
+    bad_row = 128 + 5          # first K block of a row in row block 1
+    if operand == "a":
+        x[bad_row, 0] = float("nan")
+    else:
+        w[bad_row, 0] = float("nan")
+    qa, sa = ops.mxfp8_quantize(x.to(dev))
+    qb, sb = ops.mxfp8_quantize(w.to(dev))
+    with ops.gemm_schedule(schedule):
+        clean = ops.mxfp8_gemm(qa0, sa0, qb0, sb0, m, n, k)
+        got = ops.mxfp8_gemm(qa, sa, qb, sb, m, n, k)
+    _ok(ops, dev)
+    clean, got = clean.cpu(), got.cpu()
+    _assert_output(clean, want_clean)
+    keep = torch.ones(m if operand == "a" else n, dtype=torch.bool)
+    keep[bad_row] = False
+    if operand == "a":
+        assert torch.isnan(got[bad_row].float()).all()
+        assert torch.equal(got[keep].view(torch.int16), clean[keep].view(torch.int16))
+    else:
+        assert torch.isnan(got[:, bad_row].float()).all()
+        assert torch.equal(got[:, keep].view(torch.int16), clean[:, keep].view(torch.int16))
+
+
 @pytest.mark.parametrize("dims", [(128, 128, 128, 128), (256, 512, 384, 512), (300, 256, 256, 200), (64, 96, 128, 80)])
 def test_mxfp8_glu_mlp(gpu, dims):
     ops, N, dev, ws = gpu

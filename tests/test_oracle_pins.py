@@ -203,3 +203,68 @@ def test_nvfp4_row_region_oracle_is_consistent():
     err_region = (O.nvfp4_linear_regions(x, w, 5, 4).float() - ref).norm()
     err_tensor = (O.nvfp4_linear(x, w).float() - ref).norm()
     assert err_region <= err_tensor
+
+
+# ----------------------------------------------------------------------------- NVFP4 outer scale
+
+def _outer_scale_fixture():
+    import json
+    import os
+
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    arrays = np.load(os.path.join(here, "nvfp4_outer_scale.npz"))
+    with open(os.path.join(here, "nvfp4_outer_scale.json")) as f:
+        return arrays, json.load(f)
+
+
+@pytest.mark.parametrize("mode", ["exact", "power2"])
+def test_nvfp4_outer_scale_matches_reference_on_every_bf16_magnitude(mode):
+    """rtx/fp4.py:343-365 executed on every non-negative BF16 bit pattern (zero, subnormals, +inf)
+    and NaN; the oracle's rule (division form) must give the same FP32 bits on all of them."""
+    arrays, meta = _outer_scale_fixture()
+    assert meta["bf16_inputs_where_integer_rule_differs"] == []
+    bf16_bits = arrays["bf16_bits"].astype(np.int64)
+    amax = torch.from_numpy((bf16_bits << 16).astype(np.uint32).view(np.float32).copy())
+    want = arrays[f"{mode}_scale_bits"]
+    assert len(want) == 0x7F81 + 1
+    got = np.array([O.nvfp4_scale_rule(a, mode).view(torch.int32).item() & 0xFFFFFFFF for a in amax], dtype=np.uint32)
+    bad = np.nonzero(got != want)[0]
+    assert bad.size == 0, [(hex(int(bf16_bits[i])), hex(int(got[i])), hex(int(want[i]))) for i in bad[:8]]
+    # zero and NaN decode to 1.0
+    one = np.float32(1.0).view(np.uint32)
+    assert want[0] == one and want[-1] == one
+
+
+def test_nvfp4_outer_scale_fp32_probes_list_the_known_deviation():
+    """On FP32 |max| values one ulp above 2688 * 2^e (never produced by a BF16 tensor) the kernels'
+    exponent-bump rule doubles the scale where exp2(ceil(log2(t))) rounds the logarithm down to an
+    integer.  The fixture lists those inputs; the oracle reproduces the integer rule on them and
+    the reference's bits everywhere else."""
+    arrays, meta = _outer_scale_fixture()
+    probes = torch.from_numpy(arrays["fp32_probe_bits"].view(np.float32).copy())
+    ref = arrays["fp32_probe_power2_scale_bits"]
+    listed = {e["amax_bits"]: e for e in meta["fp32_probes_where_integer_rule_differs"]}
+    assert 0 < len(listed) < len(probes)
+    for a, r in zip(probes, ref):
+        got = O.nvfp4_scale_rule(a, "power2").view(torch.int32).item() & 0xFFFFFFFF
+        key = int(a.view(torch.int32).item()) & 0xFFFFFFFF
+        if key in listed:
+            assert got == listed[key]["integer_rule_scale_bits"] == listed[key]["reference_scale_bits"] + (1 << 23)
+        else:
+            assert got == int(r)
+
+
+def test_nvfp4_kernel_form_quotient_differs_only_in_exact_mode():
+    """amax * Float32(1/2688) (quantizer kernels) against amax / 2688 (PyTorch functions): the power
+    of two is the same on every BF16 magnitude, the exact scale is not."""
+    arrays, _ = _outer_scale_fixture()
+    bits = arrays["bf16_bits"].astype(np.int64)[1:0x7F80]
+    amax = torch.from_numpy((bits << 16).astype(np.uint32).view(np.float32).copy())
+    step = 7   # a thinned sweep keeps the CPU suite short; the exhaustive division-form sweep is above
+    p2_t = [O.nvfp4_scale_rule(a, "power2", "torch").item() for a in amax[::step]]
+    p2_k = [O.nvfp4_scale_rule(a, "power2", "kernel").item() for a in amax[::step]]
+    assert p2_t == p2_k
+    ex_t = torch.cat([O.nvfp4_scale_rule(a, "exact", "torch") for a in amax[::step]])
+    ex_k = torch.cat([O.nvfp4_scale_rule(a, "exact", "kernel") for a in amax[::step]])
+    normal = ex_t >= 2.0 ** -126
+    assert (ex_t != ex_k).any() and ((ex_t - ex_k).abs()[normal] <= ex_t[normal] * 2.0 ** -22).all()
