@@ -284,10 +284,12 @@ def run_own_arm(args) -> None:
     launches_per_step = 5  # quantize X, W_gate_up, W_down + gate/up GEMM (SiLU*up and H quantization fused) + down GEMM
 
     def step():
-        ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, None, y, want_hidden=False)
+        with ops.gemm_schedule(args.schedule):
+            ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, None, y, want_hidden=False)
 
     def step_weak():
-        ops.mxfp8_glu_mlp_fwd(x_weak, wgu, wd, ws, None, y_weak, want_hidden=False)
+        with ops.gemm_schedule(args.schedule):
+            ops.mxfp8_glu_mlp_fwd(x_weak, wgu, wd, ws, None, y_weak, want_hidden=False)
 
     sampler.start()
     timer.run("fwd", step, steps, warmup)
@@ -295,6 +297,32 @@ def run_own_arm(args) -> None:
     if world > 1:
         timer.run("fwd_weak", step_weak, steps, warmup)
         ops.check_device_status(dev)
+
+    # ---------------- dominant kernel alone: the gate/up GEMM with the fused SwiGLU epilogue ----------------
+    qx, sx = ops.mxfp8_quantize(x)
+    qg, sg = ops.mxfp8_quantize(wgu)
+    if args.schedule == "fused_x":
+        timer.run("gemm", lambda: ops.mxfp8_gemm_glu_mx_fused_x(x, qg, sg, INTER), steps, 3)
+    else:
+        with ops.gemm_schedule(args.schedule):
+            timer.run("gemm", lambda: ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, per, INTER, K), steps, 3)
+    ops.check_device_status(dev)
+    del qx, sx, qg, sg
+    if args.quick:
+        clocks = sampler.stop()
+        numa.__exit__(None, None, None)
+        res = timer.reduce(dev)
+        if rank == 0:
+            print(json.dumps({
+                "metric": METRIC, "value": mlp_flops(M) / (res["fwd"] * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": steps, "warmup": warmup, "ms_per_step": res["fwd"], "quick": True, "schedule": args.schedule,
+                "config": {"workload": f"mxfp8_glu_mlp_fwd_m{M}_k{K}_i{INTER}", "m_per_gpu": per},
+                "dominant_kernel": {"ms_per_launch": res["gemm"],
+                                    "tflops": 2.0 * per * (2 * INTER) * K / (res["gemm"] * 1e-3) / 1e12},
+                "clocks": clocks.get("burst")}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---------------- end to end through host buffers (rtx_b200.host.GluMlpHostSession) ----------------
     # every step copies that step's X from pinned host memory to the device and its Y back; copy-in of step
@@ -335,13 +363,6 @@ def run_own_arm(args) -> None:
     timer.results["copies"] = max(c0.elapsed_time(c1), c2.elapsed_time(c3)) / steps
     numa.__exit__(None, None, None)
 
-    # ---------------- dominant kernel alone: the gate/up GEMM with the fused SwiGLU epilogue ----------------
-    qx, sx = ops.mxfp8_quantize(x)
-    qg, sg = ops.mxfp8_quantize(wgu)
-    timer.run("gemm", lambda: ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, per, INTER, K), steps, 3)
-    ops.check_device_status(dev)
-    del qx, sx, qg, sg
-
     # ---------------- sustained: the headline step for >= 2 s ----------------
     t = torch.tensor([timer.results["fwd"]], dtype=torch.float64, device=dev)
     if world > 1:
@@ -352,13 +373,15 @@ def run_own_arm(args) -> None:
     del x_weak, y_weak
 
     # ---------------- backward (configuration 4): dX local, FP32 dW all-reduced inside the timed region ----------------
-    bwd = make_inputs(4, m=BWD_M * world)
+    bwd = make_inputs(4, m=BWD_M)          # the same 16384 rows and weight at every N
     bper = BWD_M // world
     w_b = bwd["w"].to(dev)
     shards = {"strong": (bwd["x"][rank * bper:(rank + 1) * bper].to(dev), bwd["dy"][rank * bper:(rank + 1) * bper].to(dev))}
     if world > 1:
-        shards["weak"] = (bwd["x"][rank * BWD_M:(rank + 1) * BWD_M].to(dev),
-                          bwd["dy"][rank * BWD_M:(rank + 1) * BWD_M].to(dev))
+        wide = make_inputs(4, m=BWD_M * world)     # weak: 16384 rows per GPU out of one global draw
+        shards["weak"] = (wide["x"][rank * BWD_M:(rank + 1) * BWD_M].to(dev),
+                          wide["dy"][rank * BWD_M:(rank + 1) * BWD_M].to(dev))
+        del wide
     bwd_parity = None
     for mode, (xb, dyb) in shards.items():
         timer.run(f"bwd_{mode}", lambda: parallel.data_parallel_linear_backward(dyb, xb, w_b), steps, warmup)
@@ -370,7 +393,7 @@ def run_own_arm(args) -> None:
 
         xb, dyb = shards["strong"]
         dx_r, dw_r = parallel.data_parallel_linear_backward(dyb, xb, w_b)
-        x_all, dy_all = bwd["x"][:BWD_M].to(dev), bwd["dy"][:BWD_M].to(dev)
+        x_all, dy_all = bwd["x"].to(dev), bwd["dy"].to(dev)
         dx_1, dw_1 = ops.mxfp8_linear_bwd(dy_all, x_all, w_b, ws)
         torch.cuda.synchronize()
         rep = parity_report(dw_r.cpu(), dw_1.cpu())
@@ -442,7 +465,9 @@ def run_own_arm(args) -> None:
                     "copies_alone_gbs_each_way": x_host.numel() * 2 / (res["copies"] * 1e-3) / 1e9},
             "gpu_launches": launches_per_step * steps,
             "clocks": clocks.get("burst"),
-            "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, glu_mx> (gate/up GEMM + SiLU*up + MXFP8 encode of H)",
+            "schedule": args.schedule,
+            "roofline": {"kernel": ("gemm_mxfp8_fused_a_pair_kernel<glu_mx>" if args.schedule == "fused_x" else
+                                    "gemm_blockscaled_pair_kernel<mxfp8, glu_mx>") + " (gate/up GEMM + SiLU*up + MXFP8 encode of H)",
                          "bound": "tensor", "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": gemm_tflops / fp8_peak, "frac_of_nominal": gemm_tflops / NOMINAL_FP8_TFLOPS,
                          "traffic": traffic, "ms_per_launch": res["gemm"], "rows": per,
@@ -483,6 +508,10 @@ def main() -> None:
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip configurations 3 and 5 (1-GPU runs)")
+    ap.add_argument("--schedule", choices=["auto", "single", "pair", "fused_x"], default="auto",
+                    help="GEMM schedule of the forward step (fused_x: X is quantized inside the gate/up GEMM)")
+    ap.add_argument("--quick", action="store_true",
+                    help="forward step and dominant kernel only (profiler-sized runs): no end-to-end, sustained or backward part")
     ap.add_argument("--m", type=int, default=M, help="token rows of the batch (smaller values give profiler-sized cases)")
     ap.add_argument("--inter", type=int, default=INTER, help="SwiGLU intermediate width")
     args = ap.parse_args()

@@ -70,12 +70,18 @@ int rtxb_get_sm_margin(void);
  * call through the config object given to its compile_* factories (tile shape, stages, persistence:
  * rtx/configs/mxfp8.py:110-343, chosen by rtx/autotune); here the built schedules are an enumeration:
  * AUTO (the library picks by shape), SINGLE (one CTA per 128 x 256 tile, 4 stages), PAIR (two CTAs per
- * 256 x 256 tile, cta_group::2), STREAM (128 x 64 tiles for M <= 128; ignored for larger M).  All give
- * the same bits.  Thread-local. */
+ * 256 x 256 tile, cta_group::2), STREAM (128 x 64 tiles for M <= 128; ignored for larger M), FUSED_X (the
+ * composite MXFP8 forwards skip the activation quantizer launch and run the pair kernel whose own
+ * quantizer warps encode X tile by tile, rtxb_mxfp8_linear_fwd_fused_x; packed-operand GEMMs treat it
+ * as PAIR).  All give the same bits.
+ * The setting is a property of the calling THREAD, read when a call is made: it is safe across threads
+ * and streams, but a caller that sets it around a call must restore it itself, and nested users on one
+ * thread see each other's setting (set it immediately before the call it is meant for). */
 #define RTXB_SCHEDULE_AUTO 0
 #define RTXB_SCHEDULE_SINGLE 1
 #define RTXB_SCHEDULE_PAIR 2
 #define RTXB_SCHEDULE_STREAM 3
+#define RTXB_SCHEDULE_FUSED_X 4
 int rtxb_set_gemm_schedule(int schedule);
 int rtxb_get_gemm_schedule(void);
 
@@ -135,6 +141,18 @@ int rtxb_mxfp8_gemm_glu_mx(const void* qa, const void* sa, const void* qb, const
  * workspace: rtxb_mxfp8_linear_workspace_bytes(m, n, k); caller-owned, reusable
  * across calls on the same stream. */
 size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
+/* The reference's fused forward kernel MXFP8FusedLinearKernel (rtx/kernels/mxfp8_fwd.py:936-2934: BF16
+ * tiles staged, quantizer warps, MMA, one launch) for the operand state "dynamic X, packed W"
+ * (op mxfp8_linear_dynamic_x_prequant_w, rtx/fp8.py:1269-1302): x stays BF16 in memory and is quantized
+ * tile by tile by the GEMM's quantizer warps; qw / sw are the packed weight [n, Kp] and its mma128
+ * scales.  Bit-identical to rtxb_mxfp8_quantize(x) followed by rtxb_mxfp8_gemm.  Every 256-wide column
+ * tile re-quantizes its rows of x, so this pays only where n is a few tiles wide. */
+int rtxb_mxfp8_linear_fwd_fused_x(const void* x_bf16, int64_t ldx, const void* qw, const void* sw, void* out_bf16,
+                                  int64_t m, int64_t n, int64_t k, int64_t ldo, int rounding, void* stream, int* status);
+/* rtxb_mxfp8_gemm_glu_mx with the same in-kernel quantization of the activation operand. */
+int rtxb_mxfp8_gemm_glu_mx_fused_x(const void* x_bf16, int64_t ldx, const void* qb, const void* sb, void* h_bf16,
+                                   void* q_h, void* s_h, int64_t m, int64_t inter, int64_t k, int64_t ldo, void* stream,
+                                   int* status);
 int rtxb_mxfp8_linear_fwd(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n, int64_t k,
                           int rounding, void* workspace, size_t workspace_bytes, void* stream, int* status);
 

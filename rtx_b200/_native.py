@@ -51,6 +51,8 @@ SIGNATURES = {
     "rtxb_mxfp8_gemm": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
     "rtxb_mxfp8_gemm_glu": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "rtxb_mxfp8_gemm_glu_mx": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
+    "rtxb_mxfp8_linear_fwd_fused_x": (_I, [_P, _L, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
+    "rtxb_mxfp8_gemm_glu_mx_fused_x": (_I, [_P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "rtxb_mxfp8_linear_workspace_bytes": (_Z, [_L, _L, _L]),
     "rtxb_mxfp8_linear_fwd": (_I, [_P, _P, _P, _L, _L, _L, _I, _P, _Z, _P, _P]),
     "rtxb_mxfp8_linear_fwd_noalloc": (_I, [_P, _P, _P, _L, _L, _L, _I, _P, _P]),

@@ -15,6 +15,7 @@
 #include <atomic>
 #include "quant.cuh"
 #include "gemm_decode_fused.cuh"
+#include "gemm_fused_quant.cuh"
 
 using namespace rtxb;
 
@@ -254,14 +255,16 @@ cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, size
 }
 
 // Caller-selected GEMM schedule of this thread (0 = the library chooses): 1 single-CTA 128 x 256 tiles,
-// 2 CTA pairs with 256 x 256 tiles, 3 streaming 128 x 64 tiles (only for M <= 128, else ignored).
+// 2 CTA pairs with 256 x 256 tiles, 3 streaming 128 x 64 tiles (only for M <= 128, else ignored),
+// 4 CTA pairs that quantize the activation operand themselves (composite MXFP8 forwards only; the
+// packed-operand GEMM entry points treat it as 2).
 thread_local int t_gemm_schedule = 0;
 
 // Schedule choice: the CTA-pair kernel (256 x 256 pair tiles) unless the problem has a single
 // 128-row block of A, where half of every pair would idle.
 bool use_pair_kernel(int m_tiles) {
   if (t_gemm_schedule == 1 || t_gemm_schedule == 3) return false;
-  if (t_gemm_schedule == 2) return true;
+  if (t_gemm_schedule == 2 || t_gemm_schedule == 4) return true;
   return m_tiles >= 2;
 }
 
@@ -271,7 +274,7 @@ bool use_pair_kernel(int m_tiles) {
 bool use_skinny_kernel(int m_tiles, int64_t n_rows_b) {
   if (m_tiles != 1) return false;
   if (t_gemm_schedule == 3) return true;
-  if (t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
+  if (t_gemm_schedule == 1 || t_gemm_schedule == 2 || t_gemm_schedule == 4) return false;
   return (n_rows_b + kBlockN - 1) / kBlockN < 74;
 }
 
@@ -425,7 +428,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
 // scale tiles for every K step) leaves room for at least three ring slots of weights, and few enough
 // 256-wide column tiles that the 64-wide streaming tiling is the right one.
 bool decode_fused_eligible(const void* x, int64_t m, int64_t n, int64_t k) {
-  if (t_gemm_schedule == 1 || t_gemm_schedule == 2) return false;
+  if (t_gemm_schedule == 1 || t_gemm_schedule == 2 || t_gemm_schedule == 4) return false;
   if (m > 4 || k % 256 != 0 || !aligned(x, 16)) return false;
   const int k_tiles = static_cast<int>(k / 256);
   if (k_tiles < 2 || fused_slots_for(k_tiles, 2) < 3) return false;
@@ -473,6 +476,67 @@ int launch_decode_fused(const void* x, const void* qw, const void* sw, const flo
   return RTXB_OK;
 }
 
+// The pair GEMM that quantizes A = X (BF16) in the kernel; B packed.  `row_bytes` = padded K.
+template <int EPI>
+int launch_fused_a(const void* x, int64_t ldx, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
+                   int64_t k, int64_t ldo, int64_t out_cols, int64_t glu_inter, int rounding, cudaStream_t stream,
+                   int* status, void* q_out = nullptr, void* sf_out = nullptr) {
+  using P = PairTraits<kKindMxfp8>;
+  constexpr int KS = P::kStepsPerBarrierP;
+  const int64_t row_bytes = round_up(k, 32);
+  const int64_t sf_k_chunks = (row_bytes / 32 + 3) / 4;
+  GemmParams p = {};
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n_rows_b);
+  p.k_tiles = static_cast<int>((row_bytes + kBlockKBytes - 1) / kBlockKBytes);
+  p.m_tiles = static_cast<int>((m + kBlockM - 1) / kBlockM);
+  p.n_tiles = glu_inter ? static_cast<int>((glu_inter + 127) / 128) : static_cast<int>((n_rows_b + kBlockN - 1) / kBlockN);
+  p.glu_inter = static_cast<int>(glu_inter);
+  p.sfb = static_cast<const uint8_t*>(sb);
+  p.sf_k_chunks = static_cast<int>(sf_k_chunks);
+  p.out = out;
+  p.ldo = ldo;
+  p.out_cols = static_cast<int>(out_cols);
+  p.out_vec_ok = (aligned(out, 16) && (ldo * 2) % 16 == 0) ? 1 : 0;
+  p.x_region_rows = p.w_region_rows = 1;
+  p.q_out = static_cast<uint8_t*>(q_out);
+  p.sf_out = static_cast<uint8_t*>(sf_out);
+  p.sf_out_chunks = static_cast<int>((out_cols / 32 + 3) / 4);
+  p.status = status;
+  p.a_box_rows = 128;
+  p.ks = 1;
+  CUtensorMap map_b, map_sfb;
+  int rc;
+  p.map3d = row_bytes % 128 == 0 ? 1 : 0;
+  if (p.map3d) rc = make_payload_map_ksteps(&map_b, qb, n_rows_b, row_bytes, 128, KS);
+  else rc = make_payload_map(&map_b, qb, n_rows_b, row_bytes, 128);
+  if (rc) return rc;
+  const int64_t b_blocks = (n_rows_b + 127) / 128;
+  const int64_t half_delta = glu_inter ? glu_inter / 128 : 1;
+  p.sfb3d = (glu_inter ? (glu_inter % 128 == 0 && n_rows_b == 2 * glu_inter) : (b_blocks % 2 == 0)) ? 1 : 0;
+  if (p.sfb3d) rc = make_scale_map_halves(&map_sfb, sb, b_blocks * sf_k_chunks, KS * P::kSfChunks, half_delta * sf_k_chunks);
+  else rc = make_scale_map(&map_sfb, sb, b_blocks * sf_k_chunks, KS * P::kSfChunks);
+  if (rc) return rc;
+  FusedAParams fa;
+  fa.x = static_cast<const __nv_bfloat16*>(x);
+  fa.ldx = ldx;
+  fa.k = static_cast<int>(k);
+  fa.vec_ok = (aligned(x, 16) && ldx % 8 == 0) ? 1 : 0;
+  fa.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
+  auto kernel = gemm_mxfp8_fused_a_pair_kernel<EPI>;
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), P::kSmemBytes);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(fused-A gemm)");
+  const int m_pairs = (p.m_tiles + 1) / 2;
+  int64_t g = (32ll << 20) / (256 * 2 * row_bytes);    // the A panel of a raster group is BF16 here
+  p.group_m = static_cast<int>(g < 4 ? 4 : (g > m_pairs ? m_pairs : g));
+  const int64_t pair_tiles = static_cast<int64_t>(m_pairs) * p.n_tiles;
+  const int max_pairs = sm_count() / 2;
+  const int pairs = static_cast<int>(pair_tiles < max_pairs ? pair_tiles : max_pairs);
+  kernel<<<2 * pairs, kFusedQuantThreads, P::kSmemBytes, stream>>>(map_b, map_sfb, p, fa);
+  RTXB_CHECK_LAUNCH("gemm_mxfp8_fused_a_pair_kernel");
+  return RTXB_OK;
+}
+
 int check_gemm_args(const void* qa, const void* sa, const void* qb, const void* sb, const void* out, int64_t m,
                     int64_t n, int64_t k, int64_t ldo, int64_t out_cols, int out_elem_bytes) {
   if (!qa || !sa || !qb || !sb || !out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
@@ -515,7 +579,7 @@ int rtxb_set_sm_margin(int sms) {
 int rtxb_get_sm_margin(void) { return g_sm_margin.load(std::memory_order_relaxed); }
 
 int rtxb_set_gemm_schedule(int schedule) {
-  if (schedule < RTXB_SCHEDULE_AUTO || schedule > RTXB_SCHEDULE_STREAM)
+  if (schedule < RTXB_SCHEDULE_AUTO || schedule > RTXB_SCHEDULE_FUSED_X)
     return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown GEMM schedule");
   t_gemm_schedule = schedule;
   return RTXB_OK;
@@ -695,6 +759,33 @@ int rtxb_mxfp8_gemm_glu_mx(const void* qa, const void* sa, const void* qb, const
                                             inter, nullptr, static_cast<cudaStream_t>(stream), status, q_h, s_h);
 }
 
+int rtxb_mxfp8_linear_fwd_fused_x(const void* x, int64_t ldx, const void* qw, const void* sw, void* out, int64_t m,
+                                  int64_t n, int64_t k, int64_t ldo, int rounding, void* stream, int* status) {
+  if (!x || !qw || !sw || !out) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || n <= 0 || k <= 0 || ldx < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (ldo < n) return fail_msg(RTXB_E_INVALID_ARGUMENT, "output pitch smaller than its width");
+  if (!aligned(sw, 16)) return fail_msg(RTXB_E_ALIGNMENT, "scale tiles must be 16-byte aligned");
+  if (!aligned(out, 2) || !aligned(x, 2)) return fail_msg(RTXB_E_ALIGNMENT, "pointer is not element aligned");
+  return launch_fused_a<kEpiBf16>(x, ldx, qw, sw, out, m, n, k, ldo, n, 0, rounding, static_cast<cudaStream_t>(stream),
+                                  status);
+}
+
+int rtxb_mxfp8_gemm_glu_mx_fused_x(const void* x, int64_t ldx, const void* qb, const void* sb, void* h_bf16, void* q_h,
+                                   void* s_h, int64_t m, int64_t inter, int64_t k, int64_t ldo, void* stream,
+                                   int* status) {
+  if (!x || !qb || !sb || !q_h || !s_h) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || inter <= 0 || k <= 0 || ldx < k) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (m > INT32_MAX || 2 * inter > INT32_MAX || k > INT32_MAX - 256)
+    return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (inter % 128 != 0) return fail_msg(RTXB_E_UNSUPPORTED, "fused GLU epilogue needs inter % 128 == 0");
+  if (!aligned(sb, 16) || !aligned(q_h, 16) || !aligned(s_h, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "scale tiles and packed outputs must be 16-byte aligned");
+  if (h_bf16 && (!aligned(h_bf16, 2) || ldo < inter)) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad BF16 output");
+  return launch_fused_a<kEpiGluMx>(x, ldx, qb, sb, h_bf16, m, 2 * inter, k, h_bf16 ? ldo : inter, inter, inter,
+                                   RTXB_ROUND_INFINITY, static_cast<cudaStream_t>(stream), status, q_h, s_h);
+}
+
 size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k) {
   Carver c(nullptr);
   const int64_t kp = round_up(k, 32);
@@ -716,9 +807,11 @@ int rtxb_mxfp8_linear_fwd(const void* x, const void* w, void* out, int64_t m, in
   uint8_t* sx = c.take(rtxb_mxfp8_scale_bytes(m, k, RTXB_SCALE_MMA128));
   uint8_t* qw = c.take(n * kp);
   uint8_t* sw = c.take(rtxb_mxfp8_scale_bytes(n, k, RTXB_SCALE_MMA128));
-  int rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, rounding, stream);
+  int rc = rtxb_mxfp8_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, rounding, stream);
   if (rc) return rc;
-  rc = rtxb_mxfp8_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, rounding, stream);
+  if (t_gemm_schedule == RTXB_SCHEDULE_FUSED_X)   // X is quantized by the GEMM's own quantizer warps
+    return rtxb_mxfp8_linear_fwd_fused_x(x, k, qw, sw, out, m, n, k, n, rounding, stream, status);
+  rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, rounding, stream);
   if (rc) return rc;
   return rtxb_mxfp8_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, stream, status);
 }
@@ -755,13 +848,17 @@ int rtxb_mxfp8_glu_mlp_fwd(const void* x, const void* w_gu, const void* w_down, 
   uint8_t* qd = c.take(n_out * ip);
   uint8_t* sd = c.take(rtxb_mxfp8_scale_bytes(n_out, inter, RTXB_SCALE_MMA128));
   int rc;
-  if ((rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
+  const bool fused_x = t_gemm_schedule == RTXB_SCHEDULE_FUSED_X;
+  if (!fused_x && (rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+    return rc;
   if ((rc = rtxb_mxfp8_quantize(w_gu, 2 * inter, k, k, qg, sg, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
   if ((rc = rtxb_mxfp8_quantize(w_down, n_out, inter, inter, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
     return rc;
   // gate/up GEMM whose epilogue applies SiLU*up and writes H already quantized for the down projection
   // (and in BF16 too when the caller wants it)
-  if ((rc = rtxb_mxfp8_gemm_glu_mx(qx, sx, qg, sg, h, qh, sh, m, inter, k, inter, stream, status))) return rc;
+  if (fused_x) rc = rtxb_mxfp8_gemm_glu_mx_fused_x(x, k, qg, sg, h, qh, sh, m, inter, k, inter, stream, status);
+  else rc = rtxb_mxfp8_gemm_glu_mx(qx, sx, qg, sg, h, qh, sh, m, inter, k, inter, stream, status);
+  if (rc) return rc;
   return rtxb_mxfp8_gemm(qh, sh, qd, sd, y, m, n_out, inter, n_out, RTXB_OUT_BF16, stream, status);
 }
 

@@ -139,6 +139,20 @@ def mxfp8_gemm_glu(qa, sa, qb, sb, m: int, inter: int, k: int, out: Optional[tor
     return out
 
 
+def mxfp8_linear_fwd_fused_x(x: torch.Tensor, qw: torch.Tensor, sw: torch.Tensor, n: int,
+                             out: Optional[torch.Tensor] = None, rounding: int = N.ROUND_INFINITY) -> torch.Tensor:
+    """(x bf16 [M,K], packed weight [N,Kp] + mma128 scales) -> out bf16 [M,N] in ONE launch: the GEMM's
+    quantizer warps encode X tile by tile (no packed copy of X)."""
+    _require(x, torch.bfloat16, "x")
+    m, k = x.shape
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        N.call("rtxb_mxfp8_linear_fwd_fused_x", x.data_ptr(), x.stride(0), qw.data_ptr(), sw.data_ptr(), out.data_ptr(),
+               m, n, k, out.stride(0), rounding, _stream_ptr(), status_word(x.device).data_ptr())
+    return out
+
+
 class Workspace:
     """Caller-owned scratch for the composite entry points; grows on demand and is
     reused by every call made on the stream it was created for."""
@@ -181,6 +195,20 @@ def mxfp8_gemm_glu_mx(qa, sa, qb, sb, m: int, inter: int, k: int, *, want_bf16: 
         N.call("rtxb_mxfp8_gemm_glu_mx", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(),
                h.data_ptr() if want_bf16 else None, q.data_ptr(), s.data_ptr(), m, inter, k, inter, _stream_ptr(),
                status_word(qa.device).data_ptr())
+    return q, s, h
+
+
+def mxfp8_gemm_glu_mx_fused_x(x: torch.Tensor, qb, sb, inter: int, *, want_bf16: bool = False):
+    """mxfp8_gemm_glu_mx with X given in BF16 and quantized by the GEMM's own quantizer warps."""
+    _require(x, torch.bfloat16, "x")
+    m, k = x.shape
+    q = torch.empty(m, inter, dtype=torch.uint8, device=x.device)
+    s = torch.empty(mxfp8_scale_numel(m, inter, N.SCALE_MMA128), dtype=torch.uint8, device=x.device)
+    h = torch.empty(m, inter, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+    with torch.cuda.device(x.device):
+        N.call("rtxb_mxfp8_gemm_glu_mx_fused_x", x.data_ptr(), x.stride(0), qb.data_ptr(), sb.data_ptr(),
+               h.data_ptr() if want_bf16 else None, q.data_ptr(), s.data_ptr(), m, inter, k, inter, _stream_ptr(),
+               status_word(x.device).data_ptr())
     return q, s, h
 
 
@@ -244,7 +272,7 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
 # Launch controls: GEMM schedule of the calling thread, SM margin of the process
 # ---------------------------------------------------------------------------
 
-GEMM_SCHEDULES = {"auto": 0, "single": 1, "pair": 2, "stream": 3}
+GEMM_SCHEDULES = {"auto": 0, "single": 1, "pair": 2, "stream": 3, "fused_x": 4}
 
 
 class gemm_schedule:

@@ -694,3 +694,64 @@ def test_full_size_config2_properties(gpu):
     for r0 in (0, m - 128):
         want = (dh[r0:r0 + 128] @ dd.t()).bfloat16()
         _assert_output(y[r0:r0 + 128].contiguous(), want.cpu())
+
+
+# ----------------------------------------------------------------------------- in-kernel quantization of X
+
+@pytest.mark.parametrize("mnk", [(256, 256, 256), (384, 512, 384), (300, 700, 1000), (129, 257, 96), (1000, 3000, 2048),
+                                 (130, 64, 40), (8192, 512, 4096)])
+@pytest.mark.parametrize("rounding", ["infinity", "floor"])
+def test_fused_x_gemm_equals_quantize_then_gemm(gpu, mnk, rounding):
+    """The pair GEMM whose quantizer warps encode X in the kernel (the reference's fused forward,
+    rtx/kernels/mxfp8_fwd.py:936-2934) gives the bits of the row quantizer followed by the packed GEMM,
+    ragged M / N / K and an odd number of K steps included; the composite forward routes to it under the
+    "fused_x" schedule."""
+    ops, N, dev, ws = gpu
+    m, n, k = mnk
+    code = N.ROUND_INFINITY if rounding == "infinity" else N.ROUND_FLOOR
+    torch.manual_seed(31)
+    x = (torch.randn(m, k) * 0.5).bfloat16().to(dev)
+    w = (torch.randn(n, k) * 0.5).bfloat16().to(dev)
+    x[m // 2, k // 3] = 300.0            # an outlier block
+    qx, sx = ops.mxfp8_quantize(x, rounding=code)
+    qw, sw = ops.mxfp8_quantize(w, rounding=code)
+    with ops.gemm_schedule("pair"):
+        want = ops.mxfp8_gemm(qx, sx, qw, sw, m, n, k)
+    for _ in range(2):
+        got = ops.mxfp8_linear_fwd_fused_x(x, qw, sw, n, rounding=code)
+    _ok(ops, dev)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    with ops.gemm_schedule("fused_x"):
+        routed = ops.mxfp8_linear_fwd(x, w, ws, rounding=code)
+    _ok(ops, dev)
+    assert torch.equal(routed.view(torch.int16), want.view(torch.int16))
+    if rounding == "infinity" and m * n * k <= 1000 * 3000 * 2048:
+        _assert_output(got, O.mxfp8_linear(x.cpu(), w.cpu()))
+
+
+def test_fused_x_glu_mlp_equals_the_chain(gpu):
+    ops, N, dev, ws = gpu
+    inp = O.make_inputs(2, m=600, k=512, inter=768)
+    x, wgu, wd = (inp[key].to(dev) for key in ("x", "w_gate_up", "w_down"))
+    h0, y0 = ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws)
+    with ops.gemm_schedule("fused_x"):
+        h1, y1 = ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws)
+        _, y2 = ops.mxfp8_glu_mlp_fwd(x, wgu, wd, ws, want_hidden=False)
+    _ok(ops, dev)
+    assert torch.equal(h0, h1) and torch.equal(y0, y1) and torch.equal(y0, y2)
+
+
+def test_fused_x_nan_row_stays_in_its_row(gpu):
+    ops, N, dev, _ = gpu
+    m, n, k = 384, 256, 384
+    torch.manual_seed(5)
+    x, w = torch.randn(m, k).bfloat16().to(dev), torch.randn(n, k).bfloat16().to(dev)
+    qw, sw = ops.mxfp8_quantize(w)
+    clean = ops.mxfp8_linear_fwd_fused_x(x, qw, sw, n)
+    x[133, 0] = float("nan")
+    got = ops.mxfp8_linear_fwd_fused_x(x, qw, sw, n)
+    _ok(ops, dev)
+    keep = torch.ones(m, dtype=torch.bool, device=dev)
+    keep[133] = False
+    assert torch.isnan(got[133].float()).all()
+    assert torch.equal(got[keep].view(torch.int16), clean[keep].view(torch.int16))
