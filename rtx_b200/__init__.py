@@ -80,3 +80,28 @@ def __getattr__(name: str):
 
 def __dir__():
     return sorted(__all__)
+
+
+def install_as_rtx() -> None:
+    """Make `import rtx` (and `rtx.fp8`, `rtx.fp4`, `rtx.fp8_bwd`, `rtx.formats`, `rtx.configs`, `rtx.runtime`,
+    `rtx.ptq`, `rtx.types`) resolve to this package, for code written against the reference's package
+    name, and publish the Inductor launcher registries under the reference's attribute names
+    (`torch._rtx_mxfp8_launchers` and friends, rtx/fp8.py:207-230) next to `torch._rtx_b200_launchers`.
+    Refuses when a different `rtx` package is already imported: the two cannot both own the `rtx::` ops."""
+    import sys
+    from importlib import import_module
+
+    this = sys.modules[__name__]
+    other = sys.modules.get("rtx")
+    if other is not None and other is not this:
+        raise RuntimeError("another package named 'rtx' is already imported; rtx_b200 cannot take its name")
+    sys.modules["rtx"] = this
+    for sub in ("fp8", "fp4", "fp8_bwd", "formats", "configs", "runtime", "ptq", "types", "autotune"):
+        sys.modules[f"rtx.{sub}"] = import_module(f".{sub}", __name__)
+    import torch
+
+    from . import inductor
+
+    torch._rtx_mxfp8_launchers = inductor.REGISTRIES["mxfp8_fwd"]
+    torch._rtx_mxfp8_bwd_launchers = inductor.REGISTRIES["mxfp8_bwd"]
+    torch._rtx_nvfp4_launchers = inductor.REGISTRIES["nvfp4_jit_row_region_fwd"]

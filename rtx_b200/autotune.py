@@ -195,5 +195,52 @@ def pick(ctx: KernelContext, adapter: KernelAdapter, evaluate: Callable[[Any], T
     return best
 
 
-__all__ = ["KernelAdapter", "DiscreteKernelAdapter", "KernelContext", "TrialOutcome", "ADAPTERS", "pick",
+class ScheduleResolver:
+    """Where a frontend turns its `autotune=` argument into the schedule of a call, as the reference's
+    frontends do (rtx/fp8.py:804-886, 2302-2386): `off` keeps the configured schedule; `cache` uses the
+    stored winner of this (family, M, N, K) when there is one; `balanced` / `online` / `coordinate`
+    time every legal candidate on the first call with a new M (with the caller's evaluator), store the
+    winner and use it from then on.  Only the GEMM schedule is taken from a winner: the quantizer
+    settings (rounding, layouts) stay those of the configured schedule.  Resolutions are remembered per
+    M, so the steady state costs one dictionary lookup."""
+
+    def __init__(self, family: str, n: int, k: int, mode: str, cache_dir=None, *, variant: str = "default",
+                 device_id: str = "b200"):
+        self.family, self.n, self.k, self.mode, self.cache_dir = family, int(n), int(k), mode, cache_dir
+        self.variant, self.device_id = variant, device_id
+        self.adapter = ADAPTERS[family]()
+        self.resolved: dict[int, Any] = {}
+        self.sources: dict[int, str] = {}
+
+    def context(self, m: int) -> KernelContext:
+        return KernelContext(self.family, int(m), self.n, self.k, self.device_id, "hot", self.variant)
+
+    def resolve(self, m: int, configured: Any, evaluate: Optional[Callable[[Any], TrialOutcome]] = None) -> Any:
+        import dataclasses
+
+        if self.mode == "off":
+            return configured
+        m = int(m)
+        if m in self.resolved:
+            return self.resolved[m]
+        ctx = self.context(m)
+        winner = load_runtime_winner(ctx, self.adapter, self.cache_dir)
+        source = "stored winner"
+        if winner is None and self.mode != "cache" and evaluate is not None:
+            def trial(candidate):
+                return evaluate(dataclasses.replace(configured, gemm=candidate.gemm))
+
+            winner = pick(ctx, self.adapter, trial, mode=self.mode, cache_dir=self.cache_dir)
+            source = "tuned on first use"
+        if winner is None:
+            chosen, source = configured, "configured (no stored winner)"
+        else:
+            chosen = dataclasses.replace(configured, gemm=winner.gemm)
+        if chosen.rejection(self.adapter.problem_type(m, self.n, self.k)) is not None:
+            chosen, source = configured, "configured (winner not legal for this schedule)"
+        self.resolved[m], self.sources[m] = chosen, source
+        return chosen
+
+
+__all__ = ["KernelAdapter", "ScheduleResolver", "DiscreteKernelAdapter", "KernelContext", "TrialOutcome", "ADAPTERS", "pick",
            "runtime_winner_path", "save_runtime_winner", "load_runtime_winner", "FAMILIES"]

@@ -114,8 +114,10 @@ class MXFP8GemmConfig(_Config):
     schedule: str = "auto"
 
     # (tile_m, tile_n, tile_k_bytes, stages, cta_group); stages 0 = ring depth chosen at launch
+    # "fused_x": the pair tiling with the activation operand quantized by the GEMM's own quantizer warps (the
+    # composite forwards drop their activation-quantizer launch; packed-operand GEMMs run it as "pair")
     SCHEDULES: ClassVar[dict] = {"single": (128, 256, 128, 4, 1), "pair": (256, 256, 128, 6, 2),
-                                 "stream": (128, 64, 128, 0, 1)}
+                                 "stream": (128, 64, 128, 0, 1), "fused_x": (256, 256, 128, 6, 2)}
     BUILT: ClassVar[tuple] = tuple(SCHEDULES.values())
 
     @classmethod

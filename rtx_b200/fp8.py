@@ -208,8 +208,11 @@ def mxfp8_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor
         raise TypeError("x must be BF16 [M, K]")
     cfg = _resolve_prequant(config_key)
     x = x if x.is_contiguous() else x.contiguous()
-    qx, sx = ops.mxfp8_quantize(x, rounding=_rounding(cfg))
     sw = _kernel_scales(weight_scales, n, k, weight_scale_layout)
+    if cfg.gemm.schedule == "fused_x":
+        # one launch: the GEMM's quantizer warps encode X (the reference's fused kernel for this operand state)
+        return ops.mxfp8_linear_fwd_fused_x(x, weight_data.view(torch.uint8), sw, n, rounding=_rounding(cfg))
+    qx, sx = ops.mxfp8_quantize(x, rounding=_rounding(cfg))
     with ops.schedule_of(cfg.gemm):
         return ops.mxfp8_gemm(qx, sx, weight_data.view(torch.uint8), sw, int(x.shape[0]), n, k)
 
@@ -236,6 +239,22 @@ def _(x_data, weight_data, x_scales, weight_scales, m, n, k, x_scale_layout, wei
 
 
 # --------------------------------------------------------------------------- functional
+
+_FUNCTIONAL_RESOLVERS: dict = {}
+
+
+def _stored_winner_key(fwd_key: str, m: int, n: int, k: int, cache_dir, packed: bool) -> str:
+    from .autotune import ScheduleResolver
+
+    slot = (n, k, str(cache_dir), packed)
+    with _LOCK:
+        resolver = _FUNCTIONAL_RESOLVERS.get(slot)
+        if resolver is None:
+            resolver = ScheduleResolver("mxfp8_prequant_fwd", n, k, "cache", cache_dir,
+                                        variant="weight_prequant" if packed else "default")
+            _FUNCTIONAL_RESOLVERS[slot] = resolver
+        return _intern(resolver.resolve(m, _resolve_prequant(fwd_key)))
+
 
 @torch._dynamo.assume_constant_result
 def _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, packed: bool):
@@ -264,9 +283,14 @@ def mxfp8_linear(x, weight, *, forward_config: Optional[MXFP8FwdConfig] = None, 
     """Apply MXFP8 linear in dynamic or prequantized states (rtx/fp8.py:2019-2193).  Leading
     activation dimensions are flattened for the kernel and restored in the output."""
     _normalize_backend(backend)
-    _autotune_mode(autotune)
+    mode = _autotune_mode(autotune)
     x_packed, w_packed = isinstance(x, MXFP8Tensor), isinstance(weight, MXFP8Tensor)
     fwd_key, bwd_key = _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, w_packed)
+    if mode != "off" and not x_packed and not torch.compiler.is_compiling():
+        # functional calls use stored winners only; first-use tuning belongs to the module, which owns its state
+        n_w, k_w = mxfp8_matrix_shape(weight) if w_packed else (int(weight.shape[0]), int(weight.shape[-1]))
+        fwd_key = _stored_winner_key(fwd_key, int(x.numel() // max(int(x.shape[-1]), 1)), n_w, k_w, autotune_cache_dir,
+                                     w_packed)
     if x_packed and not w_packed:
         raise ValueError("a packed activation requires a packed weight")
     if w_packed:
@@ -340,8 +364,12 @@ class MXFP8Linear(nn.Module):
         self.tuning_policy = tuning_policy
         self.autotune_cache_dir = autotune_cache_dir
         self.backend = _normalize_backend(backend)
-        _autotune_mode(autotune)
         self.weight_mode = "prequantized" if packed_weight is not None else "dynamic"
+        from .autotune import ScheduleResolver
+
+        self._resolver = ScheduleResolver("mxfp8_prequant_fwd", self.out_features, self.in_features,
+                                          _autotune_mode(autotune), autotune_cache_dir,
+                                          variant="weight_prequant" if packed_weight is not None else "default")
         # schedules travel as interned strings so that a compiled graph sees constants (rtx/fp8.py:376-415)
         self._forward_config_key, self._backward_config_key = _select_keys(
             self.forward_config, None, self.dynamic_config, None, backward_config, packed_weight is not None)
@@ -389,12 +417,59 @@ class MXFP8Linear(nn.Module):
         layout = SCALE_LAYOUT_NAMES[int(self.weight_packing_meta[1])]
         return make_mxfp8_tensor(self.weight_data, self.weight_scales, (self.out_features, self.in_features), layout)
 
-    def explain(self) -> dict:
-        """What forward() will run for this module."""
-        return {"format": "mxfp8", "weight_mode": self.weight_mode, "backend": self.backend,
-                "pipeline": "quantize once + tcgen05 block-scaled GEMM (sm_100a)",
-                "forward_key": _select_keys(self.forward_config, None, self.dynamic_config, None, self.backward_config,
-                                            self.weight_mode == "prequantized")[0]}
+    def explain(self, m: Optional[int] = None) -> dict:
+        """What forward() will run for this module; with `m` (token rows of a call) the schedule that
+        `autotune=` resolves for that shape (a stored winner when one exists)."""
+        key = self._forward_config_key
+        out = {"format": "mxfp8", "weight_mode": self.weight_mode, "backend": self.backend,
+               "pipeline": "quantize once + tcgen05 block-scaled GEMM (sm_100a)", "autotune": self._resolver.mode,
+               "forward_key": key}
+        if m is not None:
+            cfg = self._resolver.resolve(int(m), _resolve_prequant(key))
+            out.update(forward_key=_intern(cfg), gemm_schedule=cfg.gemm.schedule,
+                       schedule_source=self._resolver.sources.get(int(m), "configured"))
+        return out
+
+    def _tuned_forward_key(self, x2d: torch.Tensor) -> str:
+        """The forward schedule key of this call: the configured one, or what `autotune=` resolves for
+        this M (stored winner / tuned on first use).  Constant under torch.compile (no tuning while tracing)."""
+        if self._resolver.mode == "off" or torch.compiler.is_compiling():
+            return self._forward_config_key
+        m = int(x2d.shape[0])
+        cfg = self._resolver.resolved.get(m)
+        if cfg is None:
+            cfg = self._resolver.resolve(m, _resolve_prequant(self._forward_config_key), self._evaluator(x2d))
+        return _intern(cfg)
+
+    def _evaluator(self, x2d: torch.Tensor):
+        """Times one candidate schedule on this call's own operands (first-hit tuning)."""
+        from .autotune import TrialOutcome
+
+        def evaluate(cfg) -> "TrialOutcome":
+            key = _intern(cfg)
+            with torch.no_grad():
+                def run():
+                    if self.weight_mode == "prequantized":
+                        return torch.ops.rtx.mxfp8_linear_dynamic_x_prequant_w(
+                            x2d, self.weight_data, self.weight_scales, self.out_features, self.in_features,
+                            self._weight_scale_layout, key)
+                    return torch.ops.rtx.mxfp8_linear_prequant(x2d, self.weight, key)
+                try:
+                    for _ in range(2):
+                        run()
+                    times = []
+                    for _ in range(5):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        run()
+                        e1.record()
+                        e1.synchronize()
+                        times.append(e0.elapsed_time(e1))
+                except RuntimeError as exc:
+                    return TrialOutcome("failed", detail=str(exc))
+            return TrialOutcome("ok", median_ms=sorted(times)[len(times) // 2])
+
+        return evaluate
 
     def to(self, *args, **kwargs):
         if self.weight_mode == "prequantized":
@@ -410,11 +485,12 @@ class MXFP8Linear(nn.Module):
         if x.shape[-1] != k:
             raise ValueError(f"K mismatch: x has {x.shape[-1]}, weight has {k}")
         x2d = x.reshape(-1, k)
+        fwd_key = self._tuned_forward_key(x2d)
         if self.weight_mode == "prequantized":
             if x.requires_grad and torch.is_grad_enabled():
                 raise RuntimeError("a prequantized MXFP8 weight is inference-only; keep the BF16 master weight to train")
             out = torch.ops.rtx.mxfp8_linear_dynamic_x_prequant_w(x2d, self.weight_data, self.weight_scales, n, k,
-                                                                  self._weight_scale_layout, self._forward_config_key)
+                                                                  self._weight_scale_layout, fwd_key)
         elif (cache := _weight_cache.active()) is not None:
             # inside a quantized_weight_cache() scope: the weight operands come from the step's cache
             _check_inputs(x2d, self.weight)
@@ -429,10 +505,9 @@ class MXFP8Linear(nn.Module):
         elif torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad):
             from . import fp8_bwd  # noqa: F401  (registers rtx::mxfp8_linear_train)
 
-            out = torch.ops.rtx.mxfp8_linear_train(x2d, self.weight, self._forward_config_key,
-                                                   self._backward_config_key)
+            out = torch.ops.rtx.mxfp8_linear_train(x2d, self.weight, fwd_key, self._backward_config_key)
         else:
-            out = torch.ops.rtx.mxfp8_linear_prequant(x2d, self.weight, self._forward_config_key)
+            out = torch.ops.rtx.mxfp8_linear_prequant(x2d, self.weight, fwd_key)
         return out.reshape(*x.shape[:-1], n)
 
 

@@ -261,3 +261,4 @@ __all__ = ["mxfp8_linear_backward", "MXFP8BwdConfig", "DEFAULT_MXFP8_BWD_CONFIG"
 from . import inductor as _inductor  # noqa: E402
 
 _inductor.register_mxfp8_train_lowering()
+_inductor.register_mxfp8_backward_lowerings()

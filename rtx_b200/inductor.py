@@ -1,4 +1,4 @@
-"""Inductor lowerings of the forward ops: inside a `torch.compile`d graph the op becomes an extern kernel
+"""Inductor lowerings of the forward and backward ops: inside a `torch.compile`d graph the op becomes an extern kernel
 that writes into a buffer Inductor owns, called through a launcher bound to the (immutable) config key.
 
 Mirrors the reference's entry points (rtx/fp8.py:207-230 and :683-721 launcher registries and lowerings;
@@ -6,6 +6,11 @@ rtx/fp4.py:2037-2604): `register_lowering(op)` returns an `ir.ExternKernelOut` w
 row-major layout whose `python_kernel_name` is an expression that looks the launcher up in a registry
 attached to the `torch` module, so wrappers that Inductor re-loads from its disk cache find (and lazily
 re-create) their launchers.  Launcher convention: `launcher(*inputs, out=buffer) -> None`.
+
+The backward ops (rtx/fp8_bwd.py:1387-1478) lower the same way: dX-only and dW-only become one extern
+kernel each; the two-output op becomes ONE extern kernel that writes `[dX | pad to 8 elements | dW]`
+into a flat buffer (the layout of the reference's packed op) followed by two views, so the gradient is
+still read once for its two quantizations.
 
 Without the lowering the ops still compile (they carry fake implementations); the lowering removes the
 dispatcher round trip and the allocation inside the op from the steady-state path.  Registration is
@@ -103,7 +108,31 @@ def _nvfp4_materialized_launcher(key: str):
     return launch
 
 
+def _mxfp8_bwd_launcher(spec):
+    """spec = (backward config key, "dx" | "dw" | "packed")."""
+    from . import fp8, fp8_bwd, ops
+
+    key, kind = spec
+    fp8_bwd._bwd_config(key)
+
+    def launch(grad_output, x, weight, *, out):
+        _count("mxfp8_bwd")
+        ws = fp8._workspace(grad_output.device)
+        if kind == "dx":
+            ops.mxfp8_linear_bwd(grad_output, None, weight, ws, need_dw=False, dx_out=out)
+        elif kind == "dw":
+            ops.mxfp8_linear_bwd(grad_output, x, None, ws, need_dx=False, dw_out=out)
+        else:
+            dx_n = x.numel()
+            off = (dx_n + 7) // 8 * 8
+            ops.mxfp8_linear_bwd(grad_output, x, weight, ws, dx_out=out[:dx_n].view(x.shape),
+                                 dw_out=out[off:off + weight.numel()].view(weight.shape))
+
+    return launch
+
+
 REGISTRIES = {
+    "mxfp8_bwd": LauncherRegistry("mxfp8_bwd", _mxfp8_bwd_launcher),
     "mxfp8_fwd": LauncherRegistry("mxfp8_fwd", _mxfp8_fwd_launcher),
     "nvfp4_jit_row_region_fwd": LauncherRegistry("nvfp4_jit_row_region_fwd", _nvfp4_region_launcher),
     "nvfp4_block_fwd": LauncherRegistry("nvfp4_block_fwd", _nvfp4_block_launcher),
@@ -162,6 +191,60 @@ def register_mxfp8_lowerings() -> bool:
 
 def register_mxfp8_train_lowering() -> bool:
     return _register("mxfp8_train", [(torch.ops.rtx.mxfp8_linear_train.default, "mxfp8_fwd", 2)])
+
+
+def register_mxfp8_backward_lowerings() -> bool:
+    """rtx::mxfp8_linear_bwd / _bwd_packed / _dx / _dw (call after fp8_bwd.py defined them)."""
+    with _LOCK:
+        if "mxfp8_bwd" in _DONE:
+            return _DONE["mxfp8_bwd"]
+        found = _inductor()
+        ok = found is not None
+        if ok:
+            ir, register_lowering = found
+            try:
+                from torch._inductor.lowering import lowerings
+
+                aten = torch.ops.aten
+
+                def extern(kind, key, grad_output, x, weight, size):
+                    inputs = [ir.ExternKernel.require_contiguous(ir.ExternKernel.realize_input(t))
+                              for t in (grad_output, x, weight)]
+                    stride = [size[1], 1] if len(size) == 2 else [1]
+                    layout = ir.FixedLayout(device=x.get_device(), dtype=torch.bfloat16, size=list(size), stride=stride)
+                    return ir.TensorBox.create(ir.ExternKernelOut(
+                        layout=layout, inputs=inputs,
+                        python_kernel_name=f"torch._rtx_b200_launchers['mxfp8_bwd'][{(key, kind)!r}]"))
+
+                def packed(grad_output, x, weight, key):
+                    xs, wsz = x.get_size(), weight.get_size()
+                    off = (xs[0] * xs[1] + 7) // 8 * 8
+                    return extern("packed", key, grad_output, x, weight, [off + wsz[0] * wsz[1]]), off
+
+                @register_lowering(torch.ops.rtx.mxfp8_linear_bwd_packed.default, type_promotion_kind=None)
+                def lower_packed(grad_output, x, weight, key):
+                    return packed(grad_output, x, weight, key)[0]
+
+                @register_lowering(torch.ops.rtx.mxfp8_linear_bwd.default, type_promotion_kind=None)
+                def lower_both(grad_output, x, weight, key):
+                    flat, off = packed(grad_output, x, weight, key)
+                    xs, wsz = x.get_size(), weight.get_size()
+                    view, cut = lowerings[aten.view.default], lowerings[aten.slice.Tensor]
+                    dx = view(cut(flat, 0, 0, xs[0] * xs[1]), list(xs))
+                    dw = view(cut(flat, 0, off, off + wsz[0] * wsz[1]), list(wsz))
+                    return dx, dw
+
+                @register_lowering(torch.ops.rtx.mxfp8_linear_dx.default, type_promotion_kind=None)
+                def lower_dx(grad_output, x, weight, key):
+                    return extern("dx", key, grad_output, x, weight, x.get_size())
+
+                @register_lowering(torch.ops.rtx.mxfp8_linear_dw.default, type_promotion_kind=None)
+                def lower_dw(grad_output, x, weight, key):
+                    return extern("dw", key, grad_output, x, weight, weight.get_size())
+            except Exception:
+                ok = False
+        _DONE["mxfp8_bwd"] = ok
+        return ok
 
 
 def register_nvfp4_lowerings() -> bool:

@@ -273,17 +273,18 @@ def test_autotune_adapter_and_winner_cache(tmp_path):
     ctx = A.KernelContext("mxfp8_prequant_fwd", 8192, 28672, 4096)
     cands = adapter.candidates(ctx)
     # the library's own choice plus one candidate per built kernel that serves the shape
-    assert [c.gemm.schedule for c in cands] == ["auto", "single", "pair"]
+    assert [c.gemm.schedule for c in cands] == ["auto", "single", "pair", "fused_x"]
     assert all(adapter.rejection(c, ctx) is None for c in cands)
     small = adapter.candidates(A.KernelContext("mxfp8_prequant_fwd", 64, 8192, 4096))
-    assert [c.gemm.schedule for c in small] == ["auto", "single", "pair", "stream"]
+    assert [c.gemm.schedule for c in small] == ["auto", "single", "pair", "stream", "fused_x"]
     nv = A.make_nvfp4_dynamic_fwd_adapter()
     assert [c.gemm.schedule for c in nv.candidates(A.KernelContext("nvfp4_dynamic_fwd", 8, 8192, 8192))] == [
         "auto", "single", "pair", "stream"]
     assert adapter.decode(adapter.encode(cands[1])) == cands[1]
     assert A.pick(ctx, adapter, None, mode="off") == adapter.default(ctx)
     assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == adapter.default(ctx)
-    times = {adapter.encode(cands[0]): 2.0, adapter.encode(cands[1]): 1.0, adapter.encode(cands[2]): 1.5}
+    times = {adapter.encode(cands[0]): 2.0, adapter.encode(cands[1]): 1.0, adapter.encode(cands[2]): 1.5,
+             adapter.encode(cands[3]): 9.0}
     calls = []
 
     def evaluate(cfg):
@@ -291,7 +292,7 @@ def test_autotune_adapter_and_winner_cache(tmp_path):
         return A.TrialOutcome("ok", median_ms=times[adapter.encode(cfg)])
 
     best = A.pick(ctx, adapter, evaluate, mode="balanced", cache_dir=tmp_path)
-    assert best == cands[1] and len(calls) == 3
+    assert best == cands[1] and len(calls) == 4
     path = A.runtime_winner_path(ctx, tmp_path)
     assert path.name == "m8192_n28672_k4096_hot_default_rev1.json" and path.parent.name == "b200"
     assert A.pick(ctx, adapter, None, mode="cache", cache_dir=tmp_path) == cands[1]
@@ -404,3 +405,42 @@ def test_numa_local_is_a_no_op_without_a_gpu(monkeypatch):
     monkeypatch.setenv("RTXB_HOST_NUMA", "0")
     with host.numa_local(torch.device("cuda", 0)) as scope:
         assert scope.cpus is None and os.sched_getaffinity(0) == before
+
+
+def test_stored_winner_changes_what_the_module_runs(tmp_path):
+    """`autotune="cache"` on MXFP8Linear resolves the stored winner of the call's (M, N, K) (rtx/fp8.py:804-886,
+    rtx/autotune/winners.py:26-45): explain() names the winner's GEMM schedule for that M and the configured one for
+    an M without a winner; the quantizer settings of the module's own schedule are kept."""
+    import rtx_b200 as rtx
+    from rtx_b200 import autotune as A
+    from rtx_b200 import configs as C
+
+    n, k = 384, 256
+    adapter = A.ADAPTERS["mxfp8_prequant_fwd"]()
+    ctx = A.KernelContext("mxfp8_prequant_fwd", 512, n, k)
+    winner = C.MXFP8PrequantConfig(gemm=C.MXFP8GemmConfig.for_schedule("single"))
+    assert "fused_x" in C.MXFP8GemmConfig.SCHEDULES and any(
+        c.gemm.schedule == "fused_x" for c in adapter.candidates(ctx))
+    A.save_runtime_winner(ctx, adapter, winner, 0.123, tmp_path)
+    floor = C.MXFP8PrequantConfig(quant=C.MXFP8QuantConfig(scale_rounding="floor"))
+    tuned = rtx.MXFP8Linear(k, n, autotune="cache", autotune_cache_dir=tmp_path, dynamic_config=floor)
+    plain = rtx.MXFP8Linear(k, n, dynamic_config=floor)
+    hit, miss = tuned.explain(m=512), tuned.explain(m=256)
+    assert hit["gemm_schedule"] == "single" and hit["schedule_source"] == "stored winner"
+    assert miss["gemm_schedule"] == "auto" and miss["forward_key"] == plain.explain()["forward_key"]
+    assert hit["forward_key"] != miss["forward_key"]
+    assert C.config_from_key(hit["forward_key"]).quant.scale_rounding == "floor"
+    assert plain.explain(m=512)["gemm_schedule"] == "auto" and plain.explain()["autotune"] == "off"
+
+
+def test_install_as_rtx_aliases_the_package():
+    """Code written against the reference's package name imports this package after `install_as_rtx()`."""
+    import subprocess
+    import sys
+
+    code = ("import rtx_b200, torch; rtx_b200.install_as_rtx(); import rtx, rtx.fp8, rtx.formats; "
+            "assert rtx.MXFP8Linear is rtx_b200.MXFP8Linear and rtx.fp8.mxfp8_linear is rtx_b200.mxfp8_linear; "
+            "assert torch._rtx_mxfp8_launchers is torch._rtx_b200_launchers['mxfp8_fwd']; print('ok')")
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-2000:]

@@ -261,10 +261,14 @@ def test_torch_compile_fullgraph_matches_eager(dev):
         return [xx.grad.clone()] + [p.grad.clone() for p in model.parameters()]
 
     want = grads(model)
+    before = dict(inductor.CALLS)
     got = grads(torch.compile(model, fullgraph=True, dynamic=False))
     _done(dev)
     for a, b in zip(want, got):
         assert torch.equal(a, b)
+    # the backward of both layers is MXFP8 and reaches its kernels through the backward lowerings too
+    if inductor._DONE.get("mxfp8_bwd"):
+        assert inductor.CALLS.get("mxfp8_bwd", 0) >= before.get("mxfp8_bwd", 0) + 2
 
 
 def test_runtime_caches_clear(dev):
@@ -377,7 +381,7 @@ def test_autotune_picks_among_the_built_kernels(dev, tmp_path):
     adapter = A.make_mxfp8_prequant_fwd_adapter()
     ctx = A.KernelContext("mxfp8_prequant_fwd", m, n, k)
     cands = adapter.candidates(ctx)
-    assert [c.gemm.schedule for c in cands] == ["auto", "single", "pair", "stream"]
+    assert [c.gemm.schedule for c in cands] == ["auto", "single", "pair", "stream", "fused_x"]
     outs = {}
 
     def evaluate(cfg):
@@ -393,7 +397,7 @@ def test_autotune_picks_among_the_built_kernels(dev, tmp_path):
 
     best = A.pick(ctx, adapter, evaluate, mode="balanced", cache_dir=tmp_path)
     _done(dev)
-    assert set(outs) == {"auto", "single", "pair", "stream"}
+    assert set(outs) == {"auto", "single", "pair", "stream", "fused_x"}
     for name, out in outs.items():
         assert torch.equal(out, outs["auto"]), name
     _close(outs["auto"], O.mxfp8_linear(x.cpu(), w.cpu()))
@@ -407,6 +411,45 @@ def test_autotune_picks_among_the_built_kernels(dev, tmp_path):
         _done(dev)
         ref = y if ref is None else ref
         assert torch.equal(y, ref), cfg.gemm.schedule
+
+
+def test_module_tunes_on_first_use_and_reuses_the_stored_winner(dev, tmp_path):
+    """`autotune="balanced"` on the module: the first call with a new M times the legal schedules on the
+    call's own operands and stores the winner; a second module in `cache` mode picks it up; outputs are
+    the bits of an untuned module whatever schedule won (rtx/fp8.py:804-886, 2302-2386)."""
+    import rtx_b200 as rtx
+    from rtx_b200 import autotune as A
+
+    torch.manual_seed(11)
+    k, n = 512, 768
+    plain = rtx.MXFP8Linear(k, n, device=dev)
+    tuned = rtx.MXFP8Linear(k, n, device=dev, autotune="balanced", autotune_cache_dir=tmp_path)
+    cached = rtx.MXFP8Linear(k, n, device=dev, autotune="cache", autotune_cache_dir=tmp_path)
+    packed = rtx.MXFP8Linear(k, n, device=dev, autotune="balanced", autotune_cache_dir=tmp_path,
+                             packed_weight=rtx.quantize_mxfp8(plain.weight.detach()))
+    with torch.no_grad():
+        tuned.weight.copy_(plain.weight)
+        cached.weight.copy_(plain.weight)
+        x = torch.randn(320, k).bfloat16().to(dev)
+        want = plain(x)
+        got = tuned(x)
+        again = tuned(x)
+        _done(dev)
+        path = A.runtime_winner_path(A.KernelContext("mxfp8_prequant_fwd", 320, n, k), tmp_path)
+        assert path.exists()
+        assert tuned.explain(m=320)["schedule_source"] == "tuned on first use"
+        assert cached.explain(m=320)["schedule_source"] == "stored winner"
+        assert cached.explain(m=320)["gemm_schedule"] == tuned.explain(m=320)["gemm_schedule"]
+        assert torch.equal(got, want) and torch.equal(again, want) and torch.equal(cached(x), want)
+        assert torch.equal(packed(x), want)          # the packed-weight state tunes its own family variant
+        assert A.runtime_winner_path(A.KernelContext("mxfp8_prequant_fwd", 320, n, k, variant="weight_prequant"),
+                                     tmp_path).exists()
+    _done(dev)
+    # training through a tuned module: the winner's key travels into the autograd op
+    xg = torch.randn(320, k).bfloat16().to(dev).requires_grad_(True)
+    tuned(xg).sum().backward()
+    _done(dev)
+    assert xg.grad is not None and tuned.weight.grad is not None
 
 
 def test_quantized_weight_cache_is_bit_identical(dev):
