@@ -79,7 +79,8 @@ struct MapKey {
   uint64_t stride[2];   // bytes, dimensions 1 and 2
   uint32_t box[3];
   uint32_t rank;        // 2 or 3
-  uint32_t words;       // 0: bytes with the 128-byte swizzle (payload); 1: 32-bit words, no swizzle (scale tiles)
+  uint32_t words;       // 0: bytes with the 128-byte swizzle (payload); 1: 32-bit words, no swizzle (scale tiles);
+                        // 2 / 3: 16-bit / 32-bit elements with the 64-byte swizzle (output tiles of the epilogue)
 };
 
 struct MapSlot {
@@ -106,10 +107,13 @@ int encode_map(CUtensorMap* out, const MapKey& key, const char* what) {
   cuuint64_t gstride[2] = {key.stride[0], key.stride[1]};
   cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
   cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = fn(out, key.words ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, key.rank,
-                  const_cast<void*>(key.base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  key.words ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  static const CUtensorMapDataType kTypes[4] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT32,
+                                               CU_TENSOR_MAP_DATA_TYPE_UINT16, CU_TENSOR_MAP_DATA_TYPE_UINT32};
+  static const CUtensorMapSwizzle kSwizzles[4] = {CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_SWIZZLE_64B};
+  CUresult r = fn(out, kTypes[key.words & 3], key.rank, const_cast<void*>(key.base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, kSwizzles[key.words & 3], CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what,
              static_cast<int>(r));
@@ -190,6 +194,20 @@ int make_scale_map_halves(CUtensorMap* map, const void* base, int64_t total_tile
   k.box[1] = static_cast<uint32_t>(box_rows);
   k.box[2] = 2u;
   return encode_map(map, k, "scale halves");
+}
+
+// output matrix [rows, cols] of 2- or 4-byte elements, row pitch ldo elements; boxes of 32 rows x 64 bytes
+// with the 64-byte swizzle (what an epilogue warp stages per store); stores are clipped at the edges
+int make_out_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ldo, int elem_bytes) {
+  MapKey k = blank_key(base);
+  k.rank = 2;
+  k.words = elem_bytes == 2 ? 2 : 3;
+  k.dim[0] = static_cast<uint64_t>(cols);
+  k.dim[1] = static_cast<uint64_t>(rows);
+  k.stride[0] = static_cast<uint64_t>(ldo) * elem_bytes;
+  k.box[0] = static_cast<uint32_t>(64 / elem_bytes);
+  k.box[1] = 32u;
+  return encode_map(map, k, "output");
 }
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device instead of per launch
@@ -313,6 +331,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.ldo = ldo;
   p.out_cols = static_cast<int>(out_cols);
   p.out_vec_ok = (aligned(out, 16) && (ldo * (EPI == kEpiF32 ? 4 : 2)) % 16 == 0) ? 1 : 0;
+  p.tma_out = 0;
   p.out_scale = out_scale;
   p.x_region_scales = regions ? regions->x : nullptr;
   p.w_region_scales = regions ? regions->w : nullptr;
@@ -365,6 +384,14 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     using P = PairTraits<KIND>;
     constexpr int KS = P::kStepsPerBarrierP;
     CUtensorMap map_sfa, map_sfb;
+    // BF16 / FP32 tiles leave through shared memory and TMA stores when the output can be described by a
+    // tensor map (16-byte aligned base and pitch); ragged pitches keep the direct stores
+    CUtensorMap map_out = {};
+    p.tma_out = (!epi_is_glu(EPI) && out != nullptr && p.out_vec_ok) ? 1 : 0;
+    if (p.tma_out) {
+      rc = make_out_map(&map_out, out, m, out_cols, ldo, EPI == kEpiF32 ? 4 : 2);
+      if (rc) return rc;
+    }
     // one load per operand brings the KS K steps of a barrier group
     p.map3d = row_bytes % 128 == 0 ? 1 : 0;
     if (p.map3d) {
@@ -396,7 +423,7 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles;
     const int max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(pair_tiles < max_pairs ? pair_tiles : max_pairs);
-    pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, p);
+    pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, map_out, p);
     RTXB_CHECK_LAUNCH("gemm_blockscaled_pair_kernel");
     return RTXB_OK;
   }

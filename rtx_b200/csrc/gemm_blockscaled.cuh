@@ -48,6 +48,10 @@ constexpr int kSingleStepsMx = 2, kSingleStepsNv = 1;
 constexpr int kPairStepsMx = 2, kPairStepsNv = 1;
 constexpr int kPairSlotsMx = 6, kPairSlotsNv = 5;
 constexpr int kGemmThreads = 192;
+// Output staging for the TMA-store epilogue: per epilogue warp two buffers of 32 rows x 64 bytes
+// (64-byte swizzle), so one 32-column BF16 chunk is in flight to global memory while the next is written.
+constexpr int kEpiStageBufBytes = 32 * 64;
+constexpr int kEpiStageBytes = 4 * 2 * kEpiStageBufBytes;   // 16 KB
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 
@@ -76,6 +80,8 @@ struct GemmTraits {
   static constexpr int kOffSfa = kOffB + kStages * kBBytes;
   static constexpr int kOffSfb = kOffSfa + kStages * kSfaBytes;
   static constexpr int kOffBars = kOffSfb + kStages * kSfbBytes;
+  // no output staging here: with four ring slots of 48 KB the NVFP4 form already fills shared memory, and this
+  // kernel serves single row blocks (M <= 128), whose output is small; it keeps the direct stores
   static constexpr int kSmemBytes = kOffBars + 1024 /*align slack*/ + 256 /*barriers*/;
   static constexpr int kStepsPerBarrier = KIND == kKindMxfp8 ? kSingleStepsMx : kSingleStepsNv;
   static constexpr uint32_t kIdesc =
@@ -95,6 +101,7 @@ struct GemmParams {
   int64_t ldo;
   int out_cols;           // n, or inter for GLU
   int out_vec_ok;         // 1 when out and its row pitch are 16-byte aligned (vector stores allowed)
+  int tma_out;            // 1: BF16 / FP32 outputs leave through shared memory and TMA stores (needs out_vec_ok)
   const float* out_scale; // device scalar or nullptr (= 1)
   const float* x_region_scales;  // kEpiRegionBf16: FP32 outer scale per x_region_rows rows of A
   const float* w_region_scales;  // kEpiRegionBf16: FP32 outer scale per w_region_rows rows of B (output columns)
@@ -143,7 +150,8 @@ __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* out, int col, int ou
 // signalled as soon as they are in registers.
 template <int KIND, int EPI>
 __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tacc, int row, bool row_ok, int n_idx,
-                                               bool odd, uint32_t overlap_bar_addr, float out_scale, int lane) {
+                                               bool odd, uint32_t overlap_bar_addr, float out_scale, int lane,
+                                               const CUtensorMap* map_out = nullptr, uint8_t* stage = nullptr) {
   using TP = TmemPlan<KIND>;
   if (epi_is_glu(EPI)) {
     // accumulator columns [0,128) = gate, [128,256) = up of the same 128 output columns; pairs of
@@ -211,93 +219,122 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
   } else {
     const int shared0 = odd ? 0 : TP::kAccWindow1;  // local column where the shared columns start
     const int col_base = n_idx * kBlockN;
+    const bool staged = p.tma_out != 0;
+    // The 32-column groups both windows share are read into registers first, all of them, and the next
+    // tile's MMAs are released before any of this tile's values is converted or stored.
+    uint32_t held[TP::kOverlapChunks][32];
+#pragma unroll
+    for (int i = 0; i < TP::kOverlapChunks; ++i) tmem_ld_32x32(tacc + (shared0 + 32 * i) % kAccCols, held[i]);
+    tmem_ld_wait();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(overlap_bar_addr);
+    const int last_region = EPI == kEpiRegionBf16 ? (p.out_cols - 1) / p.w_region_rows : 0;
+    // converts and stores one 32-column group `r` (local column c, i-th group visited)
+    auto emit = [&](const int c, const int i, const uint32_t (&r)[32]) {
+      if (!staged && !row_ok) return;
+      const int col = col_base + c;
+      // per-column factors: the launch-wide (or this row's) scale, times the column's region scale for the
+      // NVFP4 row-region policy (the product of the two outer scales is formed first, then applied:
+      // rtx/kernels/mxfp8_gemm.py:1720-1760; column scales are warp-uniform loads)
+      float v[32];
+      if (EPI == kEpiRegionBf16) {
+        if (p.w_region_rows == 4) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const float f = out_scale * __ldg(p.w_region_scales + min((col >> 2) + g, last_region));
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[4 * g + e] = __uint_as_float(r[4 * g + e]) * f;
+          }
+        } else {
+          int widx = col / p.w_region_rows, wrem = col - widx * p.w_region_rows;
+          float f = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            v[e] = __uint_as_float(r[e]) * f;
+            if (++wrem == p.w_region_rows) {
+              wrem = 0;
+              ++widx;
+              f = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * out_scale;
+      }
+      if (EPI == kEpiF32) {
+        if (staged) {
+          // two halves of 16 columns (64 bytes per row) = the two staging buffers, one store group
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<float4*>(stage + h * kEpiStageBufBytes + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                  make_float4(v[16 * h + 4 * j], v[16 * h + 4 * j + 1], v[16 * h + 4 * j + 2], v[16 * h + 4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(map_out, stage, col, row - lane);
+            tma_store_2d(map_out, stage + kEpiStageBufBytes, col + 16, row - lane);
+            tma_store_commit();
+          }
+        } else {
+          float* out = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            if (p.out_vec_ok && col + e + 4 <= p.out_cols) {
+              *reinterpret_cast<float4*>(out + col + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            } else {
+              for (int q = 0; q < 4; ++q)
+                if (col + e + q < p.out_cols) out[col + e + q] = v[e + q];
+            }
+          }
+        }
+      } else {
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+          w[e] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        if (staged) {
+          // this chunk's 32 rows x 64 bytes go to buffer i & 1; the store that read it two chunks ago is done
+          uint8_t* buf = stage + (i & 1) * kEpiStageBufBytes;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(map_out, buf, col, row - lane);
+            tma_store_commit();
+          }
+        } else {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t ww[4] = {w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]};
+            store_bf16x8(out, col + 8 * q, p.out_cols, p.out_vec_ok != 0, ww);
+          }
+        }
+      }
+    };
+    // the shared groups first (already in registers), then the rest in order
+#pragma unroll
+    for (int i = 0; i < TP::kOverlapChunks; ++i) emit((shared0 + 32 * i) % kAccCols, i, held[i]);
 #pragma unroll 1
-    for (int i = 0; i < kAccCols / 32; ++i) {
-      // visit the shared 32-column groups first, then the rest in order
+    for (int i = TP::kOverlapChunks; i < kAccCols / 32; ++i) {
       const int c = (shared0 + 32 * i) % kAccCols;
       uint32_t r[32];
       tmem_ld_32x32(tacc + c, r);
       tmem_ld_wait();
-      if (i == TP::kOverlapChunks - 1) {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(overlap_bar_addr);
-      }
-      if (!row_ok) continue;
-      const int col = col_base + c;
-      if (EPI == kEpiRegionBf16) {
-        // the product of the row's and the column's region scale is formed first, then applied to the
-        // accumulator (rtx/kernels/mxfp8_gemm.py:1720-1760); `out_scale` carries this row's scale.
-        // Column scales are the same for every thread of the warp (broadcast loads).
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
-        const int last_region = (p.out_cols - 1) / p.w_region_rows;
-        if (p.w_region_rows == 4) {
-          // the default geometry: these 32 columns are exactly eight regions
-          float fac[8];
-#pragma unroll
-          for (int g = 0; g < 8; ++g) fac[g] = out_scale * __ldg(p.w_region_scales + min((col >> 2) + g, last_region));
-#pragma unroll
-          for (int v = 0; v < 32; v += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[v + 2 * e]) * fac[(v + 2 * e) >> 2],
-                                                       __uint_as_float(r[v + 2 * e + 1]) * fac[(v + 2 * e + 1) >> 2]);
-              w[e] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            store_bf16x8(out, col + v, p.out_cols, p.out_vec_ok != 0, w);
-          }
-          continue;
-        }
-        int widx = col / p.w_region_rows, wrem = col - widx * p.w_region_rows;
-        float factor = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
-#pragma unroll
-        for (int v = 0; v < 32; v += 8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float f[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              f[h] = __uint_as_float(r[v + 2 * e + h]) * factor;
-              if (++wrem == p.w_region_rows) {
-                wrem = 0;
-                ++widx;
-                factor = out_scale * __ldg(p.w_region_scales + min(widx, last_region));
-              }
-            }
-            __nv_bfloat162 b = __floats2bfloat162_rn(f[0], f[1]);
-            w[e] = *reinterpret_cast<uint32_t*>(&b);
-          }
-          store_bf16x8(out, col + v, p.out_cols, p.out_vec_ok != 0, w);
-        }
-      } else if (EPI == kEpiBf16) {
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo;
-#pragma unroll
-        for (int v = 0; v < 32; v += 8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[v + 2 * e]) * out_scale,
-                                                     __uint_as_float(r[v + 2 * e + 1]) * out_scale);
-            w[e] = *reinterpret_cast<uint32_t*>(&b);
-          }
-          store_bf16x8(out, col + v, p.out_cols, p.out_vec_ok != 0, w);
-        }
-      } else {
-        float* out = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo;
-#pragma unroll
-        for (int v = 0; v < 32; v += 4) {
-          if (p.out_vec_ok && col + v + 4 <= p.out_cols) {
-            *reinterpret_cast<float4*>(out + col + v) =
-                make_float4(__uint_as_float(r[v]) * out_scale, __uint_as_float(r[v + 1]) * out_scale,
-                            __uint_as_float(r[v + 2]) * out_scale, __uint_as_float(r[v + 3]) * out_scale);
-          } else {
-            for (int e = 0; e < 4; ++e)
-              if (col + v + e < p.out_cols) out[col + v + e] = __uint_as_float(r[v + e]) * out_scale;
-          }
-        }
-      }
+      emit(c, i, r);
     }
   }
 }
@@ -607,7 +644,8 @@ struct PairTraits {
   static constexpr int kOffSfa = kOffB + kStagesP * kBBytes;
   static constexpr int kOffSfb = kOffSfa + kStagesP * kSfaBytes;
   static constexpr int kOffBars = kOffSfb + kStagesP * kSfbBytes;
-  static constexpr int kSmemBytes = kOffBars + 1024 + 256;
+  static constexpr int kOffStage = kOffBars + 1024;
+  static constexpr int kSmemBytes = kOffStage + kEpiStageBytes + 1024;
   static constexpr int kTxBytesPerCta = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr uint32_t kIdesc =
       idesc_block_scaled(256, 256, KIND == kKindMxfp8 ? 0u : 1u, KIND == kKindMxfp8 ? 1u : 0u);
@@ -617,7 +655,7 @@ template <int KIND, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                             const GemmParams p) {
+                             const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using T = PairTraits<KIND>;
   using TP = TmemPlan<KIND>;
   constexpr int S = T::kStagesP;
@@ -766,8 +804,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
       const float row_scale = (EPI == kEpiRegionBf16 && row_ok) ? __ldg(p.x_region_scales + row / p.x_region_rows)
                                                                 : out_scale;
       epilogue_drain<KIND, EPI>(p, tmem_base + lane_base + acc_col, row, row_ok, n_idx, (local_tile & 1) != 0,
-                                overlap_addr, row_scale, lane);
+                                overlap_addr, row_scale, lane, &map_out,
+                                smem + T::kOffStage + quad * 2 * kEpiStageBufBytes);
     }
+    if (p.tma_out && lane == 0) tma_store_wait_all<0>();   // shared memory outlives the last store's reads
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------
