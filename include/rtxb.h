@@ -198,6 +198,14 @@ int rtxb_mxfp8_linear_bwd(const void* dy_bf16, const void* x_bf16, const void* w
                           int dw_dtype, int64_t m, int64_t n, int64_t k, void* workspace, size_t workspace_bytes,
                           void* stream, int* status);
 
+/* compile_mxfp8_workspace_reduce(m, n, split, algorithm="serial", ...) -> (ws f32 [split, m, n], out bf16)
+ *   rtx/kernels/mxfp8_reduce.py:20-104; bound at rtx/fp8_bwd.py:351-386, :464-495.
+ * out[i] = bf16(parts[0][i] + parts[1][i] + ...), parts `part_stride` floats apart, summed in index order and
+ * rounded once.  The reference reduces the partial tiles of its split-K GEMMs with it; here it sums the per-rank
+ * FP32 blocks of dW that the data-parallel backward collects in the owner's staging slots. */
+int rtxb_sum_parts_f32_to_bf16(const float* parts, int n_parts, int64_t part_stride, int64_t count, void* out_bf16,
+                               void* stream);
+
 /* ---- NVFP4 -----------------------------------------------------------------
  * Outer scale: the reference computes it with PyTorch reductions
  * (_outer_tensor_scale, rtx/fp4.py:343-365).  rtxb_nvfp4_tensor_scale does the

@@ -16,6 +16,7 @@
 #include "quant.cuh"
 #include "gemm_decode_fused.cuh"
 #include "gemm_fused_quant.cuh"
+#include "reduce.cuh"
 
 using namespace rtxb;
 
@@ -887,6 +888,21 @@ int rtxb_mxfp8_glu_mlp_fwd(const void* x, const void* w_gu, const void* w_down, 
   else rc = rtxb_mxfp8_gemm_glu_mx(qx, sx, qg, sg, h, qh, sh, m, inter, k, inter, stream, status);
   if (rc) return rc;
   return rtxb_mxfp8_gemm(qh, sh, qd, sd, y, m, n_out, inter, n_out, RTXB_OUT_BF16, stream, status);
+}
+
+int rtxb_sum_parts_f32_to_bf16(const float* parts, int n_parts, int64_t part_stride, int64_t count, void* out_bf16,
+                               void* stream) {
+  if (!parts || !out_bf16) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (n_parts <= 0 || count <= 0 || part_stride < count) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (!aligned(parts, 16) || !aligned(out_bf16, 16) || part_stride % 4 != 0)
+    return fail_msg(RTXB_E_ALIGNMENT, "partials and output must be 16-byte aligned, parts a multiple of 4 floats apart");
+  const int64_t ctas = (count / 8 + kReduceThreads - 1) / kReduceThreads;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int grid = static_cast<int>(ctas < 1 ? 1 : (ctas < cap ? ctas : cap));
+  sum_parts_f32_to_bf16_kernel<<<grid, kReduceThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      parts, n_parts, part_stride, count, static_cast<__nv_bfloat16*>(out_bf16));
+  RTXB_CHECK_LAUNCH("sum_parts_f32_to_bf16_kernel");
+  return RTXB_OK;
 }
 
 size_t rtxb_mxfp8_backward_workspace_bytes(int64_t m, int64_t n, int64_t k) {

@@ -268,6 +268,21 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
     return dx, dw
 
 
+def sum_parts_f32_to_bf16(parts: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """parts f32 [S, ...] contiguous -> bf16 [...]: the S partial sums added in index order, one rounding."""
+    if parts.dtype is not torch.float32 or not parts.is_contiguous() or parts.dim() < 2:
+        raise ValueError("parts must be a contiguous FP32 tensor [S, ...]")
+    count = parts[0].numel()
+    if out is None:
+        out = torch.empty(parts.shape[1:], dtype=torch.bfloat16, device=parts.device)
+    if out.numel() != count or out.dtype is not torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous BF16 tensor with one part's element count")
+    with torch.cuda.device(parts.device):
+        N.call("rtxb_sum_parts_f32_to_bf16", parts.data_ptr(), int(parts.shape[0]), count, count, out.data_ptr(),
+               _stream_ptr())
+    return out
+
+
 # ---------------------------------------------------------------------------
 # Launch controls: GEMM schedule of the calling thread, SM margin of the process
 # ---------------------------------------------------------------------------

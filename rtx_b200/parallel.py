@@ -107,6 +107,109 @@ def _banded_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.T
     return dx, dw
 
 
+# ---------------------------------------------------------------------------------------------------------
+# dW reduce-scatter through peer memory
+# ---------------------------------------------------------------------------------------------------------
+# Every rank owns a contiguous block of N / world rows of dW.  A rank's dW GEMM for block o writes its FP32
+# partial straight into slot [rank] of owner o's staging buffer: the GEMM epilogue's TMA stores go over NVLink,
+# so the "reduce-scatter" traffic IS the GEMM's output traffic and overlaps the MMAs tile by tile (no NCCL
+# kernel, no SMs taken from the GEMM).  Once every rank's GEMMs are done (a one-word NCCL all-reduce is the
+# barrier) the owner sums its `world` slots in rank order, rounds once to BF16
+# (rtxb_sum_parts_f32_to_bf16) and the BF16 blocks are all-gathered in place: 2 bytes per element cross
+# NVLink in the second phase instead of 4, beside the dX GEMM.
+# Peer buffers come from torch.distributed's symmetric memory (plain peer mappings; NVLink multicast is not
+# bound).  Shapes whose rows do not split into whole 256-row tiles per rank, and processes where symmetric
+# memory is not available, take the banded NCCL all-reduce above.
+
+P2P_REDUCE_SCATTER = os.environ.get("RTXB_DW_P2P", "1") != "0"
+_P2P_STATES: dict = {}
+
+
+class _PeerReduceScatter:
+    """Staging slots of one (device, N, K, group): `slots[s]` on this rank receives rank s's partial of
+    the block this rank owns; `peer_slot[o]` is this rank's slot in owner o's buffer."""
+
+    def __init__(self, n: int, k: int, device: torch.device, group):
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.rows = n // self.world
+        self.n, self.k = n, k
+        block = self.rows * k
+        self.stage = symm.empty(self.world * block, dtype=torch.float32, device=device)
+        self.handle = symm.rendezvous(self.stage, self.group)
+        self.slots = self.stage.view(self.world, self.rows, k)
+        self.peer_slot = [self.handle.get_buffer(o, (self.rows, k), torch.float32, self.rank * block)
+                          for o in range(self.world)]
+        self.comm = torch.cuda.Stream(device)
+        self.side = torch.cuda.Stream(device)          # second lane for concurrent block GEMMs
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+
+
+def p2p_block_rows(n: int, world: int) -> int:
+    """Rows of dW each rank owns for the peer-memory reduce-scatter, or 0 when N does not split into
+    whole 256-row tiles per rank."""
+    return n // world if world > 1 and n % (256 * world) == 0 else 0
+
+
+def _peer_state(n: int, k: int, device: torch.device, group):
+    key = (device.index, n, k, id(group))
+    state = _P2P_STATES.get(key)
+    if state is None:
+        try:
+            state = _PeerReduceScatter(n, k, device, group)
+        except Exception as exc:   # symmetric memory unavailable here: remember and use NCCL
+            state = exc
+        _P2P_STATES[key] = state
+    return None if isinstance(state, Exception) else state
+
+
+def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, st: "_PeerReduceScatter"):
+    from . import _native as N
+    from . import ops
+
+    m, n = grad_output.shape
+    k = x.shape[1]
+    main = torch.cuda.current_stream(x.device)
+    q_dy, s_dy, q_dyt, s_dyt = ops.mxfp8_quantize_dual(grad_output)
+    q_xt, s_xt = ops.mxfp8_quantize_transposed(x)
+    chunks = ops.mxfp8_scale_numel(128, m, N.SCALE_MMA128)
+    rows, world, rank = st.rows, st.world, st.rank
+    # two block GEMMs side by side when one block is at most half a wave of CTA pairs
+    tiles = (rows // 256) * ((k + 255) // 256)
+    lanes = 2 if 2 * tiles <= 148 // 2 else 1
+    ready = torch.cuda.Event()
+    ready.record(main)
+    st.side.wait_event(ready)
+    for i in range(world):
+        o = (rank + 1 + i) % world          # neighbours first, the own block last: peers are not all hit at once
+        stream = st.side if (lanes == 2 and i % 2 == 1) else main
+        with torch.cuda.stream(stream):
+            ops.mxfp8_gemm(q_dyt[o * rows:(o + 1) * rows], s_dyt[(o * rows // 128) * chunks:], q_xt, s_xt, rows, k, m,
+                           out=st.peer_slot[o])
+    main.wait_stream(st.side)
+    done = torch.cuda.Event()
+    done.record(main)
+    dw = torch.empty(n, k, dtype=torch.bfloat16, device=x.device)
+    mine = dw[rank * rows:(rank + 1) * rows]
+    st.comm.wait_event(done)
+    with torch.cuda.stream(st.comm):
+        dist.all_reduce(st.token, group=st.group)             # every rank's partials have landed everywhere
+        ops.sum_parts_f32_to_bf16(st.slots, mine)
+        dist.all_gather_into_tensor(dw, mine, group=st.group)
+    with ops.sm_margin(OVERLAP_SM_MARGIN):
+        q_wt, s_wt = ops.mxfp8_quantize_transposed(weight)
+        dx = ops.mxfp8_gemm(q_dy, s_dy, q_wt, s_wt, m, k, n)
+    main.wait_stream(st.comm)
+    # tensors used on other streams stay alive until those streams are done with them
+    for t in (q_dyt, s_dyt, q_xt, s_xt):
+        t.record_stream(st.side)
+    dw.record_stream(st.comm)
+    return dx, dw
+
+
 def data_parallel_linear_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, *,
                                   group: Optional[dist.ProcessGroup] = None, compute=None):
     """dX (local rows, BF16) and dW (summed over ranks, BF16) for this rank's row shard.
@@ -130,5 +233,20 @@ def data_parallel_linear_backward(grad_output: torch.Tensor, x: torch.Tensor, we
 
     if alone:
         return ops.mxfp8_linear_bwd(grad_output, x, weight, _fp8._workspace(grad_output.device))
+    n, k = grad_output.shape[1], x.shape[1]
+    if P2P_REDUCE_SCATTER and p2p_block_rows(n, dist.get_world_size(group)):
+        state = _peer_state(n, k, grad_output.device, group)
+        if state is not None:
+            return _peer_backward(grad_output, x, weight, state)
     dx, dw = _banded_backward(grad_output, x, weight, group)
     return dx, dw.to(torch.bfloat16)
+
+
+def backward_collective(n: int, k: int, device: torch.device, group=None) -> str:
+    """Which route `data_parallel_linear_backward` takes for an [n, k] dW on this process (for reports)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return "none (one rank)"
+    if P2P_REDUCE_SCATTER and p2p_block_rows(n, dist.get_world_size(group)) and _peer_state(n, k, device, group):
+        return ("reduce-scatter in the dW GEMM epilogue (FP32 TMA stores into the owner's slots over NVLink), "
+                "owner sums and rounds once, BF16 all-gather (NCCL) beside dX")
+    return "NCCL all-reduce(sum) of FP32 dW per band of rows behind the dW GEMM"

@@ -24,7 +24,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str):
+def _worker(rank: int, world: int, port: int, out_dir: str, route: str):
     os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -36,21 +36,28 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         x, w, dy = inp["x"], inp["w"], inp["dy"]
         xs = parallel.shard_rows(x, rank, world).to(dev)
         gs = parallel.shard_rows(dy, rank, world).to(dev)
-        parallel.DW_BAND_ROWS = 256          # four bands of dW, four all-reduces
-        dx, dw = parallel.data_parallel_linear_backward(gs, xs, w.to(dev))
+        parallel.DW_BAND_ROWS = 256          # NCCL route: four bands of dW, four all-reduces
+        parallel.P2P_REDUCE_SCATTER = route == "peer"
+        for _ in range(3):                    # repeated steps reuse the staging slots
+            dx, dw = parallel.data_parallel_linear_backward(gs, xs, w.to(dev))
         torch.cuda.synchronize()
         ops.check_device_status(dev)
+        took = parallel.backward_collective(1024, 384, dev)
+        assert took.startswith("reduce-scatter" if route == "peer" else "NCCL all-reduce"), took
         torch.save({"dx": dx.cpu(), "dw": dw.cpu()}, os.path.join(out_dir, f"rank{rank}.pt"))
         dist.barrier(device_ids=[rank])
     finally:
         dist.destroy_process_group()
 
 
-def test_dw_all_reduce_matches_single_gpu_two_ranks(tmp_path):
+@pytest.mark.parametrize("route", ["peer", "nccl"])
+def test_dw_all_reduce_matches_single_gpu_two_ranks(tmp_path, route):
+    """Both routes of the data-parallel dW: the reduce-scatter through peer memory inside the GEMM epilogue
+    (+ BF16 all-gather) and the banded NCCL all-reduce."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True,
+    mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path), route), nprocs=world, join=True,
                        start_method="spawn")
     inp = O.make_inputs(4, m=512, n=1024, k=384)    # dW [1024, 384]: several bands, each with its own all-reduce
     x, w, dy = inp["x"], inp["w"], inp["dy"]

@@ -70,6 +70,15 @@ def test_shard_bounds_reject_partial_mx_blocks():
     assert P.all_reduce_dw(torch.zeros(2, 2)) is None      # no process group: nothing to do
 
 
+def test_peer_reduce_scatter_block_rows():
+    from rtx_b200 import parallel as P
+
+    assert P.p2p_block_rows(4096, 8) == 512 and P.p2p_block_rows(4096, 2) == 2048
+    assert P.p2p_block_rows(4096, 1) == 0          # one rank: nothing to scatter
+    assert P.p2p_block_rows(1000, 2) == 0          # ragged: blocks must be whole 256-row tiles
+    assert P.backward_collective(4096, 4096, torch.device("cpu")) == "none (one rank)"
+
+
 def test_dw_bands_cover_the_rows_in_whole_tile_rows():
     from rtx_b200 import parallel as P
 
