@@ -402,6 +402,7 @@ def run_own_arm(args) -> None:
                       "against": "the unsharded rtxb_mxfp8_linear_bwd on the same 16384 rows (rank 0's comparison)"}
         del x_all, dy_all, dx_1, dw_1, dx_r, dw_r
     del bwd, shards
+    bwd_route = parallel.backward_collective(BWD_N, BWD_K, dev)
 
     clocks = sampler.stop()
     res = timer.reduce(dev)
@@ -435,8 +436,7 @@ def run_own_arm(args) -> None:
             "metric": "fused quant+GEMM TFLOPS (MXFP8 backward dX + dW, operand quantizations and the dW all-reduce included)",
             "workload": f"mxfp8_linear_bwd_m{BWD_M}_n{BWD_N}_k{BWD_K}",
             "api": "rtx_b200.parallel.data_parallel_linear_backward",
-            "collective": (f"NCCL all-reduce(sum) of the FP32 dW ({BWD_N * BWD_K * 4 / 1e6:.0f} MB), issued per band of dW "
-                           f"rows as the dW GEMM finishes it, beside the rest of the step" if world > 1 else "none (1 GPU)"),
+            "collective": bwd_route,
             "strong": {"rows_per_gpu": bper, "ms_per_step": res["bwd_strong"],
                        "value": bwd_flops / (res["bwd_strong"] * 1e-3) / 1e12, "unit": "TFLOP/s"},
         }

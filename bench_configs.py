@@ -186,8 +186,7 @@ def config4(args, rank, world, dev):
         "value": flops * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "ms_per_step": ms,
         "scaling": "weak", "dtype": "mxfp8 (e4m3 x e8m0), fp32 accumulate", "data": "synthetic",
         "config": {"workload": "mxfp8_linear_bwd_m16384_n4096_k4096", "m_per_gpu": m,
-                   "collective": (f"NCCL all-reduce(sum) of FP32 dW (67 MB) in bands of rows behind the dW GEMM, "
-                                  f"{parallel.OVERLAP_SM_MARGIN} SMs left to it") if world > 1 else "none"},
+                   "collective": parallel.backward_collective(n, k, dev)},
         "pct_of_nominal_fp8_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / NOMINAL["fp8"],
         "gpu_launches_per_step": 5 if world == 1 else 7,
         "roofline": {"kernel": "gemm_blockscaled_pair_kernel<mxfp8, f32> (dW, K = 16384)", "bound": "tensor",

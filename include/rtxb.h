@@ -118,6 +118,16 @@ int rtxb_mxfp8_quantize_dual(const void* src_bf16, int64_t m, int64_t n, int64_t
  * rtxb_mxfp8_storage_k(k) bytes apart. */
 int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
                     int64_t k, int64_t ldo, int out_dtype, void* stream, int* status);
+/* The same GEMM with its output split into n_blocks (<= 8) blocks of `block_rows` rows (a multiple of 256, the
+ * last block may be shorter), block j written to out_blocks[j] (a [rows, n] matrix of pitch ldo, 16-byte aligned).
+ * No counterpart in the reference (single GPU).  The buffers may live on other GPUs of the node (peer-mapped
+ * addresses): the epilogue's TMA stores then travel over NVLink while the MMAs of the next tile run, which is how
+ * the data-parallel backward turns the reduce-scatter of dW into the GEMM's own output traffic.  The tile order
+ * starts at the tiles of block `first_block` so that ranks writing to one another begin at different owners.
+ * CTA-pair kernel only (m >= 256). */
+int rtxb_mxfp8_gemm_row_blocks(const void* qa, const void* sa, const void* qb, const void* sb, void* const* out_blocks,
+                               int n_blocks, int64_t block_rows, int64_t m, int64_t n, int64_t k, int64_t ldo,
+                               int out_dtype, int first_block, void* stream, int* status);
 /* SwiGLU gate/up projection with the activation fused into the epilogue:
  * qb holds [2*inter, K] (gate rows first); out bf16 [m, inter] =
  * silu(acc[:, :inter]) * acc[:, inter:], one BF16 rounding.  The reference

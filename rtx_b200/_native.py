@@ -49,6 +49,7 @@ SIGNATURES = {
     "rtxb_mxfp8_quantize_transposed": (_I, [_P, _L, _L, _L, _P, _P, _I, _I, _P]),
     "rtxb_mxfp8_quantize_dual": (_I, [_P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _P]),
     "rtxb_mxfp8_gemm": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
+    "rtxb_mxfp8_gemm_row_blocks": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _L, _L, _I, _I, _P, _P]),
     "rtxb_mxfp8_gemm_glu": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "rtxb_mxfp8_gemm_glu_mx": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "rtxb_mxfp8_linear_fwd_fused_x": (_I, [_P, _L, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),

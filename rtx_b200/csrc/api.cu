@@ -297,6 +297,14 @@ bool use_skinny_kernel(int m_tiles, int64_t n_rows_b) {
   return (n_rows_b + kBlockN - 1) / kBlockN < 74;
 }
 
+// output split into blocks of rows, each block its own buffer (pair kernel, TMA-store epilogue)
+struct BlockOutputs {
+  void* const* bases;   // n_blocks buffers of [block_rows, out_cols] elements, pitch ldo
+  int n_blocks;
+  int64_t block_rows;   // multiple of 256
+  int first_block;      // the tile order starts at the raster group that holds this block
+};
+
 // outer scales of the NVFP4 row-region policy (kEpiRegionBf16)
 struct RegionScales {
   const float* x;
@@ -308,7 +316,8 @@ template <int KIND, int EPI>
 int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n_rows_b,
                 int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
                 const float* out_scale, cudaStream_t stream, int* status, void* q_out = nullptr,
-                void* sf_out = nullptr, bool overlap_previous = false, const RegionScales* regions = nullptr) {
+                void* sf_out = nullptr, bool overlap_previous = false, const RegionScales* regions = nullptr,
+                const BlockOutputs* blocks = nullptr) {
   // overlap_previous: B and its scales do not depend on the kernel launched just before this one on
   // the stream, so the streaming kernel may start fetching them while that kernel is still running
   using T = GemmTraits<KIND>;
@@ -333,6 +342,8 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.out_cols = static_cast<int>(out_cols);
   p.out_vec_ok = (aligned(out, 16) && (ldo * (EPI == kEpiF32 ? 4 : 2)) % 16 == 0) ? 1 : 0;
   p.tma_out = 0;
+  p.out_block_rows = 0;
+  p.tile_shift = 0;
   p.out_scale = out_scale;
   p.x_region_scales = regions ? regions->x : nullptr;
   p.w_region_scales = regions ? regions->w : nullptr;
@@ -349,7 +360,9 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   p.sfb3d = 0;
   p.b_box256 = 0;
   p.overlap_previous = overlap_previous ? 1 : 0;
-  if (use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI) && EPI != kEpiRegionBf16) {
+  if (blocks != nullptr && !use_pair_kernel(p.m_tiles))
+    return fail_msg(RTXB_E_UNSUPPORTED, "block outputs are served by the CTA-pair kernel only");
+  if (blocks == nullptr && use_skinny_kernel(p.m_tiles, n_rows_b) && !epi_is_glu(EPI) && EPI != kEpiRegionBf16) {
     // one 128-row block of A: the bandwidth-shaped 128 x 64 kernel streams B once over all SMs
     using S = SkinnyTraits<KIND>;
     p.a_box_rows = static_cast<int>(round_up(m, 8));
@@ -387,10 +400,19 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     CUtensorMap map_sfa, map_sfb;
     // BF16 / FP32 tiles leave through shared memory and TMA stores when the output can be described by a
     // tensor map (16-byte aligned base and pitch); ragged pitches keep the direct stores
-    CUtensorMap map_out = {};
+    OutMaps maps_out = {};
     p.tma_out = (!epi_is_glu(EPI) && out != nullptr && p.out_vec_ok) ? 1 : 0;
-    if (p.tma_out) {
-      rc = make_out_map(&map_out, out, m, out_cols, ldo, EPI == kEpiF32 ? 4 : 2);
+    if (blocks != nullptr) {
+      if (!p.tma_out) return fail_msg(RTXB_E_ALIGNMENT, "block outputs need 16-byte aligned buffers and pitch");
+      for (int b = 0; b < blocks->n_blocks; ++b) {
+        const int64_t rows_b = m - b * blocks->block_rows < blocks->block_rows ? m - b * blocks->block_rows : blocks->block_rows;
+        if (!aligned(blocks->bases[b], 16)) return fail_msg(RTXB_E_ALIGNMENT, "block outputs must be 16-byte aligned");
+        rc = make_out_map(&maps_out.m[b], blocks->bases[b], rows_b, out_cols, ldo, EPI == kEpiF32 ? 4 : 2);
+        if (rc) return rc;
+      }
+      p.out_block_rows = static_cast<int>(blocks->block_rows);
+    } else if (p.tma_out) {
+      rc = make_out_map(&maps_out.m[0], out, m, out_cols, ldo, EPI == kEpiF32 ? 4 : 2);
       if (rc) return rc;
     }
     // one load per operand brings the KS K steps of a barrier group
@@ -424,7 +446,11 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles;
     const int max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(pair_tiles < max_pairs ? pair_tiles : max_pairs);
-    pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, map_out, p);
+    if (blocks != nullptr) {
+      const int64_t start_pair = static_cast<int64_t>(blocks->first_block) * (blocks->block_rows / 256);
+      p.tile_shift = static_cast<int>(((start_pair / p.group_m) * p.group_m * p.n_tiles) % pair_tiles);
+    }
+    pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, maps_out, p);
     RTXB_CHECK_LAUNCH("gemm_blockscaled_pair_kernel");
     return RTXB_OK;
   }
@@ -760,6 +786,31 @@ int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* 
   if (out_dtype == RTXB_OUT_BF16)
     return launch_gemm<kKindMxfp8, kEpiBf16>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status);
   return launch_gemm<kKindMxfp8, kEpiF32>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status);
+}
+
+int rtxb_mxfp8_gemm_row_blocks(const void* qa, const void* sa, const void* qb, const void* sb, void* const* out_blocks,
+                               int n_blocks, int64_t block_rows, int64_t m, int64_t n, int64_t k, int64_t ldo,
+                               int out_dtype, int first_block, void* stream, int* status) {
+  if (out_dtype != RTXB_OUT_BF16 && out_dtype != RTXB_OUT_F32)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown output dtype");
+  if (!out_blocks || n_blocks < 1 || n_blocks > kMaxOutBlocks)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "between 1 and 8 output blocks");
+  if (block_rows <= 0 || block_rows % 256 != 0 || (n_blocks - 1) * block_rows >= m || n_blocks * block_rows < m)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "blocks must be whole 256-row tiles that cover the m rows exactly");
+  if (m < 256) return fail_msg(RTXB_E_UNSUPPORTED, "block outputs need at least one 256-row tile");
+  for (int b = 0; b < n_blocks; ++b)
+    if (!out_blocks[b]) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null output block");
+  int rc = check_gemm_args(qa, sa, qb, sb, out_blocks[0], m, n, k, ldo, n, out_dtype == RTXB_OUT_BF16 ? 2 : 4);
+  if (rc) return rc;
+  const int64_t kp = round_up(k, 32);
+  const int64_t chunks = (kp / 32 + 3) / 4;
+  const BlockOutputs blocks{out_blocks, n_blocks, block_rows, first_block < 0 ? 0 : first_block % n_blocks};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == RTXB_OUT_BF16)
+    return launch_gemm<kKindMxfp8, kEpiBf16>(qa, sa, qb, sb, out_blocks[0], m, n, kp, chunks, ldo, n, 0, nullptr, s, status,
+                                             nullptr, nullptr, false, nullptr, &blocks);
+  return launch_gemm<kKindMxfp8, kEpiF32>(qa, sa, qb, sb, out_blocks[0], m, n, kp, chunks, ldo, n, 0, nullptr, s, status,
+                                          nullptr, nullptr, false, nullptr, &blocks);
 }
 
 int rtxb_mxfp8_gemm_glu(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m,

@@ -52,6 +52,14 @@ constexpr int kGemmThreads = 192;
 // (64-byte swizzle), so one 32-column BF16 chunk is in flight to global memory while the next is written.
 constexpr int kEpiStageBufBytes = 32 * 64;
 constexpr int kEpiStageBytes = 4 * 2 * kEpiStageBufBytes;   // 16 KB
+constexpr int kMaxOutBlocks = 8;
+struct OutMaps {
+  CUtensorMap m[kMaxOutBlocks];   // m[0]: the whole output, or one map per block of rows (GemmParams::out_block_rows)
+};
+__device__ __forceinline__ int rotate_tile(int tile, int shift, int total) {
+  tile += shift;
+  return tile >= total ? tile - total : tile;
+}
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 
@@ -102,6 +110,10 @@ struct GemmParams {
   int out_cols;           // n, or inter for GLU
   int out_vec_ok;         // 1 when out and its row pitch are 16-byte aligned (vector stores allowed)
   int tma_out;            // 1: BF16 / FP32 outputs leave through shared memory and TMA stores (needs out_vec_ok)
+  int out_block_rows;     // pair kernel, TMA outputs: > 0 = the output is split into blocks of this many rows (a
+                          // multiple of 256), block j described by output map j (e.g. buffers on different GPUs)
+  int tile_shift;         // pair kernel: the tile order is rotated by this many tiles (ranks that write blocks to
+                          // one another start at different owners)
   const float* out_scale; // device scalar or nullptr (= 1)
   const float* x_region_scales;  // kEpiRegionBf16: FP32 outer scale per x_region_rows rows of A
   const float* w_region_scales;  // kEpiRegionBf16: FP32 outer scale per w_region_rows rows of B (output columns)
@@ -151,7 +163,9 @@ __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* out, int col, int ou
 template <int KIND, int EPI>
 __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tacc, int row, bool row_ok, int n_idx,
                                                bool odd, uint32_t overlap_bar_addr, float out_scale, int lane,
-                                               const CUtensorMap* map_out = nullptr, uint8_t* stage = nullptr) {
+                                               const CUtensorMap* map_out = nullptr, uint8_t* stage = nullptr,
+                                               int out_row0 = 0) {
+  // out_row0: first row of the output block `map_out` describes (0 when it describes the whole output)
   using TP = TmemPlan<KIND>;
   if (epi_is_glu(EPI)) {
     // accumulator columns [0,128) = gate, [128,256) = up of the same 128 output columns; pairs of
@@ -277,8 +291,8 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(map_out, stage, col, row - lane);
-            tma_store_2d(map_out, stage + kEpiStageBufBytes, col + 16, row - lane);
+            tma_store_2d(map_out, stage, col, row - lane - out_row0);
+            tma_store_2d(map_out, stage + kEpiStageBufBytes, col + 16, row - lane - out_row0);
             tma_store_commit();
           }
         } else {
@@ -312,7 +326,7 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(map_out, buf, col, row - lane);
+            tma_store_2d(map_out, buf, col, row - lane - out_row0);
             tma_store_commit();
           }
         } else {
@@ -655,7 +669,7 @@ template <int KIND, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                             const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+                             const __grid_constant__ OutMaps maps_out, const GemmParams p) {
   using T = PairTraits<KIND>;
   using TP = TmemPlan<KIND>;
   constexpr int S = T::kStagesP;
@@ -714,7 +728,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
       bool ok = true;
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
         int mp_idx, n_idx;
-        tile_coords(tile, m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
+        tile_coords(rotate_tile(tile, p.tile_shift, total_tiles), m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
         const int m_blk = mp_idx * 2 + static_cast<int>(rank);   // 128-row block of A this CTA owns
         int b_blk0, b_blk1;                                      // 128-row blocks of B behind columns [0,128), [128,256)
         if (epi_is_glu(EPI)) {
@@ -791,7 +805,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
     uint32_t local_tile = 0;
     for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++local_tile) {
       int mp_idx, n_idx;
-      tile_coords(tile, m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
+      tile_coords(rotate_tile(tile, p.tile_shift, total_tiles), m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
       const int row = (mp_idx * 2 + static_cast<int>(rank)) * 128 + quad * 32 + lane;
       const bool row_ok = row < p.m;
       const uint32_t acc_col = (local_tile & 1) ? TP::kAccWindow1 : 0;
@@ -803,9 +817,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
       tc_fence_after_sync();
       const float row_scale = (EPI == kEpiRegionBf16 && row_ok) ? __ldg(p.x_region_scales + row / p.x_region_rows)
                                                                 : out_scale;
+      // the output block this 256-row pair tile belongs to (whole tiles never straddle blocks)
+      const int out_blk = p.out_block_rows > 0 ? (mp_idx * 256) / p.out_block_rows : 0;
       epilogue_drain<KIND, EPI>(p, tmem_base + lane_base + acc_col, row, row_ok, n_idx, (local_tile & 1) != 0,
-                                overlap_addr, row_scale, lane, &map_out,
-                                smem + T::kOffStage + quad * 2 * kEpiStageBufBytes);
+                                overlap_addr, row_scale, lane, &maps_out.m[out_blk],
+                                smem + T::kOffStage + quad * 2 * kEpiStageBufBytes, out_blk * p.out_block_rows);
     }
     if (p.tma_out && lane == 0) tma_store_wait_all<0>();   // shared memory outlives the last store's reads
     __syncwarp();

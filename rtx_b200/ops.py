@@ -130,6 +130,23 @@ def mxfp8_gemm(qa, sa, qb, sb, m: int, n: int, k: int, *, out_dtype: torch.dtype
     return out
 
 
+def mxfp8_gemm_row_blocks(qa, sa, qb, sb, m: int, n: int, k: int, blocks, *, first_block: int = 0) -> None:
+    """The packed GEMM with its [m, n] output split into row blocks: block j (rows j*R .. j*R+R-1, R = the rows of
+    blocks[0], a multiple of 256) goes to the tensor blocks[j], which may be a peer-mapped buffer of another GPU."""
+    import ctypes
+
+    rows = int(blocks[0].shape[0])
+    dtype = blocks[0].dtype
+    for b in blocks:
+        if b.dtype is not dtype or b.dim() != 2 or b.shape[1] != n or b.stride(1) != 1 or b.stride(0) != blocks[0].stride(0):
+            raise ValueError("output blocks must be row-major [rows, n] tensors of one dtype and pitch")
+    ptrs = (ctypes.c_void_p * len(blocks))(*[b.data_ptr() for b in blocks])
+    with torch.cuda.device(qa.device):
+        N.call("rtxb_mxfp8_gemm_row_blocks", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), ptrs, len(blocks),
+               rows, m, n, k, blocks[0].stride(0), N.OUT_BF16 if dtype == torch.bfloat16 else N.OUT_F32, first_block,
+               _stream_ptr(), status_word(qa.device).data_ptr())
+
+
 def mxfp8_gemm_glu(qa, sa, qb, sb, m: int, inter: int, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if out is None:
         out = torch.empty(m, inter, dtype=torch.bfloat16, device=qa.device)

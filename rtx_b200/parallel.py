@@ -48,16 +48,19 @@ def all_reduce_dw(dw_partial_f32: torch.Tensor, group: Optional[dist.ProcessGrou
     return dist.all_reduce(dw_partial_f32, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
-# SMs the kernels of the backward leave to the NCCL all-reduce that runs beside them, and the number of
-# CTAs NCCL is asked to stay within (`nccl_options`).  The GEMMs are persistent and otherwise hold every
-# SM until they finish, which pushes the collective behind them; a collective whose CTAs only partly
-# fit finishes no earlier than one that does not fit at all (its last channels still wait for the GEMM).
-# 20 SMs is what a band of dW leaves free anyway: 64 pair tiles of 256 x 256 on 128 of the 148 SMs.
-OVERLAP_SM_MARGIN = int(os.environ.get("RTXB_OVERLAP_SM_MARGIN", "20"))
-NCCL_MAX_CTAS = int(os.environ.get("RTXB_NCCL_MAX_CTAS", "16"))
-# dW is produced and reduced in bands of rows (multiples of 256, the pair-tile height): the all-reduce of
-# a band starts as soon as the GEMM has written it and runs beside the next band's GEMM, the remaining
-# quantizer and dX.  0 = as many rows as give one wave of pair tiles on the SMs left to the GEMM.
+# NCCL route (used where the peer-memory route below cannot be): SMs the persistent kernels leave to the
+# NCCL all-reduce that runs beside dX, and the number of CTAs NCCL is asked to stay within (`nccl_options`).
+# The GEMMs otherwise hold every SM until they finish, which pushes the collective behind them; a collective
+# whose CTAs only partly fit finishes no earlier than one that does not fit at all.  Measured (67 MB FP32 dW,
+# 16384 rows per GPU): 32 SMs / 32 CTAs gives 0.627 ms on two GPUs and 0.634 ms on four; 16 CTAs are enough
+# on two GPUs (0.632 ms with bands) but not on four (0.907 ms).
+OVERLAP_SM_MARGIN = int(os.environ.get("RTXB_OVERLAP_SM_MARGIN", "32"))
+NCCL_MAX_CTAS = int(os.environ.get("RTXB_NCCL_MAX_CTAS", "32"))
+# SMs left free on the peer-memory route: its only NCCL kernels are one-word barriers
+PEER_ROUTE_SM_MARGIN = int(os.environ.get("RTXB_PEER_SM_MARGIN", "4"))
+# NCCL route: dW may be produced and reduced in bands of rows (multiples of 256), each band's all-reduce
+# enqueued right behind its GEMM.  0 = one band (the whole dW): bands pay only when the collective fits in
+# the SMs a band's GEMM leaves free anyway.
 DW_BAND_ROWS = int(os.environ.get("RTXB_DW_BAND_ROWS", "0"))
 
 
@@ -71,14 +74,16 @@ def nccl_options(max_ctas: Optional[int] = None):
 
 
 def dw_bands(n: int, k: int, band_rows: int = 0, sms: int = 148, margin: Optional[int] = None):
-    """Row bands [lo, hi) of the [n, k] dW: multiples of 256 rows (last band: the rest).  With
-    band_rows == 0 a band is one wave: as many 256-row tile rows as fit the CTA pairs left to the GEMM."""
+    """Row bands [lo, hi) of the [n, k] dW: multiples of 256 rows (last band: the rest).  band_rows == 0:
+    one band; band_rows < 0: a band is one wave, as many 256-row tile rows as fit the CTA pairs left to the GEMM."""
     margin = OVERLAP_SM_MARGIN if margin is None else margin
-    if band_rows <= 0:
+    if band_rows < 0:
         pairs = max((sms - margin) // 2, 1)
         col_tiles = (k + 255) // 256
         band_rows = 256 * max(pairs // col_tiles, 1)
-    band = max(256, band_rows // 256 * 256)
+    elif band_rows == 0:
+        band_rows = max(n, 256)
+    band = max(256, (band_rows + 255) // 256 * 256)
     return [(lo, min(lo + band, n)) for lo in range(0, n, band)]
 
 
@@ -115,8 +120,10 @@ def _banded_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.T
 # so the "reduce-scatter" traffic IS the GEMM's output traffic and overlaps the MMAs tile by tile (no NCCL
 # kernel, no SMs taken from the GEMM).  Once every rank's GEMMs are done (a one-word NCCL all-reduce is the
 # barrier) the owner sums its `world` slots in rank order, rounds once to BF16
-# (rtxb_sum_parts_f32_to_bf16) and the BF16 blocks are all-gathered in place: 2 bytes per element cross
-# NVLink in the second phase instead of 4, beside the dX GEMM.
+# (rtxb_sum_parts_f32_to_bf16) into a buffer its peers can read, and after a second barrier every rank copies
+# the other owners' BF16 blocks into its dW with plain device copies: 2 bytes per element cross NVLink in the
+# second phase instead of 4, beside the dX GEMM, and no collective kernel competes with the GEMM for SMs
+# (an NCCL all-gather kept within 16 CTAs ran at about 100 GB/s on four GPUs and was the slowest link).
 # Peer buffers come from torch.distributed's symmetric memory (plain peer mappings; NVLink multicast is not
 # bound).  Shapes whose rows do not split into whole 256-row tiles per rank, and processes where symmetric
 # memory is not available, take the banded NCCL all-reduce above.
@@ -143,15 +150,21 @@ class _PeerReduceScatter:
         self.slots = self.stage.view(self.world, self.rows, k)
         self.peer_slot = [self.handle.get_buffer(o, (self.rows, k), torch.float32, self.rank * block)
                           for o in range(self.world)]
+        # reduced BF16 blocks, pulled by every rank: `result[o]` here is the block this rank would own as rank o;
+        # only `result[rank]` is ever written (by this rank) and read (by everyone)
+        self.result = symm.empty(n * k, dtype=torch.bfloat16, device=device)
+        self.result_handle = symm.rendezvous(self.result, self.group)
+        self.my_result = self.result.view(self.world, self.rows, k)[self.rank]
+        self.peer_result = [self.result_handle.get_buffer(o, (self.rows, k), torch.bfloat16, o * block)
+                            for o in range(self.world)]
         self.comm = torch.cuda.Stream(device)
-        self.side = torch.cuda.Stream(device)          # second lane for concurrent block GEMMs
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
 
 
 def p2p_block_rows(n: int, world: int) -> int:
     """Rows of dW each rank owns for the peer-memory reduce-scatter, or 0 when N does not split into
-    whole 256-row tiles per rank."""
-    return n // world if world > 1 and n % (256 * world) == 0 else 0
+    whole 256-row tiles per rank (or over more than the eight blocks one GEMM launch addresses)."""
+    return n // world if 1 < world <= 8 and n % (256 * world) == 0 else 0
 
 
 def _peer_state(n: int, k: int, device: torch.device, group):
@@ -175,38 +188,26 @@ def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Ten
     main = torch.cuda.current_stream(x.device)
     q_dy, s_dy, q_dyt, s_dyt = ops.mxfp8_quantize_dual(grad_output)
     q_xt, s_xt = ops.mxfp8_quantize_transposed(x)
-    chunks = ops.mxfp8_scale_numel(128, m, N.SCALE_MMA128)
     rows, world, rank = st.rows, st.world, st.rank
-    # two block GEMMs side by side when one block is at most half a wave of CTA pairs
-    tiles = (rows // 256) * ((k + 255) // 256)
-    lanes = 2 if 2 * tiles <= 148 // 2 else 1
-    ready = torch.cuda.Event()
-    ready.record(main)
-    st.side.wait_event(ready)
-    for i in range(world):
-        o = (rank + 1 + i) % world          # neighbours first, the own block last: peers are not all hit at once
-        stream = st.side if (lanes == 2 and i % 2 == 1) else main
-        with torch.cuda.stream(stream):
-            ops.mxfp8_gemm(q_dyt[o * rows:(o + 1) * rows], s_dyt[(o * rows // 128) * chunks:], q_xt, s_xt, rows, k, m,
-                           out=st.peer_slot[o])
-    main.wait_stream(st.side)
+    # ONE dW GEMM over all rows: every 256-row tile goes to the slot of the rank that owns its block, the tile
+    # order starting at this rank's neighbour.  Output traffic of a wave of tiles overlaps the next wave's MMAs.
+    ops.mxfp8_gemm_row_blocks(q_dyt, s_dyt, q_xt, s_xt, n, k, m, st.peer_slot, first_block=(rank + 1) % world)
     done = torch.cuda.Event()
     done.record(main)
     dw = torch.empty(n, k, dtype=torch.bfloat16, device=x.device)
-    mine = dw[rank * rows:(rank + 1) * rows]
     st.comm.wait_event(done)
     with torch.cuda.stream(st.comm):
         dist.all_reduce(st.token, group=st.group)             # every rank's partials have landed everywhere
-        ops.sum_parts_f32_to_bf16(st.slots, mine)
-        dist.all_gather_into_tensor(dw, mine, group=st.group)
-    with ops.sm_margin(OVERLAP_SM_MARGIN):
+        ops.sum_parts_f32_to_bf16(st.slots, st.my_result)
+        dist.all_reduce(st.token, group=st.group)             # every owner's block is reduced
+        for i in range(world):
+            o = (rank + i) % world
+            dw[o * rows:(o + 1) * rows].copy_(st.peer_result[o], non_blocking=True)   # plain copies over NVLink
+    with ops.sm_margin(PEER_ROUTE_SM_MARGIN):
         q_wt, s_wt = ops.mxfp8_quantize_transposed(weight)
         dx = ops.mxfp8_gemm(q_dy, s_dy, q_wt, s_wt, m, k, n)
     main.wait_stream(st.comm)
-    # tensors used on other streams stay alive until those streams are done with them
-    for t in (q_dyt, s_dyt, q_xt, s_xt):
-        t.record_stream(st.side)
-    dw.record_stream(st.comm)
+    dw.record_stream(st.comm)        # allocated on the main stream, written on the comm stream
     return dx, dw
 
 
@@ -248,5 +249,10 @@ def backward_collective(n: int, k: int, device: torch.device, group=None) -> str
         return "none (one rank)"
     if P2P_REDUCE_SCATTER and p2p_block_rows(n, dist.get_world_size(group)) and _peer_state(n, k, device, group):
         return ("reduce-scatter in the dW GEMM epilogue (FP32 TMA stores into the owner's slots over NVLink), "
-                "owner sums and rounds once, BF16 all-gather (NCCL) beside dX")
-    return "NCCL all-reduce(sum) of FP32 dW per band of rows behind the dW GEMM"
+                "owner sums and rounds once, peers copy the BF16 blocks beside dX; NCCL only as two one-word barriers")
+    why = ""
+    if P2P_REDUCE_SCATTER and p2p_block_rows(n, dist.get_world_size(group)):
+        failed = _P2P_STATES.get((device.index, n, k, id(group)))
+        if isinstance(failed, Exception):
+            why = f" (peer memory unavailable: {type(failed).__name__}: {failed})"[:300]
+    return "NCCL all-reduce(sum) of FP32 dW per band of rows behind the dW GEMM" + why

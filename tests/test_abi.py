@@ -88,7 +88,7 @@ def test_newer_entry_points_reject_bad_arguments_before_any_launch(native_lib):
     assert L.rtxb_get_gemm_schedule() == 0
     for code in (1, 2, 3):
         assert L.rtxb_set_gemm_schedule(code) == 0 and L.rtxb_get_gemm_schedule() == code
-    assert L.rtxb_set_gemm_schedule(4) == -1 and L.rtxb_set_gemm_schedule(-1) == -1
+    assert L.rtxb_set_gemm_schedule(5) == -1 and L.rtxb_set_gemm_schedule(-1) == -1
     assert L.rtxb_get_gemm_schedule() == 3
     import threading
     seen = []

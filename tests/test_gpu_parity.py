@@ -755,3 +755,29 @@ def test_fused_x_nan_row_stays_in_its_row(gpu):
     keep[133] = False
     assert torch.isnan(got[133].float()).all()
     assert torch.equal(got[keep].view(torch.int16), clean[keep].view(torch.int16))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mnk_blocks", [((1024, 512, 1024), 4, 0), ((1024, 512, 1024), 4, 3), ((2048, 384, 96), 8, 5),
+                                        ((768, 300, 256), 2, 1)])
+def test_gemm_with_row_block_outputs_equals_the_plain_gemm(gpu, mnk_blocks, out_dtype):
+    """The GEMM whose output rows are split over several buffers (on a multi-GPU node: the staging slots of the
+    ranks that own the blocks) writes, block by block, the bits of the plain GEMM, whatever block the tile order
+    starts at; a last block shorter than the others is clipped."""
+    ops, N, dev, _ = gpu
+    (m, n, k), n_blocks, first = mnk_blocks
+    torch.manual_seed(13)
+    a, b = torch.randn(m, k).bfloat16().to(dev), torch.randn(n, k).bfloat16().to(dev)
+    qa, sa = ops.mxfp8_quantize(a)
+    qb, sb = ops.mxfp8_quantize(b)
+    want = ops.mxfp8_gemm(qa, sa, qb, sb, m, n, k, out_dtype=out_dtype)
+    rows = -(-m // n_blocks) // 256 * 256 or 256
+    rows = 256 * max(1, -(-m // (256 * n_blocks)))
+    ldo = (n + 7) // 8 * 8
+    blocks = [torch.full((rows, ldo), float("nan"), dtype=out_dtype, device=dev)[:, :n] for _ in range(-(-m // rows))]
+    ops.mxfp8_gemm_row_blocks(qa, sa, qb, sb, m, n, k, blocks, first_block=first)
+    _ok(ops, dev)
+    got = torch.cat([blk for blk in blocks], dim=0)[:m]
+    assert torch.equal(got, want)
+    if m % rows:
+        assert torch.isnan(blocks[-1][m % rows:].float()).all()      # rows past m are never written

@@ -82,11 +82,12 @@ def test_peer_reduce_scatter_block_rows():
 def test_dw_bands_cover_the_rows_in_whole_tile_rows():
     from rtx_b200 import parallel as P
 
-    # K = 4096 is 16 column tiles: 64 pairs hold 4 tile rows = 1024 rows per band
-    assert P.dw_bands(4096, 4096, margin=20) == [(0, 1024), (1024, 2048), (2048, 3072), (3072, 4096)]
+    # one wave per band (band_rows < 0): K = 4096 is 16 column tiles, 64 pairs hold 4 tile rows = 1024 rows
+    assert P.dw_bands(4096, 4096, band_rows=-1, margin=20) == [(0, 1024), (1024, 2048), (2048, 3072), (3072, 4096)]
     # wide K: one tile row per band; ragged N: the last band takes the rest
-    assert P.dw_bands(700, 14336, margin=20) == [(0, 256), (256, 512), (512, 700)]
+    assert P.dw_bands(700, 14336, band_rows=-1, margin=20) == [(0, 256), (256, 512), (512, 700)]
     assert P.dw_bands(4096, 4096, band_rows=2048) == [(0, 2048), (2048, 4096)]
+    assert P.dw_bands(4096, 4096) == [(0, 4096)] and P.dw_bands(700, 300) == [(0, 700)]      # default: one band
     for n, k in ((4096, 4096), (1000, 300), (256, 256), (5, 7)):
         bands = P.dw_bands(n, k)
         assert bands[0][0] == 0 and bands[-1][1] == n
