@@ -180,13 +180,17 @@ constexpr int kQtPitch = 136;
 constexpr int kQtTileBytes = 128 * kQtPitch * 2;
 constexpr int kQtSmemBytes = 2 * kQtTileBytes;   // two tiles: the next one is fetched while this one is quantized
 
+// Pitch of the output staging rows (128 payload bytes + 16): the staged input tile is re-used, once every
+// thread has read it, to collect the tile's output bytes so that they leave the SM as whole 128-byte rows.
+constexpr int kQtOutPitch = 144;
+
 // Column pass over a staged 128 x 128 tile `tile[k_local][row_local]` (BF16 bits, pitch kQtPitch halfwords):
 // thread -> two adjacent output rows (source columns) x one block of 32 along k, so every
 // shared-memory read is one 32-bit word holding both rows' values; consecutive lanes read consecutive
-// words (conflict free).  Writes the E4M3 payload of rows row0 + r to `q` (pitch kp, columns from k0) and
-// the 128 x 4 scale codes to `tile_scales`.
+// words (conflict free).  Returns the two rows' 32 payload bytes in `o` (o[h][0..7]) and writes the
+// 128 x 4 scale codes to `tile_scales`; the payload is stored by quant_mxfp8_tile_columns_store.
 __device__ __forceinline__ void quant_mxfp8_tile_columns(const uint16_t (*tile)[kQtPitch], uint8_t (*tile_scales)[4],
-                                                         uint8_t* q, int kp, int rows, int row0, int k0,
+                                                         uint32_t (&o)[2][8], int kp, int rows, int row0, int k0,
                                                          bool round_to_infinity) {
   const int rp = threadIdx.x & 63, j = threadIdx.x >> 6;   // 64 row pairs x 4 blocks = 256 threads
   uint32_t w[32];
@@ -203,54 +207,71 @@ __device__ __forceinline__ void quant_mxfp8_tile_columns(const uint16_t (*tile)[
     const int r = 2 * rp + h, row = row0 + r;
     const bool live = row < rows && kcol < kp;
     tile_scales[r][j] = live ? static_cast<uint8_t>(code) : 0;
-    if (live) {
-      uint32_t o[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float v0 = h ? bf16_hi(w[4 * e]) : bf16_lo(w[4 * e]), v1 = h ? bf16_hi(w[4 * e + 1]) : bf16_lo(w[4 * e + 1]);
-        const float v2 = h ? bf16_hi(w[4 * e + 2]) : bf16_lo(w[4 * e + 2]), v3 = h ? bf16_hi(w[4 * e + 3]) : bf16_lo(w[4 * e + 3]);
-        o[e] = cvt_e4m3x2(v0 * recip, v1 * recip) | (cvt_e4m3x2(v2 * recip, v3 * recip) << 16);
-      }
-      uint4* dst = reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * kp + kcol);
-      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    for (int e = 0; e < 8; ++e) {
+      const float v0 = h ? bf16_hi(w[4 * e]) : bf16_lo(w[4 * e]), v1 = h ? bf16_hi(w[4 * e + 1]) : bf16_lo(w[4 * e + 1]);
+      const float v2 = h ? bf16_hi(w[4 * e + 2]) : bf16_lo(w[4 * e + 2]), v3 = h ? bf16_hi(w[4 * e + 3]) : bf16_lo(w[4 * e + 3]);
+      o[h][e] = cvt_e4m3x2(v0 * recip, v1 * recip) | (cvt_e4m3x2(v2 * recip, v3 * recip) << 16);
     }
   }
 }
 
-// Row pass over the same staged tile: thread -> one source row (k_local) x two blocks of 32 source columns.
+// Second half of the column pass, after every thread has finished reading the staged tile: the payload goes
+// into the tile's own storage as [row_local][128 bytes] and leaves as whole rows — eight lanes write one
+// 128-byte row of q, a warp four rows per instruction (the direct form wrote 16 bytes to 32 different rows
+// per instruction).
+__device__ __forceinline__ void quant_mxfp8_tile_columns_store(uint8_t* stage, const uint32_t (&o)[2][8], uint8_t* q,
+                                                               int kp, int rows, int row0, int k0) {
+  const int rp = threadIdx.x & 63, j = threadIdx.x >> 6;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint4* dst = reinterpret_cast<uint4*>(stage + (2 * rp + h) * kQtOutPitch + j * 32);
+    dst[0] = make_uint4(o[h][0], o[h][1], o[h][2], o[h][3]);
+    dst[1] = make_uint4(o[h][4], o[h][5], o[h][6], o[h][7]);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = threadIdx.x + kQuantThreads * i;
+    const int r = c >> 3, part = c & 7;
+    const int row = row0 + r, col = k0 + part * 16;
+    if (row < rows && col < kp)
+      *reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * kp + col) =
+          *reinterpret_cast<const uint4*>(stage + r * kQtOutPitch + part * 16);
+  }
+}
+
+// Row pass over the same staged tile (dual form): eight lanes cover one source row of the tile (16 values each,
+// two lanes per MX block), so a warp writes four whole 128-byte rows of the row-quantized payload per pass.
 __device__ __forceinline__ void quant_mxfp8_tile_rows(const uint16_t (*tile)[kQtPitch], uint8_t (*tile_scales)[4],
                                                       uint8_t* q, int np, int k_rows, int cols, int k0, int col0,
                                                       bool round_to_infinity) {
-  const int r = threadIdx.x & 127;
+  const int part = threadIdx.x & 7;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int jb = (threadIdx.x >> 7) + 2 * i;
-    // 16-byte reads: the row pitch is 17 chunks of 16 bytes (odd), so the eight lanes of a quarter warp --
-    // eight consecutive rows, same chunk -- fall into eight different bank groups
-    uint32_t w[16];
+  for (int pass = 0; pass < 4; ++pass) {
+    const int r = (threadIdx.x >> 3) + 32 * pass;
+    uint32_t w[8];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint4 v = *reinterpret_cast<const uint4*>(&tile[r][jb * 32 + 8 * c]);
+    for (int c = 0; c < 2; ++c) {
+      const uint4 v = *reinterpret_cast<const uint4*>(&tile[r][part * 16 + 8 * c]);
       w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
     }
     float a = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) a = fmax_nan(a, fmax_nan(fabsf(bf16_lo(w[e])), fabsf(bf16_hi(w[e]))));
+    for (int e = 0; e < 8; ++e) a = fmax_nan(a, fmax_nan(fabsf(bf16_lo(w[e])), fabsf(bf16_hi(w[e]))));
+    a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 1));
     const uint32_t code = e8m0_from_amax(a, round_to_infinity);
     const float recip = e8m0_reciprocal(code);
-    const int row = k0 + r, col = col0 + jb * 32;
+    const int row = k0 + r, col = col0 + part * 16;
     const bool live = row < k_rows && col < np;
-    tile_scales[r][jb] = live ? static_cast<uint8_t>(code) : 0;
+    if ((part & 1) == 0) tile_scales[r][part >> 1] = live ? static_cast<uint8_t>(code) : 0;
     if (live) {
-      uint32_t o[8];
+      uint32_t o[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
+      for (int e = 0; e < 4; ++e)
         o[e] = cvt_e4m3x2(bf16_lo(w[2 * e]) * recip, bf16_hi(w[2 * e]) * recip) |
                (cvt_e4m3x2(bf16_lo(w[2 * e + 1]) * recip, bf16_hi(w[2 * e + 1]) * recip) << 16);
-      uint4* dst = reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * np + col);
-      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      *reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * np + col) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
@@ -320,11 +341,13 @@ __global__ void __launch_bounds__(kQuantThreads, kQtOccupancy) quant_mxfp8_trans
       cp_async_wait<0>();
     }
     __syncthreads();
-    quant_mxfp8_tile_columns(tiles[buf], tile_scales, p.q, p.kp, p.rows, row0, k0, p.round_to_infinity != 0);
+    uint32_t o[2][8];
+    quant_mxfp8_tile_columns(tiles[buf], tile_scales, o, p.kp, p.rows, row0, k0, p.round_to_infinity != 0);
     if (DUAL)
       quant_mxfp8_tile_rows(tiles[buf], tile_scales_rows, p.q_rows, p.np, p.k, p.rows, k0, row0,
                             p.round_to_infinity != 0);
-    __syncthreads();
+    __syncthreads();   // every thread has read the staged tile: its storage now collects the transposed payload
+    quant_mxfp8_tile_columns_store(reinterpret_cast<uint8_t*>(tiles[buf]), o, p.q, p.kp, p.rows, row0, k0);
     store_scale_tile<4>(tile_scales, p.scales, p.layout, row0, k0 / 32, p.rows, p.nb, p.sf_chunks);
     if (DUAL) store_scale_tile<4>(tile_scales_rows, p.s_rows, p.layout, k0, row0 / 32, p.k, p.nb_rows, p.chunks_rows);
     __syncthreads();   // the scale tiles and this buffer are free again
