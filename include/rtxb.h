@@ -179,7 +179,9 @@ int rtxb_mxfp8_linear_fwd(const void* x_bf16, const void* w_bf16, void* out_bf16
  *     RTXB_E_SCRATCH_CAPACITY and nothing is launched.
  *   - The first call on each device looks up that device's address of the array
  *     (the device must be current, as for every entry point); make that first call
- *     before starting any stream capture.
+ *     before starting any stream capture.  `stream` must belong to the current device:
+ *     a stream of another device is refused (RTXB_E_INVALID_ARGUMENT), since the
+ *     kernels would run there with this device's address of the array.
  *   - All calls on a device share the one array and it keeps the last call's
  *     contents.  Nothing in it needs clearing between calls (each call rewrites all
  *     it reads), but two calls whose kernels overlap on the GPU — different streams

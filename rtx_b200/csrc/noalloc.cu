@@ -80,6 +80,18 @@ extern "C" int rtxb_mxfp8_linear_fwd_noalloc(const void* x_bf16, const void* w_b
   void* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != RTXB_OK) return rc;
+  // The array was looked up for the CURRENT device; a stream of another device would make the kernels run
+  // there with this device's address.  The legacy and per-thread default streams belong to the current device.
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (s != nullptr && s != cudaStreamLegacy && s != cudaStreamPerThread) {
+    int current = -1, of_stream = -1;
+    if (cudaGetDevice(&current) == cudaSuccess && cudaStreamGetDevice(s, &of_stream) == cudaSuccess &&
+        of_stream != current) {
+      char msg[160];
+      snprintf(msg, sizeof(msg), "the stream belongs to device %d but device %d is current", of_stream, current);
+      return rtxb::set_last_error(RTXB_E_INVALID_ARGUMENT, msg);
+    }
+  }
   // Same kernels as rtxb_mxfp8_linear_fwd.  They overwrite every byte of the scratch they later
   // read (payload rows and whole scale tiles, padding included), so nothing has to be cleared even
   // though the array still holds the previous call's operands.

@@ -514,6 +514,12 @@ class NVFP4Linear(nn.Module):
         self._dynamic_config, self._forward_key = _dynamic_key(
             dynamic_config, scale_config, scaling, (self.x_scale_region_rows, self.weight_scale_region_rows))
         self._backward_key = _bwd_key(backward_config)
+        from .autotune import ScheduleResolver
+
+        # `autotune=`: stored winners of the call's (M, N, K), or first-use tuning (rtx/fp4.py:1065-1207)
+        self._resolver = ScheduleResolver(
+            "nvfp4_weight_prequant_fwd" if packed_weight is not None else "nvfp4_dynamic_fwd", self.out_features,
+            self.in_features, _fp8._autotune_mode(autotune), autotune_cache_dir, variant=scaling)
         self._delayed_initialized = False
         self._delayed_problem = None
         self._x_amax_state = self._weight_amax_state = None
@@ -574,7 +580,7 @@ class NVFP4Linear(nn.Module):
             self.reset_delayed_scales()
         return super().train(mode)
 
-    def _forward_delayed(self, x2d: torch.Tensor) -> torch.Tensor:
+    def _forward_delayed(self, x2d: torch.Tensor, key: Optional[str] = None) -> torch.Tensor:
         """History handling of the delayed policy (rtx/fp4.py:3452-3535): (re)initialise from current data when
         the problem (device, stream, shape) changes, run, then swap the two generations.  The policy is a
         forward one: eval / no_grad consume and publish histories exactly like training."""
@@ -589,7 +595,7 @@ class NVFP4Linear(nn.Module):
                 self._next_weight_amax_state = torch.empty_like(self._weight_amax_state)
             self._delayed_initialized, self._delayed_problem = True, problem
         args = (x2d, self.weight, self._x_amax_state, self._weight_amax_state, self._next_x_amax_state,
-                self._next_weight_amax_state, self._forward_key, self._forward_key, self._backward_key)
+                self._next_weight_amax_state, key or self._forward_key, key or self._forward_key, self._backward_key)
         if torch.is_grad_enabled() and (x2d.requires_grad or self.weight.requires_grad):
             from . import fp8_bwd  # noqa: F401  (registers the backward ops)
             out = _NVFP4DelayedAutograd.apply(*args)
@@ -599,11 +605,57 @@ class NVFP4Linear(nn.Module):
         self._weight_amax_state, self._next_weight_amax_state = self._next_weight_amax_state, self._weight_amax_state
         return out
 
-    def explain(self) -> dict:
-        return {"format": "nvfp4", "weight_mode": self.weight_mode, "scaling": self.scaling,
-                "x_scale_region_rows": self.x_scale_region_rows if self.scaling == "jit_row_region" else 0,
-                "weight_scale_region_rows": self.weight_scale_region_rows if self.scaling == "jit_row_region" else 0,
-                "pipeline": "outer scale(s) + quantize once + tcgen05 mxf4nvf4 GEMM (sm_100a)", "backward": "mxfp8"}
+    def explain(self, m: Optional[int] = None) -> dict:
+        """What forward() runs; with `m` (token rows of a call) also the GEMM schedule `autotune=` resolves for it."""
+        out = {"format": "nvfp4", "weight_mode": self.weight_mode, "scaling": self.scaling,
+               "x_scale_region_rows": self.x_scale_region_rows if self.scaling == "jit_row_region" else 0,
+               "weight_scale_region_rows": self.weight_scale_region_rows if self.scaling == "jit_row_region" else 0,
+               "pipeline": "outer scale(s) + quantize once + tcgen05 mxf4nvf4 GEMM (sm_100a)", "backward": "mxfp8",
+               "autotune": self._resolver.mode, "forward_key": self._forward_key}
+        if m is not None:
+            cfg = self._resolver.resolve(int(m), self._dynamic_config)
+            out.update(forward_key=cfg.to_key(), gemm_schedule=cfg.gemm.schedule,
+                       schedule_source=self._resolver.sources.get(int(m), "configured"))
+        return out
+
+    def _tuned_forward_key(self, x2d: torch.Tensor) -> str:
+        """The forward schedule key of this call: the configured one, or what `autotune=` resolves for this M.
+        The delayed policy carries state from call to call, so it is never re-run for timing: it uses stored
+        winners only.  Constant while torch.compile traces."""
+        if self._resolver.mode == "off" or torch.compiler.is_compiling():
+            return self._forward_key
+        m = int(x2d.shape[0])
+        cfg = self._resolver.resolved.get(m)
+        if cfg is None:
+            evaluate = None if self.scaling == "delayed" else self._evaluator(x2d)
+            cfg = self._resolver.resolve(m, self._dynamic_config, evaluate)
+        return cfg.to_key()
+
+    def _evaluator(self, x2d: torch.Tensor):
+        from .autotune import TrialOutcome
+
+        def evaluate(cfg) -> "TrialOutcome":
+            saved = self._forward_key, self._dynamic_config, self._resolver.mode
+            self._forward_key, self._dynamic_config, self._resolver.mode = cfg.to_key(), cfg, "off"
+            try:
+                with torch.no_grad():
+                    for _ in range(2):
+                        self.forward(x2d)
+                    times = []
+                    for _ in range(5):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        self.forward(x2d)
+                        e1.record()
+                        e1.synchronize()
+                        times.append(e0.elapsed_time(e1))
+            except RuntimeError as exc:
+                return TrialOutcome("failed", detail=str(exc))
+            finally:
+                self._forward_key, self._dynamic_config, self._resolver.mode = saved
+            return TrialOutcome("ok", median_ms=sorted(times)[len(times) // 2])
+
+        return evaluate
 
     def to(self, *args, **kwargs):
         if self.weight_mode == "prequantized":
@@ -619,7 +671,7 @@ class NVFP4Linear(nn.Module):
         if x.shape[-1] != k:
             raise ValueError(f"K mismatch: x has {x.shape[-1]}, weight has {k}")
         x2d = x.reshape(-1, k)
-        key, bwd_key = self._forward_key, self._backward_key
+        key, bwd_key = self._tuned_forward_key(x2d), self._backward_key
         if self.weight_mode == "prequantized":
             if x.requires_grad and torch.is_grad_enabled():
                 raise RuntimeError("a prequantized NVFP4 weight is inference-only; keep the BF16 master weight to train")
@@ -629,7 +681,7 @@ class NVFP4Linear(nn.Module):
                 self._weight_scale_layout, key)
             return out.reshape(*x.shape[:-1], n)
         if self._dynamic_config.scale.policy == "delayed":
-            return self._forward_delayed(x2d).reshape(*x.shape[:-1], n)
+            return self._forward_delayed(x2d, key).reshape(*x.shape[:-1], n)
         train = torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad)
         if train:
             from . import fp8_bwd  # noqa: F401  (registers the backward ops)

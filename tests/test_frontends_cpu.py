@@ -444,3 +444,26 @@ def test_install_as_rtx_aliases_the_package():
     root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
     out = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-2000:]
+
+
+def test_stored_winner_reaches_nvfp4_modules(tmp_path):
+    """`autotune="cache"` on NVFP4Linear: a winner stored for (family, M, N, K, policy) changes the schedule explain()
+    reports for that M; other policies and other M keep the configured schedule (rtx/fp4.py:1065-1207)."""
+    import rtx_b200 as rtx
+    from rtx_b200 import autotune as A
+    from rtx_b200 import configs as C
+
+    n, k = 256, 128
+    adapter = A.ADAPTERS["nvfp4_dynamic_fwd"]()
+    ctx = A.KernelContext("nvfp4_dynamic_fwd", 64, n, k, variant="jit_row_region")
+    winner = C.NVFP4DynamicConfig(gemm=C.NVFP4GemmConfig.for_schedule("stream"))
+    A.save_runtime_winner(ctx, adapter, winner, 0.01, tmp_path)
+    tuned = rtx.NVFP4Linear(k, n, autotune="cache", autotune_cache_dir=tmp_path)
+    hit, miss = tuned.explain(m=64), tuned.explain(m=4096)
+    assert hit["gemm_schedule"] == "stream" and hit["schedule_source"] == "stored winner"
+    assert miss["gemm_schedule"] == "auto"
+    kept = C.config_from_key(hit["forward_key"])
+    assert kept.scale.policy == "jit_row_region" and kept.x_scale_region_rows == tuned.x_scale_region_rows
+    other = rtx.NVFP4Linear(k, n, scaling="current", autotune="cache", autotune_cache_dir=tmp_path)
+    assert other.explain(m=64)["gemm_schedule"] == "auto"          # a different policy is a different variant
+    assert rtx.NVFP4Linear(k, n).explain()["autotune"] == "off"

@@ -452,6 +452,35 @@ def test_module_tunes_on_first_use_and_reuses_the_stored_winner(dev, tmp_path):
     assert xg.grad is not None and tuned.weight.grad is not None
 
 
+def test_nvfp4_module_tunes_on_first_use(dev, tmp_path):
+    """`autotune="balanced"` on NVFP4Linear (row-region policy and packed weight): first call times the built
+    schedules, stores a winner per (family, policy variant), later calls reuse it; same bits as an untuned module."""
+    import rtx_b200 as rtx
+    from rtx_b200 import autotune as A
+
+    torch.manual_seed(12)
+    k, n = 512, 1024
+    plain = rtx.NVFP4Linear(k, n, device=dev)
+    tuned = rtx.NVFP4Linear(k, n, device=dev, autotune="balanced", autotune_cache_dir=tmp_path)
+    with torch.no_grad():
+        tuned.weight.copy_(plain.weight)
+        x = torch.randn(96, k).bfloat16().to(dev)
+        want = plain(x)
+        got, again = tuned(x), tuned(x)
+        _done(dev)
+        assert torch.equal(got, want) and torch.equal(again, want)
+        assert A.runtime_winner_path(A.KernelContext("nvfp4_dynamic_fwd", 96, n, k, variant="jit_row_region"),
+                                     tmp_path).exists()
+        assert tuned.explain(m=96)["schedule_source"] == "tuned on first use"
+        packed_plain = plain.to_quantized_weight()
+        packed = rtx.NVFP4Linear(k, n, device=dev, autotune="balanced", autotune_cache_dir=tmp_path,
+                                 packed_weight=packed_plain.packed_weight())
+        assert torch.equal(packed(x), packed_plain(x))
+        assert A.runtime_winner_path(A.KernelContext("nvfp4_weight_prequant_fwd", 96, n, k, variant="current"),
+                                     tmp_path).exists()
+    _done(dev)
+
+
 def test_quantized_weight_cache_is_bit_identical(dev):
     """Inside `quantized_weight_cache()` modules reuse the quantized weight across micro-batches; outputs,
     dX and accumulated dW equal the uncached run bit for bit, an in-place weight update is seen, and the

@@ -73,3 +73,19 @@ def test_noalloc_refuses_shapes_beyond_its_array(env):
     with pytest.raises(N.NativeError, match=r"built-in scratch array.*needs \d+ bytes.*holds 33554432"):
         N.check(code, "rtxb_mxfp8_linear_fwd_noalloc")
     torch.cuda.synchronize()
+
+
+def test_noalloc_refuses_a_stream_of_another_device(env):
+    """The array's address is looked up for the current device, so a stream that lives on a different GPU is
+    refused before anything is launched.  Needs two GPUs (skipped otherwise)."""
+    N, ops, dev = env
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device=dev)
+    other = torch.cuda.Stream(device=torch.device("cuda", 1))
+    code = N.load().rtxb_mxfp8_linear_fwd_noalloc(x.data_ptr(), x.data_ptr(), x.data_ptr(), 128, 128, 64, 1,
+                                                  other.cuda_stream, None)
+    assert code == -1
+    with pytest.raises(N.NativeError, match="stream belongs to device 1"):
+        N.check(code, "rtxb_mxfp8_linear_fwd_noalloc")
+    torch.cuda.synchronize()
