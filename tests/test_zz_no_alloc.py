@@ -82,8 +82,10 @@ def test_noalloc_refuses_a_stream_of_another_device(env):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device=dev)
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(128, 128, dtype=torch.bfloat16, device=dev)     # real buffers of the right sizes all the same
     other = torch.cuda.Stream(device=torch.device("cuda", 1))
-    code = N.load().rtxb_mxfp8_linear_fwd_noalloc(x.data_ptr(), x.data_ptr(), x.data_ptr(), 128, 128, 64, 1,
+    code = N.load().rtxb_mxfp8_linear_fwd_noalloc(x.data_ptr(), w.data_ptr(), out.data_ptr(), 128, 128, 64, 1,
                                                   other.cuda_stream, None)
     assert code == -1
     with pytest.raises(N.NativeError, match="stream belongs to device 1"):
