@@ -175,6 +175,11 @@ def _peer_state(n: int, k: int, device: torch.device, group):
             state = _PeerReduceScatter(n, k, device, group)
         except Exception as exc:   # symmetric memory unavailable here: remember and use NCCL
             state = exc
+        # the route is a collective decision: if the set-up failed on any rank, every rank takes the NCCL route
+        ok = torch.tensor([0.0 if isinstance(state, Exception) else 1.0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if float(ok.item()) == 0.0 and not isinstance(state, Exception):
+            state = RuntimeError("peer-memory set-up failed on another rank")
         _P2P_STATES[key] = state
     return None if isinstance(state, Exception) else state
 
