@@ -323,7 +323,10 @@ def main():
     ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5, 6))
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--dw-route", choices=["peer", "nccl"], default="peer",
+                    help="configuration 4 on several GPUs: reduce-scatter through peer memory in the dW GEMM, or NCCL all-reduce")
     args = ap.parse_args()
+    parallel.P2P_REDUCE_SCATTER = args.dw_route == "peer"
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():

@@ -99,13 +99,15 @@ gemm_decode_fused_kernel(const __grid_constant__ CUtensorMap map_b, const GemmPa
 
   const int first_pass = total_groups < S ? total_groups : S;
   if (warp == 0) {
+    // one lane per ring slot initialises its two barriers (S <= 24), so the first load is not behind 2 S serial inits
+    if (lane == 0) prefetch_tensormap(&map_b);
+    if (lane < S) {
+      mbar_init(&full_bar[lane], 1);
+      mbar_init(&empty_bar[lane], 1);
+    }
+    fence_barrier_init();
+    __syncwarp();
     if (lane == 0) {
-      prefetch_tensormap(&map_b);
-      for (int s = 0; s < S; ++s) {
-        mbar_init(&full_bar[s], 1);
-        mbar_init(&empty_bar[s], 1);
-      }
-      fence_barrier_init();
       int tile = blockIdx.x, kg = 0;
       for (int i = 0; i < first_pass; ++i) {   // the weights never depend on the grid before this one
         load_weights(i, tile, kg);

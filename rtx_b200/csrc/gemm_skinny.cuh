@@ -140,14 +140,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int total_groups = my_tiles * k_groups;
   const int first_pass = total_groups < S ? total_groups : S;
   if (warp == 0) {
+    // one lane per ring slot initialises its two barriers (S <= 24), so the first load is not behind 2 S serial inits
     if (lane == 0) {
       prefetch_tensormap(&map_a);
       prefetch_tensormap(&map_b);
-      for (int s = 0; s < S; ++s) {
-        mbar_init(&full_bar[s], 1);
-        mbar_init(&empty_bar[s], 1);
-      }
-      fence_barrier_init();
+    }
+    if (lane < S) {
+      mbar_init(&full_bar[lane], 1);
+      mbar_init(&empty_bar[lane], 1);
+    }
+    fence_barrier_init();
+    __syncwarp();
+    if (lane == 0) {
       // First ring pass (every slot is free).  The weights B / SFB never depend on the grid launched
       // just before this one, the activations A / SFA may: when the launch is marked as overlapping
       // its predecessor, all weight loads of the pass go first, then the wait, then the activations.

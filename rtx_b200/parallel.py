@@ -54,14 +54,14 @@ def all_reduce_dw(dw_partial_f32: torch.Tensor, group: Optional[dist.ProcessGrou
 # whose CTAs only partly fit finishes no earlier than one that does not fit at all.  Measured (67 MB FP32 dW,
 # 16384 rows per GPU): 32 SMs / 32 CTAs gives 0.627 ms on two GPUs and 0.634 ms on four; 16 CTAs are enough
 # on two GPUs (0.632 ms with bands) but not on four (0.907 ms).
-OVERLAP_SM_MARGIN = int(os.environ.get("RTXB_OVERLAP_SM_MARGIN", "32"))
-NCCL_MAX_CTAS = int(os.environ.get("RTXB_NCCL_MAX_CTAS", "32"))
+OVERLAP_SM_MARGIN = 32
+NCCL_MAX_CTAS = 32
 # SMs left free on the peer-memory route: its only NCCL kernels are one-word barriers
-PEER_ROUTE_SM_MARGIN = int(os.environ.get("RTXB_PEER_SM_MARGIN", "4"))
+PEER_ROUTE_SM_MARGIN = 4
 # NCCL route: dW may be produced and reduced in bands of rows (multiples of 256), each band's all-reduce
 # enqueued right behind its GEMM.  0 = one band (the whole dW): bands pay only when the collective fits in
 # the SMs a band's GEMM leaves free anyway.
-DW_BAND_ROWS = int(os.environ.get("RTXB_DW_BAND_ROWS", "0"))
+DW_BAND_ROWS = 0
 
 
 def nccl_options(max_ctas: Optional[int] = None):
@@ -128,7 +128,7 @@ def _banded_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.T
 # bound).  Shapes whose rows do not split into whole 256-row tiles per rank, and processes where symmetric
 # memory is not available, take the banded NCCL all-reduce above.
 
-P2P_REDUCE_SCATTER = os.environ.get("RTXB_DW_P2P", "1") != "0"
+P2P_REDUCE_SCATTER = True     # module attribute: set False to force the NCCL route
 _P2P_STATES: dict = {}
 
 
