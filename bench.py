@@ -274,7 +274,7 @@ def run_own_arm(args) -> None:
     x_host = inp["x"][rank * per:(rank + 1) * per].contiguous().pin_memory()
     x = x_host.to(dev, non_blocking=True)
     # weak sub-record: M rows per GPU out of a global draw of M * world rows
-    x_weak = make_inputs(2, m=M * world)["x"][rank * M:(rank + 1) * M].to(dev) if world > 1 else x
+    x_weak = make_inputs(2, m=M * world, rows=(rank * M, (rank + 1) * M))["x"].to(dev) if world > 1 else x
     wgu = inp["w_gate_up"].to(dev)
     wd = inp["w_down"].to(dev)
     del inp
@@ -378,9 +378,9 @@ def run_own_arm(args) -> None:
     w_b = bwd["w"].to(dev)
     shards = {"strong": (bwd["x"][rank * bper:(rank + 1) * bper].to(dev), bwd["dy"][rank * bper:(rank + 1) * bper].to(dev))}
     if world > 1:
-        wide = make_inputs(4, m=BWD_M * world)     # weak: 16384 rows per GPU out of one global draw
-        shards["weak"] = (wide["x"][rank * BWD_M:(rank + 1) * BWD_M].to(dev),
-                          wide["dy"][rank * BWD_M:(rank + 1) * BWD_M].to(dev))
+        # weak: 16384 rows per GPU out of one global draw of 16384 * N rows (only this rank's block is held)
+        wide = make_inputs(4, m=BWD_M * world, rows=(rank * BWD_M, (rank + 1) * BWD_M))
+        shards["weak"] = (wide["x"].to(dev), wide["dy"].to(dev))
         del wide
     bwd_parity = None
     for mode, (xb, dyb) in shards.items():

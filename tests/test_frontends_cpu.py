@@ -467,3 +467,18 @@ def test_stored_winner_reaches_nvfp4_modules(tmp_path):
     other = rtx.NVFP4Linear(k, n, scaling="current", autotune="cache", autotune_cache_dir=tmp_path)
     assert other.explain(m=64)["gemm_schedule"] == "auto"          # a different policy is a different variant
     assert rtx.NVFP4Linear(k, n).explain()["autotune"] == "off"
+
+
+def test_row_block_of_a_global_draw_equals_the_slice():
+    """workloads.make_inputs(rows=(lo, hi)): a rank of a weak-scaling run keeps only its block of the global
+    tensors, with the values of the full draw (never seeded by rank); weights are unaffected."""
+    from rtx_b200.workloads import make_inputs
+
+    full = make_inputs(2, m=8192 + 4096, k=256, inter=128)
+    part = make_inputs(2, m=8192 + 4096, k=256, inter=128, rows=(3000, 9000))
+    assert torch.equal(full["x"][3000:9000], part["x"]) and torch.equal(full["w_gate_up"], part["w_gate_up"])
+    assert torch.equal(full["w_down"], part["w_down"])
+    full = make_inputs(4, m=12288, k=128, n=256)
+    part = make_inputs(4, m=12288, k=128, n=256, rows=(4096, 12288))
+    assert torch.equal(full["x"][4096:], part["x"]) and torch.equal(full["dy"][4096:], part["dy"])
+    assert torch.equal(full["w"], part["w"])
