@@ -771,8 +771,7 @@ def test_gemm_with_row_block_outputs_equals_the_plain_gemm(gpu, mnk_blocks, out_
     qa, sa = ops.mxfp8_quantize(a)
     qb, sb = ops.mxfp8_quantize(b)
     want = ops.mxfp8_gemm(qa, sa, qb, sb, m, n, k, out_dtype=out_dtype)
-    rows = -(-m // n_blocks) // 256 * 256 or 256
-    rows = 256 * max(1, -(-m // (256 * n_blocks)))
+    rows = 256 * max(1, -(-m // (256 * n_blocks)))      # rows per block: whole 256-row tiles
     ldo = (n + 7) // 8 * 8
     blocks = [torch.full((rows, ldo), float("nan"), dtype=out_dtype, device=dev)[:, :n] for _ in range(-(-m // rows))]
     ops.mxfp8_gemm_row_blocks(qa, sa, qb, sb, m, n, k, blocks, first_block=first)
