@@ -4,6 +4,7 @@
     python bench_configs.py --config 4            # MXFP8 backward dX + dW, 16384 x 4096 x 4096
     python bench_configs.py --config 5            # NVFP4 decode, packed weights, M in {1, 8, 16, 64}
     python bench_configs.py --config 6            # configuration 2's shapes with the step-scoped weight cache
+    python bench_configs.py --config 7            # host <-> device copies of the end-to-end step alone, one process, all GPUs
     python -m torch.distributed.run --nproc-per-node N ... bench_configs.py --config 4
 
 One JSON line per measured case (rank 0).  Token rows are sharded over ranks (weak scaling: the
@@ -318,9 +319,51 @@ def config6(args, rank, world, dev):
     return lines
 
 
+def config7(args, rank, world, dev):
+    """Host path alone: ONE process drives every visible GPU with the end-to-end step's copies (67 MB of pinned X in,
+    67 MB of Y out per GPU and step, both directions at once, one stream pair per GPU) and no compute.  Separates
+    "several processes contend for the host" from "the host's PCIe / memory path is the limit" when the
+    end-to-end figure of bench.py does not scale with the GPU count."""
+    import time
+
+    n = torch.cuda.device_count()
+    nbytes = 8192 * 4096 * 2
+    lines = []
+    for active in sorted({1, 2, 4, n} & set(range(1, n + 1))):
+        devs = [torch.device("cuda", i) for i in range(active)]
+        hx = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in devs]
+        hy = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in devs]
+        dx = [torch.empty(nbytes, dtype=torch.uint8, device=d) for d in devs]
+        dy = [torch.empty(nbytes, dtype=torch.uint8, device=d) for d in devs]
+        s_in = [torch.cuda.Stream(d) for d in devs]
+        s_out = [torch.cuda.Stream(d) for d in devs]
+
+        def run(steps):
+            for i, d in enumerate(devs):
+                with torch.cuda.stream(s_in[i]):
+                    for _ in range(steps):
+                        dx[i].copy_(hx[i], non_blocking=True)
+                with torch.cuda.stream(s_out[i]):
+                    for _ in range(steps):
+                        hy[i].copy_(dy[i], non_blocking=True)
+            for d in devs:
+                torch.cuda.synchronize(d)
+
+        run(3)
+        t0 = time.perf_counter()
+        run(args.steps)
+        dt = time.perf_counter() - t0
+        lines.append({
+            "metric": "host <-> device copy GB/s per GPU and direction (pinned, both directions at once, no compute)",
+            "value": nbytes * args.steps / dt / 1e9, "unit": "GB/s", "n_gpus": active, "ms_per_step": 1e3 * dt / args.steps,
+            "config": {"workload": "host_copies_67MB_in_67MB_out_per_gpu", "processes": 1, "gpus_driven": active,
+                       "aggregate_gbs_each_way": active * nbytes * args.steps / dt / 1e9}})
+    return lines
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5, 6))
+    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5, 6, 7))
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--dw-route", choices=["peer", "nccl"], default="peer",
@@ -336,7 +379,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev, pg_options=parallel.nccl_options())
-    lines = {3: config3, 4: config4, 5: config5, 6: config6}[args.config](args, rank, world, dev)
+    lines = {3: config3, 4: config4, 5: config5, 6: config6, 7: config7}[args.config](args, rank, world, dev)
     if rank == 0:
         for line in lines:
             line.update({"steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True})
