@@ -20,17 +20,40 @@ _status_words: dict[int, torch.Tensor] = {}
 
 
 def _stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the current stream of the current device (no Stream object is built: this sits on the
+    launch path of microsecond-scale decode steps)."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
+
+
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device: torch.device):
+    """Context in which `device` is current: nothing at all when it already is (the usual case)."""
+    idx = device.index
+    if idx is None or idx == torch._C._cuda_getDevice():
+        return _NO_SWITCH
+    return torch.cuda.device(idx)
 
 
 def status_word(device: torch.device) -> torch.Tensor:
     """Per-device int32 the kernels set when a bounded wait runs out."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    with _status_lock:
-        word = _status_words.get(idx)
-        if word is None:
-            word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
-            _status_words[idx] = word
+    word = _status_words.get(idx)      # dict reads are atomic; the lock only guards creation
+    if word is None:
+        with _status_lock:
+            word = _status_words.get(idx)
+            if word is None:
+                word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+                _status_words[idx] = word
     return word
 
 
@@ -82,7 +105,7 @@ def mxfp8_quantize(src: torch.Tensor, *, layout: int = N.SCALE_MMA128, rounding:
         q = torch.empty(rows, kp, dtype=torch.uint8, device=src.device)
     if scales is None:
         scales = torch.empty(mxfp8_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_mxfp8_quantize", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout, rounding,
                _stream_ptr())
     return q, scales
@@ -96,7 +119,7 @@ def mxfp8_quantize_transposed(src: torch.Tensor, *, layout: int = N.SCALE_MMA128
     kp = mx_storage_k(k)
     q = torch.empty(rows, kp, dtype=torch.uint8, device=src.device)
     scales = torch.empty(mxfp8_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_mxfp8_quantize_transposed", src.data_ptr(), rows, k, rows, q.data_ptr(), scales.data_ptr(),
                layout, rounding, _stream_ptr())
     return q, scales
@@ -112,7 +135,7 @@ def mxfp8_quantize_dual(src: torch.Tensor, *, layout: int = N.SCALE_MMA128, roun
     s_rows = torch.empty(mxfp8_scale_numel(m, n, layout), dtype=torch.uint8, device=src.device)
     q_t = torch.empty(n, mp, dtype=torch.uint8, device=src.device)
     s_t = torch.empty(mxfp8_scale_numel(n, m, layout), dtype=torch.uint8, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_mxfp8_quantize_dual", src.data_ptr(), m, n, n, q_rows.data_ptr(), s_rows.data_ptr(), q_t.data_ptr(),
                s_t.data_ptr(), layout, rounding, _stream_ptr())
     return q_rows, s_rows, q_t, s_t
@@ -124,7 +147,7 @@ def mxfp8_gemm(qa, sa, qb, sb, m: int, n: int, k: int, *, out_dtype: torch.dtype
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=qa.device)
     code = N.OUT_BF16 if out.dtype == torch.bfloat16 else N.OUT_F32
-    with torch.cuda.device(qa.device):
+    with _on(qa.device):
         N.call("rtxb_mxfp8_gemm", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k,
                out.stride(0), code, _stream_ptr(), status_word(qa.device).data_ptr())
     return out
@@ -141,7 +164,7 @@ def mxfp8_gemm_row_blocks(qa, sa, qb, sb, m: int, n: int, k: int, blocks, *, fir
         if b.dtype is not dtype or b.dim() != 2 or b.shape[1] != n or b.stride(1) != 1 or b.stride(0) != blocks[0].stride(0):
             raise ValueError("output blocks must be row-major [rows, n] tensors of one dtype and pitch")
     ptrs = (ctypes.c_void_p * len(blocks))(*[b.data_ptr() for b in blocks])
-    with torch.cuda.device(qa.device):
+    with _on(qa.device):
         N.call("rtxb_mxfp8_gemm_row_blocks", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), ptrs, len(blocks),
                rows, m, n, k, blocks[0].stride(0), N.OUT_BF16 if dtype == torch.bfloat16 else N.OUT_F32, first_block,
                _stream_ptr(), status_word(qa.device).data_ptr())
@@ -150,7 +173,7 @@ def mxfp8_gemm_row_blocks(qa, sa, qb, sb, m: int, n: int, k: int, blocks, *, fir
 def mxfp8_gemm_glu(qa, sa, qb, sb, m: int, inter: int, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if out is None:
         out = torch.empty(m, inter, dtype=torch.bfloat16, device=qa.device)
-    with torch.cuda.device(qa.device):
+    with _on(qa.device):
         N.call("rtxb_mxfp8_gemm_glu", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(), m,
                inter, k, out.stride(0), _stream_ptr(), status_word(qa.device).data_ptr())
     return out
@@ -164,7 +187,7 @@ def mxfp8_linear_fwd_fused_x(x: torch.Tensor, qw: torch.Tensor, sw: torch.Tensor
     m, k = x.shape
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_mxfp8_linear_fwd_fused_x", x.data_ptr(), x.stride(0), qw.data_ptr(), sw.data_ptr(), out.data_ptr(),
                m, n, k, out.stride(0), rounding, _stream_ptr(), status_word(x.device).data_ptr())
     return out
@@ -197,7 +220,7 @@ def mxfp8_linear_fwd(x: torch.Tensor, w: torch.Tensor, ws: Workspace, out: Optio
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
     nbytes = N.query("rtxb_mxfp8_linear_workspace_bytes", m, n, k)
     buf = ws.get(nbytes)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_mxfp8_linear_fwd", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, rounding, buf.data_ptr(),
                buf.numel(), _stream_ptr(), status_word(x.device).data_ptr())
     return out
@@ -208,7 +231,7 @@ def mxfp8_gemm_glu_mx(qa, sa, qb, sb, m: int, inter: int, k: int, *, want_bf16: 
     q = torch.empty(m, inter, dtype=torch.uint8, device=qa.device)
     s = torch.empty(mxfp8_scale_numel(m, inter, N.SCALE_MMA128), dtype=torch.uint8, device=qa.device)
     h = torch.empty(m, inter, dtype=torch.bfloat16, device=qa.device) if want_bf16 else None
-    with torch.cuda.device(qa.device):
+    with _on(qa.device):
         N.call("rtxb_mxfp8_gemm_glu_mx", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(),
                h.data_ptr() if want_bf16 else None, q.data_ptr(), s.data_ptr(), m, inter, k, inter, _stream_ptr(),
                status_word(qa.device).data_ptr())
@@ -222,7 +245,7 @@ def mxfp8_gemm_glu_mx_fused_x(x: torch.Tensor, qb, sb, inter: int, *, want_bf16:
     q = torch.empty(m, inter, dtype=torch.uint8, device=x.device)
     s = torch.empty(mxfp8_scale_numel(m, inter, N.SCALE_MMA128), dtype=torch.uint8, device=x.device)
     h = torch.empty(m, inter, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_mxfp8_gemm_glu_mx_fused_x", x.data_ptr(), x.stride(0), qb.data_ptr(), sb.data_ptr(),
                h.data_ptr() if want_bf16 else None, q.data_ptr(), s.data_ptr(), m, inter, k, inter, _stream_ptr(),
                status_word(x.device).data_ptr())
@@ -246,7 +269,7 @@ def mxfp8_glu_mlp_fwd(x, w_gate_up, w_down, ws: Workspace, h: Optional[torch.Ten
         y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x.device)
     nbytes = N.query("rtxb_mxfp8_glu_mlp_workspace_bytes", m, k, inter, n_out)
     buf = ws.get(nbytes)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_mxfp8_glu_mlp_fwd", x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(),
                h.data_ptr() if h is not None else None, y.data_ptr(), m, k, inter, n_out, buf.data_ptr(), buf.numel(), _stream_ptr(),
                status_word(x.device).data_ptr())
@@ -277,7 +300,7 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
         _require(x, torch.bfloat16, "x")
     nbytes = N.query("rtxb_mxfp8_backward_workspace_bytes", m, n, k)
     buf = ws.get(nbytes)
-    with torch.cuda.device(dy.device):
+    with _on(dy.device):
         N.call("rtxb_mxfp8_linear_bwd", dy.data_ptr(), x.data_ptr() if x is not None else None,
                w.data_ptr() if w is not None else None, dx.data_ptr() if need_dx else None,
                dw.data_ptr() if need_dw else None, N.OUT_BF16 if dw_dtype == torch.bfloat16 else N.OUT_F32, m, n, k,
@@ -294,7 +317,7 @@ def sum_parts_f32_to_bf16(parts: torch.Tensor, out: Optional[torch.Tensor] = Non
         out = torch.empty(parts.shape[1:], dtype=torch.bfloat16, device=parts.device)
     if out.numel() != count or out.dtype is not torch.bfloat16 or not out.is_contiguous():
         raise ValueError("out must be a contiguous BF16 tensor with one part's element count")
-    with torch.cuda.device(parts.device):
+    with _on(parts.device):
         N.call("rtxb_sum_parts_f32_to_bf16", parts.data_ptr(), int(parts.shape[0]), count, count, out.data_ptr(),
                _stream_ptr())
     return out
@@ -374,7 +397,7 @@ def nvfp4_tensor_scale(src: torch.Tensor, mode: int = N.TENSOR_SCALE_POWER2,
     scratch = torch.empty(1, dtype=torch.int32, device=src.device)
     scale = torch.empty(1, dtype=torch.float32, device=src.device)
     prod = torch.empty(1, dtype=torch.float32, device=src.device) if other_scale is not None else None
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_nvfp4_tensor_scale", src.data_ptr(), rows, k, k, mode, scratch.data_ptr(), scale.data_ptr(),
                other_scale.data_ptr() if other_scale is not None else None,
                prod.data_ptr() if prod is not None else None, _stream_ptr())
@@ -388,7 +411,7 @@ def nvfp4_quantize(src: torch.Tensor, tensor_scale: Optional[torch.Tensor], *, l
     kp = mx_storage_k(k)
     q = torch.empty(rows, kp // 2, dtype=torch.uint8, device=src.device)
     scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_nvfp4_quantize", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout,
                tensor_scale.data_ptr() if tensor_scale is not None else None, _stream_ptr())
     return q, scales
@@ -406,11 +429,14 @@ def nvfp4_quantize_dynamic(src: torch.Tensor, mode: int = N.TENSOR_SCALE_POWER2,
     scratch = torch.empty(64, dtype=torch.int32, device=src.device)
     scale = torch.empty(1, dtype=torch.float32, device=src.device)
     prod = torch.empty(1, dtype=torch.float32, device=src.device) if other_scale is not None else None
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_nvfp4_quantize_dynamic", src.data_ptr(), rows, k, k, mode, q.data_ptr(), scales.data_ptr(), layout,
                scale.data_ptr(), other_scale.data_ptr() if other_scale is not None else None,
                prod.data_ptr() if prod is not None else None, scratch.data_ptr(), _stream_ptr())
     return q, scales, scale, prod
+
+
+_PREQUANT_W_BYTES: dict = {}
 
 
 def nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n: int, ws: Workspace, out: Optional[torch.Tensor] = None,
@@ -421,9 +447,11 @@ def nvfp4_linear_fwd_prequant_w(x, qw, sw, w_scale, n: int, ws: Workspace, out: 
     m, k = x.shape
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
-    nbytes = N.query("rtxb_nvfp4_linear_prequant_w_workspace_bytes", m, k)
+    nbytes = _PREQUANT_W_BYTES.get((m, k))
+    if nbytes is None:
+        nbytes = _PREQUANT_W_BYTES[(m, k)] = N.query("rtxb_nvfp4_linear_prequant_w_workspace_bytes", m, k)
     buf = ws.get(nbytes)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_nvfp4_linear_fwd_prequant_w", x.data_ptr(), qw.data_ptr(), sw.data_ptr(), w_scale.data_ptr(),
                out.data_ptr(), m, n, k, scale_mode, buf.data_ptr(), buf.numel(), _stream_ptr(),
                status_word(x.device).data_ptr())
@@ -442,7 +470,7 @@ def nvfp4_quantize_delayed(src: torch.Tensor, history: torch.Tensor, next_histor
     scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
     scale = torch.empty(1, dtype=torch.float32, device=src.device)
     prod = torch.empty(1, dtype=torch.float32, device=src.device) if other_scale is not None else None
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_nvfp4_quantize_delayed", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout,
                history.data_ptr(), next_history.data_ptr(), history.numel(), int(window_max), mode, scale.data_ptr(),
                other_scale.data_ptr() if other_scale is not None else None,
@@ -468,7 +496,7 @@ def nvfp4_linear_fwd_delayed(x, w, ws: Workspace, x_history, w_history, next_x_h
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
     nbytes = N.query("rtxb_nvfp4_linear_workspace_bytes", m, n, k)
     buf = ws.get(nbytes)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_nvfp4_linear_fwd_delayed", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
                x_history.data_ptr(), w_history.data_ptr(), next_x_history.data_ptr(), next_w_history.data_ptr(),
                x_history.numel(), int(window_max), scale_mode, buf.data_ptr(), buf.numel(), _stream_ptr(),
@@ -490,7 +518,7 @@ def nvfp4_region_scales(src: torch.Tensor, region_rows: int, mode: int = N.TENSO
     rows, k = src.shape
     scales = torch.empty(rows // max(region_rows, 1), dtype=torch.float32, device=src.device)
     scratch = torch.empty(1, dtype=torch.int32, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_nvfp4_region_scales", src.data_ptr(), rows, k, k, region_rows, mode, scratch.data_ptr(),
                scales.data_ptr(), _stream_ptr())
     return scales
@@ -504,7 +532,7 @@ def nvfp4_quantize_regions(src: torch.Tensor, region_scales: torch.Tensor, regio
     kp = mx_storage_k(k)
     q = torch.empty(rows, kp // 2, dtype=torch.uint8, device=src.device)
     scales = torch.empty(nvfp4_scale_numel(rows, k, layout), dtype=torch.uint8, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         N.call("rtxb_nvfp4_quantize_regions", src.data_ptr(), rows, k, k, q.data_ptr(), scales.data_ptr(), layout,
                region_scales.data_ptr(), region_rows, _stream_ptr())
     return q, scales
@@ -515,7 +543,7 @@ def nvfp4_gemm_regions(qa, sa, qb, sb, m: int, n: int, k: int, x_region_scales, 
     """out[m, n] = bf16(acc * (xs[m / Rx] * ws[n / Rw]))."""
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=qa.device)
-    with torch.cuda.device(qa.device):
+    with _on(qa.device):
         N.call("rtxb_nvfp4_gemm_regions", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(),
                m, n, k, out.stride(0), x_region_scales.data_ptr(), x_region_rows, w_region_scales.data_ptr(),
                w_region_rows, _stream_ptr(), status_word(qa.device).data_ptr())
@@ -537,7 +565,7 @@ def nvfp4_linear_fwd_regions(x, w, ws: Workspace, x_region_rows: int, w_region_r
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
     nbytes = N.query("rtxb_nvfp4_linear_regions_workspace_bytes", m, n, k, x_region_rows, w_region_rows)
     buf = ws.get(nbytes)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_nvfp4_linear_fwd_regions", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x_region_rows,
                w_region_rows, scale_mode, buf.data_ptr(), buf.numel(), _stream_ptr(),
                status_word(x.device).data_ptr())
@@ -549,7 +577,7 @@ def nvfp4_gemm(qa, sa, qb, sb, m: int, n: int, k: int, output_scale: Optional[to
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=qa.device)
     code = N.OUT_BF16 if out.dtype == torch.bfloat16 else N.OUT_F32
-    with torch.cuda.device(qa.device):
+    with _on(qa.device):
         N.call("rtxb_nvfp4_gemm", qa.data_ptr(), sa.data_ptr(), qb.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k,
                out.stride(0), code, output_scale.data_ptr() if output_scale is not None else None, _stream_ptr(),
                status_word(qa.device).data_ptr())
@@ -568,7 +596,7 @@ def nvfp4_linear_fwd(x, w, ws: Workspace, out: Optional[torch.Tensor] = None,
         out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
     nbytes = N.query("rtxb_nvfp4_linear_workspace_bytes", m, n, k)
     buf = ws.get(nbytes)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         N.call("rtxb_nvfp4_linear_fwd", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, scale_mode,
                buf.data_ptr(), buf.numel(), _stream_ptr(), status_word(x.device).data_ptr())
     return out
