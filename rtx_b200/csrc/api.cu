@@ -1359,37 +1359,6 @@ int64_t effective_region_rows(int64_t rows, int64_t requested) {
 }
 }  // namespace
 
-namespace {
-// Region scales + quantization of one operand, a block of rows at a time: the quantizer of a block re-reads
-// the rows its |max| pass has just pulled through L2, so the tensor crosses DRAM once instead of twice.
-// Blocks are about 48 MB of BF16 (well inside the 126 MB L2 together with what the quantizer writes), whole
-// 128-row scale tiles and whole regions.  The bits are those of the two whole-tensor launches.
-int quantize_regions_chunked(const void* src, int64_t rows, int64_t k, int64_t region_rows, int scale_mode,
-                             void* amax_scratch, float* region_scales, uint8_t* q, uint8_t* sf, void* stream) {
-  int rc;
-  const int64_t kp = round_up(k, 32);
-  int64_t unit = 128;   // lcm(128, region_rows)
-  while (unit % region_rows) unit += 128;
-  int64_t block = (48ll << 20) / (k * 2) / unit * unit;
-  if (region_rows == rows || block <= 0 || block >= rows) {
-    if ((rc = rtxb_nvfp4_region_scales(src, rows, k, k, region_rows, scale_mode, amax_scratch, region_scales, stream)))
-      return rc;
-    return rtxb_nvfp4_quantize_regions(src, rows, k, k, q, sf, RTXB_SCALE_MMA128, region_scales, region_rows, stream);
-  }
-  const size_t sf_per_128 = rtxb_nvfp4_scale_bytes(128, k, RTXB_SCALE_MMA128);
-  for (int64_t r0 = 0; r0 < rows; r0 += block) {
-    const int64_t r = rows - r0 < block ? rows - r0 : block;
-    const __nv_bfloat16* s0 = static_cast<const __nv_bfloat16*>(src) + r0 * k;
-    float* sc0 = region_scales + r0 / region_rows;
-    if ((rc = rtxb_nvfp4_region_scales(s0, r, k, k, region_rows, scale_mode, amax_scratch, sc0, stream))) return rc;
-    if ((rc = rtxb_nvfp4_quantize_regions(s0, r, k, k, q + r0 * (kp / 2), sf + (r0 / 128) * sf_per_128, RTXB_SCALE_MMA128,
-                                          sc0, region_rows, stream)))
-      return rc;
-  }
-  return RTXB_OK;
-}
-}  // namespace
-
 size_t rtxb_nvfp4_linear_regions_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t x_region_rows,
                                                  int64_t w_region_rows) {
   Carver c(nullptr);
@@ -1423,8 +1392,10 @@ int rtxb_nvfp4_linear_fwd_regions(const void* x, const void* w, void* out, int64
   uint8_t* qw = c.take(n * kp / 2);
   uint8_t* sw = c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
   int rc;
-  if ((rc = quantize_regions_chunked(x, m, k, rx, scale_mode, scal, xs, qx, sx, stream))) return rc;
-  if ((rc = quantize_regions_chunked(w, n, k, rw, scale_mode, scal + 4, wsc, qw, sw, stream))) return rc;
+  if ((rc = rtxb_nvfp4_region_scales(x, m, k, k, rx, scale_mode, scal, xs, stream))) return rc;
+  if ((rc = rtxb_nvfp4_region_scales(w, n, k, k, rw, scale_mode, scal + 4, wsc, stream))) return rc;
+  if ((rc = rtxb_nvfp4_quantize_regions(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, xs, rx, stream))) return rc;
+  if ((rc = rtxb_nvfp4_quantize_regions(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, wsc, rw, stream))) return rc;
   return rtxb_nvfp4_gemm_regions(qx, sx, qw, sw, out, m, n, k, n, xs, rx, wsc, rw, stream, status);
 }
 

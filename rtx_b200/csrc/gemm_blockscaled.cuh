@@ -180,13 +180,22 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
     for (int i = 0; i < 4; ++i) {
       const int c = (c_first + 32 * i) & 127;
       uint32_t g[32], u[32];
-      tmem_ld_32x32(tacc + c, g);
-      tmem_ld_32x32(tacc + 128 + c, u);
-      tmem_ld_wait();
       if (i == 0) {
+        // only one of the two groups lies in the columns the windows share (up for the even window, gate for
+        // the odd one): fetch it alone, release the next tile's MMAs, then fetch the other
+        if (odd) tmem_ld_32x32(tacc + c, g);
+        else tmem_ld_32x32(tacc + 128 + c, u);
+        tmem_ld_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(overlap_bar_addr);
+        if (odd) tmem_ld_32x32(tacc + 128 + c, u);
+        else tmem_ld_32x32(tacc + c, g);
+        tmem_ld_wait();
+      } else {
+        tmem_ld_32x32(tacc + c, g);
+        tmem_ld_32x32(tacc + 128 + c, u);
+        tmem_ld_wait();
       }
       if (!row_ok) continue;
       // H in BF16 (one rounding of the FP32 result), packed two per word
