@@ -364,7 +364,26 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const __nv_bfloat16* src
                                                         uint32_t* amax_bits) {
   uint32_t m = 0;
   const bool vec_ok = (ld % 8 == 0) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-  if (vec_ok) {
+  if (vec_ok && ld == k) {
+    // contiguous tensor: plain linear indexing (no division per load), eight 16-byte loads in flight per thread
+    const uint4* base = reinterpret_cast<const uint4*>(src);
+    const int64_t total = rows * (k / 8);
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < total; i0 += 8 * stride) {
+      uint4 raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) raw[j] = i0 + j * stride < total ? __ldg(base + i0 + j * stride) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+          m = max(m, w[e] & 0x7FFF0000u);
+        }
+      }
+    }
+  } else if (vec_ok) {
     // four 16-byte loads in flight per thread
     const int64_t vec_per_row = k / 8;
     const int64_t total = rows * vec_per_row;
