@@ -175,6 +175,27 @@ def load_runtime_winner(ctx: KernelContext, adapter: KernelAdapter, cache_dir=No
     return config if adapter.rejection(config, ctx) is None else None
 
 
+def time_call(run: Callable[[], Any], warmup: int = 2, samples: int = 5) -> TrialOutcome:
+    """Median device time of `run()` over `samples` calls after `warmup` untimed ones, by CUDA events on the
+    current stream; a RuntimeError from the call (an illegal schedule for the shape) is a failed trial."""
+    import torch
+
+    try:
+        for _ in range(max(0, warmup)):
+            run()
+        times = []
+        for _ in range(max(1, samples)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+    except RuntimeError as exc:
+        return TrialOutcome("failed", detail=str(exc))
+    return TrialOutcome("ok", median_ms=sorted(times)[len(times) // 2])
+
+
 def pick(ctx: KernelContext, adapter: KernelAdapter, evaluate: Callable[[Any], TrialOutcome], *, mode: str = "cache",
          cache_dir=None):
     """Resolve the schedule for `ctx`: `off` -> the adapter default; `cache` -> the stored winner or the
@@ -243,4 +264,4 @@ class ScheduleResolver:
 
 
 __all__ = ["KernelAdapter", "ScheduleResolver", "DiscreteKernelAdapter", "KernelContext", "TrialOutcome", "ADAPTERS", "pick",
-           "runtime_winner_path", "save_runtime_winner", "load_runtime_winner", "FAMILIES"]
+           "runtime_winner_path", "save_runtime_winner", "load_runtime_winner", "FAMILIES", "time_call"]

@@ -631,31 +631,25 @@ class NVFP4Linear(nn.Module):
             cfg = self._resolver.resolve(m, self._dynamic_config, evaluate)
         return cfg.to_key()
 
-    def _evaluator(self, x2d: torch.Tensor):
-        from .autotune import TrialOutcome
+    def _candidate_call(self, x2d: torch.Tensor, cfg):
+        """A zero-argument callable that runs this module's forward on `x2d` with the schedule `cfg`
+        (the configured schedule is put back after every call)."""
 
-        def evaluate(cfg) -> "TrialOutcome":
+        def run():
             saved = self._forward_key, self._dynamic_config, self._resolver.mode
             self._forward_key, self._dynamic_config, self._resolver.mode = cfg.to_key(), cfg, "off"
             try:
                 with torch.no_grad():
-                    for _ in range(2):
-                        self.forward(x2d)
-                    times = []
-                    for _ in range(5):
-                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        e0.record()
-                        self.forward(x2d)
-                        e1.record()
-                        e1.synchronize()
-                        times.append(e0.elapsed_time(e1))
-            except RuntimeError as exc:
-                return TrialOutcome("failed", detail=str(exc))
+                    return self.forward(x2d)
             finally:
                 self._forward_key, self._dynamic_config, self._resolver.mode = saved
-            return TrialOutcome("ok", median_ms=sorted(times)[len(times) // 2])
 
-        return evaluate
+        return run
+
+    def _evaluator(self, x2d: torch.Tensor, warmup: int = 2, samples: int = 5):
+        from .autotune import time_call
+
+        return lambda cfg: time_call(self._candidate_call(x2d, cfg), warmup, samples)
 
     def to(self, *args, **kwargs):
         if self.weight_mode == "prequantized":

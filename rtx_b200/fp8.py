@@ -441,35 +441,25 @@ class MXFP8Linear(nn.Module):
             cfg = self._resolver.resolve(m, _resolve_prequant(self._forward_config_key), self._evaluator(x2d))
         return _intern(cfg)
 
-    def _evaluator(self, x2d: torch.Tensor):
-        """Times one candidate schedule on this call's own operands (first-hit tuning)."""
-        from .autotune import TrialOutcome
+    def _candidate_call(self, x2d: torch.Tensor, cfg):
+        """A zero-argument callable that runs this module's forward on `x2d` with the schedule `cfg`."""
+        key = _intern(cfg)
 
-        def evaluate(cfg) -> "TrialOutcome":
-            key = _intern(cfg)
+        def run():
             with torch.no_grad():
-                def run():
-                    if self.weight_mode == "prequantized":
-                        return torch.ops.rtx.mxfp8_linear_dynamic_x_prequant_w(
-                            x2d, self.weight_data, self.weight_scales, self.out_features, self.in_features,
-                            self._weight_scale_layout, key)
-                    return torch.ops.rtx.mxfp8_linear_prequant(x2d, self.weight, key)
-                try:
-                    for _ in range(2):
-                        run()
-                    times = []
-                    for _ in range(5):
-                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        e0.record()
-                        run()
-                        e1.record()
-                        e1.synchronize()
-                        times.append(e0.elapsed_time(e1))
-                except RuntimeError as exc:
-                    return TrialOutcome("failed", detail=str(exc))
-            return TrialOutcome("ok", median_ms=sorted(times)[len(times) // 2])
+                if self.weight_mode == "prequantized":
+                    return torch.ops.rtx.mxfp8_linear_dynamic_x_prequant_w(
+                        x2d, self.weight_data, self.weight_scales, self.out_features, self.in_features,
+                        self._weight_scale_layout, key)
+                return torch.ops.rtx.mxfp8_linear_prequant(x2d, self.weight, key)
 
-        return evaluate
+        return run
+
+    def _evaluator(self, x2d: torch.Tensor, warmup: int = 2, samples: int = 5):
+        """Times one candidate schedule on this call's own operands (first-hit tuning)."""
+        from .autotune import time_call
+
+        return lambda cfg: time_call(self._candidate_call(x2d, cfg), warmup, samples)
 
     def to(self, *args, **kwargs):
         if self.weight_mode == "prequantized":

@@ -481,6 +481,43 @@ def test_nvfp4_module_tunes_on_first_use(dev, tmp_path):
     _done(dev)
 
 
+def test_campaign_over_a_manifest_installs_winners_the_modules_find(dev, tmp_path):
+    """A campaign in the reference's manifest format (autotune_manifests/*.json) over every tunable family:
+    each target gets a winner whose output passed the bit-equality gate, stored where a module with
+    autotune="cache" looks it up; the backward family is reported as skipped."""
+    import json
+
+    import rtx_b200 as rtx
+    from rtx_b200 import campaign
+
+    manifest = campaign.Manifest.from_dict({
+        "schema_version": 2, "name": "gpu_unit", "seed": 5,
+        "jobs": [{"family": f, "shapes": [{"m": 96, "n": 512, "k": 512, "name": "small"}], "regimes": regimes,
+                  "promote": 2, "protocol": {"warmup_calls": 1, "samples": 3, "confirm_samples": 3}}
+                 for f, regimes in (("mxfp8_prequant_fwd", ["hot", "rotate"]), ("mxfp8_weight_prequant_fwd", ["hot"]),
+                                    ("nvfp4_dynamic_fwd", ["hot"]), ("nvfp4_jit_row_region_fwd", ["hot"]),
+                                    ("nvfp4_delayed_fwd", ["hot"]), ("nvfp4_weight_prequant_fwd", ["hot"]),
+                                    ("mxfp8_bwd", ["hot"]))]})
+    summary = campaign.run_campaign(manifest, tmp_path / "out", cache_dir=tmp_path / "cache")
+    _done(dev)
+    assert [s["family"] for s in summary["skipped"]] == ["mxfp8_bwd"]
+    assert len(summary["targets"]) == 7
+    for t in summary["targets"]:
+        assert t["decision"] == "winner" and "installed" in t, t
+    trials = [json.loads(l) for l in open(tmp_path / "out" / "gpu_unit" / "trials.jsonl")]
+    assert all(t["status"] == "ok" for t in trials), [t for t in trials if t["status"] != "ok"]
+    # M = 96 admits every built schedule: 5 MXFP8 candidates (auto, single, pair, stream, fused_x), 4 NVFP4
+    searched = [t for t in trials if t["phase"] == "search" and t["family"] == "mxfp8_prequant_fwd" and
+                t["regime"] == "hot" and t["variant"] == "default"]
+    assert len(searched) == 5
+    for mod in (rtx.MXFP8Linear(512, 512, device=dev, autotune="cache", autotune_cache_dir=tmp_path / "cache"),
+                rtx.NVFP4Linear(512, 512, device=dev, autotune="cache", autotune_cache_dir=tmp_path / "cache"),
+                rtx.NVFP4Linear(512, 512, device=dev, scaling="delayed", autotune="cache",
+                                autotune_cache_dir=tmp_path / "cache")):
+        assert mod.explain(m=96)["schedule_source"] == "stored winner"
+        assert mod.explain(m=128)["schedule_source"] == "configured (no stored winner)"
+
+
 def test_quantized_weight_cache_is_bit_identical(dev):
     """Inside `quantized_weight_cache()` modules reuse the quantized weight across micro-batches; outputs,
     dX and accumulated dW equal the uncached run bit for bit, an in-place weight update is seen, and the
