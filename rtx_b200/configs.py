@@ -12,6 +12,7 @@ through custom ops as an interned JSON key (`to_key` / `config_from_key`).
 
 from __future__ import annotations
 
+import functools
 import json
 from dataclasses import asdict, dataclass, field, fields
 from typing import ClassVar, Optional
@@ -49,7 +50,10 @@ class _Config:
         return cls(**kwargs)
 
 
+@functools.lru_cache(maxsize=1024)
 def config_from_key(key: str):
+    """The schedule a key names.  Configs are frozen, so one parsed instance serves every call that carries
+    the key (keys ride on the launch path of every op call)."""
     d = json.loads(key)
     return _REGISTRY[d["type"]].from_dict(d)
 

@@ -15,12 +15,14 @@ current |max| is only observed, in the same pass that quantizes) and `block`
 
 from __future__ import annotations
 
+import functools
 from pathlib import Path
 from typing import Optional
 
 import torch
 from torch import nn
 
+from ._oplib import custom_op
 from . import _native as N
 from . import fp8 as _fp8
 from . import ops
@@ -38,7 +40,7 @@ _LAYOUT_CODE = {"row_major": N.SCALE_ROW_MAJOR, "mma128": N.SCALE_MMA128}
 _SCALE_MODE = {"exact": N.TENSOR_SCALE_EXACT, "power2": N.TENSOR_SCALE_POWER2}
 
 
-@torch.library.custom_op("rtx::nvfp4_outer_scale", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_outer_scale", mutates_args=(), device_types="cuda")
 def nvfp4_outer_scale(x: torch.Tensor, mode: str) -> torch.Tensor:
     """FP32[1] outer decode scale of a BF16 matrix: one device pass (|max| reduction + scale rule),
     no host synchronisation.  The reference computes it with PyTorch reductions (rtx/fp4.py:343-365)."""
@@ -100,6 +102,7 @@ def quantize_nvfp4(tensor: torch.Tensor, *, tensor_scale: Optional[torch.Tensor]
     return make_nvfp4_tensor(q, s, scale.reshape(()), tuple(int(v) for v in tensor.shape), selected.scale_layout)
 
 
+@functools.lru_cache(maxsize=1024)
 def _resolve_dynamic(key: str) -> NVFP4DynamicConfig:
     cfg = config_from_key(key)
     if not isinstance(cfg, NVFP4DynamicConfig):
@@ -122,7 +125,7 @@ def _materialized_forward(x, weight, x_scale, weight_scale, output_scale):
 
 # --------------------------------------------------------------------------- custom ops
 
-@torch.library.custom_op("rtx::nvfp4_linear_materialized_fwd", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_materialized_fwd", mutates_args=(), device_types="cuda")
 def nvfp4_linear_materialized_fwd(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor,
                                   weight_scale: torch.Tensor, output_scale: torch.Tensor, key: str) -> torch.Tensor:
     """`current` policy: outer scales computed by the caller, dual quantize, GEMM x output_scale
@@ -136,7 +139,7 @@ def _(x, weight, x_scale, weight_scale, output_scale, key):
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_materialized_train", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_materialized_train", mutates_args=(), device_types="cuda")
 def nvfp4_linear_materialized_train(x: torch.Tensor, weight: torch.Tensor, x_scale: torch.Tensor,
                                     weight_scale: torch.Tensor, output_scale: torch.Tensor, key: str,
                                     bwd_key: str) -> torch.Tensor:
@@ -175,7 +178,7 @@ def _nv_train_backward(ctx, grad_output):
 nvfp4_linear_materialized_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_block_fwd", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_block_fwd", mutates_args=(), device_types="cuda")
 def nvfp4_linear_block_fwd(x: torch.Tensor, weight: torch.Tensor, key: str) -> torch.Tensor:
     """`block` policy: outer scale 1 folded out of both kernels (rtx/fp4.py:859-875)."""
     with ops.schedule_of(_resolve_dynamic(key).gemm):
@@ -187,7 +190,7 @@ def _(x, weight, key):
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_block_train", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_block_train", mutates_args=(), device_types="cuda")
 def nvfp4_linear_block_train(x: torch.Tensor, weight: torch.Tensor, key: str, bwd_key: str) -> torch.Tensor:
     with ops.schedule_of(_resolve_dynamic(key).gemm):
         return _materialized_forward(x, weight, None, None, None)
@@ -213,7 +216,7 @@ def _jit_row_region_forward(x, weight, key):
                                             scale_mode=_SCALE_MODE[cfg.scale.tensor_scale_mode])
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_jit_row_region_fwd", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_jit_row_region_fwd", mutates_args=(), device_types="cuda")
 def nvfp4_linear_jit_row_region_fwd(x: torch.Tensor, weight: torch.Tensor, key: str) -> torch.Tensor:
     """`jit_row_region` policy: per-region outer scales observed and applied inside the call
     (rtx/fp4.py:1604-1626, _JITRegionDynamicRunner :522-560); region sizes travel in the config key."""
@@ -225,7 +228,7 @@ def _(x, weight, key):
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_jit_row_region_train", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_jit_row_region_train", mutates_args=(), device_types="cuda")
 def nvfp4_linear_jit_row_region_train(x: torch.Tensor, weight: torch.Tensor, key: str, bwd_key: str) -> torch.Tensor:
     return _jit_row_region_forward(x, weight, key)
 
@@ -238,7 +241,7 @@ def _(x, weight, key, bwd_key):
 nvfp4_linear_jit_row_region_train.register_autograd(_nv_train_backward, setup_context=_nv_train_setup)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_train_delayed",
+@custom_op("rtx::nvfp4_linear_train_delayed",
                          mutates_args=("next_x_amax_state", "next_weight_amax_state"), device_types="cuda")
 def nvfp4_linear_train_delayed(x: torch.Tensor, weight: torch.Tensor, x_amax_state: torch.Tensor,
                                weight_amax_state: torch.Tensor, next_x_amax_state: torch.Tensor,
@@ -289,7 +292,7 @@ def _delayed_amax_state(tensor: torch.Tensor, values: int) -> torch.Tensor:
     return amax.expand(values).clone()
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
 def nvfp4_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor, weight_block_scales: torch.Tensor,
                                       x_scale: torch.Tensor, output_scale: torch.Tensor, n: int, k: int, layout: str,
                                       key: str) -> torch.Tensor:
@@ -308,7 +311,7 @@ def _(x, weight_data, weight_block_scales, x_scale, output_scale, n, k, layout, 
     return x.new_empty((x.shape[0], n), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_prequant_w_current", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_prequant_w_current", mutates_args=(), device_types="cuda")
 def nvfp4_linear_prequant_w_current(x: torch.Tensor, weight_data: torch.Tensor, weight_block_scales: torch.Tensor,
                                     weight_tensor_scale: torch.Tensor, n: int, k: int, layout: str,
                                     key: str) -> torch.Tensor:
@@ -330,7 +333,7 @@ def _(x, weight_data, weight_block_scales, weight_tensor_scale, n, k, layout, ke
     return x.new_empty((x.shape[0], n), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::nvfp4_linear_prequantized", mutates_args=(), device_types="cuda")
+@custom_op("rtx::nvfp4_linear_prequantized", mutates_args=(), device_types="cuda")
 def nvfp4_linear_prequantized(x_data: torch.Tensor, weight_data: torch.Tensor, x_block_scales: torch.Tensor,
                               weight_block_scales: torch.Tensor, output_scale: torch.Tensor, m: int, n: int, k: int,
                               x_layout: str, weight_layout: str, key: str) -> torch.Tensor:
@@ -347,12 +350,12 @@ def _(x_data, weight_data, x_block_scales, weight_block_scales, output_scale, m,
 
 
 def _kernel_block_scales(scales: torch.Tensor, rows: int, k: int, layout: str) -> torch.Tensor:
+    if layout == "mma128":
+        return scales.reshape(-1).view(torch.uint8)
     from .formats.common import scales_row_major_to_mma128
     from .formats.nvfp4 import nvfp4_scale_chunks
 
     storage_k = nvfp4_storage_k(k)
-    if layout == "mma128":
-        return scales.reshape(-1).view(torch.uint8)
     if layout == "row_major":
         return scales_row_major_to_mma128(scales, rows, storage_k // 16, nvfp4_scale_chunks(storage_k))
     raise RuntimeError(f"NVFP4 scale layout {layout!r} cannot feed the sm_100a GEMM")

@@ -12,6 +12,7 @@ Schedules travel through the ops as interned JSON keys (rtx/fp8.py:376-415).
 
 from __future__ import annotations
 
+import functools
 from pathlib import Path
 from threading import RLock
 from typing import Optional
@@ -19,6 +20,7 @@ from typing import Optional
 import torch
 from torch import nn
 
+from ._oplib import custom_op
 from . import _native as N
 from . import ops
 from . import weight_cache as _weight_cache
@@ -72,7 +74,8 @@ def _check_inputs(x: torch.Tensor, weight: torch.Tensor) -> None:
 def _workspace(device: torch.device) -> ops.Workspace:
     """One scratch buffer per (device, stream): launches on a stream are ordered, so one
     in-flight use at a time (rtx/fp8.py:954-970)."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    index = device.index if device.index is not None else torch._C._cuda_getDevice()
+    key = (index, torch._C._cuda_getCurrentRawStream(index))
     with _LOCK:
         ws = _WORKSPACES.get(key)
         if ws is None:
@@ -87,6 +90,7 @@ def _clear_runtime_caches() -> dict:
     return {"workspaces": stats}
 
 
+@functools.lru_cache(maxsize=1024)
 def _resolve_prequant(config_key: str) -> MXFP8PrequantConfig:
     cfg = config_from_key(config_key)
     if isinstance(cfg, MXFP8FwdConfig):
@@ -127,7 +131,7 @@ def quantize_mxfp8(tensor: torch.Tensor, *, config: Optional[MXFP8QuantConfig] =
 
 # --------------------------------------------------------------------------- custom ops
 
-@torch.library.custom_op("rtx::mxfp8_linear_fwd", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_fwd", mutates_args=(), device_types="cuda")
 def mxfp8_linear_fwd(x: torch.Tensor, weight: torch.Tensor, config_key: str) -> torch.Tensor:
     _check_inputs(x, weight)
     cfg = _resolve_prequant(config_key)
@@ -146,10 +150,10 @@ def _(x, weight, config_key):
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_prequant", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_prequant", mutates_args=(), device_types="cuda")
 def mxfp8_linear_prequant(x: torch.Tensor, weight: torch.Tensor, config_key: str) -> torch.Tensor:
     """Materialized pipeline: quantize both operands once, then the packed GEMM (rtx/fp8.py:1016-1030)."""
-    return mxfp8_linear_fwd(x, weight, config_key)
+    return mxfp8_linear_fwd.fn(x, weight, config_key)   # the implementation itself: one dispatch per call, not two
 
 
 @mxfp8_linear_prequant.register_fake
@@ -200,7 +204,7 @@ def _(x, weight, config_key, out):
     return None
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_dynamic_x_prequant_w", mutates_args=(), device_types="cuda")
 def mxfp8_linear_dynamic_x_prequant_w(x: torch.Tensor, weight_data: torch.Tensor, weight_scales: torch.Tensor, n: int,
                                       k: int, weight_scale_layout: str, config_key: str) -> torch.Tensor:
     """BF16 activations, packed weight (rtx/fp8.py:1269-1302)."""
@@ -222,7 +226,7 @@ def _(x, weight_data, weight_scales, n, k, weight_scale_layout, config_key):
     return x.new_empty((x.shape[0], n), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_prequantized", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_prequantized", mutates_args=(), device_types="cuda")
 def mxfp8_linear_prequantized(x_data: torch.Tensor, weight_data: torch.Tensor, x_scales: torch.Tensor,
                               weight_scales: torch.Tensor, m: int, n: int, k: int, x_scale_layout: str,
                               weight_scale_layout: str, config_key: str) -> torch.Tensor:

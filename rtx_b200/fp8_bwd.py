@@ -16,6 +16,7 @@ from typing import Optional, Tuple
 
 import torch
 
+from ._oplib import custom_op
 from . import fp8 as _fp8
 from . import ops
 from .configs import MXFP8BwdConfig, config_from_key
@@ -62,7 +63,7 @@ def _run(grad_output, x, weight, need_dx, need_dw, dw_dtype=torch.bfloat16):
                                 need_dx=need_dx, need_dw=need_dw, dw_dtype=dw_dtype)
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_bwd", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_bwd", mutates_args=(), device_types="cuda")
 def mxfp8_linear_bwd(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
                      config_key: str) -> Tuple[torch.Tensor, torch.Tensor]:
     _bwd_config(config_key)
@@ -75,7 +76,7 @@ def _(grad_output, x, weight, config_key):
     return torch.empty_like(x), torch.empty_like(weight)
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_bwd_packed", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_bwd_packed", mutates_args=(), device_types="cuda")
 def mxfp8_linear_bwd_packed(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
                             config_key: str) -> torch.Tensor:
     """One flat allocation `[dX | pad to 8 elements | dW]` (rtx/fp8_bwd.py:1040-1094)."""
@@ -102,7 +103,7 @@ def unpack_bwd(flat: torch.Tensor, x_shape, w_shape):
     return flat[:dx_n].view(x_shape), flat[dw_off:dw_off + w_shape[0] * w_shape[1]].view(w_shape)
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_dx", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_dx", mutates_args=(), device_types="cuda")
 def mxfp8_linear_dx(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
                     config_key: str) -> torch.Tensor:
     """dX only; `x` gives the result's shape, as in the reference (rtx/fp8_bwd.py:1097-1118)."""
@@ -115,7 +116,7 @@ def _(grad_output, x, weight, config_key):
     return torch.empty_like(x)
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_dw", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_dw", mutates_args=(), device_types="cuda")
 def mxfp8_linear_dw(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
                     config_key: str) -> torch.Tensor:
     """dW only; `weight` gives the result's shape (rtx/fp8_bwd.py:1121-1142)."""
@@ -182,7 +183,7 @@ def _(grad_output, x, weight, config_key, *, grad_weight):
     return grad_weight
 
 
-@torch.library.custom_op("rtx::mxfp8_linear_dw_f32", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_dw_f32", mutates_args=(), device_types="cuda")
 def mxfp8_linear_dw_f32(grad_output: torch.Tensor, x: torch.Tensor, config_key: str) -> torch.Tensor:
     """FP32 dW for the data-parallel all-reduce (no counterpart in the single-GPU reference)."""
     _bwd_config(config_key)
@@ -196,7 +197,7 @@ def _(grad_output, x, config_key):
 
 # --------------------------------------------------------------------------- training op
 
-@torch.library.custom_op("rtx::mxfp8_linear_train", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_linear_train", mutates_args=(), device_types="cuda")
 def mxfp8_linear_train(x: torch.Tensor, weight: torch.Tensor, fwd_key: str, bwd_key: str) -> torch.Tensor:
     """Forward of the differentiable op (rtx/fp8_bwd.py:1481-1494); saves BF16 (x, weight)."""
     return torch.ops.rtx.mxfp8_linear_prequant(x, weight, fwd_key)

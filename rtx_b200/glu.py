@@ -13,12 +13,13 @@ from __future__ import annotations
 import torch
 from torch import nn
 
+from ._oplib import custom_op
 from . import fp8 as _fp8
 from . import ops
 from . import weight_cache as _weight_cache
 
 
-@torch.library.custom_op("rtx::mxfp8_glu_mlp_fwd", mutates_args=(), device_types="cuda")
+@custom_op("rtx::mxfp8_glu_mlp_fwd", mutates_args=(), device_types="cuda")
 def mxfp8_glu_mlp_fwd(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
     """x [M, K], w_gate_up [2*I, K] (gate rows first, I a multiple of 128), w_down [N, I] -> y [M, N]:
     three quantizer launches, the gate/up GEMM whose epilogue emits H = silu(g) * u already MXFP8-encoded,
