@@ -326,7 +326,8 @@ def run_own_arm(args) -> None:
 
     # ---------------- end to end through host buffers (rtx_b200.host.GluMlpHostSession) ----------------
     # every step copies that step's X from pinned host memory to the device and its Y back; copy-in of step
-    # i+1 and copy-out of step i-1 overlap the compute of step i (three streams, three device buffer sets)
+    # i+1 and copy-out of step i-1 overlap the compute of step i (three streams, three device buffer sets),
+    # and a step of 8192 rows or more is itself pipelined in blocks of 2048 rows
     session = GluMlpHostSession(wgu, wd, per)
     x_hosts = [x_host, x_host.clone().pin_memory()]
     y_hosts = [y_host, torch.empty_like(y_host).pin_memory()]
@@ -343,6 +344,7 @@ def run_own_arm(args) -> None:
     timer.results["e2e"] = (time.perf_counter() - t0) * 1e3 / steps   # spans three streams: host clock, submit..drain
     sampler.mark("burst", w0, time.time())
     timer.barrier()
+    e2e_launches = session.launches_per_step
     del session
 
     # the copies of the end-to-end step alone (X in and Y out at the same time, no compute): its PCIe floor
@@ -459,7 +461,9 @@ def run_own_arm(args) -> None:
             "pct_of_measured_fp8_proxy": 100.0 * value / world / fp8_peak,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world, "ms_per_step": res["e2e"],
-                    "api": "rtx_b200.host.GluMlpHostSession.submit/drain (copies overlapped with compute)",
+                    "api": "rtx_b200.host.GluMlpHostSession.submit/drain (copies overlapped with compute; steps of "
+                           "8192 rows or more also run as blocks of 2048 rows, weights quantized once per step)",
+                    "gpu_launches_per_step": e2e_launches,
                     "host_cpus": f"{len(numa.cpus)} CPUs next to the GPU" if numa.cpus else "unbound",
                     "copies_alone_ms_per_step": res["copies"],
                     "copies_alone_gbs_each_way": x_host.numel() * 2 / (res["copies"] * 1e-3) / 1e9},

@@ -4,7 +4,9 @@ runs the MXFP8 MLP (quantize, gate/up GEMM with fused SiLU*up, quantize, down GE
 and copies Y back to pinned host memory.  Three streams and three device buffer sets
 let the copy-in of step i+1 and the copy-out of step i-1 overlap the compute of
 step i (a buffer set's X is free again as soon as its previous compute has finished,
-its Y once the previous copy-out has); `drain()` waits for everything submitted.
+its Y once the previous copy-out has), and by default each step is itself cut into
+blocks of token rows that are copied, computed and returned one after another;
+`drain()` waits for everything submitted.
 """
 
 from __future__ import annotations
@@ -67,9 +69,18 @@ class numa_local:
 
 
 class GluMlpHostSession:
-    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, max_rows: int, depth: int = 3):
+    """`chunk_rows` (default: 2048 for steps of 8192 rows or more; 0 = off) pipelines WITHIN a step as well: the weights are quantized once per step, then every
+    block of `chunk_rows` token rows is copied in, run through the two GEMMs and copied out on its own, so the
+    first bytes of Y leave while later rows of X are still arriving.  A step's latency drops from (copy in +
+    compute + copy out) to about one chunk of each beyond the longest of the three; the bits are those of
+    the whole-step call (rows are independent, K is accumulated in the same order)."""
+
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, max_rows: int, depth: int = 3,
+                 chunk_rows: Optional[int] = None):
         if w_gate_up.device.type != "cuda":
             raise ValueError("weights must already be resident on the GPU")
+        if chunk_rows is not None and (chunk_rows < 0 or chunk_rows % 128):
+            raise ValueError("chunk_rows must be a non-negative multiple of 128 (whole scale tiles)")
         self.device = w_gate_up.device
         self.w_gate_up, self.w_down = w_gate_up.contiguous(), w_down.contiguous()
         self.k = w_gate_up.shape[1]
@@ -77,15 +88,16 @@ class GluMlpHostSession:
         self.n_out = w_down.shape[0]
         self.max_rows = max_rows
         self.depth = depth
+        self.chunk_rows = chunk_rows
         with torch.cuda.device(self.device):
             self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream() for _ in range(3))
         self.x = [torch.empty(max_rows, self.k, dtype=torch.bfloat16, device=self.device) for _ in range(depth)]
         self.y = [torch.empty(max_rows, self.n_out, dtype=torch.bfloat16, device=self.device) for _ in range(depth)]
         self.ws = ops.Workspace(self.device)
-        self._in_done: List[Optional[torch.cuda.Event]] = [None] * depth
         self._compute_done: List[Optional[torch.cuda.Event]] = [None] * depth
         self._out_done: List[Optional[torch.cuda.Event]] = [None] * depth
         self._step = 0
+        self.launches_per_step = 0      # kernels launched by the last submit
 
     def submit(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
         """Enqueue one MLP forward; `x_host` / `y_host` must be pinned and stay alive until `drain()`."""
@@ -95,27 +107,53 @@ class GluMlpHostSession:
         if m > self.max_rows or x_host.shape[1] != self.k:
             raise ValueError("activation shape does not fit this session")
         b = self._step % self.depth
+        if self.chunk_rows is None:
+            # blocks of 2048 rows once a step has four of them: there the copies outlast the compute and the
+            # GEMMs still run near their full-size rate (measured on B200: 8192 rows 1.42 ms per step against
+            # 1.56 whole; at 4096 rows and below the step is compute bound and whole steps are faster)
+            chunk = 2048 if m >= 8192 else m
+        else:
+            chunk = self.chunk_rows
+        if chunk <= 0 or chunk >= m:
+            chunk = m
         with torch.cuda.device(self.device):
             # x[b] is free once the previous occupant's kernels have read it; y[b] once it has been copied out
             if self._compute_done[b] is not None:
                 self.copy_in.wait_event(self._compute_done[b])
             if self._out_done[b] is not None:
                 self.compute.wait_event(self._out_done[b])
-            with torch.cuda.stream(self.copy_in):
-                self.x[b][:m].copy_(x_host, non_blocking=True)
-                self._in_done[b] = torch.cuda.Event()
-                self._in_done[b].record(self.copy_in)
-            self.compute.wait_event(self._in_done[b])
-            with torch.cuda.stream(self.compute):
-                ops.mxfp8_glu_mlp_fwd(self.x[b][:m], self.w_gate_up, self.w_down, self.ws, None, self.y[b][:m],
-                                      want_hidden=False)
-                self._compute_done[b] = torch.cuda.Event()
-                self._compute_done[b].record(self.compute)
-            self.copy_out.wait_event(self._compute_done[b])
-            with torch.cuda.stream(self.copy_out):
-                y_host.copy_(self.y[b][:m], non_blocking=True)
-                self._out_done[b] = torch.cuda.Event()
-                self._out_done[b].record(self.copy_out)
+            launches = 0
+            if chunk < m:
+                with torch.cuda.stream(self.compute):   # the step's weights, quantized once
+                    qg, sg = ops.mxfp8_quantize(self.w_gate_up)
+                    qd, sd = ops.mxfp8_quantize(self.w_down)
+                launches += 2
+            for r0 in range(0, m, chunk):
+                r1 = min(r0 + chunk, m)
+                with torch.cuda.stream(self.copy_in):
+                    self.x[b][r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(self.copy_in)
+                self.compute.wait_event(arrived)
+                with torch.cuda.stream(self.compute):
+                    if chunk < m:
+                        qx, sx = ops.mxfp8_quantize(self.x[b][r0:r1])
+                        qh, sh, _ = ops.mxfp8_gemm_glu_mx(qx, sx, qg, sg, r1 - r0, self.inter, self.k)
+                        ops.mxfp8_gemm(qh, sh, qd, sd, r1 - r0, self.n_out, self.inter, out=self.y[b][r0:r1])
+                        launches += 3
+                    else:
+                        ops.mxfp8_glu_mlp_fwd(self.x[b][:m], self.w_gate_up, self.w_down, self.ws, None, self.y[b][:m],
+                                              want_hidden=False)
+                        launches += 5
+                    computed = torch.cuda.Event()
+                    computed.record(self.compute)
+                self.copy_out.wait_event(computed)
+                with torch.cuda.stream(self.copy_out):
+                    y_host[r0:r1].copy_(self.y[b][r0:r1], non_blocking=True)
+            self._compute_done[b] = computed
+            self._out_done[b] = torch.cuda.Event()
+            self._out_done[b].record(self.copy_out)
+            self.launches_per_step = launches
         self._step += 1
 
     def drain(self) -> None:

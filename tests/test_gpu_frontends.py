@@ -518,6 +518,31 @@ def test_campaign_over_a_manifest_installs_winners_the_modules_find(dev, tmp_pat
         assert mod.explain(m=128)["schedule_source"] == "configured (no stored winner)"
 
 
+@pytest.mark.parametrize("chunk_rows", [None, 0, 256, 512])
+def test_host_session_returns_the_bits_of_the_device_call(dev, chunk_rows):
+    """`GluMlpHostSession` (host buffers in, host buffers out): whole-step and row-block pipelining give the
+    bits of the device-resident MLP call, over several steps that re-use the buffer sets, ragged last block."""
+    from rtx_b200 import ops
+    from rtx_b200.host import GluMlpHostSession
+
+    torch.manual_seed(21)
+    m, k, inter, n_out = 1200, 512, 768, 384
+    wgu = (torch.randn(2 * inter, k) / k ** 0.5).bfloat16().to(dev)
+    wd = (torch.randn(n_out, inter) / inter ** 0.5).bfloat16().to(dev)
+    session = GluMlpHostSession(wgu, wd, m, chunk_rows=chunk_rows)
+    ws = ops.Workspace(dev)
+    xs = [torch.randn(m if i != 2 else 700, k).bfloat16().pin_memory() for i in range(5)]
+    ys = [torch.empty(x.shape[0], n_out, dtype=torch.bfloat16).pin_memory() for x in xs]
+    for x, y in zip(xs, ys):
+        session.submit(x, y)
+    session.drain()
+    assert session.launches_per_step == (2 + 3 * -(-1200 // chunk_rows) if chunk_rows else 5)
+    for x, y in zip(xs, ys):
+        _, want = ops.mxfp8_glu_mlp_fwd(x.to(dev), wgu, wd, ws, want_hidden=False)
+        assert torch.equal(y, want.cpu())
+    _done(dev)
+
+
 def test_quantized_weight_cache_is_bit_identical(dev):
     """Inside `quantized_weight_cache()` modules reuse the quantized weight across micro-batches; outputs,
     dX and accumulated dW equal the uncached run bit for bit, an in-place weight update is seen, and the
