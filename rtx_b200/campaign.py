@@ -9,7 +9,7 @@ winner store that `autotune="cache"` on the modules reads (rtx/autotune/promotio
 rtx/autotune/winners.py:117-170).  Every trial is appended to `<out>/<manifest name>/trials.jsonl`.
 
 The candidate space here is the handful of built kernels, so the search is exhaustive: the manifest's
-`tuning` block (trial budgets, cost-model and bandit settings of the reference's search engine) is read and
+`tuning` block (trial limits, cost-model and bandit settings of the reference's search engine) is read and
 recorded but drives nothing.  `protocol.warmup_calls`, `protocol.samples`, `protocol.confirm_samples` and
 `promote` (how many candidates go to confirmation) are honoured.
 
