@@ -229,6 +229,12 @@ def test_custom_ops_dispatch_on_fake_cuda_tensors():
         assert ops.nvfp4_linear_prequantized(q, q, sc, sc, s, 80, 80, 96, "mma128", "mma128", nk).shape == (80, 80)
     schema = str(torch.ops.rtx.mxfp8_linear_fwd.default._schema)
     assert "Tensor x, Tensor weight, str config_key" in schema
+    # declared with the dispatcher directly (rtx_b200/_oplib.py): compile-safe tag, and no kernel for CPU tensors —
+    # the product path has no CPU fallback
+    assert torch.Tag.pt2_compliant_tag in torch.ops.rtx.mxfp8_linear_fwd.default.tags
+    assert torch.Tag.pt2_compliant_tag in torch.ops.rtx.nvfp4_linear_prequant_w_current.default.tags
+    with pytest.raises(NotImplementedError):
+        torch.ops.rtx.mxfp8_linear_fwd(torch.zeros(32, 32, dtype=torch.bfloat16), torch.zeros(32, 32, dtype=torch.bfloat16), fk)
 
 
 def test_scale_layout_conversion_matches_the_oracle():
