@@ -54,10 +54,25 @@ extern "C" {
 #define RTXB_TENSOR_SCALE_EXACT 0
 #define RTXB_TENSOR_SCALE_POWER2 1
 
+/* codes a kernel leaves in the caller's `status` word when one of its bounded waits runs out */
+#define RTXB_DEV_OK 0
+#define RTXB_DEV_WAIT_PRODUCER 1   /* TMA producer: no free ring slot */
+#define RTXB_DEV_WAIT_MMA 2        /* MMA issuer: operands or accumulator columns never arrived */
+#define RTXB_DEV_WAIT_EPILOGUE 3   /* epilogue: accumulator never completed */
+#define RTXB_DEV_WAIT_QUANT 4      /* in-kernel quantizer warps */
+#define RTXB_DEV_WAIT_SELFTEST 5   /* rtxb_selftest_wait_timeout */
+
 int rtxb_version(void);
 const char* rtxb_error_string(int code);
 /* last CUDA/driver error text recorded by this thread's most recent failing call */
 const char* rtxb_last_cuda_error(void);
+
+/* Self-test of the failure path every kernel role shares.  No counterpart in the reference.  Launches one warp
+ * that waits, with the bounded wait the GEMM and quantizer roles use, on a barrier that nothing completes; after
+ * `limit_ns` nanoseconds (1 ms .. 2 s) the wait gives up, the kernel stores RTXB_DEV_WAIT_SELFTEST in `status`
+ * (and the time it waited in `waited_ns`, optional) and returns normally: the context stays usable and the next
+ * launch runs.  This is how a lost arrival reaches the host, instead of a hung GPU. */
+int rtxb_selftest_wait_timeout(int64_t limit_ns, void* stream, int* status, unsigned long long* waited_ns);
 
 /* SMs that the persistent kernels of this library leave unused from now on (process-wide; 0 =
  * use every SM).  No counterpart in the reference (single GPU): the GEMMs here hold every SM for

@@ -956,6 +956,15 @@ int rtxb_sum_parts_f32_to_bf16(const float* parts, int n_parts, int64_t part_str
   return RTXB_OK;
 }
 
+int rtxb_selftest_wait_timeout(int64_t limit_ns, void* stream, int* status, unsigned long long* waited_ns) {
+  if (!status) return fail_msg(RTXB_E_INVALID_ARGUMENT, "the self-test reports through the status word");
+  if (limit_ns < 1000000 || limit_ns > 2000000000ll)
+    return fail_msg(RTXB_E_INVALID_ARGUMENT, "limit between 1 ms and 2 s");
+  wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint64_t>(limit_ns), status, waited_ns);
+  RTXB_CHECK_LAUNCH("wait_selftest_kernel");
+  return RTXB_OK;
+}
+
 size_t rtxb_mxfp8_backward_workspace_bytes(int64_t m, int64_t n, int64_t k) {
   Carver c(nullptr);
   const int64_t np = round_up(n, 32), mp = round_up(m, 32);

@@ -21,6 +21,7 @@ enum DeviceStatus : int {
   kStatusWaitMma = 2,        // MMA issuer gave up waiting for operands / TMEM
   kStatusWaitEpilogue = 3,   // epilogue gave up waiting for accumulators
   kStatusWaitQuant = 4,      // quantizer warps gave up waiting for a BF16 tile
+  kStatusWaitSelfTest = 5,   // the wait self-test's barrier (which nothing ever completes) ran out, as it must
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -80,7 +81,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // caller then records a status and leaves its loop.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t start = 0;
   uint32_t polls = 0;
@@ -89,7 +91,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (start == 0) start = now;
-      else if (now - start > kWaitLimitNs) return false;
+      else if (now - start > limit_ns) return false;
     }
   }
   return true;

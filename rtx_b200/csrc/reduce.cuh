@@ -46,4 +46,27 @@ __global__ void __launch_bounds__(kReduceThreads) sum_parts_f32_to_bf16_kernel(c
   }
 }
 
+// Self-test of the bounded wait every kernel role uses: one warp waits on a barrier that nothing will ever
+// complete, with the limit given; when the limit runs out it records kStatusWaitSelfTest in the status word,
+// raises the abort flag as the GEMM roles do, and the kernel returns normally.  Nothing traps, nothing spins
+// without a bound: this is how a lost arrival shows up to the host instead of as a hung GPU.
+__global__ void wait_selftest_kernel(uint64_t limit_ns, int* status, unsigned long long* waited_ns) {
+  __shared__ uint64_t never;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&never, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const uint64_t t0 = global_timer_ns();
+  const bool completed = mbar_wait(&never, 0, &abort_flag, limit_ns);
+  const uint64_t t1 = global_timer_ns();
+  if (!completed && threadIdx.x == 0) {
+    if (status) atomicCAS(status, 0, kStatusWaitSelfTest);
+    abort_flag = 1;
+    if (waited_ns) *waited_ns = t1 - t0;
+  }
+}
+
 }  // namespace rtxb

@@ -106,3 +106,16 @@ def test_missing_library_is_loud(monkeypatch, tmp_path):
     monkeypatch.setattr(N, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         N.load()
+
+
+def test_device_status_codes_agree_between_header_kernels_and_python():
+    """RTXB_DEV_* in the header, the DeviceStatus enum the kernels store, and the names Python reports."""
+    from rtx_b200 import _native
+
+    header = open(os.path.join(ROOT, "include", "rtxb.h")).read()
+    macros = {name: int(v) for name, v in re.findall(r"#define (RTXB_DEV_[A-Z_]+) (\d+)", header)}
+    device = open(os.path.join(ROOT, "rtx_b200", "csrc", "common.cuh")).read()
+    enum = {name: int(v) for name, v in re.findall(r"(kStatus[A-Za-z]+) = (\d+)", device)}
+    assert sorted(macros.values()) == sorted(enum.values()) == sorted(_native.DEVICE_STATUS_NAMES)
+    assert macros["RTXB_DEV_WAIT_SELFTEST"] == enum["kStatusWaitSelfTest"] == 5
+    assert macros["RTXB_DEV_WAIT_QUANT"] == enum["kStatusWaitQuant"]

@@ -308,6 +308,37 @@ def test_mxfp8_glu_rejects_ragged_inter(gpu):
                               torch.zeros(32, 96, dtype=torch.bfloat16, device=dev), ws)
 
 
+# ----------------------------------------------------------------------------- failure path
+
+def test_a_wait_that_nothing_completes_runs_out_and_reports(gpu):
+    """Every kernel role waits with a bound.  The self-test kernel waits on a barrier that nothing completes:
+    after the limit it stores its code in the status word and returns normally; the host sees the code through
+    the same check every call site uses, the context stays usable and the next GEMM gives the right bits.
+    Nothing traps or hangs: the failure is a wait that is allowed to run out."""
+    import ctypes
+
+    ops, N, dev, _ = gpu
+    status = ops.status_word(dev)
+    waited = torch.zeros(1, dtype=torch.int64, device=dev)
+    limit_ns = 20_000_000
+    N.call("rtxb_selftest_wait_timeout", limit_ns, torch.cuda.current_stream().cuda_stream, status.data_ptr(),
+           waited.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5
+    assert limit_ns <= int(waited.item()) < 50 * limit_ns
+    with pytest.raises(RuntimeError, match="self-test wait ran out"):
+        ops.check_device_status(dev)
+    assert int(status.item()) == 0                      # the check clears the word
+    with pytest.raises(N.NativeError):
+        N.call("rtxb_selftest_wait_timeout", 10, None, status.data_ptr(), None)    # limit below 1 ms: refused
+    # the context is intact: a GEMM right after gives the oracle's bits
+    x, w = torch.randn(128, 128).bfloat16(), torch.randn(128, 128).bfloat16()
+    qa, sa = ops.mxfp8_quantize(x.to(dev))
+    qb, sb = ops.mxfp8_quantize(w.to(dev))
+    _assert_output(ops.mxfp8_gemm(qa, sa, qb, sb, 128, 128, 128), O.mxfp8_linear(x, w))
+    _ok(ops, dev)
+
+
 # ----------------------------------------------------------------------------- backward
 
 @pytest.mark.parametrize("mnk", [(128, 128, 128), (256, 384, 512), (100, 70, 50), (512, 256, 1024), (33, 1, 7)])
