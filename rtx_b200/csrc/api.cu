@@ -108,12 +108,15 @@ int encode_map(CUtensorMap* out, const MapKey& key, const char* what) {
   cuuint64_t gstride[2] = {key.stride[0], key.stride[1]};
   cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
   cuuint32_t estr[3] = {1u, 1u, 1u};
-  static const CUtensorMapDataType kTypes[4] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT32,
-                                               CU_TENSOR_MAP_DATA_TYPE_UINT16, CU_TENSOR_MAP_DATA_TYPE_UINT32};
-  static const CUtensorMapSwizzle kSwizzles[4] = {CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_SWIZZLE_64B};
-  CUresult r = fn(out, kTypes[key.words & 3], key.rank, const_cast<void*>(key.base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, kSwizzles[key.words & 3], CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  static const CUtensorMapDataType kTypes[5] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT32,
+                                               CU_TENSOR_MAP_DATA_TYPE_UINT16, CU_TENSOR_MAP_DATA_TYPE_UINT32,
+                                               CU_TENSOR_MAP_DATA_TYPE_UINT32};
+  static const CUtensorMapSwizzle kSwizzles[5] = {CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_SWIZZLE_64B,
+                                                  CU_TENSOR_MAP_SWIZZLE_128B};
+  const int kind = key.words < 5 ? key.words : 0;
+  CUresult r = fn(out, kTypes[kind], key.rank, const_cast<void*>(key.base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, kSwizzles[kind], CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what,
@@ -197,16 +200,17 @@ int make_scale_map_halves(CUtensorMap* map, const void* base, int64_t total_tile
   return encode_map(map, k, "scale halves");
 }
 
-// output matrix [rows, cols] of 2- or 4-byte elements, row pitch ldo elements; boxes of 32 rows x 64 bytes
-// with the 64-byte swizzle (what an epilogue warp stages per store); stores are clipped at the edges
+// output matrix [rows, cols] of 2- or 4-byte elements, row pitch ldo elements; one box = the 32 rows x 32 columns an
+// epilogue warp stages per store: 64-byte rows with the 64-byte swizzle (BF16), 128-byte rows with the 128-byte
+// swizzle (FP32: whole 128-byte lines, also over NVLink); stores are clipped at the edges
 int make_out_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ldo, int elem_bytes) {
   MapKey k = blank_key(base);
   k.rank = 2;
-  k.words = elem_bytes == 2 ? 2 : 3;
+  k.words = elem_bytes == 2 ? 2 : 4;
   k.dim[0] = static_cast<uint64_t>(cols);
   k.dim[1] = static_cast<uint64_t>(rows);
   k.stride[0] = static_cast<uint64_t>(ldo) * elem_bytes;
-  k.box[0] = static_cast<uint32_t>(64 / elem_bytes);
+  k.box[0] = 32u;
   k.box[1] = 32u;
   return encode_map(map, k, "output");
 }

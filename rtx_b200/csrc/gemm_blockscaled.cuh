@@ -288,20 +288,18 @@ __device__ __forceinline__ void epilogue_drain(const GemmParams& p, uint32_t tac
       }
       if (EPI == kEpiF32) {
         if (staged) {
-          // two halves of 16 columns (64 bytes per row) = the two staging buffers, one store group
+          // 32 rows x 128 bytes = both staging buffers as one box (128-byte swizzle: 16-byte chunk j of row r at
+          // chunk j ^ (r % 8)), one store: whole 128-byte lines leave the SM, which is what a write over NVLink wants
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<float4*>(stage + h * kEpiStageBufBytes + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                  make_float4(v[16 * h + 4 * j], v[16 * h + 4 * j + 1], v[16 * h + 4 * j + 2], v[16 * h + 4 * j + 3]);
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
             tma_store_2d(map_out, stage, col, row - lane - out_row0);
-            tma_store_2d(map_out, stage + kEpiStageBufBytes, col + 16, row - lane - out_row0);
             tma_store_commit();
           }
         } else {
