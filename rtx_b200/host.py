@@ -4,7 +4,7 @@ runs the MXFP8 MLP (quantize, gate/up GEMM with fused SiLU*up, quantize, down GE
 and copies Y back to pinned host memory.  Three streams and three device buffer sets
 let the copy-in of step i+1 and the copy-out of step i-1 overlap the compute of
 step i (a buffer set's X is free again as soon as its previous compute has finished,
-its Y once the previous copy-out has), and by default each step is itself cut into
+its Y once the previous copy-out has); optionally each step is itself cut into
 blocks of token rows that are copied, computed and returned one after another;
 `drain()` waits for everything submitted.
 """
@@ -69,7 +69,7 @@ class numa_local:
 
 
 class GluMlpHostSession:
-    """`chunk_rows` (default: 2048 for steps of 8192 rows or more; 0 = off) pipelines WITHIN a step as well: the weights are quantized once per step, then every
+    """`chunk_rows` > 0 (default: off) pipelines WITHIN a step as well: the weights are quantized once per step, then every
     block of `chunk_rows` token rows is copied in, run through the two GEMMs and copied out on its own, so the
     first bytes of Y leave while later rows of X are still arriving.  A step's latency drops from (copy in +
     compute + copy out) to about one chunk of each beyond the longest of the three; the bits are those of
@@ -107,13 +107,10 @@ class GluMlpHostSession:
         if m > self.max_rows or x_host.shape[1] != self.k:
             raise ValueError("activation shape does not fit this session")
         b = self._step % self.depth
-        if self.chunk_rows is None:
-            # blocks of 2048 rows once a step has four of them: there the copies outlast the compute and the
-            # GEMMs still run near their full-size rate (measured on B200: 8192 rows 1.42 ms per step against
-            # 1.56 whole; at 4096 rows and below the step is compute bound and whole steps are faster)
-            chunk = 2048 if m >= 8192 else m
-        else:
-            chunk = self.chunk_rows
+        # Whole steps by default.  Blocks of 2048 rows on 8192-row steps measured 1.39-1.56 ms per step against
+        # 1.48-1.51 whole on the same box (shorter fill and drain, but four times the dependencies between the
+        # three streams): within noise; at 4096 rows and below the step is compute bound and blocks are slower.
+        chunk = self.chunk_rows if self.chunk_rows else m
         if chunk <= 0 or chunk >= m:
             chunk = m
         with torch.cuda.device(self.device):

@@ -158,6 +158,8 @@ class _PeerReduceScatter:
         self.peer_result = [self.result_handle.get_buffer(o, (self.rows, k), torch.bfloat16, o * block)
                             for o in range(self.world)]
         self.comm = torch.cuda.Stream(device)
+        # the reduced blocks come from world - 1 different peers: a few streams let those copies run at once
+        self.fan = [torch.cuda.Stream(device) for _ in range(max(0, min(3, self.world - 2)))]
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
 
 
@@ -205,14 +207,24 @@ def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Ten
         dist.all_reduce(st.token, group=st.group)             # every rank's partials have landed everywhere
         ops.sum_parts_f32_to_bf16(st.slots, st.my_result)
         dist.all_reduce(st.token, group=st.group)             # every owner's block is reduced
+        reduced = torch.cuda.Event()
+        reduced.record(st.comm)
+        lanes = [st.comm] + st.fan
+        for s in st.fan:
+            s.wait_event(reduced)
         for i in range(world):
             o = (rank + i) % world
-            dw[o * rows:(o + 1) * rows].copy_(st.peer_result[o], non_blocking=True)   # plain copies over NVLink
+            with torch.cuda.stream(lanes[i % len(lanes)]):
+                dw[o * rows:(o + 1) * rows].copy_(st.peer_result[o], non_blocking=True)   # plain copies over NVLink
+        for s in st.fan:
+            st.comm.wait_stream(s)
     with ops.sm_margin(PEER_ROUTE_SM_MARGIN):
         q_wt, s_wt = ops.mxfp8_quantize_transposed(weight)
         dx = ops.mxfp8_gemm(q_dy, s_dy, q_wt, s_wt, m, k, n)
     main.wait_stream(st.comm)
-    dw.record_stream(st.comm)        # allocated on the main stream, written on the comm stream
+    dw.record_stream(st.comm)        # allocated on the main stream, written on the comm and fan streams
+    for s in st.fan:
+        dw.record_stream(s)
     return dx, dw
 
 

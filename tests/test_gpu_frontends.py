@@ -536,7 +536,7 @@ def test_host_session_returns_the_bits_of_the_device_call(dev, chunk_rows):
     for x, y in zip(xs, ys):
         session.submit(x, y)
     session.drain()
-    assert session.launches_per_step == (2 + 3 * -(-1200 // chunk_rows) if chunk_rows else 5)
+    assert session.launches_per_step == (2 + 3 * -(-1200 // chunk_rows) if chunk_rows else 5)   # the last step: 1200 rows
     for x, y in zip(xs, ys):
         _, want = ops.mxfp8_glu_mlp_fwd(x.to(dev), wgu, wd, ws, want_hidden=False)
         assert torch.equal(y, want.cpu())
