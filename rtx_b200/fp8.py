@@ -4,9 +4,9 @@ custom ops, with the reference's signatures (rtx/fp8.py:745-793, :2019-2193,
 
 Routing follows the reference: operand state (dynamic / weight-prequantized /
 fully-prequantized), leading dimensions flattened, autograd through the training
-op.  The reference's `fused` and `materialized` backends both map to the
-quantize-once + packed tcgen05 GEMM pipeline, the only forward schedule built for
-sm_100a; `backend` is accepted and validated for API compatibility.
+op.  `backend="materialized"` and `"auto"` are the quantize-once + packed tcgen05 GEMM
+pipeline; `backend="fused"` selects the GEMM that quantizes the activations in the kernel
+(the reference's fused forward; several times slower on compute-bound shapes, same bits).
 Schedules travel through the ops as interned JSON keys (rtx/fp8.py:376-415).
 """
 
@@ -24,7 +24,7 @@ from ._oplib import custom_op
 from . import _native as N
 from . import ops
 from . import weight_cache as _weight_cache
-from .configs import (DEFAULT_MXFP8_INFERENCE_CONFIG, DEFAULT_MXFP8_PREQUANT_CONFIG, MXFP8BwdConfig, MXFP8FwdConfig,
+from .configs import (DEFAULT_MXFP8_INFERENCE_CONFIG, DEFAULT_MXFP8_PREQUANT_CONFIG, MXFP8BwdConfig, MXFP8FwdConfig, MXFP8GemmConfig,
                       MXFP8PrequantConfig, MXFP8Problem, MXFP8QuantConfig, config_from_key)
 from .formats import (PACKED_OPERAND_SCHEMA_VERSION, SCALE_LAYOUT_CODES, SCALE_LAYOUT_NAMES, MXFP8Tensor,
                       make_mxfp8_tensor, mxfp8_matrix_shape, mxfp8_qdata_2d, mxfp8_scale_layout,
@@ -261,8 +261,12 @@ def _stored_winner_key(fwd_key: str, m: int, n: int, k: int, cache_dir, packed: 
 
 
 @torch._dynamo.assume_constant_result
-def _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, packed: bool):
-    """Interned (forward, backward) schedule keys; a constant under torch.compile."""
+def _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, packed: bool,
+                 backend: str = "auto"):
+    """Interned (forward, backward) schedule keys; a constant under torch.compile.  `backend="fused"` names the
+    reference's one-kernel forward (rtx/fp8.py:292-312): unless the config already names a schedule, it selects
+    the GEMM that quantizes the activations in its own quantizer warps (`fused_x`); `auto` and `materialized`
+    are the quantize-once pipeline, which is what the reference's `auto` resolves to on these shapes."""
     if config is not None and forward_config is not None:
         raise ValueError("pass only forward_config, not both config aliases")
     if prequant_config is not None and dynamic_config is not None:
@@ -274,6 +278,10 @@ def _select_keys(forward_config, config, dynamic_config, prequant_config, backwa
             pre = MXFP8PrequantConfig(quant=fwd.quant, gemm=fwd.gemm)
         else:
             pre = DEFAULT_MXFP8_INFERENCE_CONFIG if packed else DEFAULT_MXFP8_PREQUANT_CONFIG
+    if backend == "fused" and pre.gemm.schedule == "auto":
+        import dataclasses
+
+        pre = dataclasses.replace(pre, gemm=MXFP8GemmConfig.for_schedule("fused_x"))
     bwd = backward_config or MXFP8BwdConfig()
     return _intern(pre), _intern(bwd)
 
@@ -289,7 +297,8 @@ def mxfp8_linear(x, weight, *, forward_config: Optional[MXFP8FwdConfig] = None, 
     _normalize_backend(backend)
     mode = _autotune_mode(autotune)
     x_packed, w_packed = isinstance(x, MXFP8Tensor), isinstance(weight, MXFP8Tensor)
-    fwd_key, bwd_key = _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, w_packed)
+    fwd_key, bwd_key = _select_keys(forward_config, config, dynamic_config, prequant_config, backward_config, w_packed,
+                                    backend)
     if mode != "off" and not x_packed and not torch.compiler.is_compiling():
         # functional calls use stored winners only; first-use tuning belongs to the module, which owns its state
         n_w, k_w = mxfp8_matrix_shape(weight) if w_packed else (int(weight.shape[0]), int(weight.shape[-1]))
@@ -376,7 +385,8 @@ class MXFP8Linear(nn.Module):
                                           variant="weight_prequant" if packed_weight is not None else "default")
         # schedules travel as interned strings so that a compiled graph sees constants (rtx/fp8.py:376-415)
         self._forward_config_key, self._backward_config_key = _select_keys(
-            self.forward_config, None, self.dynamic_config, None, backward_config, packed_weight is not None)
+            self.forward_config, None, self.dynamic_config, None, backward_config, packed_weight is not None,
+            self.backend)
         if packed_weight is None:
             weight = torch.empty(self.out_features, self.in_features, device=device, dtype=torch.bfloat16)
             self.weight = nn.Parameter(weight)

@@ -123,7 +123,18 @@ def test_module_constructors_and_state_dict_schema():
         MXFP8Linear(8, 8, dtype=torch.float16)
     with pytest.raises(ValueError, match="unknown MXFP8 backend"):
         MXFP8Linear(8, 8, backend="cutlass")
-    from rtx_b200.configs import MXFP8FwdConfig, MXFP8PrequantConfig, NVFP4ScaleConfig
+    from rtx_b200.configs import MXFP8FwdConfig, MXFP8GemmConfig, MXFP8PrequantConfig, NVFP4ScaleConfig
+
+    # backend="fused" = the reference's one-kernel forward: the GEMM that quantizes X itself, unless the config
+    # already names a schedule; auto / materialized = quantize once, packed GEMM (rtx/fp8.py:292-312)
+    import json as _json
+
+    sched = lambda mod: _json.loads(mod._forward_config_key)["gemm"]["schedule"]
+    assert sched(MXFP8Linear(64, 64, device="meta", backend="fused")) == "fused_x"
+    assert sched(MXFP8Linear(64, 64, device="meta", backend="auto")) == "auto"
+    assert sched(MXFP8Linear(64, 64, device="meta", backend="materialized")) == "auto"
+    assert sched(MXFP8Linear(64, 64, device="meta", backend="fused",
+                             dynamic_config=MXFP8PrequantConfig(gemm=MXFP8GemmConfig.for_schedule("pair")))) == "pair"
 
     with pytest.raises(ValueError, match="both config aliases"):
         MXFP8Linear(8, 8, config=MXFP8FwdConfig(), forward_config=MXFP8FwdConfig())

@@ -543,6 +543,33 @@ def test_host_session_returns_the_bits_of_the_device_call(dev, chunk_rows):
     _done(dev)
 
 
+def test_backend_fused_runs_the_in_kernel_quantizer_and_gives_the_same_bits(dev):
+    """`backend="fused"` (module and function): the reference's one-kernel forward, here the CTA-pair GEMM whose own
+    warps quantize the activations; bit-identical to the materialized pipeline, forward and through autograd."""
+    import rtx_b200 as rtx
+
+    torch.manual_seed(17)
+    k, n = 512, 768
+    plain = rtx.MXFP8Linear(k, n, device=dev)
+    fused = rtx.MXFP8Linear(k, n, device=dev, backend="fused")
+    with torch.no_grad():
+        fused.weight.copy_(plain.weight)
+    assert fused.explain()["backend"] == "fused"
+    x = torch.randn(3, 100, k, device=dev).bfloat16()
+    with torch.no_grad():
+        want = plain(x)
+        assert torch.equal(fused(x), want)
+        assert torch.equal(rtx.mxfp8_linear(x, plain.weight, backend="fused"), want)
+        packed = fused.to_quantized_weight()
+        assert torch.equal(packed(x), want)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, yb = plain(xa), fused(xb)
+    ya.float().sum().backward()
+    yb.float().sum().backward()
+    assert torch.equal(ya, yb) and torch.equal(xa.grad, xb.grad) and torch.equal(plain.weight.grad, fused.weight.grad)
+    _done(dev)
+
+
 def test_quantized_weight_cache_is_bit_identical(dev):
     """Inside `quantized_weight_cache()` modules reuse the quantized weight across micro-batches; outputs,
     dX and accumulated dW equal the uncached run bit for bit, an in-place weight update is seen, and the
