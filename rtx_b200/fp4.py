@@ -417,13 +417,20 @@ def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
     if scaling == "jit_row_region" and w_packed:
         raise ValueError("jit_row_region scaling requires dynamic BF16 X and W; a packed weight uses current scaling")
     _fp8._normalize_backend(backend)
-    _fp8._autotune_mode(autotune)
+    mode = _fp8._autotune_mode(autotune)
     if x_packed and not w_packed:
         raise ValueError("a packed activation requires a packed weight")
     bwd_key = _bwd_key(backward_config)
     region_rows = (_resolve_scale_region_rows(scale_region_rows, x_scale_region_rows, weight_scale_region_rows)
                    if scaling == "jit_row_region" else (0, 0))
     cfg, key = _dynamic_key(dynamic_config, scale_config, scaling, region_rows)
+    if mode != "off" and not x_packed and not torch.compiler.is_compiling():
+        # functional calls use stored winners only (first-use tuning belongs to the module, which owns its state):
+        # the family and variant a module of the same operand state and policy would look up
+        n_w, k_w = nvfp4_matrix_shape(weight) if w_packed else (int(weight.shape[0]), int(weight.shape[-1]))
+        cfg = _stored_winner_config(cfg, int(x.numel() // max(int(x.shape[-1]), 1)), n_w, k_w, autotune_cache_dir,
+                                    w_packed, scaling)
+        key = cfg.to_key()
     if w_packed:
         n, k = nvfp4_matrix_shape(weight)
         wq, wscales = nvfp4_qdata_2d(weight), nvfp4_scales_for_kernel(weight)
@@ -468,6 +475,21 @@ def nvfp4_linear(x, weight, *, scale_config: Optional[NVFP4ScaleConfig] = None,
                if train else
                torch.ops.rtx.nvfp4_linear_materialized_fwd(x2d, weight, x_scale, w_scale, output_scale, key))
     return out.reshape(*x.shape[:-1], weight.shape[0])
+
+
+_FUNCTIONAL_RESOLVERS: dict = {}
+
+
+def _stored_winner_config(cfg: NVFP4DynamicConfig, m: int, n: int, k: int, cache_dir, packed: bool, scaling: str):
+    from .autotune import ScheduleResolver
+
+    slot = (n, k, str(cache_dir), packed, scaling)
+    resolver = _FUNCTIONAL_RESOLVERS.get(slot)
+    if resolver is None:
+        resolver = ScheduleResolver("nvfp4_weight_prequant_fwd" if packed else "nvfp4_dynamic_fwd", n, k, "cache",
+                                    cache_dir, variant=scaling)
+        _FUNCTIONAL_RESOLVERS[slot] = resolver
+    return resolver.resolve(m, cfg)
 
 
 # --------------------------------------------------------------------------- module

@@ -484,6 +484,14 @@ def test_stored_winner_reaches_nvfp4_modules(tmp_path):
     other = rtx.NVFP4Linear(k, n, scaling="current", autotune="cache", autotune_cache_dir=tmp_path)
     assert other.explain(m=64)["gemm_schedule"] == "auto"          # a different policy is a different variant
     assert rtx.NVFP4Linear(k, n).explain()["autotune"] == "off"
+    # the functional form resolves stored winners the same way (no first-use tuning there)
+    from rtx_b200 import fp4
+
+    base = tuned._dynamic_config
+    got = fp4._stored_winner_config(base, 64, n, k, tmp_path, False, "jit_row_region")
+    assert got.gemm.schedule == "stream" and got.scale.policy == "jit_row_region"
+    assert fp4._stored_winner_config(base, 4096, n, k, tmp_path, False, "jit_row_region").gemm.schedule == "auto"
+    assert fp4._stored_winner_config(base, 64, n, k, tmp_path, True, "current").gemm.schedule == "auto"
 
 
 def test_row_block_of_a_global_draw_equals_the_slice():
