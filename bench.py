@@ -209,23 +209,32 @@ class Timer:
         if self.world > 1:
             self.dist.barrier(device_ids=[self.local_rank])
 
-    def run(self, name, fn, steps, warmup, label="burst"):
+    def run(self, name, fn, steps, warmup, label="burst", per_step=False):
+        """per_step: an event after every step as well, so that the record can show median and worst step beside
+        the mean (a single stall inside a 20-step region otherwise hides in the mean)."""
         torch = self.torch
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps)] if per_step else None
         self.barrier()
         torch.cuda.synchronize()
         w0 = time.time()
         ev0.record()
-        for _ in range(steps):
+        for i in range(steps):
             fn()
+            if marks is not None:
+                marks[i].record()
         ev1.record()
         torch.cuda.synchronize()
         self.sampler.mark(label, w0, time.time())
         self.barrier()
         self.results[name] = ev0.elapsed_time(ev1) / steps
+        if marks is not None:
+            each = sorted(a.elapsed_time(b) for a, b in zip([ev0] + marks[:-1], marks))
+            self.results[name + "_median"] = each[len(each) // 2]
+            self.results[name + "_max"] = each[-1]
         return self.results[name]
 
     def reduce(self, dev):
@@ -262,7 +271,7 @@ def run_own_arm(args) -> None:
     if M % (world * 128) or BWD_M % (world * 128):
         raise SystemExit(f"{M} and {BWD_M} token rows must split into whole 128-row tiles over {world} ranks")
     steps, warmup = args.steps, max(args.warmup, 3)
-    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler = ClockSampler(physical_gpu_index(local_rank), period_ms=args.sample_ms)
     timer = Timer(torch, dist, world, local_rank, sampler)
     ws = ops.Workspace(dev)
 
@@ -378,7 +387,8 @@ def run_own_arm(args) -> None:
         del wide
     bwd_parity = None
     for mode, (xb, dyb) in shards.items():
-        timer.run(f"bwd_{mode}", lambda: parallel.data_parallel_linear_backward(dyb, xb, w_b), steps, warmup)
+        timer.run(f"bwd_{mode}", lambda: parallel.data_parallel_linear_backward(dyb, xb, w_b), steps, warmup,
+                  per_step=True)
         ops.check_device_status(dev)
     if world > 1:
         # parity of the sharded step: dX rows bit-equal to the unsharded rows, all-reduced dW within the
@@ -441,10 +451,12 @@ def run_own_arm(args) -> None:
             "api": "rtx_b200.parallel.data_parallel_linear_backward",
             "collective": bwd_route,
             "strong": {"rows_per_gpu": bper, "ms_per_step": res["bwd_strong"],
+                       "ms_per_step_median": res["bwd_strong_median"], "ms_per_step_max": res["bwd_strong_max"],
                        "value": bwd_flops / (res["bwd_strong"] * 1e-3) / 1e12, "unit": "TFLOP/s"},
         }
         if world > 1:
             backward["weak"] = {"rows_per_gpu": BWD_M, "ms_per_step": res["bwd_weak"],
+                                "ms_per_step_median": res["bwd_weak_median"], "ms_per_step_max": res["bwd_weak_max"],
                                 "value": bwd_flops * world / (res["bwd_weak"] * 1e-3) / 1e12, "unit": "TFLOP/s"}
             backward["parity"] = bwd_parity
         line = {
@@ -511,6 +523,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sample-ms", type=int, default=10, help="period of the clock / power sampler (nvidia-smi -lms)")
     ap.add_argument("--no-other-configs", action="store_true", help="skip configurations 3 and 5 (1-GPU runs)")
     ap.add_argument("--schedule", choices=["auto", "single", "pair", "fused_x"], default="auto",
                     help="GEMM schedule of the forward step (fused_x: X is quantized inside the gate/up GEMM)")

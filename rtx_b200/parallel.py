@@ -221,10 +221,11 @@ def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Ten
     with ops.sm_margin(PEER_ROUTE_SM_MARGIN):
         q_wt, s_wt = ops.mxfp8_quantize_transposed(weight)
         dx = ops.mxfp8_gemm(q_dy, s_dy, q_wt, s_wt, m, k, n)
+    # dw was allocated on the main stream and is written on the comm and fan streams; the main stream waits for
+    # all of them here, before anything later on it, so the allocator may hand the block out again (on the main
+    # stream) as soon as the caller drops it.  No record_stream: that would park every step's block until the
+    # side streams' events are polled and make a host that runs ahead allocate fresh memory step after step.
     main.wait_stream(st.comm)
-    dw.record_stream(st.comm)        # allocated on the main stream, written on the comm and fan streams
-    for s in st.fan:
-        dw.record_stream(s)
     return dx, dw
 
 
