@@ -6,10 +6,11 @@
     python bench_configs.py --config 6            # configuration 2's shapes with the step-scoped weight cache
     python bench_configs.py --config 7            # host <-> device copies of the end-to-end step alone, one process, all GPUs
     python -m torch.distributed.run --nproc-per-node N ... bench_configs.py --config 4
+    python -m torch.distributed.run --nproc-per-node N ... bench_configs.py --config 8   # phases of that backward step
 
 One JSON line per measured case (rank 0).  Token rows are sharded over ranks (weak scaling: the
-configuration's M per GPU); configuration 4 all-reduces the FP32 dW with NCCL inside the timed
-region.  Timing: CUDA events around K steps after W warm-ups, max over ranks; inputs exceed L2 for
+configuration's M per GPU); configuration 4 reduces dW across ranks inside the timed region (through peer
+memory by default, `--dw-route nccl` for the all-reduce).  Timing: CUDA events around K steps after W warm-ups, max over ranks; inputs exceed L2 for
 configurations 3 and 4; configuration 5 rotates over enough weight copies to exceed L2.
 """
 
@@ -30,7 +31,7 @@ if ROOT not in sys.path:
 
 from rtx_b200 import _native as N  # noqa: E402
 from rtx_b200 import ops, parallel  # noqa: E402
-from rtx_b200.workloads import make_inputs  # noqa: E402
+from rtx_b200.workloads import CONFIG_NAMES, make_inputs  # noqa: E402
 
 NOMINAL = {"fp8": 4500.0, "fp4": 9000.0, "hbm": 8000.0}
 
@@ -361,9 +362,56 @@ def config7(args, rank, world, dev):
     return lines
 
 
+def config8(args, rank, world, dev):
+    """Where a data-parallel backward step (configuration 4, 16384 rows per GPU, peer-memory route) spends its
+    time: one event per phase on the stream the phase runs on, averaged over the steps, as milliseconds since
+    the step's start (slowest rank); and the dW GEMM alone with local outputs against outputs in the owners'
+    (peer) slots."""
+    if world < 2:
+        raise SystemExit("--config 8 needs two or more ranks (torchrun)")
+    m, n, k = 16384, 4096, 4096
+    inp = make_inputs(4, m=m)
+    x, w, dy = inp["x"].to(dev), inp["w"].to(dev), inp["dy"].to(dev)
+    st = parallel._peer_state(n, k, dev, None)
+    if st is None:
+        raise SystemExit("the peer-memory route is not available for this shape / group")
+    for _ in range(max(args.warmup, 3)):
+        parallel._peer_backward(dy, x, w, st)
+    torch.cuda.synchronize()
+    acc = {}
+    for _ in range(args.steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        marks = {}
+        parallel._peer_backward(dy, x, w, st, marks=marks)
+        torch.cuda.synchronize()
+        for name, ev in marks.items():
+            if name != "start":
+                acc[name] = acc.get(name, 0.0) + marks["start"].elapsed_time(ev) / args.steps
+    names = list(acc)
+    t = torch.tensor([acc[nm] for nm in names], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    phases = {nm: round(float(v), 4) for nm, v in zip(names, t.tolist())}
+    q_dy, s_dy, q_dyt, s_dyt = ops.mxfp8_quantize_dual(dy)
+    q_xt, s_xt = ops.mxfp8_quantize_transposed(x)
+    local = [torch.empty(st.rows, k, dtype=torch.float32, device=dev) for _ in range(world)]
+    first = (rank + 1) % world
+    t_local = _time(lambda: ops.mxfp8_gemm_row_blocks(q_dyt, s_dyt, q_xt, s_xt, n, k, m, local, first_block=first),
+                    args.steps, args.warmup, world, dev)
+    t_peer = _time(lambda: ops.mxfp8_gemm_row_blocks(q_dyt, s_dyt, q_xt, s_xt, n, k, m, st.peer_slot, first_block=first),
+                   args.steps, args.warmup, world, dev)
+    return [{"metric": "data-parallel MXFP8 backward: milliseconds from the step's start to the end of each phase "
+                       "(slowest rank; a synchronised start per step, so the first kernel carries its launch latency)",
+             "value": phases["end"], "unit": "ms", "n_gpus": world, "ms_per_step": phases["end"],
+             "config": {"workload": CONFIG_NAMES[4], "rows_per_gpu": m, "phases_ms_since_start": phases,
+                        "main_stream": ["quantized_dy_and_xt", "dw_gemm", "quantized_wt", "dx_gemm", "end"],
+                        "side_streams": ["barrier_partials_landed", "owner_sum", "barrier_blocks_reduced", "blocks_copied"],
+                        "dw_gemm_alone_ms": {"local_outputs": round(t_local, 4), "outputs_in_peer_slots": round(t_peer, 4)}}}]
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5, 6, 7))
+    ap.add_argument("--config", type=int, required=True, choices=(3, 4, 5, 6, 7, 8))
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--dw-route", choices=["peer", "nccl"], default="peer",
@@ -379,7 +427,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev, pg_options=parallel.nccl_options())
-    lines = {3: config3, 4: config4, 5: config5, 6: config6, 7: config7}[args.config](args, rank, world, dev)
+    lines = {3: config3, 4: config4, 5: config5, 6: config6, 7: config7, 8: config8}[args.config](args, rank, world, dev)
     if rank == 0:
         for line in lines:
             line.update({"steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True})

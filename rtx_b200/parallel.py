@@ -186,27 +186,41 @@ def _peer_state(n: int, k: int, device: torch.device, group):
     return None if isinstance(state, Exception) else state
 
 
-def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, st: "_PeerReduceScatter"):
+def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, st: "_PeerReduceScatter",
+                   marks: Optional[dict] = None):
+    """`marks`: a dict that receives one timing event per phase, recorded on the stream the phase runs on
+    (`python bench_configs.py --config 8` prints them); None on the product path."""
     from . import _native as N
     from . import ops
+
+    def mark(name, stream):
+        if marks is not None:
+            marks[name] = torch.cuda.Event(enable_timing=True)
+            marks[name].record(stream)
 
     m, n = grad_output.shape
     k = x.shape[1]
     main = torch.cuda.current_stream(x.device)
+    mark("start", main)
     q_dy, s_dy, q_dyt, s_dyt = ops.mxfp8_quantize_dual(grad_output)
     q_xt, s_xt = ops.mxfp8_quantize_transposed(x)
+    mark("quantized_dy_and_xt", main)
     rows, world, rank = st.rows, st.world, st.rank
     # ONE dW GEMM over all rows: every 256-row tile goes to the slot of the rank that owns its block, the tile
     # order starting at this rank's neighbour.  Output traffic of a wave of tiles overlaps the next wave's MMAs.
     ops.mxfp8_gemm_row_blocks(q_dyt, s_dyt, q_xt, s_xt, n, k, m, st.peer_slot, first_block=(rank + 1) % world)
+    mark("dw_gemm", main)
     done = torch.cuda.Event()
     done.record(main)
     dw = torch.empty(n, k, dtype=torch.bfloat16, device=x.device)
     st.comm.wait_event(done)
     with torch.cuda.stream(st.comm):
         dist.all_reduce(st.token, group=st.group)             # every rank's partials have landed everywhere
+        mark("barrier_partials_landed", st.comm)
         ops.sum_parts_f32_to_bf16(st.slots, st.my_result)
+        mark("owner_sum", st.comm)
         dist.all_reduce(st.token, group=st.group)             # every owner's block is reduced
+        mark("barrier_blocks_reduced", st.comm)
         reduced = torch.cuda.Event()
         reduced.record(st.comm)
         lanes = [st.comm] + st.fan
@@ -218,14 +232,18 @@ def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Ten
                 dw[o * rows:(o + 1) * rows].copy_(st.peer_result[o], non_blocking=True)   # plain copies over NVLink
         for s in st.fan:
             st.comm.wait_stream(s)
+        mark("blocks_copied", st.comm)
     with ops.sm_margin(PEER_ROUTE_SM_MARGIN):
         q_wt, s_wt = ops.mxfp8_quantize_transposed(weight)
+        mark("quantized_wt", main)
         dx = ops.mxfp8_gemm(q_dy, s_dy, q_wt, s_wt, m, k, n)
+        mark("dx_gemm", main)
     # dw was allocated on the main stream and is written on the comm and fan streams; the main stream waits for
     # all of them here, before anything later on it, so the allocator may hand the block out again (on the main
     # stream) as soon as the caller drops it.  No record_stream: that would park every step's block until the
     # side streams' events are polled and make a host that runs ahead allocate fresh memory step after step.
     main.wait_stream(st.comm)
+    mark("end", main)
     return dx, dw
 
 
