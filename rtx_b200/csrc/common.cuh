@@ -22,6 +22,7 @@ enum DeviceStatus : int {
   kStatusWaitEpilogue = 3,   // epilogue gave up waiting for accumulators
   kStatusWaitQuant = 4,      // quantizer warps gave up waiting for a BF16 tile
   kStatusWaitSelfTest = 5,   // the wait self-test's barrier (which nothing ever completes) ran out, as it must
+  kStatusWaitPeer = 6,       // node barrier: another rank's flag never arrived
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -308,6 +308,17 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
     return dx, dw
 
 
+def peer_barrier(flag_ptrs, rank: int, epoch: int, device: torch.device, limit_ns: int = 2_000_000_000) -> None:
+    """Node barrier through flag words in peer-mapped memory on the current stream: `flag_ptrs[t]` is the address
+    of rank t's array of eight int32 words as mapped into this process; `epoch` grows by one per barrier."""
+    import ctypes
+
+    ptrs = (ctypes.c_void_p * len(flag_ptrs))(*flag_ptrs)
+    with _on(device):
+        N.call("rtxb_peer_barrier", ptrs, len(flag_ptrs), rank, epoch, limit_ns, _stream_ptr(),
+               status_word(device).data_ptr())
+
+
 def sum_parts_f32_to_bf16(parts: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """parts f32 [S, ...] contiguous -> bf16 [...]: the S partial sums added in index order, one rounding."""
     if parts.dtype is not torch.float32 or not parts.is_contiguous() or parts.dim() < 2:

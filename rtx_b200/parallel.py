@@ -56,7 +56,7 @@ def all_reduce_dw(dw_partial_f32: torch.Tensor, group: Optional[dist.ProcessGrou
 # on two GPUs (0.632 ms with bands) but not on four (0.907 ms).
 OVERLAP_SM_MARGIN = 32
 NCCL_MAX_CTAS = 32
-# SMs left free on the peer-memory route: its only NCCL kernels are one-word barriers
+# SMs left free on the peer-memory route for its small kernels (flag barriers, the owner's sum)
 PEER_ROUTE_SM_MARGIN = 4
 # NCCL route: dW may be produced and reduced in bands of rows (multiples of 256), each band's all-reduce
 # enqueued right behind its GEMM.  0 = one band (the whole dW): bands pay only when the collective fits in
@@ -118,8 +118,8 @@ def _banded_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.T
 # Every rank owns a contiguous block of N / world rows of dW.  A rank's dW GEMM for block o writes its FP32
 # partial straight into slot [rank] of owner o's staging buffer: the GEMM epilogue's TMA stores go over NVLink,
 # so the "reduce-scatter" traffic IS the GEMM's output traffic and overlaps the MMAs tile by tile (no NCCL
-# kernel, no SMs taken from the GEMM).  Once every rank's GEMMs are done (a one-word NCCL all-reduce is the
-# barrier) the owner sums its `world` slots in rank order, rounds once to BF16
+# kernel, no SMs taken from the GEMM).  Once every rank's GEMMs are done (a flag barrier through peer memory,
+# rtxb_peer_barrier) the owner sums its `world` slots in rank order, rounds once to BF16
 # (rtxb_sum_parts_f32_to_bf16) into a buffer its peers can read, and after a second barrier every rank copies
 # the other owners' BF16 blocks into its dW with plain device copies: 2 bytes per element cross NVLink in the
 # second phase instead of 4, beside the dX GEMM, and no collective kernel competes with the GEMM for SMs
@@ -157,10 +157,28 @@ class _PeerReduceScatter:
         self.my_result = self.result.view(self.world, self.rows, k)[self.rank]
         self.peer_result = [self.result_handle.get_buffer(o, (self.rows, k), torch.bfloat16, o * block)
                             for o in range(self.world)]
+        # flag words for the node barrier kernel (rtxb_peer_barrier): eight int32 per rank, zero before first use
+        self.flags = symm.empty(8, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flags_handle = symm.rendezvous(self.flags, self.group)
+        self.flag_views = [self.flags_handle.get_buffer(o, (8,), torch.int32, 0) for o in range(self.world)]
+        self.flag_ptrs = [v.data_ptr() for v in self.flag_views]
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group, device_ids=[device.index])   # every rank's flags are zero before anyone signals
         self.comm = torch.cuda.Stream(device)
         # the reduced blocks come from world - 1 different peers: a few streams let those copies run at once
         self.fan = [torch.cuda.Stream(device) for _ in range(max(0, min(3, self.world - 2)))]
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
+
+
+def _node_barrier(st: "_PeerReduceScatter") -> None:
+    """Orders the ranks on the current stream with the flag kernel (a few microseconds) instead of a one-word
+    NCCL all-reduce (20-40 us on the stream); a rank that never arrives shows up in the status word."""
+    from . import ops
+
+    st.epoch += 1
+    ops.peer_barrier(st.flag_ptrs, st.rank, st.epoch, st.stage.device)
 
 
 def p2p_block_rows(n: int, world: int) -> int:
@@ -215,11 +233,11 @@ def _peer_backward(grad_output: torch.Tensor, x: torch.Tensor, weight: torch.Ten
     dw = torch.empty(n, k, dtype=torch.bfloat16, device=x.device)
     st.comm.wait_event(done)
     with torch.cuda.stream(st.comm):
-        dist.all_reduce(st.token, group=st.group)             # every rank's partials have landed everywhere
+        _node_barrier(st)                                     # every rank's partials have landed everywhere
         mark("barrier_partials_landed", st.comm)
         ops.sum_parts_f32_to_bf16(st.slots, st.my_result)
         mark("owner_sum", st.comm)
-        dist.all_reduce(st.token, group=st.group)             # every owner's block is reduced
+        _node_barrier(st)                                     # every owner's block is reduced
         mark("barrier_blocks_reduced", st.comm)
         reduced = torch.cuda.Event()
         reduced.record(st.comm)
@@ -285,7 +303,8 @@ def backward_collective(n: int, k: int, device: torch.device, group=None) -> str
         return "none (one rank)"
     if P2P_REDUCE_SCATTER and p2p_block_rows(n, dist.get_world_size(group)) and _peer_state(n, k, device, group):
         return ("reduce-scatter in the dW GEMM epilogue (FP32 TMA stores into the owner's slots over NVLink), "
-                "owner sums and rounds once, peers copy the BF16 blocks beside dX; NCCL only as two one-word barriers")
+                "owner sums and rounds once, peers copy the BF16 blocks beside dX; ranks ordered by two flag barriers through "
+                "peer memory (no NCCL kernel in the step)")
     why = ""
     if P2P_REDUCE_SCATTER and p2p_block_rows(n, dist.get_world_size(group)):
         failed = _P2P_STATES.get((device.index, n, k, id(group)))

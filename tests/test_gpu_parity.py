@@ -339,6 +339,29 @@ def test_a_wait_that_nothing_completes_runs_out_and_reports(gpu):
     _ok(ops, dev)
 
 
+def test_node_barrier_alone_and_with_a_rank_that_never_arrives(gpu):
+    """rtxb_peer_barrier on one GPU: a group of one passes at once, epoch after epoch; in a group of two whose other
+    rank never signals, the bounded wait runs out after the limit, the status word says which wait it was, and the
+    context stays usable.  (Ranks that do arrive are covered by the two-GPU tests: kernels that wait for one
+    another are never run as separate launches on one GPU.)"""
+    ops, N, dev, _ = gpu
+    mine = torch.zeros(8, dtype=torch.int32, device=dev)
+    absent = torch.zeros(8, dtype=torch.int32, device=dev)
+    for epoch in (1, 2, 3):
+        ops.peer_barrier([mine.data_ptr()], 0, epoch, dev)
+    _ok(ops, dev)
+    assert mine.tolist()[0] == 3
+    ops.peer_barrier([mine.data_ptr(), absent.data_ptr()], 0, 4, dev, limit_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert absent.tolist()[0] == 4 and mine.tolist()[:2] == [4, 0]      # we signalled both; rank 1 never did
+    with pytest.raises(RuntimeError, match="another rank's flag never arrived"):
+        ops.check_device_status(dev)
+    with pytest.raises(N.NativeError):
+        ops.peer_barrier([mine.data_ptr()], 1, 5, dev)                   # rank outside the group
+    ops.peer_barrier([mine.data_ptr()], 0, 5, dev)
+    _ok(ops, dev)
+
+
 # ----------------------------------------------------------------------------- backward
 
 @pytest.mark.parametrize("mnk", [(128, 128, 128), (256, 384, 512), (100, 70, 50), (512, 256, 1024), (33, 1, 7)])
