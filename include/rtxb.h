@@ -69,13 +69,14 @@ const char* rtxb_error_string(int code);
 const char* rtxb_last_cuda_error(void);
 
 /* Barrier among the (<= 8) ranks of one node through flag words in peer-mapped memory; every rank calls it on its
- * own GPU with the same `epoch` (a number that grows by one per barrier).  No counterpart in the reference
- * (single GPU).  rank_flags[t] is rank t's array of 8 int32 words, mapped into this process (zero before the
- * first barrier).  Work enqueued before the call on `stream`, including stores into other ranks' memory, is
+ * own GPU, the same number of times.  No counterpart in the reference (single GPU).  rank_flags[t] is rank t's
+ * array of 8 int32 words, mapped into this process; epoch_counter is one int32 of this rank's own device memory
+ * that the kernel advances (the launch carries no per-call number, so it can be replayed from a captured
+ * graph); all of them zero before the first barrier.  Work enqueued before the call on `stream`, including stores into other ranks' memory, is
  * visible to every rank's work enqueued after its own call.  Each wait is bounded by `limit_ns` (1 ms .. 2 s): if a
  * rank never arrives, RTXB_DEV_WAIT_PEER is stored in `status` and the kernel returns. */
-int rtxb_peer_barrier(void* const* rank_flags, int world, int rank, int epoch, int64_t limit_ns, void* stream,
-                      int* status);
+int rtxb_peer_barrier(void* const* rank_flags, int world, int rank, int* epoch_counter, int64_t limit_ns,
+                      void* stream, int* status);
 
 /* Self-test of the failure path every kernel role shares.  No counterpart in the reference.  Launches one warp
  * that waits, with the bounded wait the GEMM and quantizer roles use, on a barrier that nothing completes; after

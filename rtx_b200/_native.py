@@ -65,7 +65,7 @@ SIGNATURES = {
     "rtxb_mxfp8_linear_bwd": (_I, [_P, _P, _P, _P, _P, _I, _L, _L, _L, _P, _Z, _P, _P]),
     "rtxb_sum_parts_f32_to_bf16": (_I, [_P, _I, _L, _L, _P, _P]),
     "rtxb_selftest_wait_timeout": (_I, [_L, _P, _P, _P]),
-    "rtxb_peer_barrier": (_I, [_P, _I, _I, _I, _L, _P, _P]),
+    "rtxb_peer_barrier": (_I, [_P, _I, _I, _P, _L, _P, _P]),
     "rtxb_nvfp4_tensor_scale": (_I, [_P, _L, _L, _L, _I, _P, _P, _P, _P, _P]),
     "rtxb_nvfp4_quantize": (_I, [_P, _L, _L, _L, _P, _P, _I, _P, _P]),
     "rtxb_nvfp4_gemm": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P, _P]),

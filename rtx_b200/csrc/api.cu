@@ -963,10 +963,11 @@ int rtxb_sum_parts_f32_to_bf16(const float* parts, int n_parts, int64_t part_str
   return RTXB_OK;
 }
 
-int rtxb_peer_barrier(void* const* rank_flags, int world, int rank, int epoch, int64_t limit_ns, void* stream,
-                      int* status) {
+int rtxb_peer_barrier(void* const* rank_flags, int world, int rank, int* epoch_counter, int64_t limit_ns,
+                      void* stream, int* status) {
   if (!rank_flags || world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
     return fail_msg(RTXB_E_INVALID_ARGUMENT, "between 1 and 8 ranks, rank inside the group");
+  if (!epoch_counter || !aligned(epoch_counter, 4)) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null epoch counter");
   if (limit_ns < 1000000 || limit_ns > 2000000000ll)
     return fail_msg(RTXB_E_INVALID_ARGUMENT, "limit between 1 ms and 2 s");
   PeerFlags flags = {};
@@ -974,7 +975,7 @@ int rtxb_peer_barrier(void* const* rank_flags, int world, int rank, int epoch, i
     if (!rank_flags[t] || !aligned(rank_flags[t], 4)) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null or unaligned flag array");
     flags.rank_flags[t] = static_cast<int*>(rank_flags[t]);
   }
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, rank, epoch,
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, rank, epoch_counter,
                                                                        static_cast<uint64_t>(limit_ns), status);
   RTXB_CHECK_LAUNCH("peer_barrier_kernel");
   return RTXB_OK;

@@ -308,14 +308,18 @@ def mxfp8_linear_bwd(dy, x, w, ws: Workspace, *, need_dx: bool = True, need_dw: 
     return dx, dw
 
 
-def peer_barrier(flag_ptrs, rank: int, epoch: int, device: torch.device, limit_ns: int = 2_000_000_000) -> None:
+def peer_barrier(flag_ptrs, rank: int, epoch_counter: torch.Tensor, limit_ns: int = 2_000_000_000) -> None:
     """Node barrier through flag words in peer-mapped memory on the current stream: `flag_ptrs[t]` is the address
-    of rank t's array of eight int32 words as mapped into this process; `epoch` grows by one per barrier."""
+    of rank t's array of eight int32 words as mapped into this process; `epoch_counter` is one int32 of this
+    rank's device memory that the kernel advances (zero before the first barrier)."""
     import ctypes
 
+    if epoch_counter.dtype is not torch.int32 or epoch_counter.numel() != 1 or epoch_counter.device.type != "cuda":
+        raise ValueError("epoch_counter must be one int32 on the device")
     ptrs = (ctypes.c_void_p * len(flag_ptrs))(*flag_ptrs)
+    device = epoch_counter.device
     with _on(device):
-        N.call("rtxb_peer_barrier", ptrs, len(flag_ptrs), rank, epoch, limit_ns, _stream_ptr(),
+        N.call("rtxb_peer_barrier", ptrs, len(flag_ptrs), rank, epoch_counter.data_ptr(), limit_ns, _stream_ptr(),
                status_word(device).data_ptr())
 
 

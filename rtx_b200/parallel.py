@@ -163,7 +163,7 @@ class _PeerReduceScatter:
         self.flags_handle = symm.rendezvous(self.flags, self.group)
         self.flag_views = [self.flags_handle.get_buffer(o, (8,), torch.int32, 0) for o in range(self.world)]
         self.flag_ptrs = [v.data_ptr() for v in self.flag_views]
-        self.epoch = 0
+        self.epoch_counter = torch.zeros(1, dtype=torch.int32, device=device)   # advanced by the barrier kernel
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group, device_ids=[device.index])   # every rank's flags are zero before anyone signals
         self.comm = torch.cuda.Stream(device)
@@ -177,8 +177,7 @@ def _node_barrier(st: "_PeerReduceScatter") -> None:
     NCCL all-reduce (20-40 us on the stream); a rank that never arrives shows up in the status word."""
     from . import ops
 
-    st.epoch += 1
-    ops.peer_barrier(st.flag_ptrs, st.rank, st.epoch, st.stage.device)
+    ops.peer_barrier(st.flag_ptrs, st.rank, st.epoch_counter)
 
 
 def p2p_block_rows(n: int, world: int) -> int:

@@ -347,18 +347,31 @@ def test_node_barrier_alone_and_with_a_rank_that_never_arrives(gpu):
     ops, N, dev, _ = gpu
     mine = torch.zeros(8, dtype=torch.int32, device=dev)
     absent = torch.zeros(8, dtype=torch.int32, device=dev)
-    for epoch in (1, 2, 3):
-        ops.peer_barrier([mine.data_ptr()], 0, epoch, dev)
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    for _ in range(3):
+        ops.peer_barrier([mine.data_ptr()], 0, epoch)
     _ok(ops, dev)
-    assert mine.tolist()[0] == 3
-    ops.peer_barrier([mine.data_ptr(), absent.data_ptr()], 0, 4, dev, limit_ns=20_000_000)
+    assert mine.tolist()[0] == 3 and epoch.item() == 3                   # the kernel keeps the count itself
+    # the same launch replayed from a captured graph keeps counting (no per-call number in the launch)
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ops.peer_barrier([mine.data_ptr()], 0, epoch)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        ops.peer_barrier([mine.data_ptr()], 0, epoch)
+    for _ in range(3):
+        graph.replay()
+    _ok(ops, dev)
+    assert epoch.item() == 7 and mine.tolist()[0] == 7
+    ops.peer_barrier([mine.data_ptr(), absent.data_ptr()], 0, epoch, limit_ns=20_000_000)
     torch.cuda.synchronize()
-    assert absent.tolist()[0] == 4 and mine.tolist()[:2] == [4, 0]      # we signalled both; rank 1 never did
+    assert absent.tolist()[0] == 8 and mine.tolist()[:2] == [8, 0]      # we signalled both; rank 1 never did
     with pytest.raises(RuntimeError, match="another rank's flag never arrived"):
         ops.check_device_status(dev)
     with pytest.raises(N.NativeError):
-        ops.peer_barrier([mine.data_ptr()], 1, 5, dev)                   # rank outside the group
-    ops.peer_barrier([mine.data_ptr()], 0, 5, dev)
+        ops.peer_barrier([mine.data_ptr()], 1, epoch)                    # rank outside the group
+    ops.peer_barrier([mine.data_ptr()], 0, epoch)
     _ok(ops, dev)
 
 
