@@ -97,6 +97,18 @@ def test_newer_entry_points_reject_bad_arguments_before_any_launch(native_lib):
     worker.join()
     assert seen == [0]
     assert L.rtxb_set_gemm_schedule(0) == 0
+    # the multi-GPU helpers refuse bad arguments before anything is launched
+    import ctypes
+
+    one = (ctypes.c_void_p * 1)(ctypes.c_void_p(0x1000))
+    word = ctypes.c_void_p(0x2000)
+    assert L.rtxb_peer_barrier(None, 1, 0, word, 2_000_000, None, None) == -1          # no flag arrays
+    assert L.rtxb_peer_barrier(one, 9, 0, word, 2_000_000, None, None) == -1           # more than eight ranks
+    assert L.rtxb_peer_barrier(one, 1, 1, word, 2_000_000, None, None) == -1           # rank outside the group
+    assert L.rtxb_peer_barrier(one, 1, 0, None, 2_000_000, None, None) == -1           # no epoch counter
+    assert L.rtxb_peer_barrier(one, 1, 0, word, 10, None, None) == -1                  # limit below 1 ms
+    assert L.rtxb_selftest_wait_timeout(10, None, word, None) == -1
+    assert L.rtxb_selftest_wait_timeout(20_000_000, None, None, None) == -1            # reports through the status word
 
 
 def test_missing_library_is_loud(monkeypatch, tmp_path):
