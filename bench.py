@@ -478,7 +478,11 @@ def run_own_arm(args) -> None:
                     "gpu_launches_per_step": e2e_launches,
                     "host_cpus": f"{len(numa.cpus)} CPUs next to the GPU" if numa.cpus else "unbound",
                     "copies_alone_ms_per_step": res["copies"],
-                    "copies_alone_gbs_each_way": x_host.numel() * 2 / (res["copies"] * 1e-3) / 1e9},
+                    "copies_alone_gbs_each_way": x_host.numel() * 2 / (res["copies"] * 1e-3) / 1e9,
+                    "note": ("host path of this pool: the host side of a box delivers 50-87 GB/s each way in total "
+                             "however many GPUs or processes share it (bench_configs.py --config 7), so the copies "
+                             "alone bound this figure at N > 1" if world > 1 else
+                             "bound by this rank's own PCIe copies (copies_alone_ms_per_step)")},
             "gpu_launches": launches_per_step * steps,
             "clocks": clocks.get("burst"),
             "schedule": args.schedule,
