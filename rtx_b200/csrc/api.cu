@@ -681,8 +681,18 @@ size_t rtxb_nvfp4_scale_bytes(int64_t rows, int64_t k, int layout) {
   return 0;
 }
 
+// `beside_previous`: launched as a programmatic dependent that never waits, so it may run beside the kernel before it
+// on the stream (which must not touch its operands)
+static int mxfp8_quantize_impl(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                               int scale_layout, int rounding, void* stream, bool beside_previous);
+
 int rtxb_mxfp8_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales, int scale_layout,
                         int rounding, void* stream) {
+  return mxfp8_quantize_impl(src, rows, k, ld, q, scales, scale_layout, rounding, stream, false);
+}
+
+static int mxfp8_quantize_impl(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
+                               int scale_layout, int rounding, void* stream, bool beside_previous) {
   if (scale_layout == RTXB_SCALE_MMA64) return fail_msg(RTXB_E_UNSUPPORTED, "mma64 scale layout is SM120-only");
   if (scale_layout != RTXB_SCALE_ROW_MAJOR && scale_layout != RTXB_SCALE_MMA128)
     return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown scale layout");
@@ -704,8 +714,9 @@ int rtxb_mxfp8_quantize(const void* src, int64_t rows, int64_t k, int64_t ld, vo
   p.layout = scale_layout;
   p.round_to_infinity = rounding != RTXB_ROUND_FLOOR;
   const int64_t tiles = ((rows + 127) / 128) * ((p.kp + 127) / 128);
-  quant_mxfp8_rows_kernel<<<quant_grid(tiles, 6), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  RTXB_CHECK_LAUNCH("quant_mxfp8_rows_kernel");
+  cudaError_t le = launch_dependent(quant_mxfp8_rows_kernel, quant_grid(tiles, 6), kQuantThreads, 0,
+                                    static_cast<cudaStream_t>(stream), beside_previous, p);
+  if (le != cudaSuccess) return fail_cuda(le, "quant_mxfp8_rows_kernel launch");
   return RTXB_OK;
 }
 
@@ -938,13 +949,23 @@ int rtxb_mxfp8_glu_mlp_fwd(const void* x, const void* w_gu, const void* w_down, 
   if (!fused_x && (rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
     return rc;
   if ((rc = rtxb_mxfp8_quantize(w_gu, 2 * inter, k, k, qg, sg, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream))) return rc;
-  if ((rc = rtxb_mxfp8_quantize(w_down, n_out, inter, inter, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
+  // The down weight's quantizer (HBM bound, 40 registers, 0.5 KB of shared memory: its CTAs fit beside a GEMM CTA)
+  // is launched AFTER the gate/up GEMM as a programmatic dependent that never waits: the GEMM releases its
+  // dependents at entry, so the quantizer runs beside it.  Nothing the GEMM touches is read or written by it, and
+  // the down GEMM (an ordinary launch) waits for both.  Measured: 0.231 against 0.248 ms per step at 1024 rows
+  // (an eight-GPU shard), 0.610 against 0.643 at 4096, no difference at 8192 rows (power bound there).
+  const bool beside = !fused_x;
+  if (!beside &&
+      (rc = rtxb_mxfp8_quantize(w_down, n_out, inter, inter, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY, stream)))
     return rc;
   // gate/up GEMM whose epilogue applies SiLU*up and writes H already quantized for the down projection
   // (and in BF16 too when the caller wants it)
   if (fused_x) rc = rtxb_mxfp8_gemm_glu_mx_fused_x(x, k, qg, sg, h, qh, sh, m, inter, k, inter, stream, status);
   else rc = rtxb_mxfp8_gemm_glu_mx(qx, sx, qg, sg, h, qh, sh, m, inter, k, inter, stream, status);
   if (rc) return rc;
+  if (beside && (rc = mxfp8_quantize_impl(w_down, n_out, inter, inter, qd, sd, RTXB_SCALE_MMA128, RTXB_ROUND_INFINITY,
+                                          stream, true)))
+    return rc;
   return rtxb_mxfp8_gemm(qh, sh, qd, sd, y, m, n_out, inter, n_out, RTXB_OUT_BF16, stream, status);
 }
 

@@ -698,6 +698,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
   const int m_pairs = (p.m_tiles + 1) >> 1;
   const int total_tiles = m_pairs * p.n_tiles;
 
+  griddep_launch_dependents();   // a kernel launched as a programmatic dependent may run beside this one
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full_bar[s], 1);
