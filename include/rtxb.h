@@ -219,7 +219,10 @@ int rtxb_mxfp8_linear_fwd_noalloc(const void* x_bf16, const void* w_bf16, void* 
 /* SwiGLU MLP forward: H = silu(X Wg^T) * (X Wu^T), Y = H Wd^T, every GEMM
  * operand MXFP8-quantized along its K.  w_gate_up bf16 [2*inter, k], w_down
  * bf16 [n_out, inter]; y_bf16 [m, n_out] is the output; h_bf16 [m, inter] is an optional output
- * (NULL: H only ever exists in its MXFP8 form, written by the gate/up epilogue). */
+ * (NULL: H only ever exists in its MXFP8 form, written by the gate/up epilogue).
+ * Five launches on `stream`: quantizers of X and W_gate_up, the gate/up GEMM, the quantizer of W_down (a
+ * programmatic dependent that runs beside that GEMM), the down GEMM.  All operands must be complete on the stream
+ * before the call; none may be written by other streams while it runs. */
 size_t rtxb_mxfp8_glu_mlp_workspace_bytes(int64_t m, int64_t k, int64_t inter, int64_t n_out);
 int rtxb_mxfp8_glu_mlp_fwd(const void* x_bf16, const void* w_gate_up_bf16, const void* w_down_bf16, void* h_bf16,
                            void* y_bf16, int64_t m, int64_t k, int64_t inter, int64_t n_out, void* workspace,
