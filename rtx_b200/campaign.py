@@ -26,7 +26,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Callable, Iterable, Mapping, Optional, Sequence
 
-from .autotune import ADAPTERS, KernelContext, TrialOutcome, save_runtime_winner, time_call
+from .autotune import ADAPTERS, KernelContext, save_runtime_winner, time_call
 
 SUPPORTED_SCHEMA_VERSIONS = (1, 2)
 REGIMES = ("hot", "rotate")

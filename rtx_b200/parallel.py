@@ -169,7 +169,6 @@ class _PeerReduceScatter:
         self.comm = torch.cuda.Stream(device)
         # the reduced blocks come from world - 1 different peers: a few streams let those copies run at once
         self.fan = [torch.cuda.Stream(device) for _ in range(max(0, min(3, self.world - 2)))]
-        self.token = torch.zeros(1, dtype=torch.float32, device=device)
 
 
 def _node_barrier(st: "_PeerReduceScatter") -> None:
