@@ -40,3 +40,36 @@ def test_reference_arm_is_silent_on_other_ranks():
     done = _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}, "--gpus", "2", "--steps", "1", "--warmup", "0")
     assert done.returncode == 0, done.stderr[-2000:]
     assert not [ln for ln in done.stdout.splitlines() if ln.startswith("{")]
+
+
+def test_clock_sampler_assigns_samples_to_marked_regions(tmp_path):
+    """bench.py's sampler: nvidia-smi lines whose timestamp falls inside a marked region count for that label;
+    median clock, power and the active throttle reasons come out per label."""
+    import datetime
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class _Done:
+        def terminate(self): pass
+        def wait(self, timeout=None): return 0
+        def kill(self): pass
+
+    t0 = datetime.datetime(2026, 1, 2, 3, 4, 5).timestamp()
+    stamp = lambda dt: datetime.datetime.fromtimestamp(t0 + dt).strftime("%Y/%m/%d %H:%M:%S.%f")[:-3]
+    rows = [(0.00, 1965, 300, "Not Active"), (0.01, 1950, 310, "Not Active"), (0.02, 1900, 320, "Active"),
+            (1.00, 1300, 990, "Active"), (1.01, 1290, 995, "Active"), (5.00, 210, 90, "Not Active")]
+    path = tmp_path / "smi.csv"
+    path.write_text("".join(f"{stamp(dt)}, {mhz}, 1965, {w}, Not Active, Not Active, Not Active, {cap}\n"
+                            for dt, mhz, w, cap in rows) + "garbage line\n")
+    s = bench.ClockSampler(0)
+    s.proc, s.path = _Done(), str(path)
+    s.mark("burst", t0 - 0.001, t0 + 0.025)
+    s.mark("sustained", t0 + 0.99, t0 + 1.02)
+    out = s.stop()
+    assert out["burst"]["samples"] == 3 and out["burst"]["sm_mhz"] == 1950 and out["burst"]["sm_max_mhz"] == 1965
+    assert out["burst"]["reasons"] == ["sw_power_cap"] and out["burst"]["power_w"] == 310
+    assert out["sustained"]["samples"] == 2 and out["sustained"]["sm_mhz"] == 1295 and out["sustained"]["samples_total"] == 6
+    assert not os.path.exists(path)          # the sampler removes its file
