@@ -145,6 +145,14 @@ def physical_gpu_index(local_rank: int) -> int:
 # reference arm and CPU baseline: the reference's CPU path (oracle/cpu_path.py)
 # --------------------------------------------------------------------------
 
+def host_threads() -> int:
+    """Host threads this process may use: the CPUs of its affinity mask (a container's share), not the machine's."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
 def cpu_workload_run(m_rows: int, threads: int, repeats: int, warmup: int):
     """Times the reference's CPU formulation (encode + FP32 dequantized matmul) of the MLP forward on the
     first m_rows token rows of configuration 2 with the full weights.  -> (seconds per run, flop per run)"""
@@ -172,7 +180,7 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
+    threads = host_threads()
     times, flops = cpu_workload_run(M, threads, args.steps, max(min(args.warmup, 2), 1))
     total = sum(times)
     value = flops * len(times) / total / 1e12
@@ -509,7 +517,7 @@ def run_own_arm(args) -> None:
         if others is not None:
             line["configs"] = others
         if world == 1 and not args.no_cpu_baseline:
-            threads = os.cpu_count() or 1
+            threads = host_threads()
             times, flops = cpu_workload_run(M, threads, 3, 1)
             line["cpu_baseline"] = {
                 "value": flops * len(times) / sum(times) / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
