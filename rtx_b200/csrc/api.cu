@@ -322,7 +322,10 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
                 int64_t row_bytes, int64_t sf_k_chunks, int64_t ldo, int64_t out_cols, int64_t glu_inter,
                 const float* out_scale, cudaStream_t stream, int* status, void* q_out = nullptr,
                 void* sf_out = nullptr, bool overlap_previous = false, const RegionScales* regions = nullptr,
-                const BlockOutputs* blocks = nullptr) {
+                const BlockOutputs* blocks = nullptr, bool after_quantizer = false) {
+  // after_quantizer: EVERY operand comes from the kernel enqueued just before this one (the composite forwards'
+  // quantizer); the pair and single-CTA kernels are then launched as programmatic dependents — they wait for that
+  // grid before their first load, their set-up runs beside its tail.  The streaming kernel is launched normally.
   // overlap_previous: B and its scales do not depend on the kernel launched just before this one on
   // the stream, so the streaming kernel may start fetching them while that kernel is still running
   using T = GemmTraits<KIND>;
@@ -455,8 +458,9 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
       const int64_t start_pair = static_cast<int64_t>(blocks->first_block) * (blocks->block_rows / 256);
       p.tile_shift = static_cast<int>(((start_pair / p.group_m) * p.group_m * p.n_tiles) % pair_tiles);
     }
-    pk<<<2 * pairs, kGemmThreads, P::kSmemBytes, stream>>>(map_a, map_b, map_sfa, map_sfb, maps_out, p);
-    RTXB_CHECK_LAUNCH("gemm_blockscaled_pair_kernel");
+    cudaError_t le = launch_dependent(pk, 2 * pairs, kGemmThreads, P::kSmemBytes, stream,
+                                      overlap_previous || after_quantizer, map_a, map_b, map_sfa, map_sfb, maps_out, p);
+    if (le != cudaSuccess) return fail_cuda(le, "gemm_blockscaled_pair_kernel launch");
     return RTXB_OK;
   }
   if (p.m_tiles == 1) {
@@ -476,7 +480,8 @@ int launch_gemm(const void* qa, const void* sa, const void* qb, const void* sb, 
   if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(gemm)");
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  e = launch_dependent(kernel, grid, kGemmThreads, T::kSmemBytes, stream, overlap_previous, map_a, map_b, p);
+  e = launch_dependent(kernel, grid, kGemmThreads, T::kSmemBytes, stream, overlap_previous || after_quantizer, map_a, map_b,
+                       p);
   if (e != cudaSuccess) return fail_cuda(e, "gemm_blockscaled_kernel launch");
   return RTXB_OK;
 }
@@ -720,6 +725,40 @@ static int mxfp8_quantize_impl(const void* src, int64_t rows, int64_t k, int64_t
   return RTXB_OK;
 }
 
+// X [m, k] and W [n, k] (contiguous BF16) to mma128-scaled MXFP8 in one launch
+static int mxfp8_quantize_pair(const void* x, int64_t m, const void* w, int64_t n, int64_t k, void* qx, void* sx, void* qw,
+                               void* sw, int rounding, void* stream) {
+  if (!x || !w || !qx || !sx || !qw || !sw) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
+  if (m <= 0 || n <= 0 || k <= 0) return fail_msg(RTXB_E_INVALID_ARGUMENT, "bad shape");
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX - 256) return fail_msg(RTXB_E_UNSUPPORTED, "dimension exceeds int32");
+  if (!aligned(qx, 16) || !aligned(qw, 16) || !aligned(sx, 16) || !aligned(sw, 16))
+    return fail_msg(RTXB_E_ALIGNMENT, "packed outputs must be 16-byte aligned");
+  QuantMxParams p[2];
+  const void* src[2] = {x, w};
+  void* q[2] = {qx, qw};
+  void* sc[2] = {sx, sw};
+  const int64_t rows[2] = {m, n};
+  int64_t tiles = 0;
+  for (int i = 0; i < 2; ++i) {
+    p[i] = QuantMxParams{};
+    p[i].src = static_cast<const __nv_bfloat16*>(src[i]);
+    p[i].q = static_cast<uint8_t*>(q[i]);
+    p[i].scales = static_cast<uint8_t*>(sc[i]);
+    p[i].rows = static_cast<int>(rows[i]);
+    p[i].k = static_cast<int>(k);
+    p[i].kp = static_cast<int>(round_up(k, 32));
+    p[i].ld = k;
+    p[i].nb = p[i].kp / 32;
+    p[i].sf_chunks = (p[i].nb + 3) / 4;
+    p[i].layout = RTXB_SCALE_MMA128;
+    p[i].round_to_infinity = rounding != RTXB_ROUND_FLOOR;
+    tiles += ((rows[i] + 127) / 128) * ((p[i].kp + 127) / 128);
+  }
+  quant_mxfp8_rows2_kernel<<<quant_grid(tiles, 6), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(p[0], p[1]);
+  RTXB_CHECK_LAUNCH("quant_mxfp8_rows2_kernel");
+  return RTXB_OK;
+}
+
 int rtxb_mxfp8_quantize_transposed(const void* src, int64_t rows, int64_t k, int64_t ld, void* q, void* scales,
                                    int scale_layout, int rounding, void* stream) {
   if (!src || !q || !scales) return fail_msg(RTXB_E_INVALID_ARGUMENT, "null operand");
@@ -792,8 +831,10 @@ int rtxb_mxfp8_quantize_dual(const void* src, int64_t m, int64_t n, int64_t ld, 
   return RTXB_OK;
 }
 
-int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
-                    int64_t k, int64_t ldo, int out_dtype, void* stream, int* status) {
+// rtxb_mxfp8_gemm; `after_quantizer`: launched as a programmatic dependent of the quantizer enqueued just before it
+// (the kernels wait for that grid before they touch an operand; their set-up runs beside its tail)
+static int mxfp8_gemm_impl(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
+                           int64_t k, int64_t ldo, int out_dtype, void* stream, int* status, bool after_quantizer) {
   if (out_dtype != RTXB_OUT_BF16 && out_dtype != RTXB_OUT_F32)
     return fail_msg(RTXB_E_INVALID_ARGUMENT, "unknown output dtype");
   int rc = check_gemm_args(qa, sa, qb, sb, out, m, n, k, ldo, n, out_dtype == RTXB_OUT_BF16 ? 2 : 4);
@@ -802,8 +843,15 @@ int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* 
   const int64_t chunks = (kp / 32 + 3) / 4;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (out_dtype == RTXB_OUT_BF16)
-    return launch_gemm<kKindMxfp8, kEpiBf16>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status);
-  return launch_gemm<kKindMxfp8, kEpiF32>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status);
+    return launch_gemm<kKindMxfp8, kEpiBf16>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status, nullptr,
+                                             nullptr, false, nullptr, nullptr, after_quantizer);
+  return launch_gemm<kKindMxfp8, kEpiF32>(qa, sa, qb, sb, out, m, n, kp, chunks, ldo, n, 0, nullptr, s, status, nullptr,
+                                          nullptr, false, nullptr, nullptr, after_quantizer);
+}
+
+int rtxb_mxfp8_gemm(const void* qa, const void* sa, const void* qb, const void* sb, void* out, int64_t m, int64_t n,
+                    int64_t k, int64_t ldo, int out_dtype, void* stream, int* status) {
+  return mxfp8_gemm_impl(qa, sa, qb, sb, out, m, n, k, ldo, out_dtype, stream, status, false);
 }
 
 int rtxb_mxfp8_gemm_row_blocks(const void* qa, const void* sa, const void* qb, const void* sb, void* const* out_blocks,
@@ -904,13 +952,16 @@ int rtxb_mxfp8_linear_fwd(const void* x, const void* w, void* out, int64_t m, in
   uint8_t* sx = c.take(rtxb_mxfp8_scale_bytes(m, k, RTXB_SCALE_MMA128));
   uint8_t* qw = c.take(n * kp);
   uint8_t* sw = c.take(rtxb_mxfp8_scale_bytes(n, k, RTXB_SCALE_MMA128));
-  int rc = rtxb_mxfp8_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, rounding, stream);
-  if (rc) return rc;
-  if (t_gemm_schedule == RTXB_SCHEDULE_FUSED_X)   // X is quantized by the GEMM's own quantizer warps
+  int rc;
+  if (t_gemm_schedule == RTXB_SCHEDULE_FUSED_X) {   // X is quantized by the GEMM's own quantizer warps
+    if ((rc = rtxb_mxfp8_quantize(w, n, k, k, qw, sw, RTXB_SCALE_MMA128, rounding, stream))) return rc;
     return rtxb_mxfp8_linear_fwd_fused_x(x, k, qw, sw, out, m, n, k, n, rounding, stream, status);
-  rc = rtxb_mxfp8_quantize(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, rounding, stream);
-  if (rc) return rc;
-  return rtxb_mxfp8_gemm(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, stream, status);
+  }
+  // Both operands in ONE quantizer launch (the reference's dual quantizer), the GEMM behind it as a programmatic
+  // dependent: two launches per forward instead of three, and the GEMM's set-up runs beside the quantizer's tail.
+  // On small layers the launches, not the work, are the time.
+  if ((rc = mxfp8_quantize_pair(x, m, w, n, k, qx, sx, qw, sw, rounding, stream))) return rc;
+  return mxfp8_gemm_impl(qx, sx, qw, sw, out, m, n, k, n, RTXB_OUT_BF16, stream, status, true);
 }
 
 size_t rtxb_mxfp8_glu_mlp_workspace_bytes(int64_t m, int64_t k, int64_t inter, int64_t n_out) {

@@ -735,6 +735,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
       int group = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // launched as a programmatic dependent (composite forwards): the operands come from the quantizer launched just
+      // before this kernel; everything above ran beside its tail.  Returns at once for an ordinary launch.
+      griddep_wait();
       for (int tile = pair_id; tile < total_tiles && ok; tile += num_pairs) {
         int mp_idx, n_idx;
         tile_coords(rotate_tile(tile, p.tile_shift, total_tiles), m_pairs, p.n_tiles, p.group_m, mp_idx, n_idx);
@@ -809,6 +812,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int quad = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    griddep_wait();   // the output scale (and, for the region epilogue, the scale arrays) may come from the grid before
     const float out_scale = p.out_scale ? __ldg(p.out_scale) : 1.0f;
     const uint32_t overlap_addr = mapa_shared(smem_u32(acc_overlap_bar), 0);
     uint32_t local_tile = 0;

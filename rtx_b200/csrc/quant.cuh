@@ -98,58 +98,75 @@ __device__ __forceinline__ void unpack8(const uint4 raw, float (&v)[8]) {
   v[4] = bf16_lo(raw.z); v[5] = bf16_hi(raw.z); v[6] = bf16_lo(raw.w); v[7] = bf16_hi(raw.w);
 }
 
+// One 128 x 128 tile of the row quantizer (see quant_mxfp8_rows_kernel); ends with a block-wide barrier.
+__device__ __forceinline__ void quant_mxfp8_rows_tile(const QuantMxParams& p, int tile, uint8_t (*tile_scales)[4]) {
+  const int sub = threadIdx.x & 15, rsel = threadIdx.x >> 4;
+  const int col_tiles = (p.kp + 127) / 128;
+  const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
+  const bool q_vec_ok = (reinterpret_cast<uintptr_t>(p.q) & 7) == 0;  // kp % 32 == 0 keeps rows 8-byte aligned
+  const bool rinf = p.round_to_infinity != 0;
+  const int row0 = (tile / col_tiles) * 128;
+  const int col = (tile % col_tiles) * 128 + sub * 8;
+  const bool col_ok = col < p.kp;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint4 raw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = row0 + rsel + 16 * (half * 4 + j);
+      raw[j] = (row < p.rows && col_ok) ? load8_raw(p.src + static_cast<int64_t>(row) * p.ld, col, p.k, vec_ok)
+                                        : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = rsel + 16 * (half * 4 + j);
+      const int row = row0 + r;
+      const bool live = row < p.rows && col_ok;
+      float v[8];
+      unpack8(raw[j], v);
+      float a = amax8(v);
+      a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 1));
+      a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 2));
+      const uint32_t code = e8m0_from_amax(a, rinf);
+      const float recip = e8m0_reciprocal(code);
+      if ((sub & 3) == 0) tile_scales[r][sub >> 2] = live ? static_cast<uint8_t>(code) : 0;
+      if (live) {
+        const uint32_t lo = cvt_e4m3x2(v[0] * recip, v[1] * recip) | (cvt_e4m3x2(v[2] * recip, v[3] * recip) << 16);
+        const uint32_t hi = cvt_e4m3x2(v[4] * recip, v[5] * recip) | (cvt_e4m3x2(v[6] * recip, v[7] * recip) << 16);
+        uint8_t* dst = p.q + static_cast<int64_t>(row) * p.kp + col;
+        if (q_vec_ok) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+        } else {
+          for (int e = 0; e < 4; ++e) { dst[e] = lo >> (8 * e); dst[4 + e] = hi >> (8 * e); }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  store_scale_tile<4>(tile_scales, p.scales, p.layout, row0, (tile % col_tiles) * 4, p.rows, p.nb, p.sf_chunks);
+  __syncthreads();
+}
+
 // Tile = 128 rows x 128 columns (exactly one 512-byte scale tile).  Thread t owns 8 columns
 // (t & 15) of row (t >> 4) + 16 i; four neighbouring lanes share a block of 32.  Four row loads
 // are issued before any is consumed so that each thread keeps 64 bytes in flight.
 __global__ void __launch_bounds__(kQuantThreads, 6) quant_mxfp8_rows_kernel(const QuantMxParams p) {
   __shared__ __align__(16) uint8_t tile_scales[128][4];
-  const int sub = threadIdx.x & 15, rsel = threadIdx.x >> 4;
-  const int col_tiles = (p.kp + 127) / 128;
-  const int row_tiles = (p.rows + 127) / 128;
-  const bool vec_ok = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.src) & 15) == 0);
-  const bool q_vec_ok = (reinterpret_cast<uintptr_t>(p.q) & 7) == 0;  // kp % 32 == 0 keeps rows 8-byte aligned
-  const bool rinf = p.round_to_infinity != 0;
-  for (int tile = blockIdx.x; tile < col_tiles * row_tiles; tile += gridDim.x) {
-    const int row0 = (tile / col_tiles) * 128;
-    const int col = (tile % col_tiles) * 128 + sub * 8;
-    const bool col_ok = col < p.kp;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint4 raw[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int row = row0 + rsel + 16 * (half * 4 + j);
-        raw[j] = (row < p.rows && col_ok) ? load8_raw(p.src + static_cast<int64_t>(row) * p.ld, col, p.k, vec_ok)
-                                          : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = rsel + 16 * (half * 4 + j);
-        const int row = row0 + r;
-        const bool live = row < p.rows && col_ok;
-        float v[8];
-        unpack8(raw[j], v);
-        float a = amax8(v);
-        a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 1));
-        a = fmax_nan(a, __shfl_xor_sync(0xffffffffu, a, 2));
-        const uint32_t code = e8m0_from_amax(a, rinf);
-        const float recip = e8m0_reciprocal(code);
-        if ((sub & 3) == 0) tile_scales[r][sub >> 2] = live ? static_cast<uint8_t>(code) : 0;
-        if (live) {
-          const uint32_t lo = cvt_e4m3x2(v[0] * recip, v[1] * recip) | (cvt_e4m3x2(v[2] * recip, v[3] * recip) << 16);
-          const uint32_t hi = cvt_e4m3x2(v[4] * recip, v[5] * recip) | (cvt_e4m3x2(v[6] * recip, v[7] * recip) << 16);
-          uint8_t* dst = p.q + static_cast<int64_t>(row) * p.kp + col;
-          if (q_vec_ok) {
-            *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
-          } else {
-            for (int e = 0; e < 4; ++e) { dst[e] = lo >> (8 * e); dst[4 + e] = hi >> (8 * e); }
-          }
-        }
-      }
-    }
-    __syncthreads();
-    store_scale_tile<4>(tile_scales, p.scales, p.layout, row0, (tile % col_tiles) * 4, p.rows, p.nb, p.sf_chunks);
-    __syncthreads();
+  const int tiles = ((p.kp + 127) / 128) * ((p.rows + 127) / 128);
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) quant_mxfp8_rows_tile(p, tile, tile_scales);
+}
+
+// Two tensors in one launch (the reference's dual quantizer, rtx/kernels/mxfp8_quant.py:398-1399: activations and
+// weight of a dynamic forward): the tiles of `a`, then the tiles of `b`.  On small layers a launch costs more than
+// the quantization, and the GEMM launched behind this kernel as a programmatic dependent can set up meanwhile.
+__global__ void __launch_bounds__(kQuantThreads, 6) quant_mxfp8_rows2_kernel(const QuantMxParams a, const QuantMxParams b) {
+  __shared__ __align__(16) uint8_t tile_scales[128][4];
+  griddep_launch_dependents();
+  const int tiles_a = ((a.kp + 127) / 128) * ((a.rows + 127) / 128);
+  const int tiles_b = ((b.kp + 127) / 128) * ((b.rows + 127) / 128);
+  for (int tile = blockIdx.x; tile < tiles_a + tiles_b; tile += gridDim.x) {
+    if (tile < tiles_a) quant_mxfp8_rows_tile(a, tile, tile_scales);
+    else quant_mxfp8_rows_tile(b, tile - tiles_a, tile_scales);
   }
 }
 
