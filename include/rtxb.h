@@ -174,6 +174,8 @@ int rtxb_mxfp8_gemm_glu_mx(const void* qa, const void* sa, const void* qb, const
  *   rtx/kernels/mxfp8_fwd.py:2963-3029; bound at rtx/fp8.py:560, :581, :635.
  * and the materialized pair compile_mxfp8_dual_quant + compile_mxfp8_gemm run by
  *   _PrequantRunner (rtx/fp8.py:292-312).
+ * Two launches on `stream`: one quantizer launch for both operands, then the GEMM as a programmatic dependent of
+ * it (the GEMM waits for the quantizer's grid before its first operand load).
  * workspace: rtxb_mxfp8_linear_workspace_bytes(m, n, k); caller-owned, reusable
  * across calls on the same stream. */
 size_t rtxb_mxfp8_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
