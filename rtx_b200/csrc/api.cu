@@ -1498,6 +1498,53 @@ int rtxb_nvfp4_linear_fwd_regions(const void* x, const void* w, void* out, int64
   uint8_t* qw = c.take(n * kp / 2);
   uint8_t* sw = c.take(rtxb_nvfp4_scale_bytes(n, k, RTXB_SCALE_MMA128));
   int rc;
+  const bool small_regions = rx != m && rw != n && rx * k * 2 < 32768 && rw * k * 2 < 32768 && m <= INT32_MAX &&
+                             n <= INT32_MAX && k <= INT32_MAX - 512 && x && w &&
+                             (scale_mode == RTXB_TENSOR_SCALE_EXACT || scale_mode == RTXB_TENSOR_SCALE_POWER2);
+  if (small_regions) {
+    // Layers whose regions are small (one warp per region): both operands' region scales in one launch, both
+    // quantizations in a second one (a programmatic dependent of the first), the GEMM behind them as a dependent
+    // too: three launches instead of five.  On such layers the launches, not the work, are the time.
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const RegionScaleJob ja{static_cast<const __nv_bfloat16*>(x), xs, static_cast<int>(m), static_cast<int>(rx), k};
+    const RegionScaleJob jb{static_cast<const __nv_bfloat16*>(w), wsc, static_cast<int>(n), static_cast<int>(rw), k};
+    const int64_t regions = m / rx + n / rw;
+    const int64_t ctas = (regions + 7) / 8;
+    amax_regions2_kernel<<<static_cast<int>(ctas < sm_count() * 8 ? ctas : sm_count() * 8), 256, 0, st>>>(
+        ja, jb, static_cast<int>(k), scale_mode);
+    RTXB_CHECK_LAUNCH("amax_regions2_kernel");
+    QuantNvParams p[2];
+    const void* src[2] = {x, w};
+    uint8_t* q[2] = {qx, qw};
+    uint8_t* sc[2] = {sx, sw};
+    const float* rs[2] = {xs, wsc};
+    const int64_t rows[2] = {m, n}, rr[2] = {rx, rw};
+    int64_t tiles = 0;
+    for (int i = 0; i < 2; ++i) {
+      p[i] = QuantNvParams{};
+      p[i].src = static_cast<const __nv_bfloat16*>(src[i]);
+      p[i].q = q[i];
+      p[i].scales = sc[i];
+      p[i].tensor_scale = nullptr;
+      p[i].region_scales = rs[i];
+      p[i].region_rows = static_cast<int>(rr[i]);
+      p[i].rows = static_cast<int>(rows[i]);
+      p[i].k = static_cast<int>(k);
+      p[i].kp = static_cast<int>(kp);
+      p[i].ld = k;
+      p[i].nb = p[i].kp / 16;
+      p[i].sf_chunks = static_cast<int>(round_up((p[i].nb + 3) / 4, 4));
+      p[i].layout = RTXB_SCALE_MMA128;
+      tiles += ((rows[i] + 127) / 128) * ((p[i].kp + 255) / 256);
+    }
+    cudaError_t le = launch_dependent(quant_nvfp4_regions2_kernel, quant_grid(tiles, 4), kQuantThreads, 0, st, true, p[0],
+                                      p[1]);
+    if (le != cudaSuccess) return fail_cuda(le, "quant_nvfp4_regions2_kernel launch");
+    if ((rc = check_gemm_args(qx, sx, qw, sw, out, m, n, k, n, n, 2))) return rc;
+    const RegionScales rsc{xs, wsc, static_cast<int>(rx), static_cast<int>(rw)};
+    return launch_gemm<kKindNvfp4, kEpiRegionBf16>(qx, sx, qw, sw, out, m, n, kp / 2, round_up((kp / 16 + 3) / 4, 4), n, n, 0,
+                                                   nullptr, st, status, nullptr, nullptr, false, &rsc, nullptr, true);
+  }
   if ((rc = rtxb_nvfp4_region_scales(x, m, k, k, rx, scale_mode, scal, xs, stream))) return rc;
   if ((rc = rtxb_nvfp4_region_scales(w, n, k, k, rw, scale_mode, scal + 4, wsc, stream))) return rc;
   if ((rc = rtxb_nvfp4_quantize_regions(x, m, k, k, qx, sx, RTXB_SCALE_MMA128, xs, rx, stream))) return rc;

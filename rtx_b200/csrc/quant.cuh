@@ -635,6 +635,58 @@ __global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_delayed_kernel(c
 // rows, from the region's current |max|.  Here: one warp reduces a region and applies the scale rule
 // (amax_regions_kernel), then the tiled quantizer looks the scale up per row.
 // ---------------------------------------------------------------------------
+// |max| bits of one region (region_rows rows of k values), reduced by one warp
+__device__ __forceinline__ uint32_t amax_region_warp(const __nv_bfloat16* src, int k, int64_t ld, int region_rows, int region,
+                                                     int lane, bool vec_ok) {
+  uint32_t m = 0;
+  if (vec_ok && ld == k) {
+    // contiguous region: one flat range, eight 16-byte loads in flight per lane (a region of a small layer is a few
+    // tens of kilobytes read by ONE warp: the number of dependent load rounds is its whole cost)
+    const uint4* base = reinterpret_cast<const uint4*>(src + static_cast<int64_t>(region) * region_rows * ld);
+    const int vecs = region_rows * (k / 8);
+    for (int i0 = lane; i0 < vecs; i0 += 256) {
+      uint4 raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) raw[j] = i0 + 32 * j < vecs ? __ldg(base + i0 + 32 * j) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+          m = max(m, w[e] & 0x7FFF0000u);
+        }
+      }
+    }
+    return __reduce_max_sync(0xffffffffu, m);
+  }
+  for (int r = 0; r < region_rows; ++r) {
+    const __nv_bfloat16* rp = src + static_cast<int64_t>(region * region_rows + r) * ld;
+    if (vec_ok) {
+      const int vecs = k / 8;
+      for (int i0 = lane; i0 < vecs; i0 += 128) {   // four 16-byte loads in flight per lane
+        uint4 raw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          raw[j] = i0 + 32 * j < vecs ? __ldg(reinterpret_cast<const uint4*>(rp) + i0 + 32 * j) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
+            m = max(m, w[e] & 0x7FFF0000u);
+          }
+        }
+      }
+    } else {
+      const uint16_t* sp = reinterpret_cast<const uint16_t*>(rp);
+      for (int i = lane; i < k; i += 32) m = max(m, (static_cast<uint32_t>(sp[i]) << 16) & 0x7FFFFFFFu);
+    }
+  }
+  return __reduce_max_sync(0xffffffffu, m);
+}
+
 __global__ void __launch_bounds__(256) amax_regions_kernel(const __nv_bfloat16* src, int rows, int k, int64_t ld,
                                                            int region_rows, int mode, float* region_scales) {
   const int regions = rows / region_rows;
@@ -642,33 +694,30 @@ __global__ void __launch_bounds__(256) amax_regions_kernel(const __nv_bfloat16* 
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const bool vec_ok = (ld % 8 == 0) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
   for (int region = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; region < regions; region += warps) {
-    uint32_t m = 0;
-    for (int r = 0; r < region_rows; ++r) {
-      const __nv_bfloat16* rp = src + static_cast<int64_t>(region * region_rows + r) * ld;
-      if (vec_ok) {
-        const int vecs = k / 8;
-        for (int i0 = lane; i0 < vecs; i0 += 128) {   // four 16-byte loads in flight per lane
-          uint4 raw[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            raw[j] = i0 + 32 * j < vecs ? __ldg(reinterpret_cast<const uint4*>(rp) + i0 + 32 * j) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              m = max(m, (w[e] << 16) & 0x7FFFFFFFu);
-              m = max(m, w[e] & 0x7FFF0000u);
-            }
-          }
-        }
-      } else {
-        const uint16_t* sp = reinterpret_cast<const uint16_t*>(rp);
-        for (int i = lane; i < k; i += 32) m = max(m, (static_cast<uint32_t>(sp[i]) << 16) & 0x7FFFFFFFu);
-      }
-    }
-    m = __reduce_max_sync(0xffffffffu, m);
+    const uint32_t m = amax_region_warp(src, k, ld, region_rows, region, lane, vec_ok);
     if (lane == 0) region_scales[region] = nvfp4_scale_from_amax_bits(m, mode, true);
+  }
+}
+
+// Region scales of two tensors with the same k (activations and weight of a dynamic forward) in one launch: on
+// small layers the launches cost more than the reductions.
+struct RegionScaleJob {
+  const __nv_bfloat16* src;
+  float* region_scales;
+  int rows, region_rows;
+  int64_t ld;
+};
+__global__ void __launch_bounds__(256) amax_regions2_kernel(const RegionScaleJob a, const RegionScaleJob b, int k, int mode) {
+  griddep_launch_dependents();
+  const int regions_a = a.rows / a.region_rows, regions_b = b.rows / b.region_rows;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; idx < regions_a + regions_b; idx += warps) {
+    const RegionScaleJob& j = idx < regions_a ? a : b;
+    const int region = idx < regions_a ? idx : idx - regions_a;
+    const bool vec_ok = (j.ld % 8 == 0) && (k % 8 == 0) && ((reinterpret_cast<uintptr_t>(j.src) & 15) == 0);
+    const uint32_t m = amax_region_warp(j.src, k, j.ld, j.region_rows, region, lane, vec_ok);
+    if (lane == 0) j.region_scales[region] = nvfp4_scale_from_amax_bits(m, mode, true);
   }
 }
 
@@ -734,6 +783,36 @@ __global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_regions_kernel(c
         row_factors[threadIdx.x] = make_float2(6.0f * st, __fdiv_rn(1.0f, st));
       }
       table_row0 = row0;
+      __syncthreads();
+    }
+    quant_nvfp4_tile<true>(p, c, tile, tile_scales, row_factors);   // ends with a block-wide barrier
+  }
+}
+
+// Two tensors in one launch (tiles of `a`, then tiles of `b`), launched as a programmatic dependent of
+// amax_regions2_kernel: it waits for that grid before it reads a region scale.
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_nvfp4_regions2_kernel(const QuantNvParams a, const QuantNvParams b) {
+  __shared__ __align__(16) uint8_t tile_scales[128][16];
+  __shared__ float2 row_factors[128];
+  griddep_launch_dependents();
+  const QuantNvTileCtx ca = quant_nvfp4_ctx(a, 1.0f), cb = quant_nvfp4_ctx(b, 1.0f);
+  const int tiles_a = ca.col_tiles * ((a.rows + 127) / 128), tiles_b = cb.col_tiles * ((b.rows + 127) / 128);
+  griddep_wait();
+  int table_key = -1;
+  for (int idx = blockIdx.x; idx < tiles_a + tiles_b; idx += gridDim.x) {
+    const bool first = idx < tiles_a;
+    const QuantNvParams& p = first ? a : b;
+    const QuantNvTileCtx& c = first ? ca : cb;
+    const int tile = first ? idx : idx - tiles_a;
+    const int row0 = (tile / c.col_tiles) * 128;
+    const int key = 2 * row0 + (first ? 0 : 1);
+    if (key != table_key) {
+      if (threadIdx.x < 128) {
+        const int row = row0 + threadIdx.x;
+        const float st = row < p.rows ? __ldg(p.region_scales + row / p.region_rows) : 1.0f;
+        row_factors[threadIdx.x] = make_float2(6.0f * st, __fdiv_rn(1.0f, st));
+      }
+      table_key = key;
       __syncthreads();
     }
     quant_nvfp4_tile<true>(p, c, tile, tile_scales, row_factors);   // ends with a block-wide barrier
