@@ -311,7 +311,9 @@ int rtxb_nvfp4_gemm_regions(const void* qa, const void* sa, const void* qb, cons
                             const float* w_region_scales, int64_t w_region_rows, void* stream, int* status);
 /* _JITRegionDynamicRunner (rtx/fp4.py:522-560, built at :758-845).  Region sizes are requests: one
  * that does not split the operand's rows evenly into more than one region falls back to a single
- * region over the tensor (rtx/fp4.py:89-94). */
+ * region over the tensor (rtx/fp4.py:89-94).  Five launches (region scales and quantizer per operand, GEMM); where
+ * both operands' regions are small (below 32 KB) three: the two operands share the region-scale launch and the
+ * quantizer launch, and the GEMM follows as a programmatic dependent. */
 size_t rtxb_nvfp4_linear_regions_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t x_region_rows,
                                                  int64_t w_region_rows);
 int rtxb_nvfp4_linear_fwd_regions(const void* x_bf16, const void* w_bf16, void* out_bf16, int64_t m, int64_t n,
