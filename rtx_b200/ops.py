@@ -569,7 +569,8 @@ def nvfp4_linear_fwd_regions(x, w, ws: Workspace, x_region_rows: int, w_region_r
                              out: Optional[torch.Tensor] = None,
                              scale_mode: int = N.TENSOR_SCALE_POWER2) -> torch.Tensor:
     """NVFP4 forward with the row-region outer scales (region sizes are requests, see
-    nvfp4_effective_region_rows): two region-|max| launches, two quantizers, the GEMM."""
+    nvfp4_effective_region_rows): two region-|max| launches, two quantizers, the GEMM — or, where both operands'
+    regions are small, one region-|max| launch, one quantizer launch and the GEMM as its programmatic dependent."""
     _require(x, torch.bfloat16, "x")
     _require(w, torch.bfloat16, "weight")
     m, k = x.shape
